@@ -1,0 +1,184 @@
+/*
+ * b200_moe.h - C ABI of the B200-native quantized mixture-of-experts path.
+ *
+ * A drop-in for the part of oxiglade/mlx-rs that an MLX-affine-quantized MoE block runs
+ * through: one function per op wrapper of the reference (same names, argument order and
+ * defaults), plus fused entry points for the routed block.  It sits beside mlx-sys: where the
+ * reference binds `int mlx_<op>(mlx_array* res, ..., mlx_stream s)` (status int, result
+ * handle first; mlx-rs/src/utils/guard.rs:20-49), this library exports
+ * `int b200_<op>(b200_ctx*, <device pointers and sizes>, void* cuda_stream)`.
+ *
+ * Conventions
+ *  - return 0 on success, non-zero on failure; the message is available from
+ *    b200_last_error() (thread-local) and is also passed to the handler registered with
+ *    b200_set_error_handler(), whose signature equals the one mlx_set_error_handler() takes
+ *    (mlx-rs/src/error.rs:232-251).  Bad arguments never abort and never launch anything.
+ *  - every pointer is a DEVICE pointer unless stated otherwise; inputs are const, outputs are
+ *    caller-allocated.  bf16 tensors are `void*`.  Indices are uint32 like the reference's.
+ *  - calls are eager and stream-ordered: work is enqueued on `stream` (a cudaStream_t passed
+ *    as void*) and the call returns; "eval" is cudaStreamSynchronize.
+ *  - a b200_ctx owns scratch memory (it grows on demand; b200_ctx_reserve pre-sizes it) and is
+ *    used by one thread at a time on one device, like the reference's per-thread streams.
+ *  - quantized layout = MLX affine: `32/bits` codes per uint32, element i in bits
+ *    [bits*i, bits*i+bits), one bf16 scale and bias per `group_size` elements of the last axis,
+ *    w_hat = scale*q + bias.  Matmul kernels require group_size 64 and bits 4 or 8.
+ */
+#ifndef B200_MOE_H_
+#define B200_MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_DEFAULT_GROUP_SIZE 64 /* mlx-rs/src/ops/quantization.rs:12 */
+#define B200_DEFAULT_BITS 4        /* mlx-rs/src/ops/quantization.rs:13 */
+
+typedef struct b200_ctx b200_ctx;
+
+enum { B200_F32 = 0, B200_BF16 = 1 };
+enum { B200_ROUTER_SOFTMAX_TOPK = 0, B200_ROUTER_TOPK_SOFTMAX = 1 };
+
+/* Stacked quantized projection of all experts: weight [E, out, in*bits/32] uint32,
+ * scales/biases [E, out, in/group_size] bf16 (field names as in QuantizedLinear,
+ * mlx-rs/src/nn/quantized.rs:307-328). */
+typedef struct {
+  const uint32_t* weight;
+  const void* scales;
+  const void* biases;
+} b200_qlinear;
+
+typedef struct {
+  int32_t hidden;         /* H */
+  int32_t inter;          /* I, moe_intermediate_size */
+  int32_t n_experts;      /* E (<= 256) */
+  int32_t top_k;          /* k (<= 32) */
+  int32_t bits;           /* 4 or 8 */
+  int32_t group_size;     /* 64 */
+  int32_t router_mode;    /* B200_ROUTER_* */
+  int32_t norm_topk_prob; /* renormalise the selected probabilities (mode 0) */
+} b200_moe_config;
+
+typedef struct {
+  const void* router_weight;      /* bf16 [E, H]  (Linear layout [out,in], mlx-rs/src/nn/linear.rs:39) */
+  const float* router_logit_bias; /* optional float32 [E] added to the logits; NULL for none */
+  b200_qlinear gate_proj;         /* [E, I, H] */
+  b200_qlinear up_proj;           /* [E, I, H] */
+  b200_qlinear down_proj;         /* [E, H, I] */
+} b200_moe_params;
+
+/* Optional routing outputs of the block; any pointer may be NULL. */
+typedef struct {
+  uint32_t* indices;  /* [T, k]   selected experts, (value desc, expert asc) order */
+  void* scores;       /* [T, k]   bf16 routing weights */
+  uint32_t* perm;     /* [T*k]    stable argsort of the flat index list */
+  uint32_t* inv_perm; /* [T*k]    inverse of perm */
+  uint32_t* counts;   /* [E]      assignments per expert */
+  uint32_t* offsets;  /* [E+1]    exclusive prefix sum of counts */
+  void* logits;       /* [T, E]   bf16 router logits */
+} b200_moe_aux;
+
+/* ---- library / context ----------------------------------------------------------------- */
+
+/* Message of the last failing call on this thread (valid until the next failing call). */
+const char* b200_last_error(void);
+/* Same contract as mlx_set_error_handler (mlx-rs/src/error.rs:232-251). */
+void b200_set_error_handler(void (*handler)(const char* msg, void* data), void* data, void (*dtor)(void*));
+/* Creates a context on CUDA device `device` (cudaSetDevice is called). */
+int b200_ctx_create(b200_ctx** out, int device);
+int b200_ctx_destroy(b200_ctx* ctx);
+/* Pre-sizes the scratch memory for blocks of up to `max_tokens` tokens so that later calls
+ * do not allocate (allocation synchronises the device). */
+int b200_ctx_reserve(b200_ctx* ctx, const b200_moe_config* cfg, int64_t max_tokens);
+/* Synchronises `stream` and reports device-side findings (an expert or gather index out of
+ * range) of the calls issued since the last check; they surface here because argument values
+ * living on the device cannot be validated before launch. */
+int b200_ctx_check(b200_ctx* ctx, void* stream);
+/* Number of kernels launched through this context so far. */
+int64_t b200_ctx_launch_count(const b200_ctx* ctx);
+
+/* ---- op surface of the reference -------------------------------------------------------- */
+
+/* quantize(w, group_size, bits) -> (w_q, scales, biases); mlx-rs/src/ops/quantization.rs:48-83.
+ * w [rows, K] of `dtype` (B200_F32 or B200_BF16); scales/biases come back in the same dtype.
+ * group_size in {32, 64, 128}, bits in {2, 4, 8}. */
+int b200_quantize(b200_ctx* ctx, const void* w, int dtype, int64_t rows, int64_t K, int group_size, int bits,
+                  uint32_t* w_q, void* scales, void* biases, void* stream);
+
+/* dequantize(w, scales, biases, group_size, bits); mlx-rs/src/ops/quantization.rs:129-158.
+ * Output [rows, K] in the dtype of the scales. */
+int b200_dequantize(b200_ctx* ctx, const uint32_t* w_q, const void* scales, const void* biases, int dtype, int64_t rows,
+                    int64_t K, int group_size, int bits, void* out, void* stream);
+
+/* quantized_matmul(x, w, scales, biases, transpose, group_size, bits);
+ * mlx-rs/src/ops/quantization.rs:88-122.  x bf16 [M, K]; transpose != 0: w [N, K*bits/32]
+ * and out = x . w_hat^T (the form every layer uses, mlx-rs/src/nn/quantized.rs:363-381);
+ * transpose == 0: w [K, N*bits/32] and out = x . w_hat.  out bf16 [M, N]. */
+int b200_quantized_matmul(b200_ctx* ctx, const void* x, const uint32_t* w, const void* scales, const void* biases,
+                          int transpose, int group_size, int bits, int64_t M, int64_t K, int64_t N, void* out,
+                          void* stream);
+
+/* gather_qmm(x, w, scales, biases, lhs_indices, rhs_indices, transpose, group_size, bits,
+ * sorted_indices); mlx-rs/src/ops/quantization.rs:160-230.
+ * out[i] = x[lhs[i]] . dequantize(w[rhs[i]])^T with x bf16 [Bx, M, K], w [E, N, K*bits/32],
+ * out bf16 [n_idx, M, N].  lhs_indices may be NULL (lhs[i] = i).  transpose must be non-zero.
+ * `sorted_indices` is accepted for signature parity; rows are always grouped internally. */
+int b200_gather_qmm(b200_ctx* ctx, const void* x, const uint32_t* w, const void* scales, const void* biases,
+                    const uint32_t* lhs_indices, const uint32_t* rhs_indices, int transpose, int group_size, int bits,
+                    int sorted_indices, int64_t Bx, int64_t M, int64_t K, int64_t E, int64_t N, int64_t n_idx, void* out,
+                    void* stream);
+
+/* softmax_axis(a, -1, precise); mlx-rs/src/ops/arithmetic.rs:1312-1327.  bf16 [rows, cols],
+ * cols <= 256.  Always the precise form: exact softmax, correctly rounded to bf16. */
+int b200_softmax_axis(b200_ctx* ctx, const void* a, int64_t rows, int64_t cols, int precise, void* out, void* stream);
+
+/* argpartition_axis(a, kth, -1); mlx-rs/src/ops/sort.rs:186-226.  bf16 [rows, cols], cols <= 256.
+ * Columns 0..kth hold the kth+1 smallest elements in (value asc, index asc) order, the rest
+ * hold the remaining indices in ascending order. */
+int b200_argpartition_axis(b200_ctx* ctx, const void* a, int64_t rows, int64_t cols, int kth, uint32_t* out, void* stream);
+
+/* take_along_axis(a, indices, -1); mlx-rs/src/ops/indexing/mod.rs:424-453.  2-byte elements:
+ * a [rows, cols], indices [rows, icols] -> out [rows, icols]. */
+int b200_take_along_axis(b200_ctx* ctx, const void* a, int64_t rows, int64_t cols, const uint32_t* indices, int64_t icols,
+                         void* out, void* stream);
+
+/* fast::rms_norm(x, weight, eps); mlx-rs/src/fast.rs:178-205.  bf16 [rows, cols]; weight
+ * bf16 [cols] or NULL for ones. */
+int b200_rms_norm(b200_ctx* ctx, const void* x, const void* weight, float eps, int64_t rows, int64_t cols, void* out,
+                  void* stream);
+/* Residual add fused with the norm (the wiring of mlx-lm/src/models/qwen3.rs:310-325):
+ * sum_out = bf16(x + residual), out = rms_norm(sum_out, weight, eps). */
+int b200_add_rms_norm(b200_ctx* ctx, const void* x, const void* residual, const void* weight, float eps, int64_t rows,
+                      int64_t cols, void* sum_out, void* out, void* stream);
+/* out = bf16(a + b), n elements. */
+int b200_add(b200_ctx* ctx, const void* a, const void* b, int64_t n, void* out, void* stream);
+
+/* ---- fused entry points of the routed block ---------------------------------------------- */
+
+/* Router: gate Linear (mlx-rs/src/nn/linear.rs:83-95) + softmax_axis + argpartition_axis +
+ * take_along_axis + sum_axis/divide in the order the router mode prescribes.
+ * x bf16 [T, H] -> indices [T, k], scores bf16 [T, k]; logits (bf16 [T, E]) may be NULL. */
+int b200_router_topk(b200_ctx* ctx, const b200_moe_config* cfg, const void* x, const void* router_weight,
+                     const float* logit_bias, int64_t T, uint32_t* indices, void* scores, void* logits, void* stream);
+
+/* Token -> expert sort: argsort_axis (mlx-rs/src/ops/sort.rs:57-83) of the flat index list,
+ * its inverse, histogram and prefix sum.  indices [n]; perm, inv_perm [n]; counts [E];
+ * offsets [E+1].  Bit-exact with a stable argsort. */
+int b200_moe_permute(b200_ctx* ctx, const uint32_t* indices, int64_t n, int n_experts, uint32_t* perm, uint32_t* inv_perm,
+                     uint32_t* counts, uint32_t* offsets, void* stream);
+
+/* SwitchGLU forward: (x bf16 [T, H], indices [T, k]) -> out bf16 [T, k, H],
+ * out[t, j] = down_e( silu(gate_e(x_t)) * up_e(x_t) ), e = indices[t, j]. */
+int b200_switch_glu_forward(b200_ctx* ctx, const b200_moe_config* cfg, const b200_moe_params* params, const void* x,
+                            const uint32_t* indices, int64_t T, void* out, void* stream);
+
+/* MoE block forward: x bf16 [T, H] -> out bf16 [T, H]; aux may be NULL. */
+int b200_moe_block_forward(b200_ctx* ctx, const b200_moe_config* cfg, const b200_moe_params* params, const void* x,
+                           int64_t T, void* out, const b200_moe_aux* aux, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_MOE_H_ */

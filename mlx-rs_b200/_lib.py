@@ -1,0 +1,149 @@
+"""ctypes binding of include/b200_moe.h (the same entry points a Rust `extern "C"` crate binds)."""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libb200moe.so")
+_lib = None
+
+
+class B200Error(RuntimeError):
+    """Raised when a library call returns non-zero (mirrors mlx_rs::error::Exception)."""
+
+
+class QLinear(C.Structure):
+    _fields_ = [("weight", C.c_void_p), ("scales", C.c_void_p), ("biases", C.c_void_p)]
+
+
+class MoeConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("hidden", "inter", "n_experts", "top_k", "bits", "group_size",
+                                         "router_mode", "norm_topk_prob")]
+
+
+class MoeParams(C.Structure):
+    _fields_ = [("router_weight", C.c_void_p), ("router_logit_bias", C.c_void_p), ("gate_proj", QLinear),
+                ("up_proj", QLinear), ("down_proj", QLinear)]
+
+
+class MoeAux(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("indices", "scores", "perm", "inv_perm", "counts", "offsets", "logits")]
+
+
+EXPORTS = {
+    # name: (restype, argtypes)
+    "b200_last_error": (C.c_char_p, []),
+    "b200_set_error_handler": (None, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200_ctx_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int]),
+    "b200_ctx_destroy": (C.c_int, [C.c_void_p]),
+    "b200_ctx_reserve": (C.c_int, [C.c_void_p, C.POINTER(MoeConfig), C.c_int64]),
+    "b200_ctx_check": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b200_ctx_launch_count": (C.c_int64, [C.c_void_p]),
+    "b200_quantize": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_void_p,
+                                C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200_dequantize": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64,
+                                  C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "b200_quantized_matmul": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                        C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
+    "b200_gather_qmm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                  C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                  C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
+    "b200_softmax_axis": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
+    "b200_argpartition_axis": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
+    "b200_take_along_axis": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
+                                       C.c_void_p]),
+    "b200_rms_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int64, C.c_int64, C.c_void_p,
+                                C.c_void_p]),
+    "b200_add_rms_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int64, C.c_int64,
+                                    C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200_add": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
+    "b200_router_topk": (C.c_int, [C.c_void_p, C.POINTER(MoeConfig), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                   C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200_moe_permute": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                   C.c_void_p, C.c_void_p]),
+    "b200_switch_glu_forward": (C.c_int, [C.c_void_p, C.POINTER(MoeConfig), C.POINTER(MoeParams), C.c_void_p, C.c_void_p,
+                                          C.c_int64, C.c_void_p, C.c_void_p]),
+    "b200_moe_block_forward": (C.c_int, [C.c_void_p, C.POINTER(MoeConfig), C.POINTER(MoeParams), C.c_void_p, C.c_int64,
+                                         C.c_void_p, C.POINTER(MoeAux), C.c_void_p]),
+}
+
+
+def library_path():
+    return _LIB_PATH
+
+
+def lib():
+    """Loads libb200moe.so.  Fails loudly if it has not been built: there is no other code path."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise B200Error(f"{_LIB_PATH} is missing: run `python -c 'import __graft_entry__ as g; g.build()'` "
+                            "(nvcc, sm_100a) first; this package has no fallback implementation")
+        l = C.CDLL(_LIB_PATH)
+        for name, (res, args) in EXPORTS.items():
+            fn = getattr(l, name)  # AttributeError if the header and the library ever drift apart
+            fn.restype = res
+            fn.argtypes = args
+        _lib = l
+    return _lib
+
+
+def check(rc):
+    if rc != 0:
+        raise B200Error(lib().b200_last_error().decode("utf-8", "replace"))
+
+
+def ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def stream_ptr():
+    import torch
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class Context:
+    """Owns the library's scratch memory on one device (one per thread, like the reference's streams)."""
+
+    def __init__(self, device=None):
+        import torch
+        if not torch.cuda.is_available():
+            raise B200Error("no CUDA device: this library runs on a B200 only")
+        self.device = torch.cuda.current_device() if device is None else int(device)
+        h = C.c_void_p()
+        check(lib().b200_ctx_create(C.byref(h), self.device))
+        self._h = h
+
+    @property
+    def handle(self):
+        return self._h
+
+    def reserve(self, cfg, max_tokens):
+        check(lib().b200_ctx_reserve(self._h, C.byref(cfg), int(max_tokens)))
+
+    def check(self):
+        check(lib().b200_ctx_check(self._h, stream_ptr()))
+
+    def launch_count(self):
+        return int(lib().b200_ctx_launch_count(self._h))
+
+    def close(self):
+        if self._h:
+            lib().b200_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+_default = {}
+
+
+def default_context():
+    import torch
+    d = torch.cuda.current_device() if torch.cuda.is_available() else -1
+    if d not in _default:
+        _default[d] = Context(d if d >= 0 else None)
+    return _default[d]

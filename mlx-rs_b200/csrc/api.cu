@@ -1,0 +1,507 @@
+// C ABI of the library (see include/b200_moe.h): argument validation, scratch management and
+// the composition of kernels behind every entry point.  No kernel lives here.
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/b200_moe.h"
+#include "common.cuh"
+#include "kernels.h"
+
+namespace b200 {
+
+// ---- error slot: thread-local message + optional process-wide handler ----------------------
+static thread_local std::string g_last_error;
+static std::mutex g_handler_mu;
+static void (*g_handler)(const char*, void*) = nullptr;
+static void* g_handler_data = nullptr;
+static void (*g_handler_dtor)(void*) = nullptr;
+
+void set_error(const std::string& msg) {
+  g_last_error = msg;
+  std::lock_guard<std::mutex> lk(g_handler_mu);
+  if (g_handler) g_handler(g_last_error.c_str(), g_handler_data);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// ---- context ----------------------------------------------------------------------------------
+struct b200_ctx {
+  int device = 0;
+  unsigned char* ws = nullptr;  // scratch arena
+  size_t ws_bytes = 0;
+  size_t ws_used = 0;           // bump pointer of the call in progress
+  int* err = nullptr;           // device status word
+  int64_t launches = 0;
+
+  void begin() { ws_used = 0; }
+  // Bump-allocates from the arena; returns null when it does not fit (caller grows first).
+  void* take(size_t bytes) {
+    size_t off = (ws_used + 255) & ~size_t(255);
+    if (off + bytes > ws_bytes) return nullptr;
+    ws_used = off + bytes;
+    return ws + off;
+  }
+};
+
+static int ctx_grow(b200_ctx* c, size_t bytes) {
+  if (bytes <= c->ws_bytes) return 0;
+  B200_CUDA(cudaDeviceSynchronize());
+  if (c->ws) B200_CUDA(cudaFree(c->ws));
+  c->ws = nullptr;
+  c->ws_bytes = 0;
+  size_t want = bytes + bytes / 8 + (1 << 20);
+  B200_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->ws), want));
+  c->ws_bytes = want;
+  return 0;
+}
+
+static inline size_t al(size_t b) { return (b + 255) & ~size_t(255); }
+
+// scratch needed by one block forward over T tokens
+static size_t block_scratch_bytes(const b200_moe_config& cfg, int64_t T) {
+  const int64_t n = T * cfg.top_k, E = cfg.n_experts;
+  size_t b = 0;
+  b += al(sizeof(uint16_t) * T * E);                 // logits
+  b += al(sizeof(uint32_t) * n) * 3;                 // idx, perm, inv
+  b += al(sizeof(uint16_t) * n);                     // scores
+  b += al(sizeof(uint32_t) * (E + 1)) * 3 + al(16);  // counts, offsets, active, n_active
+  b += al(sizeof(uint32_t) * permute_scratch_words(n, (int)E));
+  b += al(sizeof(uint16_t) * n * cfg.inter);         // h
+  b += al(sizeof(uint16_t) * n * cfg.hidden);        // per-assignment outputs
+  return b + 4096;
+}
+
+static int check_cfg(const b200_moe_config* cfg) {
+  B200_REQUIRE(cfg != nullptr, "config is null");
+  B200_REQUIRE(cfg->bits == 4 || cfg->bits == 8, "bits must be 4 or 8");
+  B200_REQUIRE(cfg->group_size == 64, "group_size must be 64");
+  B200_REQUIRE(cfg->hidden > 0 && cfg->hidden % 64 == 0, "hidden must be a positive multiple of 64");
+  B200_REQUIRE(cfg->inter > 0 && cfg->inter % 64 == 0, "inter must be a positive multiple of 64");
+  B200_REQUIRE(cfg->n_experts > 0 && cfg->n_experts <= 256, "n_experts must be in 1..256");
+  B200_REQUIRE(cfg->top_k > 0 && cfg->top_k <= 32 && cfg->top_k <= cfg->n_experts, "top_k must be in 1..min(32, n_experts)");
+  B200_REQUIRE(cfg->router_mode == B200_ROUTER_SOFTMAX_TOPK || cfg->router_mode == B200_ROUTER_TOPK_SOFTMAX,
+               "unknown router_mode");
+  return 0;
+}
+
+#define CTX_ENTER(ctx)                             \
+  B200_REQUIRE((ctx) != nullptr, "context is null"); \
+  B200_CUDA(cudaSetDevice((ctx)->device));          \
+  (ctx)->begin()
+
+#define LAUNCHED(ctx, n)                                                        \
+  do {                                                                          \
+    (ctx)->launches += (n);                                                     \
+    cudaError_t _le = cudaGetLastError();                                       \
+    if (_le != cudaSuccess) B200_FAIL(std::string("kernel launch failed: ") + cudaGetErrorString(_le)); \
+  } while (0)
+
+static inline int permute_launches(int64_t n) { return n <= 1024 ? 1 : 3; }
+
+extern "C" {
+
+const char* b200_last_error(void) { return g_last_error.c_str(); }
+
+void b200_set_error_handler(void (*handler)(const char*, void*), void* data, void (*dtor)(void*)) {
+  std::lock_guard<std::mutex> lk(g_handler_mu);
+  if (g_handler_dtor && g_handler_data) g_handler_dtor(g_handler_data);
+  g_handler = handler;
+  g_handler_data = data;
+  g_handler_dtor = dtor;
+}
+
+int b200_ctx_create(b200_ctx** out, int device) {
+  B200_REQUIRE(out != nullptr, "out is null");
+  int n = 0;
+  B200_CUDA(cudaGetDeviceCount(&n));
+  B200_REQUIRE(device >= 0 && device < n, "no such CUDA device");
+  B200_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  B200_CUDA(cudaGetDeviceProperties(&prop, device));
+  B200_REQUIRE(prop.major == 10, "this library contains sm_100a code only; a Blackwell B200 is required");
+  b200_ctx* c = new b200_ctx();
+  c->device = device;
+  if (cudaMalloc(reinterpret_cast<void**>(&c->err), 256) != cudaSuccess || cudaMemset(c->err, 0, 256) != cudaSuccess) {
+    delete c;
+    B200_FAIL("cannot allocate the status word");
+  }
+  *out = c;
+  return 0;
+}
+
+int b200_ctx_destroy(b200_ctx* c) {
+  if (!c) return 0;
+  cudaSetDevice(c->device);
+  cudaDeviceSynchronize();
+  if (c->ws) cudaFree(c->ws);
+  if (c->err) cudaFree(c->err);
+  delete c;
+  return 0;
+}
+
+int b200_ctx_reserve(b200_ctx* c, const b200_moe_config* cfg, int64_t max_tokens) {
+  CTX_ENTER(c);
+  if (check_cfg(cfg)) return 1;
+  B200_REQUIRE(max_tokens >= 0, "max_tokens is negative");
+  return ctx_grow(c, block_scratch_bytes(*cfg, max_tokens));
+}
+
+int b200_ctx_check(b200_ctx* c, void* stream) {
+  CTX_ENTER(c);
+  B200_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  int h = 0;
+  B200_CUDA(cudaMemcpy(&h, c->err, sizeof(int), cudaMemcpyDeviceToHost));
+  if (h != 0) {
+    B200_CUDA(cudaMemset(c->err, 0, sizeof(int)));
+    B200_FAIL(h == 2 ? "an expert index was out of range" : "a gather index was out of range");
+  }
+  return 0;
+}
+
+int64_t b200_ctx_launch_count(const b200_ctx* c) { return c ? c->launches : 0; }
+
+// ---- plain ops ----------------------------------------------------------------------------------
+
+static int check_quant_args(int gs, int bits, int64_t K) {
+  B200_REQUIRE(bits == 2 || bits == 4 || bits == 8, "bits must be 2, 4 or 8");
+  B200_REQUIRE(gs == 32 || gs == 64 || gs == 128, "group_size must be 32, 64 or 128");
+  B200_REQUIRE(K > 0 && K % gs == 0, "the last axis must be a multiple of group_size");
+  return 0;
+}
+
+int b200_quantize(b200_ctx* c, const void* w, int dtype, int64_t rows, int64_t K, int gs, int bits, uint32_t* wq,
+                  void* scales, void* biases, void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(dtype == B200_F32 || dtype == B200_BF16, "dtype must be float32 or bfloat16");
+  if (check_quant_args(gs, bits, K)) return 1;
+  B200_REQUIRE(rows >= 0, "rows is negative");
+  B200_REQUIRE(rows == 0 || (w && wq && scales && biases), "null tensor");
+  if (launch_quantize(w, dtype == B200_BF16, rows, K, gs, bits, wq, scales, biases, static_cast<cudaStream_t>(stream)))
+    return 1;
+  LAUNCHED(c, rows ? 1 : 0);
+  return 0;
+}
+
+int b200_dequantize(b200_ctx* c, const uint32_t* wq, const void* scales, const void* biases, int dtype, int64_t rows,
+                    int64_t K, int gs, int bits, void* out, void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(dtype == B200_F32 || dtype == B200_BF16, "dtype must be float32 or bfloat16");
+  if (check_quant_args(gs, bits, K)) return 1;
+  B200_REQUIRE(rows >= 0, "rows is negative");
+  B200_REQUIRE(rows == 0 || (wq && scales && biases && out), "null tensor");
+  if (launch_dequantize(wq, scales, biases, dtype == B200_BF16, rows, K, gs, bits, out, static_cast<cudaStream_t>(stream)))
+    return 1;
+  LAUNCHED(c, rows ? 1 : 0);
+  return 0;
+}
+
+// Shared by quantized_matmul, gather_qmm and the block: run one grouped product.
+static int run_grouped(b200_ctx* c, GroupedArgs& a, int nmat, int bits, int max_active, int64_t rows, cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (launch_grouped_qmm_small(a, nmat, bits, max_active, rows, st)) return 1;
+  LAUNCHED(c, 1);
+  return 0;
+}
+
+int b200_quantized_matmul(b200_ctx* c, const void* x, const uint32_t* w, const void* scales, const void* biases,
+                          int transpose, int gs, int bits, int64_t M, int64_t K, int64_t N, void* out, void* stream) {
+  CTX_ENTER(c);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  B200_REQUIRE(bits == 4 || bits == 8, "bits must be 4 or 8");
+  B200_REQUIRE(gs == 64, "group_size must be 64");
+  B200_REQUIRE(M >= 0 && K > 0 && N > 0, "bad shape");
+  B200_REQUIRE(biases != nullptr, "biases are required in affine mode");
+  B200_REQUIRE(M == 0 || (x && w && scales && out), "null tensor");
+  if (M == 0) return 0;
+  if (!transpose) {
+    B200_REQUIRE(N % gs == 0, "N must be a multiple of group_size when transpose is false");
+    if (launch_qmm_rowmajor(x, w, scales, biases, M, K, N, gs, bits, out, st)) return 1;
+    LAUNCHED(c, 1);
+    return 0;
+  }
+  B200_REQUIRE(K % gs == 0, "K must be a multiple of group_size");
+  if (ctx_grow(c, 4096)) return 1;
+  uint32_t* seg = static_cast<uint32_t*>(c->take(64));
+  launch_dense_segments(seg + 0, seg + 4, seg + 8, seg + 12, (uint32_t)M, st);
+  LAUNCHED(c, 1);
+  GroupedArgs a{};
+  a.x = x;
+  a.w[0] = w;
+  a.scales[0] = scales;
+  a.biases[0] = biases;
+  a.offsets = seg + 4;
+  a.active = seg + 8;
+  a.n_active = seg + 12;
+  a.src_mode = kSrcIdent;
+  a.dst_perm = 0;
+  a.out = out;
+  a.K = (int)K;
+  a.N = (int)N;
+  return run_grouped(c, a, 1, bits, 1, M, st);
+}
+
+int b200_gather_qmm(b200_ctx* c, const void* x, const uint32_t* w, const void* scales, const void* biases,
+                    const uint32_t* lhs, const uint32_t* rhs, int transpose, int gs, int bits, int sorted_indices,
+                    int64_t Bx, int64_t M, int64_t K, int64_t E, int64_t N, int64_t n_idx, void* out, void* stream) {
+  (void)sorted_indices;
+  (void)Bx;
+  CTX_ENTER(c);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  B200_REQUIRE(transpose != 0, "only transpose = true is supported (the form every layer uses)");
+  B200_REQUIRE(bits == 4 || bits == 8, "bits must be 4 or 8");
+  B200_REQUIRE(gs == 64, "group_size must be 64");
+  B200_REQUIRE(M > 0 && K > 0 && N > 0 && n_idx >= 0, "bad shape");
+  B200_REQUIRE(K % gs == 0, "K must be a multiple of group_size");
+  B200_REQUIRE(E > 0 && E <= 256, "the number of weight matrices must be in 1..256");
+  B200_REQUIRE(biases != nullptr, "biases are required in affine mode");
+  B200_REQUIRE(rhs != nullptr, "rhs_indices is required");
+  if (n_idx == 0) return 0;
+  B200_REQUIRE(x && w && scales && out, "null tensor");
+  const int64_t n = n_idx * M;
+  B200_REQUIRE(n < (int64_t(1) << 31), "too many rows");
+  size_t need = al(sizeof(uint32_t) * n) * 4 + al(sizeof(uint32_t) * (E + 1)) * 3 + al(16) +
+                al(sizeof(uint32_t) * permute_scratch_words(n, (int)E)) + 4096;
+  if (ctx_grow(c, need)) return 1;
+  uint32_t* flat_e = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
+  uint32_t* flat_s = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
+  uint32_t* perm = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
+  uint32_t* inv = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
+  uint32_t* counts = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  uint32_t* offsets = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  uint32_t* active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  uint32_t* n_active = static_cast<uint32_t*>(c->take(16));
+  uint32_t* chunk = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * permute_scratch_words(n, (int)E)));
+  launch_expand_indices(lhs, rhs, n_idx, (int)M, flat_e, flat_s, st);
+  launch_permute(flat_e, n, (int)E, perm, inv, counts, offsets, active, n_active, chunk, c->err, st);
+  LAUNCHED(c, 1 + permute_launches(n));
+  GroupedArgs a{};
+  a.x = x;
+  a.w[0] = w;
+  a.scales[0] = scales;
+  a.biases[0] = biases;
+  a.offsets = offsets;
+  a.active = active;
+  a.n_active = n_active;
+  a.perm = perm;
+  a.src_map = flat_s;
+  a.src_mode = kSrcMap;
+  a.dst_perm = 1;
+  a.out = out;
+  a.K = (int)K;
+  a.N = (int)N;
+  return run_grouped(c, a, 1, bits, (int)(E < n ? E : n), n, st);
+}
+
+int b200_softmax_axis(b200_ctx* c, const void* a, int64_t rows, int64_t cols, int precise, void* out, void* stream) {
+  (void)precise;
+  CTX_ENTER(c);
+  B200_REQUIRE(cols > 0 && cols <= 256, "cols must be in 1..256");
+  B200_REQUIRE(rows >= 0 && (rows == 0 || (a && out)), "bad arguments");
+  launch_softmax(a, (int)rows, (int)cols, out, static_cast<cudaStream_t>(stream));
+  LAUNCHED(c, rows ? 1 : 0);
+  return 0;
+}
+
+int b200_argpartition_axis(b200_ctx* c, const void* a, int64_t rows, int64_t cols, int kth, uint32_t* out, void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(cols > 0 && cols <= 256, "cols must be in 1..256");
+  B200_REQUIRE(kth >= 0 && kth < cols, "kth is out of range for the axis");
+  B200_REQUIRE(rows >= 0 && (rows == 0 || (a && out)), "bad arguments");
+  launch_argpartition(a, (int)rows, (int)cols, kth, out, static_cast<cudaStream_t>(stream));
+  LAUNCHED(c, rows ? 1 : 0);
+  return 0;
+}
+
+int b200_take_along_axis(b200_ctx* c, const void* a, int64_t rows, int64_t cols, const uint32_t* idx, int64_t icols,
+                         void* out, void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(rows >= 0 && cols > 0 && icols >= 0, "bad shape");
+  B200_REQUIRE(rows * icols == 0 || (a && idx && out), "null tensor");
+  launch_take_along(a, (int)rows, (int)cols, idx, (int)icols, out, c->err, static_cast<cudaStream_t>(stream));
+  LAUNCHED(c, rows * icols ? 1 : 0);
+  return 0;
+}
+
+int b200_rms_norm(b200_ctx* c, const void* x, const void* weight, float eps, int64_t rows, int64_t cols, void* out,
+                  void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(rows >= 0 && cols > 0 && (rows == 0 || (x && out)), "bad arguments");
+  launch_rms_norm(x, nullptr, weight, eps, rows, cols, out, nullptr, static_cast<cudaStream_t>(stream));
+  LAUNCHED(c, rows ? 1 : 0);
+  return 0;
+}
+
+int b200_add_rms_norm(b200_ctx* c, const void* x, const void* residual, const void* weight, float eps, int64_t rows,
+                      int64_t cols, void* sum_out, void* out, void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(rows >= 0 && cols > 0 && (rows == 0 || (x && residual && out)), "bad arguments");
+  launch_rms_norm(x, residual, weight, eps, rows, cols, out, sum_out, static_cast<cudaStream_t>(stream));
+  LAUNCHED(c, rows ? 1 : 0);
+  return 0;
+}
+
+int b200_add(b200_ctx* c, const void* a, const void* b, int64_t n, void* out, void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(n >= 0 && (n == 0 || (a && b && out)), "bad arguments");
+  launch_add(a, b, n, out, static_cast<cudaStream_t>(stream));
+  LAUNCHED(c, n ? 1 : 0);
+  return 0;
+}
+
+// ---- fused entry points ---------------------------------------------------------------------------
+
+int b200_router_topk(b200_ctx* c, const b200_moe_config* cfg, const void* x, const void* wr, const float* logit_bias,
+                     int64_t T, uint32_t* indices, void* scores, void* logits, void* stream) {
+  CTX_ENTER(c);
+  if (check_cfg(cfg)) return 1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  B200_REQUIRE(T >= 0 && T < (1 << 24), "bad token count");
+  if (T == 0) return 0;
+  B200_REQUIRE(x && wr && indices && scores, "null tensor");
+  if (!logits) {
+    if (ctx_grow(c, al(sizeof(uint16_t) * T * cfg->n_experts) + 4096)) return 1;
+    logits = c->take(sizeof(uint16_t) * T * cfg->n_experts);
+  }
+  launch_router_logits(x, wr, logit_bias, logits, (int)T, cfg->hidden, cfg->n_experts, st);
+  launch_route_topk(logits, (int)T, cfg->n_experts, cfg->top_k, cfg->router_mode, cfg->norm_topk_prob, indices, scores,
+                    nullptr, st);
+  LAUNCHED(c, 2);
+  return 0;
+}
+
+int b200_moe_permute(b200_ctx* c, const uint32_t* indices, int64_t n, int E, uint32_t* perm, uint32_t* inv,
+                     uint32_t* counts, uint32_t* offsets, void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(E > 0 && E <= 256, "n_experts must be in 1..256");
+  B200_REQUIRE(n >= 0 && n < (int64_t(1) << 31), "bad assignment count");
+  B200_REQUIRE(counts && offsets, "counts and offsets are required");
+  B200_REQUIRE(n == 0 || (indices && perm && inv), "null tensor");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  size_t need = al(sizeof(uint32_t) * (E + 1)) + al(16) + al(sizeof(uint32_t) * permute_scratch_words(n, E)) + 4096;
+  if (ctx_grow(c, need)) return 1;
+  uint32_t* active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  uint32_t* n_active = static_cast<uint32_t*>(c->take(16));
+  uint32_t* chunk = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * permute_scratch_words(n, E)));
+  launch_permute(indices, n, E, perm, inv, counts, offsets, active, n_active, chunk, c->err, st);
+  LAUNCHED(c, permute_launches(n));
+  return 0;
+}
+
+// Shared tail of switch_glu_forward and moe_block_forward: permute, gate/up, down.
+// `scores` null: unweighted per-assignment outputs go to `yk` ([T*k, H]).
+static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_moe_params& p, const void* x,
+                           const uint32_t* idx, const void* scores, int64_t T, void* yk, const b200_moe_aux* aux,
+                           cudaStream_t st) {
+  const int64_t n = T * cfg.top_k;
+  const int E = cfg.n_experts;
+  uint32_t* perm = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
+  uint32_t* inv = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
+  uint32_t* counts = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  uint32_t* offsets = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  uint32_t* active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  uint32_t* n_active = static_cast<uint32_t*>(c->take(16));
+  uint32_t* chunk = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * permute_scratch_words(n, E)));
+  void* h = c->take(sizeof(uint16_t) * n * cfg.inter);
+  B200_REQUIRE(perm && inv && counts && offsets && active && n_active && chunk && h, "scratch arena too small");
+  if (aux) {
+    if (aux->perm) perm = aux->perm;
+    if (aux->inv_perm) inv = aux->inv_perm;
+    if (aux->counts) counts = aux->counts;
+    if (aux->offsets) offsets = aux->offsets;
+  }
+  launch_permute(idx, n, E, perm, inv, counts, offsets, active, n_active, chunk, c->err, st);
+  LAUNCHED(c, permute_launches(n));
+  const int max_active = (int)(E < n ? E : n);
+
+  GroupedArgs gu{};
+  gu.x = x;
+  gu.w[0] = p.gate_proj.weight;
+  gu.scales[0] = p.gate_proj.scales;
+  gu.biases[0] = p.gate_proj.biases;
+  gu.w[1] = p.up_proj.weight;
+  gu.scales[1] = p.up_proj.scales;
+  gu.biases[1] = p.up_proj.biases;
+  gu.offsets = offsets;
+  gu.active = active;
+  gu.n_active = n_active;
+  gu.perm = perm;
+  gu.src_mode = kSrcPermDiv;
+  gu.src_div = cfg.top_k;
+  gu.dst_perm = 0;
+  gu.out = h;
+  gu.K = cfg.hidden;
+  gu.N = cfg.inter;
+  if (run_grouped(c, gu, 2, cfg.bits, max_active, n, st)) return 1;
+
+  GroupedArgs dn{};
+  dn.x = h;
+  dn.w[0] = p.down_proj.weight;
+  dn.scales[0] = p.down_proj.scales;
+  dn.biases[0] = p.down_proj.biases;
+  dn.offsets = offsets;
+  dn.active = active;
+  dn.n_active = n_active;
+  dn.perm = perm;
+  dn.src_mode = kSrcIdent;
+  dn.dst_perm = 1;
+  dn.row_scale = scores;
+  dn.out = yk;
+  dn.K = cfg.inter;
+  dn.N = cfg.hidden;
+  return run_grouped(c, dn, 1, cfg.bits, max_active, n, st);
+}
+
+static int check_params(const b200_moe_params* p, bool need_router) {
+  B200_REQUIRE(p != nullptr, "params is null");
+  B200_REQUIRE(!need_router || p->router_weight, "router_weight is null");
+  B200_REQUIRE(p->gate_proj.weight && p->gate_proj.scales && p->gate_proj.biases, "gate_proj is incomplete");
+  B200_REQUIRE(p->up_proj.weight && p->up_proj.scales && p->up_proj.biases, "up_proj is incomplete");
+  B200_REQUIRE(p->down_proj.weight && p->down_proj.scales && p->down_proj.biases, "down_proj is incomplete");
+  return 0;
+}
+
+int b200_switch_glu_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_moe_params* params, const void* x,
+                            const uint32_t* indices, int64_t T, void* out, void* stream) {
+  CTX_ENTER(c);
+  if (check_cfg(cfg) || check_params(params, false)) return 1;
+  B200_REQUIRE(T >= 0 && T * cfg->top_k < (int64_t(1) << 31), "bad token count");
+  if (T == 0) return 0;
+  B200_REQUIRE(x && indices && out, "null tensor");
+  if (ctx_grow(c, block_scratch_bytes(*cfg, T))) return 1;
+  return experts_forward(c, *cfg, *params, x, indices, nullptr, T, out, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int b200_moe_block_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_moe_params* params, const void* x,
+                           int64_t T, void* out, const b200_moe_aux* aux, void* stream) {
+  CTX_ENTER(c);
+  if (check_cfg(cfg) || check_params(params, true)) return 1;
+  B200_REQUIRE(T >= 0 && T < (1 << 24) && T * cfg->top_k < (int64_t(1) << 31), "bad token count");
+  if (T == 0) return 0;
+  B200_REQUIRE(x && out, "null tensor");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (ctx_grow(c, block_scratch_bytes(*cfg, T))) return 1;
+  const int64_t n = T * cfg->top_k;
+  void* logits = c->take(sizeof(uint16_t) * T * cfg->n_experts);
+  uint32_t* idx = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
+  void* scores = c->take(sizeof(uint16_t) * n);
+  void* yk = c->take(sizeof(uint16_t) * n * cfg->hidden);
+  B200_REQUIRE(logits && idx && scores && yk, "scratch arena too small");
+  if (aux) {
+    if (aux->logits) logits = aux->logits;
+    if (aux->indices) idx = aux->indices;
+    if (aux->scores) scores = aux->scores;
+  }
+  launch_router_logits(x, params->router_weight, params->router_logit_bias, logits, (int)T, cfg->hidden, cfg->n_experts, st);
+  launch_route_topk(logits, (int)T, cfg->n_experts, cfg->top_k, cfg->router_mode, cfg->norm_topk_prob, idx, scores,
+                    nullptr, st);
+  LAUNCHED(c, 2);
+  if (experts_forward(c, *cfg, *params, x, idx, scores, T, yk, aux, st)) return 1;
+  if (launch_combine(yk, T, cfg->top_k, cfg->hidden, out, st)) return 1;
+  LAUNCHED(c, 1);
+  return 0;
+}
+
+}  // extern "C"

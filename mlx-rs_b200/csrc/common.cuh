@@ -1,0 +1,71 @@
+// Shared device/host helpers for the quantized mixture-of-experts kernels (sm_100a only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+namespace b200 {
+
+// ---- error plumbing (status int + thread-local message, like the reference's
+// mlx_set_error_handler convention: mlx-rs/src/error.rs:226-280) --------------------------
+void set_error(const std::string& msg);
+#define B200_FAIL(msg)                                   \
+  do {                                                   \
+    ::b200::set_error(std::string(__func__) + ": " + (msg)); \
+    return 1;                                            \
+  } while (0)
+#define B200_REQUIRE(cond, msg) \
+  do {                          \
+    if (!(cond)) B200_FAIL(msg); \
+  } while (0)
+#define B200_CUDA(expr)                                                      \
+  do {                                                                       \
+    cudaError_t _e = (expr);                                                 \
+    if (_e != cudaSuccess) B200_FAIL(std::string(#expr) + " -> " + cudaGetErrorString(_e)); \
+  } while (0)
+
+static inline int cdiv(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
+
+// ---- bf16 bit helpers ------------------------------------------------------------------
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
+
+__device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) {
+  return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f)));
+}
+
+// float64 -> bf16 with a single round-to-nearest-even: squeeze to float32 with round-to-odd
+// (truncate, OR a sticky bit when inexact), then round that to bf16.
+__device__ __forceinline__ uint32_t f64_to_bf16_bits(double d) {
+  float f = __double2float_rz(d);
+  uint32_t u = __float_as_uint(f);
+  if (static_cast<double>(f) != d && (u & 0x7f800000u) != 0x7f800000u) u |= 1u;
+  return f32_to_bf16_bits(__uint_as_float(u));
+}
+
+// exact bf16 -> float64 (normal numbers by integer re-biasing; zero/subnormal/inf/nan by cvt)
+__device__ __forceinline__ double bf16_bits_to_f64(uint32_t b) {
+  uint32_t ex = b & 0x7f80u;
+  if (ex != 0u && ex != 0x7f80u) {
+    uint32_t f = b << 16;
+    uint32_t hi = (f & 0x80000000u) | (((f & 0x7fffffffu) >> 3) + (896u << 20));
+    return __hiloint2double(static_cast<int>(hi), 0);
+  }
+  return static_cast<double>(bf16_bits_to_f32(b));
+}
+
+__device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ldg_nc_v2(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+
+}  // namespace b200

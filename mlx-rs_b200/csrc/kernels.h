@@ -1,0 +1,64 @@
+// Internal launch interface between the C-ABI layer (api.cu) and the kernel files.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+enum { kSrcIdent = 0, kSrcPermDiv = 1, kSrcMap = 2 };
+
+// One grouped product over rows that are sorted by expert.
+struct GroupedArgs {
+  const void* x;              // bf16 source rows [*, K]
+  const uint32_t* w[2];       // packed weights [E, N, K*bits/32]   ([1] = second matrix when NMAT == 2)
+  const void* scales[2];      // bf16 [E, N, K/64]
+  const void* biases[2];      // bf16 [E, N, K/64]
+  const uint32_t* offsets;    // [E+1] first sorted position of each expert
+  const uint32_t* active;     // experts that own at least one row
+  const uint32_t* n_active;   // device scalar
+  const uint32_t* perm;       // sorted position -> flat assignment index (may be null for identity modes)
+  const uint32_t* src_map;    // flat assignment index -> source row (kSrcMap)
+  int src_mode;               // kSrcIdent: row p; kSrcPermDiv: perm[p] / src_div; kSrcMap: src_map[perm[p]]
+  int src_div;
+  int dst_perm;               // 0: out row = sorted position, 1: out row = perm[p]
+  const void* row_scale;      // bf16, indexed by out row; may be null
+  void* out;                  // bf16 [rows, N]
+  int K, N;
+};
+
+// router.cu
+int launch_router_logits(const void* x, const void* w, const float* logit_bias, void* logits, int T, int H, int E,
+                         cudaStream_t st);
+int launch_route_topk(const void* logits, int T, int E, int k, int mode, int renorm, uint32_t* idx, void* scores,
+                      void* probs, cudaStream_t st);
+int launch_argpartition(const void* a, int rows, int cols, int kth, uint32_t* out, cudaStream_t st);
+int launch_softmax(const void* a, int rows, int cols, void* out, cudaStream_t st);
+int launch_take_along(const void* a, int rows, int cols, const uint32_t* idx, int icol, void* out, int* err,
+                      cudaStream_t st);
+
+// permute.cu
+int launch_permute(const uint32_t* idx, int64_t n, int E, uint32_t* perm, uint32_t* inv, uint32_t* counts,
+                   uint32_t* offsets, uint32_t* active, uint32_t* n_active, uint32_t* chunk_scratch, int* err,
+                   cudaStream_t st);
+size_t permute_scratch_words(int64_t n, int E);
+
+// qmm_decode.cu
+int launch_grouped_qmm_small(const GroupedArgs& a, int nmat, int bits, int max_active, int64_t rows, cudaStream_t st);
+
+// misc.cu
+int launch_quantize(const void* w, int is_bf16, int64_t rows, int64_t K, int gs, int bits, uint32_t* wq, void* scales,
+                    void* biases, cudaStream_t st);
+int launch_dequantize(const uint32_t* wq, const void* scales, const void* biases, int is_bf16, int64_t rows, int64_t K,
+                      int gs, int bits, void* out, cudaStream_t st);
+int launch_combine(const void* yk, int64_t T, int k, int64_t H, void* out, cudaStream_t st);
+int launch_rms_norm(const void* x, const void* residual, const void* weight, float eps, int64_t rows, int64_t cols,
+                    void* out, void* sum_out, cudaStream_t st);
+int launch_add(const void* a, const void* b, int64_t n, void* out, cudaStream_t st);
+int launch_qmm_rowmajor(const void* x, const uint32_t* wq, const void* scales, const void* biases, int64_t M, int64_t K,
+                        int64_t N, int gs, int bits, void* out, cudaStream_t st);
+int launch_dense_segments(uint32_t* counts, uint32_t* offsets, uint32_t* active, uint32_t* n_active, uint32_t rows,
+                          cudaStream_t st);
+int launch_expand_indices(const uint32_t* lhs, const uint32_t* rhs, int64_t n_idx, int M, uint32_t* flat_expert,
+                          uint32_t* flat_src, cudaStream_t st);
+
+}  // namespace b200

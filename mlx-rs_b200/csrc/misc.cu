@@ -1,0 +1,261 @@
+// Memory-bound helpers of the quantized path: affine quantize / dequantize, the k-way
+// combine, residual-add + RMSNorm, and small index utilities.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace b200 {
+
+// ---------------------------------------------------------------------------------------
+// quantize (mlx-rs/src/ops/quantization.rs:48-83, mode "affine"): one thread per group.
+// The group extreme with the larger magnitude is made exactly representable, the scale takes
+// its sign from which extreme that is, the bias is that extreme (or 0 when it rounds to code
+// 0); codes use the unrounded float32 scale and bias; element i of a word sits in bits
+// [bits*i, bits*i+bits).  Every operation is a single IEEE float32 operation so that the
+// result is reproducible bit for bit on any conforming implementation.
+// ---------------------------------------------------------------------------------------
+template <bool BF16>
+__global__ void __launch_bounds__(128) quantize_kernel(const void* __restrict__ w, int64_t n_groups, int gs, int bits,
+                                                       uint32_t* __restrict__ wq, void* __restrict__ scales,
+                                                       void* __restrict__ biases) {
+  int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gi >= n_groups) return;
+  const float n_bins = (float)((1 << bits) - 1);
+  const int epw = 32 / bits;
+  auto ld = [&](int i) -> float {
+    if constexpr (BF16)
+      return bf16_bits_to_f32(static_cast<const unsigned short*>(w)[gi * gs + i]);
+    else
+      return static_cast<const float*>(w)[gi * gs + i];
+  };
+  float wmin = ld(0), wmax = wmin;
+  for (int i = 1; i < gs; ++i) {
+    float v = ld(i);
+    wmin = fminf(wmin, v);
+    wmax = fmaxf(wmax, v);
+  }
+  float scale = fmaxf(__fdiv_rn(__fsub_rn(wmax, wmin), n_bins), 1e-7f);
+  const bool side = fabsf(wmin) > fabsf(wmax);
+  scale = side ? scale : -scale;
+  const float edge = side ? wmin : wmax;
+  const float q0 = roundf(__fdiv_rn(edge, scale));
+  const bool at_zero = (q0 == 0.0f);
+  scale = at_zero ? scale : __fdiv_rn(edge, q0);
+  const float bias = at_zero ? 0.0f : edge;
+  if constexpr (BF16) {
+    static_cast<__nv_bfloat16*>(scales)[gi] = __float2bfloat16_rn(scale);
+    static_cast<__nv_bfloat16*>(biases)[gi] = __float2bfloat16_rn(bias);
+  } else {
+    static_cast<float*>(scales)[gi] = scale;
+    static_cast<float*>(biases)[gi] = bias;
+  }
+  for (int i = 0; i < gs; i += epw) {
+    uint32_t word = 0;
+    for (int j = 0; j < epw; ++j) {
+      float q = roundf(__fdiv_rn(__fsub_rn(ld(i + j), bias), scale));
+      q = fminf(fmaxf(q, 0.0f), n_bins);
+      word |= (uint32_t)q << (bits * j);
+    }
+    wq[(gi * gs + i) / epw] = word;
+  }
+}
+
+int launch_quantize(const void* w, int is_bf16, int64_t rows, int64_t K, int gs, int bits, uint32_t* wq, void* scales,
+                    void* biases, cudaStream_t st) {
+  int64_t ng = rows * (K / gs);
+  if (ng == 0) return 0;
+  if (is_bf16)
+    quantize_kernel<true><<<cdiv(ng, 128), 128, 0, st>>>(w, ng, gs, bits, wq, scales, biases);
+  else
+    quantize_kernel<false><<<cdiv(ng, 128), 128, 0, st>>>(w, ng, gs, bits, wq, scales, biases);
+  return 0;
+}
+
+// dequantize (mlx-rs/src/ops/quantization.rs:129-158): w_hat = scale*q + bias, one float32
+// multiply then one float32 add, stored in the dtype of the scales.  One thread per word.
+template <bool BF16>
+__global__ void dequantize_kernel(const uint32_t* __restrict__ wq, const void* __restrict__ scales,
+                                  const void* __restrict__ biases, int64_t n_words, int gs, int bits,
+                                  void* __restrict__ out) {
+  int64_t wi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (wi >= n_words) return;
+  const int epw = 32 / bits;
+  const uint32_t mask = (1u << bits) - 1u;
+  const uint32_t word = wq[wi];
+  const int64_t gi = wi * epw / gs;
+  float s, b;
+  if constexpr (BF16) {
+    s = bf16_bits_to_f32(static_cast<const unsigned short*>(scales)[gi]);
+    b = bf16_bits_to_f32(static_cast<const unsigned short*>(biases)[gi]);
+  } else {
+    s = static_cast<const float*>(scales)[gi];
+    b = static_cast<const float*>(biases)[gi];
+  }
+  for (int j = 0; j < epw; ++j) {
+    float v = __fadd_rn(__fmul_rn(s, (float)((word >> (bits * j)) & mask)), b);
+    if constexpr (BF16)
+      static_cast<__nv_bfloat16*>(out)[wi * epw + j] = __float2bfloat16_rn(v);
+    else
+      static_cast<float*>(out)[wi * epw + j] = v;
+  }
+}
+
+int launch_dequantize(const uint32_t* wq, const void* scales, const void* biases, int is_bf16, int64_t rows, int64_t K,
+                      int gs, int bits, void* out, cudaStream_t st) {
+  int64_t nw = rows * (K * bits / 32);
+  if (nw == 0) return 0;
+  if (is_bf16)
+    dequantize_kernel<true><<<cdiv(nw, 256), 256, 0, st>>>(wq, scales, biases, nw, gs, bits, out);
+  else
+    dequantize_kernel<false><<<cdiv(nw, 256), 256, 0, st>>>(wq, scales, biases, nw, gs, bits, out);
+  return 0;
+}
+
+// combine: out[t, c] = bf16( sum_j float(yk[t, j, c]) ), j ascending (sum_axis(-2),
+// mlx-rs/src/ops/reduction.rs:260-275; the routing weights were applied by the producer).
+__global__ void combine_kernel(const uint4* __restrict__ yk, int64_t T, int k, int64_t H8, uint4* __restrict__ out) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * H8) return;
+  const int64_t t = i / H8, c = i % H8;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int j = 0; j < k; ++j) {
+    const uint4 v = __ldg(&yk[(t * k + j) * H8 + c]);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      acc[2 * q] += __uint_as_float(u[q] << 16);
+      acc[2 * q + 1] += __uint_as_float(u[q] & 0xffff0000u);
+    }
+  }
+  uint4 o;
+  uint32_t* ou = &o.x;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) ou[q] = f32_to_bf16_bits(acc[2 * q]) | (f32_to_bf16_bits(acc[2 * q + 1]) << 16);
+  out[i] = o;
+}
+
+int launch_combine(const void* yk, int64_t T, int k, int64_t H, void* out, cudaStream_t st) {
+  if (T == 0) return 0;
+  B200_REQUIRE(H % 8 == 0, "hidden size must be a multiple of 8");
+  int64_t n = T * (H / 8);
+  combine_kernel<<<cdiv(n, 256), 256, 0, st>>>(static_cast<const uint4*>(yk), T, k, H / 8, static_cast<uint4*>(out));
+  return 0;
+}
+
+// Residual add + RMSNorm (fast::rms_norm, mlx-rs/src/fast.rs:178-205; residual wiring as in
+// mlx-lm/src/models/qwen3.rs:310-325).  s = bf16(x + residual) is written to sum_out (when
+// given) and the norm is taken over that rounded sum: out = w * s * rsqrt(mean(s^2) + eps).
+__global__ void __launch_bounds__(256) rms_norm_kernel(const __nv_bfloat16* __restrict__ x,
+                                                       const __nv_bfloat16* __restrict__ residual,
+                                                       const __nv_bfloat16* __restrict__ weight, float eps, int64_t cols,
+                                                       __nv_bfloat16* __restrict__ out, __nv_bfloat16* __restrict__ sum_out) {
+  const int64_t r = blockIdx.x;
+  const __nv_bfloat16* xr = x + r * cols;
+  __shared__ float part[8];
+  float ss = 0.f;
+  for (int64_t c = threadIdx.x; c < cols; c += 256) {
+    float v = __bfloat162float(xr[c]);
+    if (residual) {
+      __nv_bfloat16 s = __float2bfloat16_rn(v + __bfloat162float(residual[r * cols + c]));
+      if (sum_out) sum_out[r * cols + c] = s;
+      v = __bfloat162float(s);
+    }
+    ss += v * v;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += part[i];
+  const float inv = rsqrtf(tot / (float)cols + eps);
+  for (int64_t c = threadIdx.x; c < cols; c += 256) {
+    float v = __bfloat162float(xr[c]);
+    if (residual) v = __bfloat162float(__float2bfloat16_rn(v + __bfloat162float(residual[r * cols + c])));
+    float wv = weight ? __bfloat162float(weight[c]) : 1.0f;
+    out[r * cols + c] = __float2bfloat16_rn(wv * (v * inv));
+  }
+}
+
+int launch_rms_norm(const void* x, const void* residual, const void* weight, float eps, int64_t rows, int64_t cols,
+                    void* out, void* sum_out, cudaStream_t st) {
+  if (rows == 0) return 0;
+  rms_norm_kernel<<<(unsigned)rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x),
+                                                  static_cast<const __nv_bfloat16*>(residual),
+                                                  static_cast<const __nv_bfloat16*>(weight), eps, cols,
+                                                  static_cast<__nv_bfloat16*>(out), static_cast<__nv_bfloat16*>(sum_out));
+  return 0;
+}
+
+__global__ void add_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, int64_t n, __nv_bfloat16* out) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __float2bfloat16_rn(__bfloat162float(a[i]) + __bfloat162float(b[i]));
+}
+int launch_add(const void* a, const void* b, int64_t n, void* out, cudaStream_t st) {
+  if (n == 0) return 0;
+  add_kernel<<<cdiv(n, 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b),
+                                          n, static_cast<__nv_bfloat16*>(out));
+  return 0;
+}
+
+// quantized_matmul with transpose = false (mlx-rs/src/ops/quantization.rs:88-122): w is
+// [K, N/epw], quantised along N; out = x . w_hat.  Not on the routed path (layers always pass
+// transpose = true); a plain one-thread-per-output kernel keeps the op surface complete.
+__global__ void qmm_rowmajor_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ wq,
+                                    const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ biases,
+                                    int64_t M, int64_t K, int64_t N, int gs, int bits, __nv_bfloat16* __restrict__ out) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= M * N) return;
+  const int64_t m = i / N, n = i % N;
+  const int epw = 32 / bits;
+  const uint32_t mask = (1u << bits) - 1u;
+  const int64_t Wp = N / epw, G = N / gs;
+  float acc = 0.f;
+  for (int64_t k = 0; k < K; ++k) {
+    uint32_t q = (wq[k * Wp + n / epw] >> (bits * (n % epw))) & mask;
+    float wv = __bfloat162float(scales[k * G + n / gs]) * (float)q + __bfloat162float(biases[k * G + n / gs]);
+    acc += __bfloat162float(x[m * K + k]) * wv;
+  }
+  out[i] = __float2bfloat16_rn(acc);
+}
+int launch_qmm_rowmajor(const void* x, const uint32_t* wq, const void* scales, const void* biases, int64_t M, int64_t K,
+                        int64_t N, int gs, int bits, void* out, cudaStream_t st) {
+  if (M * N == 0) return 0;
+  qmm_rowmajor_kernel<<<cdiv(M * N, 256), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), wq, static_cast<const __nv_bfloat16*>(scales),
+      static_cast<const __nv_bfloat16*>(biases), M, K, N, gs, bits, static_cast<__nv_bfloat16*>(out));
+  return 0;
+}
+
+// One segment holding every row (dense quantized Linear as the E = 1 case of the grouped kernel).
+__global__ void dense_segments_kernel(uint32_t* counts, uint32_t* offsets, uint32_t* active, uint32_t* n_active, uint32_t rows) {
+  counts[0] = rows;
+  offsets[0] = 0;
+  offsets[1] = rows;
+  active[0] = 0;
+  *n_active = rows ? 1u : 0u;
+}
+int launch_dense_segments(uint32_t* counts, uint32_t* offsets, uint32_t* active, uint32_t* n_active, uint32_t rows,
+                          cudaStream_t st) {
+  dense_segments_kernel<<<1, 1, 0, st>>>(counts, offsets, active, n_active, rows);
+  return 0;
+}
+
+// gather_qmm with M rows per batch entry: assignment i*M + m uses expert rhs[i] and source
+// row lhs[i]*M + m (lhs == null: i*M + m).
+__global__ void expand_indices_kernel(const uint32_t* __restrict__ lhs, const uint32_t* __restrict__ rhs, int64_t n_idx,
+                                      int M, uint32_t* __restrict__ flat_expert, uint32_t* __restrict__ flat_src) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_idx * M) return;
+  int64_t b = i / M, m = i % M;
+  flat_expert[i] = rhs[b];
+  flat_src[i] = (lhs ? lhs[b] : (uint32_t)b) * (uint32_t)M + (uint32_t)m;
+}
+int launch_expand_indices(const uint32_t* lhs, const uint32_t* rhs, int64_t n_idx, int M, uint32_t* flat_expert,
+                          uint32_t* flat_src, cudaStream_t st) {
+  if (n_idx * M == 0) return 0;
+  expand_indices_kernel<<<cdiv(n_idx * M, 256), 256, 0, st>>>(lhs, rhs, n_idx, M, flat_expert, flat_src);
+  return 0;
+}
+
+}  // namespace b200

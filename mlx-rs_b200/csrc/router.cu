@@ -1,0 +1,364 @@
+// Router kernels: gate Linear (exact, correctly rounded bf16 logits), softmax / top-k /
+// renormalisation per token, plus the stand-alone softmax, argpartition and take_along_axis
+// ops of the reference surface.
+//
+// Reference call sites replaced: nn::Linear forward (mlx-rs/src/nn/linear.rs:83-95),
+// softmax_axis (mlx-rs/src/ops/arithmetic.rs:1312-1327), argpartition_axis
+// (mlx-rs/src/ops/sort.rs:186-226), take_along_axis (mlx-rs/src/ops/indexing/mod.rs:424-453),
+// sum_axis + divide for the renormalisation.
+//
+// Routing must be bit-exact, so every value a routing decision depends on is defined as the
+// correctly rounded bf16 of an exactly specified quantity: the logit is the exact dot product
+// of the bf16 operands (accumulated in float64: products of two bf16 numbers are exact in
+// float64 and the sum carries ~2^-53 relative error, far below half a bf16 ulp), the
+// probability is the exact softmax of those bf16 logits.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace b200 {
+
+// ---------------------------------------------------------------------------------------
+// logits[t,e] = RN_bf16( sum_h x[t,h] * w[e,h] )   in float64.
+// CTA tile: (RT*TGX) tokens x (4*EGX) experts, 256 threads.  A thread owns an RT x 4 output
+// tile (tokens tgx + TGX*j, experts egx + EGX*i) and a K-slice: the 256 threads are split
+// into KS = 256/(TGX*EGX) slices of every staged K-chunk.  Operands are converted to float64
+// once while staging them k-major in shared memory, so the inner loop is LDS.64 + DFMA.
+// ---------------------------------------------------------------------------------------
+template <int RT, int TGX, int EGX>
+__global__ void __launch_bounds__(256) router_logits_kernel(const __nv_bfloat16* __restrict__ x,
+                                                            const __nv_bfloat16* __restrict__ w,
+                                                            const float* __restrict__ logit_bias,
+                                                            __nv_bfloat16* __restrict__ logits, int T, int H, int E) {
+  constexpr int TT = RT * TGX, TE = 4 * EGX, NTILE = TGX * EGX, KS = 256 / NTILE;
+  constexpr int KC = (TT + TE > 64) ? 32 : 64;  // keeps static shared memory under 48 KB
+  static_assert(256 % NTILE == 0 && KC % KS == 0, "tile shape");
+  constexpr int KPT = KC / KS;  // k-steps per thread per chunk
+  // rows padded by one double so that the transposing stores below spread over all banks
+  __shared__ double xs[KC][TT + 1];
+  __shared__ double ws[KC][TE + 1];
+
+  const int tid = threadIdx.x;
+  const int tile = tid % NTILE, ks = tid / NTILE;
+  const int tgx = tile % TGX, egx = tile / TGX;
+  const int t0 = blockIdx.y * TT, e0 = blockIdx.x * TE;
+
+  double acc[RT][4];
+#pragma unroll
+  for (int j = 0; j < RT; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[j][i] = 0.0;
+
+  const unsigned short* xb = reinterpret_cast<const unsigned short*>(x);
+  const unsigned short* wb = reinterpret_cast<const unsigned short*>(w);
+
+  for (int k0 = 0; k0 < H; k0 += KC) {
+    // stage: rows along tid / KC, k along tid % KC (coalesced 128 B per row segment)
+    for (int i = tid; i < TT * KC; i += 256) {
+      int r = i / KC, k = i % KC;
+      int t = t0 + r;
+      uint32_t b = (t < T && k0 + k < H) ? xb[(size_t)t * H + k0 + k] : 0u;
+      xs[k][r] = bf16_bits_to_f64(b);
+    }
+    for (int i = tid; i < TE * KC; i += 256) {
+      int r = i / KC, k = i % KC;
+      int e = e0 + r;
+      uint32_t b = (e < E && k0 + k < H) ? wb[(size_t)e * H + k0 + k] : 0u;
+      ws[k][r] = bf16_bits_to_f64(b);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < KPT; ++kk) {
+      const int k = ks * KPT + kk;
+      double xv[RT], wv[4];
+#pragma unroll
+      for (int j = 0; j < RT; ++j) xv[j] = xs[k][tgx + TGX * j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) wv[i] = ws[k][egx + EGX * i];
+#pragma unroll
+      for (int j = 0; j < RT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = fma(xv[j], wv[i], acc[j][i]);
+    }
+    __syncthreads();
+  }
+
+  // cross-slice reduction in a fixed order (slice 0 + slice 1 + ...)
+  if constexpr (KS > 1) {
+    __shared__ double red[256 * RT * 4];
+#pragma unroll
+    for (int j = 0; j < RT; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) red[(j * 4 + i) * 256 + tid] = acc[j][i];
+    __syncthreads();
+    if (ks == 0) {
+#pragma unroll
+      for (int j = 0; j < RT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          double s = acc[j][i];
+          for (int q = 1; q < KS; ++q) s += red[(j * 4 + i) * 256 + q * NTILE + tile];
+          acc[j][i] = s;
+        }
+    }
+  }
+  if (ks == 0) {
+#pragma unroll
+    for (int j = 0; j < RT; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        int t = t0 + tgx + TGX * j, e = e0 + egx + EGX * i;
+        if (t < T && e < E) {
+          uint32_t bits = f64_to_bf16_bits(acc[j][i]);
+          if (logit_bias) bits = f32_to_bf16_bits(bf16_bits_to_f32(bits) + logit_bias[e]);
+          logits[(size_t)t * E + e] = __ushort_as_bfloat16((unsigned short)bits);
+        }
+      }
+  }
+}
+
+int launch_router_logits(const void* x, const void* w, const float* logit_bias, void* logits, int T, int H, int E,
+                         cudaStream_t st) {
+  auto xp = static_cast<const __nv_bfloat16*>(x);
+  auto wp = static_cast<const __nv_bfloat16*>(w);
+  auto lp = static_cast<__nv_bfloat16*>(logits);
+  if (T <= 4) {
+    dim3 grid(cdiv(E, 16), T);
+    router_logits_kernel<1, 1, 4><<<grid, 256, 0, st>>>(xp, wp, logit_bias, lp, T, H, E);
+  } else if (T <= 256) {
+    dim3 grid(cdiv(E, 16), cdiv(T, 8));
+    router_logits_kernel<4, 2, 4><<<grid, 256, 0, st>>>(xp, wp, logit_bias, lp, T, H, E);
+  } else {
+    dim3 grid(cdiv(E, 64), cdiv(T, 64));
+    router_logits_kernel<4, 16, 16><<<grid, 256, 0, st>>>(xp, wp, logit_bias, lp, T, H, E);
+  }
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Per-token routing: one warp per token, each lane keeps E/32 (<= 8) experts.
+// mode 0: p = RN_bf16(softmax_f64(logits)); top-k by (p desc, expert asc); score = p or
+//         RN_bf16(p / sum of selected p).   mode 1: top-k by (logit desc, expert asc);
+//         score = RN_bf16(softmax_f64 over the k selected logits).
+// Selection key: order-preserving 16-bit image of the bf16 value in the high half, inverted
+// expert index in the low half; k rounds of warp-wide max.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t order_key(uint32_t bf16_bits) {
+  if (bf16_bits == 0x8000u) bf16_bits = 0u;  // -0 and +0 compare equal
+  return (bf16_bits & 0x8000u) ? (~bf16_bits & 0xffffu) : (bf16_bits | 0x8000u);
+}
+__device__ __forceinline__ uint32_t key_to_bits(uint32_t key16) {
+  return (key16 & 0x8000u) ? (key16 & 0x7fffu) : (~key16 & 0xffffu);
+}
+
+constexpr int kMaxPerLane = 8;   // experts per lane -> E <= 256
+constexpr int kMaxTopK = 32;
+
+__global__ void __launch_bounds__(128) route_topk_kernel(const __nv_bfloat16* __restrict__ logits, int T, int E, int k,
+                                                         int mode, int renorm, uint32_t* __restrict__ idx,
+                                                         __nv_bfloat16* __restrict__ scores,
+                                                         __nv_bfloat16* __restrict__ probs /*nullable [T,E]*/) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const unsigned short* row = reinterpret_cast<const unsigned short*>(logits) + (size_t)t * E;
+
+  uint32_t bits[kMaxPerLane];
+  float lf[kMaxPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    int e = lane + 32 * i;
+    bits[i] = (e < E) ? row[e] : 0xff80u;  // -inf padding
+    lf[i] = bf16_bits_to_f32(bits[i]);
+  }
+
+  if (mode == 0) {
+    float m = lf[0];
+#pragma unroll
+    for (int i = 1; i < kMaxPerLane; ++i) m = fmaxf(m, lf[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    double ex[kMaxPerLane];
+    double s = 0.0;
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+      int e = lane + 32 * i;
+      ex[i] = (e < E) ? exp((double)lf[i] - (double)m) : 0.0;
+      s += ex[i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+      int e = lane + 32 * i;
+      bits[i] = f64_to_bf16_bits(ex[i] / s);
+      if (probs && e < E) probs[(size_t)t * E + e] = __ushort_as_bfloat16((unsigned short)bits[i]);
+      if (e >= E) bits[i] = 0xff80u;
+    }
+  }
+
+  uint32_t keys[kMaxPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    int e = lane + 32 * i;
+    keys[i] = (e < E) ? ((order_key(bits[i]) << 16) | (0xffffu - (uint32_t)e)) : 0u;
+  }
+
+  uint32_t my_sel = 0;  // lane j keeps the j-th winner
+  for (int j = 0; j < k; ++j) {
+    uint32_t best = keys[0];
+#pragma unroll
+    for (int i = 1; i < kMaxPerLane; ++i) best = max(best, keys[i]);
+    best = __reduce_max_sync(0xffffffffu, best);
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i)
+      if (keys[i] == best) keys[i] = 0u;
+    if (lane == j) my_sel = best;
+  }
+
+  const bool active = lane < k;
+  const uint32_t e_sel = 0xffffu - (my_sel & 0xffffu);
+  const uint32_t v_bits = key_to_bits(my_sel >> 16);
+  const float v = active ? bf16_bits_to_f32(v_bits) : 0.f;
+  uint32_t out_bits = v_bits;
+  if (mode == 0) {
+    if (renorm) {
+      double s = active ? (double)v : 0.0;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      out_bits = f64_to_bf16_bits((double)v / s);
+    }
+  } else {
+    float m = __shfl_sync(0xffffffffu, v, 0);  // winner 0 holds the largest logit
+    double ex = active ? exp((double)v - (double)m) : 0.0;
+    double s = ex;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    out_bits = f64_to_bf16_bits(ex / s);
+  }
+  if (active) {
+    idx[(size_t)t * k + lane] = e_sel;
+    scores[(size_t)t * k + lane] = __ushort_as_bfloat16((unsigned short)out_bits);
+  }
+}
+
+int launch_route_topk(const void* logits, int T, int E, int k, int mode, int renorm, uint32_t* idx, void* scores,
+                      void* probs, cudaStream_t st) {
+  if (T == 0) return 0;
+  route_topk_kernel<<<cdiv(T, 4), 128, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), T, E, k, mode, renorm, idx,
+                                                static_cast<__nv_bfloat16*>(scores),
+                                                static_cast<__nv_bfloat16*>(probs));
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// argpartition_axis(a, kth, axis=-1) over bf16 rows: the first kth+1 output columns are the
+// kth+1 smallest elements in (value ascending, index ascending) order, the remaining columns
+// are the other indices in ascending index order (the reference leaves the order inside a
+// partition undefined).  One warp per row, cols <= 256.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) argpartition_kernel(const __nv_bfloat16* __restrict__ a, int rows, int cols,
+                                                           int kth, uint32_t* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const unsigned short* row = reinterpret_cast<const unsigned short*>(a) + (size_t)r * cols;
+  uint32_t keys[kMaxPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    int e = lane + 32 * i;
+    // smallest value first, smallest index first -> maximise (inverted value, inverted index)
+    keys[i] = (e < cols) ? (((0xffffu - order_key(row[e])) << 16) | (0xffffu - (uint32_t)e)) : 0u;
+  }
+  for (int j = 0; j <= kth; ++j) {
+    uint32_t best = keys[0];
+#pragma unroll
+    for (int i = 1; i < kMaxPerLane; ++i) best = max(best, keys[i]);
+    best = __reduce_max_sync(0xffffffffu, best);
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i)
+      if (keys[i] == best) keys[i] = 0u;
+    if (lane == 0) out[(size_t)r * cols + j] = 0xffffu - (best & 0xffffu);
+  }
+  // remaining indices in ascending order: warp-wide compaction
+  int base = kth + 1;
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    int e = lane + 32 * i;
+    bool left = (e < cols) && keys[i] != 0u;
+    uint32_t m = __ballot_sync(0xffffffffu, left);
+    if (left) out[(size_t)r * cols + base + __popc(m & ((1u << lane) - 1u))] = (uint32_t)e;
+    base += __popc(m);
+  }
+}
+
+int launch_argpartition(const void* a, int rows, int cols, int kth, uint32_t* out, cudaStream_t st) {
+  if (rows == 0) return 0;
+  argpartition_kernel<<<cdiv(rows, 4), 128, 0, st>>>(static_cast<const __nv_bfloat16*>(a), rows, cols, kth, out);
+  return 0;
+}
+
+// softmax_axis(-1, precise) over bf16 rows (cols <= 256): exact softmax, correctly rounded.
+__global__ void __launch_bounds__(128) softmax_kernel(const __nv_bfloat16* __restrict__ a, int rows, int cols,
+                                                      __nv_bfloat16* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const unsigned short* row = reinterpret_cast<const unsigned short*>(a) + (size_t)r * cols;
+  float lf[kMaxPerLane];
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    int e = lane + 32 * i;
+    lf[i] = (e < cols) ? bf16_bits_to_f32(row[e]) : -INFINITY;
+    m = fmaxf(m, lf[i]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  double ex[kMaxPerLane], s = 0.0;
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    ex[i] = (lane + 32 * i < cols) ? exp((double)lf[i] - (double)m) : 0.0;
+    s += ex[i];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    int e = lane + 32 * i;
+    if (e < cols) out[(size_t)r * cols + e] = __ushort_as_bfloat16((unsigned short)f64_to_bf16_bits(ex[i] / s));
+  }
+}
+
+int launch_softmax(const void* a, int rows, int cols, void* out, cudaStream_t st) {
+  if (rows == 0) return 0;
+  softmax_kernel<<<cdiv(rows, 4), 128, 0, st>>>(static_cast<const __nv_bfloat16*>(a), rows, cols,
+                                                static_cast<__nv_bfloat16*>(out));
+  return 0;
+}
+
+// take_along_axis(a, idx, axis=-1) for 2-byte elements.  Out-of-range indices set *err = 1.
+__global__ void take_along_kernel(const unsigned short* __restrict__ a, int rows, int cols,
+                                  const uint32_t* __restrict__ idx, int icol, unsigned short* __restrict__ out,
+                                  int* __restrict__ err) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)rows * icol) return;
+  size_t r = i / icol;
+  uint32_t j = idx[i];
+  if (j >= (uint32_t)cols) {
+    *err = 1;
+    out[i] = 0;
+    return;
+  }
+  out[i] = a[r * cols + j];
+}
+
+int launch_take_along(const void* a, int rows, int cols, const uint32_t* idx, int icol, void* out, int* err,
+                      cudaStream_t st) {
+  size_t n = (size_t)rows * icol;
+  if (n == 0) return 0;
+  take_along_kernel<<<cdiv(n, 256), 256, 0, st>>>(static_cast<const unsigned short*>(a), rows, cols, idx, icol,
+                                                  static_cast<unsigned short*>(out), err);
+  return 0;
+}
+
+}  // namespace b200

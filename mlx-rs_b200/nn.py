@@ -1,0 +1,126 @@
+"""Module layer: SwitchGlu and MoeBlock with the forward signatures the reference's modules use.
+
+`forward` mirrors `Module::forward` (mlx-rs/src/module/module.rs:27-44; template
+mlx-lm/src/models/qwen3.rs:204-255): MoeBlock.forward(x [B,L,H]) -> [B,L,H],
+SwitchGlu.forward(x [..,H], indices [..,k]) -> [..,k,H].  Parameters keep the QuantizedLinear
+field names weight / scales / biases, group_size, bits (mlx-rs/src/nn/quantized.rs:307-335)
+stacked over experts.
+"""
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib as L
+from . import ops
+
+ROUTER_SOFTMAX_TOPK = 0
+ROUTER_TOPK_SOFTMAX = 1
+
+
+@dataclass
+class QuantizedSwitchLinear:
+    """Stacked quantized projection: weight [E,out,in*bits/32] int32, scales/biases [E,out,in/gs] bf16."""
+    weight: torch.Tensor
+    scales: torch.Tensor
+    biases: torch.Tensor
+    group_size: int = ops.DEFAULT_GROUP_SIZE
+    bits: int = ops.DEFAULT_BITS
+
+    @classmethod
+    def from_weight(cls, w, group_size=ops.DEFAULT_GROUP_SIZE, bits=ops.DEFAULT_BITS, ctx=None):
+        """Quantizable::try_into_quantized (mlx-rs/src/quantization.rs:6-25) for a stacked [E,out,in] weight."""
+        return cls(*ops.quantize(w, group_size, bits, ctx=ctx), group_size=group_size, bits=bits)
+
+    def forward(self, x, indices, sorted_indices=False, ctx=None):
+        """x [n,1,in] (or [n,in]), indices [n] -> [n,1,out] via gather_qmm(transpose=true)."""
+        x3 = x if x.dim() == 3 else x.unsqueeze(-2)
+        y = ops.gather_qmm(x3, self.weight, self.scales, self.biases, None, indices, True, self.group_size, self.bits,
+                           sorted_indices, ctx=ctx)
+        return y if x.dim() == 3 else y.squeeze(-2)
+
+    def c_struct(self):
+        return L.QLinear(self.weight.data_ptr(), self.scales.data_ptr(), self.biases.data_ptr())
+
+
+class SwitchGlu:
+    def __init__(self, gate_proj, up_proj, down_proj, ctx=None):
+        self.gate_proj, self.up_proj, self.down_proj = gate_proj, up_proj, down_proj
+        self.ctx = ctx
+        E, I, _ = gate_proj.weight.shape
+        H = down_proj.weight.shape[1]
+        self.hidden, self.inter, self.n_experts = H, I, E
+
+    def _cfg(self, top_k, router_mode=0, norm_topk_prob=True):
+        return L.MoeConfig(self.hidden, self.inter, self.n_experts, top_k, self.gate_proj.bits, self.gate_proj.group_size,
+                           router_mode, int(norm_topk_prob))
+
+    def _params(self, router_weight=None, logit_bias=None):
+        return L.MoeParams(router_weight.data_ptr() if router_weight is not None else None,
+                           logit_bias.data_ptr() if logit_bias is not None else None, self.gate_proj.c_struct(),
+                           self.up_proj.c_struct(), self.down_proj.c_struct())
+
+    def forward(self, x, indices):
+        ops._cuda(x, indices)
+        ops._req(x.dtype == torch.bfloat16 and indices.dtype == torch.int32, "SwitchGlu: bf16 x, int32 indices")
+        k = indices.shape[-1]
+        T = indices.numel() // k
+        out = torch.empty(tuple(indices.shape) + (self.hidden,), dtype=x.dtype, device=x.device)
+        cfg, params = self._cfg(k), self._params()
+        L.check(L.lib().b200_switch_glu_forward(ops._ctx(self.ctx), C.byref(cfg), C.byref(params), L.ptr(x),
+                                                L.ptr(indices), T, L.ptr(out), L.stream_ptr()))
+        return out
+
+
+class MoeBlock:
+    """gate (router Linear, weight [E,H] bf16) + switch_mlp (SwitchGlu)."""
+
+    def __init__(self, gate_weight, switch_mlp, top_k, norm_topk_prob=True, router_mode=ROUTER_SOFTMAX_TOPK,
+                 router_logit_bias=None, ctx=None):
+        self.gate_weight, self.switch_mlp = gate_weight, switch_mlp
+        self.top_k, self.norm_topk_prob, self.router_mode = top_k, norm_topk_prob, router_mode
+        self.router_logit_bias = router_logit_bias
+        self.ctx = ctx
+        self._cfg = switch_mlp._cfg(top_k, router_mode, norm_topk_prob)
+        self._params = switch_mlp._params(gate_weight, router_logit_bias)
+
+    @property
+    def config(self):
+        return self._cfg
+
+    def forward(self, x, return_aux=False):
+        ops._cuda(x)
+        ops._req(x.dtype == torch.bfloat16 and x.shape[-1] == self.switch_mlp.hidden, "MoeBlock: bf16 x [.., hidden]")
+        T = x.numel() // x.shape[-1]
+        out = torch.empty_like(x)
+        aux_c, aux = None, None
+        if return_aux:
+            n, E, dev = T * self.top_k, self.switch_mlp.n_experts, x.device
+            aux = dict(indices=torch.empty((T, self.top_k), dtype=torch.int32, device=dev),
+                       scores=torch.empty((T, self.top_k), dtype=torch.bfloat16, device=dev),
+                       perm=torch.empty(n, dtype=torch.int32, device=dev),
+                       inv_perm=torch.empty(n, dtype=torch.int32, device=dev),
+                       counts=torch.empty(E, dtype=torch.int32, device=dev),
+                       offsets=torch.empty(E + 1, dtype=torch.int32, device=dev),
+                       logits=torch.empty((T, E), dtype=torch.bfloat16, device=dev))
+            aux_c = L.MoeAux(*[aux[n_].data_ptr() for n_ in ("indices", "scores", "perm", "inv_perm", "counts",
+                                                             "offsets", "logits")])
+        L.check(L.lib().b200_moe_block_forward(ops._ctx(self.ctx), C.byref(self._cfg), C.byref(self._params), L.ptr(x),
+                                               T, L.ptr(out), C.byref(aux_c) if aux_c is not None else None,
+                                               L.stream_ptr()))
+        return (out, aux) if return_aux else out
+
+
+def router_topk(x, gate_weight, top_k, router_mode=ROUTER_SOFTMAX_TOPK, norm_topk_prob=True, logit_bias=None,
+                return_logits=False, ctx=None):
+    """Router alone -> (indices [T,k] int32, scores [T,k] bf16[, logits [T,E] bf16])."""
+    ops._cuda(x, gate_weight, logit_bias)
+    T, H = x.numel() // x.shape[-1], x.shape[-1]
+    E = gate_weight.shape[0]
+    cfg = L.MoeConfig(H, 64, E, top_k, 4, 64, router_mode, int(norm_topk_prob))
+    idx = torch.empty((T, top_k), dtype=torch.int32, device=x.device)
+    sc = torch.empty((T, top_k), dtype=torch.bfloat16, device=x.device)
+    lg = torch.empty((T, E), dtype=torch.bfloat16, device=x.device) if return_logits else None
+    L.check(L.lib().b200_router_topk(ops._ctx(ctx), C.byref(cfg), L.ptr(x), L.ptr(gate_weight), L.ptr(logit_bias), T,
+                                     L.ptr(idx), L.ptr(sc), L.ptr(lg), L.stream_ptr()))
+    return (idx, sc, lg) if return_logits else (idx, sc)

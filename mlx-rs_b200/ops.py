@@ -1,0 +1,155 @@
+"""Op surface of the reference, one function per wrapper, same names / argument order / defaults.
+
+quantize / dequantize / quantized_matmul / gather_qmm: mlx-rs/src/ops/quantization.rs:48-230
+softmax_axis: mlx-rs/src/ops/arithmetic.rs:1312-1327; argpartition_axis: mlx-rs/src/ops/sort.rs:186-226
+take_along_axis: mlx-rs/src/ops/indexing/mod.rs:424-453; rms_norm: mlx-rs/src/fast.rs:178-205
+
+Tensors are torch CUDA tensors (torch only holds the memory).  Index tensors are int32 (same
+bits as the reference's uint32 for every valid index).  Calls are eager and stream-ordered.
+"""
+import torch
+
+from . import _lib as L
+
+DEFAULT_GROUP_SIZE = 64
+DEFAULT_BITS = 4
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def _ctx(ctx):
+    return (ctx or L.default_context()).handle
+
+
+def _req(cond, msg):
+    if not cond:
+        raise L.B200Error(msg)
+
+
+def _cuda(*ts):
+    for t in ts:
+        _req(t is None or (t.is_cuda and t.is_contiguous()), "tensors must be contiguous CUDA tensors")
+
+
+def quantize(w, group_size=DEFAULT_GROUP_SIZE, bits=DEFAULT_BITS, ctx=None):
+    """-> (w_q uint32-as-int32 [..., K*bits/32], scales [..., K/gs], biases [..., K/gs])."""
+    _cuda(w)
+    _req(w.dtype in _DT, "quantize: float32 or bfloat16 input")
+    _req(w.dim() >= 2, "quantize: at least 2 dimensions")  # the reference rejects 1-D input too
+    K = w.shape[-1]
+    _req(bits in (2, 4, 8) and group_size in (32, 64, 128) and K % group_size == 0,
+         f"quantize: unsupported group_size={group_size} bits={bits} for last axis {K}")
+    rows = w.numel() // K
+    wq = torch.empty(w.shape[:-1] + (K * bits // 32,), dtype=torch.int32, device=w.device)
+    s = torch.empty(w.shape[:-1] + (K // group_size,), dtype=w.dtype, device=w.device)
+    b = torch.empty_like(s)
+    L.check(L.lib().b200_quantize(_ctx(ctx), L.ptr(w), _DT[w.dtype], rows, K, group_size, bits, L.ptr(wq), L.ptr(s),
+                                  L.ptr(b), L.stream_ptr()))
+    return wq, s, b
+
+
+def dequantize(w, scales, biases, group_size=DEFAULT_GROUP_SIZE, bits=DEFAULT_BITS, ctx=None):
+    _cuda(w, scales, biases)
+    _req(scales.dtype in _DT and biases.dtype == scales.dtype, "dequantize: scales/biases float32 or bfloat16")
+    K = w.shape[-1] * 32 // bits
+    rows = w.numel() // w.shape[-1]
+    out = torch.empty(w.shape[:-1] + (K,), dtype=scales.dtype, device=w.device)
+    L.check(L.lib().b200_dequantize(_ctx(ctx), L.ptr(w), L.ptr(scales), L.ptr(biases), _DT[scales.dtype], rows, K,
+                                    group_size, bits, L.ptr(out), L.stream_ptr()))
+    return out
+
+
+def quantized_matmul(x, w, scales, biases, transpose=False, group_size=DEFAULT_GROUP_SIZE, bits=DEFAULT_BITS, ctx=None):
+    _cuda(x, w, scales, biases)
+    _req(x.dtype == torch.bfloat16 and scales.dtype == torch.bfloat16, "quantized_matmul: bf16 activations and scales")
+    K = x.shape[-1]
+    M = x.numel() // K
+    N = w.shape[0] if transpose else w.shape[1] * 32 // bits
+    _req((w.shape[1] * 32 // bits == K) if transpose else (w.shape[0] == K), "quantized_matmul: shape mismatch")
+    out = torch.empty(x.shape[:-1] + (N,), dtype=x.dtype, device=x.device)
+    L.check(L.lib().b200_quantized_matmul(_ctx(ctx), L.ptr(x), L.ptr(w), L.ptr(scales), L.ptr(biases), int(transpose),
+                                          group_size, bits, M, K, N, L.ptr(out), L.stream_ptr()))
+    return out
+
+
+def gather_qmm(x, w, scales, biases, lhs_indices=None, rhs_indices=None, transpose=True, group_size=DEFAULT_GROUP_SIZE,
+               bits=DEFAULT_BITS, sorted_indices=False, ctx=None):
+    """x [..., M, K] (batch dims flattened), w [E, N, K*bits/32] -> [*idx.shape, M, N]."""
+    _cuda(x, w, scales, biases, lhs_indices, rhs_indices)
+    _req(x.dtype == torch.bfloat16 and scales.dtype == torch.bfloat16, "gather_qmm: bf16 activations and scales")
+    _req(rhs_indices is not None, "gather_qmm: rhs_indices is required")
+    M, K = x.shape[-2], x.shape[-1]
+    Bx = x.numel() // (M * K)
+    N = w.shape[-2]
+    E = w.numel() // (N * w.shape[-1])
+    n_idx = rhs_indices.numel()
+    _req(lhs_indices is None or lhs_indices.numel() == n_idx, "gather_qmm: index shapes differ")
+    _req(lhs_indices is not None or Bx == n_idx, "gather_qmm: without lhs_indices x needs one batch entry per index")
+    out = torch.empty(tuple(rhs_indices.shape) + (M, N), dtype=x.dtype, device=x.device)
+    L.check(L.lib().b200_gather_qmm(_ctx(ctx), L.ptr(x), L.ptr(w), L.ptr(scales), L.ptr(biases), L.ptr(lhs_indices),
+                                    L.ptr(rhs_indices), int(transpose), group_size, bits, int(sorted_indices), Bx, M, K,
+                                    E, N, n_idx, L.ptr(out), L.stream_ptr()))
+    return out
+
+
+def softmax_axis(a, axis=-1, precise=True, ctx=None):
+    _cuda(a)
+    _req(axis in (-1, a.dim() - 1) and a.dtype == torch.bfloat16, "softmax_axis: last axis of a bf16 tensor")
+    cols = a.shape[-1]
+    out = torch.empty_like(a)
+    L.check(L.lib().b200_softmax_axis(_ctx(ctx), L.ptr(a), a.numel() // cols, cols, int(precise), L.ptr(out),
+                                      L.stream_ptr()))
+    return out
+
+
+def argpartition_axis(a, kth, axis=-1, ctx=None):
+    _cuda(a)
+    _req(axis in (-1, a.dim() - 1) and a.dtype == torch.bfloat16, "argpartition_axis: last axis of a bf16 tensor")
+    cols = a.shape[-1]
+    out = torch.empty(a.shape, dtype=torch.int32, device=a.device)
+    L.check(L.lib().b200_argpartition_axis(_ctx(ctx), L.ptr(a), a.numel() // cols, cols, int(kth), L.ptr(out),
+                                           L.stream_ptr()))
+    return out
+
+
+def take_along_axis(a, indices, axis=-1, ctx=None):
+    _cuda(a, indices)
+    _req(axis in (-1, a.dim() - 1) and a.element_size() == 2, "take_along_axis: last axis of a 2-byte tensor")
+    _req(a.shape[:-1] == indices.shape[:-1], "take_along_axis: leading dimensions differ")
+    cols, icols = a.shape[-1], indices.shape[-1]
+    out = torch.empty(indices.shape, dtype=a.dtype, device=a.device)
+    L.check(L.lib().b200_take_along_axis(_ctx(ctx), L.ptr(a), a.numel() // cols, cols, L.ptr(indices), icols,
+                                         L.ptr(out), L.stream_ptr()))
+    return out
+
+
+def rms_norm(x, weight=None, eps=1e-5, ctx=None):
+    _cuda(x, weight)
+    cols = x.shape[-1]
+    out = torch.empty_like(x)
+    L.check(L.lib().b200_rms_norm(_ctx(ctx), L.ptr(x), L.ptr(weight), float(eps), x.numel() // cols, cols, L.ptr(out),
+                                  L.stream_ptr()))
+    return out
+
+
+def add_rms_norm(x, residual, weight=None, eps=1e-5, ctx=None):
+    """-> (bf16(x + residual), rms_norm of that sum)."""
+    _cuda(x, residual, weight)
+    cols = x.shape[-1]
+    s, out = torch.empty_like(x), torch.empty_like(x)
+    L.check(L.lib().b200_add_rms_norm(_ctx(ctx), L.ptr(x), L.ptr(residual), L.ptr(weight), float(eps),
+                                      x.numel() // cols, cols, L.ptr(s), L.ptr(out), L.stream_ptr()))
+    return s, out
+
+
+def moe_permute(indices, n_experts, ctx=None):
+    """Stable token->expert sort of the flat index list -> (perm, inv_perm, counts [E], offsets [E+1])."""
+    _cuda(indices)
+    n = indices.numel()
+    dev = indices.device
+    perm = torch.empty(n, dtype=torch.int32, device=dev)
+    inv = torch.empty(n, dtype=torch.int32, device=dev)
+    counts = torch.empty(n_experts, dtype=torch.int32, device=dev)
+    offsets = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
+    L.check(L.lib().b200_moe_permute(_ctx(ctx), L.ptr(indices), n, n_experts, L.ptr(perm), L.ptr(inv), L.ptr(counts),
+                                     L.ptr(offsets), L.stream_ptr()))
+    return perm, inv, counts, offsets

@@ -1,0 +1,133 @@
+"""GPU: the routed block through the C ABI against the CPU oracle.
+
+Bars (BASELINE.json): top-k indices, permutation and per-expert counts bit-exact; layer output
+max|delta| <= 2e-2 * rms(oracle output)."""
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import bf16_cuda, make_block, rel_err, to_device, u32
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+
+def check_block(pkg, O, blk, mode=0, renorm=True):
+    ref = O.moe_block(blk["x"], blk["wr"], blk["gate"], blk["up"], blk["down"], blk["k"], mode, renorm, blk["bias"],
+                      64, blk["bits"])
+    dev = to_device(pkg, blk, mode, renorm)
+    out, aux = dev.forward(bf16_cuda(blk["x"]), return_aux=True)
+    pkg.default_context().check()
+    assert np.array_equal(u32(aux["indices"]), ref["idx"]), "top-k indices"
+    assert np.array_equal(aux["scores"].float().cpu().numpy(), ref["scores"]), "scores"
+    assert np.array_equal(u32(aux["perm"]), ref["perm"]), "perm"
+    assert np.array_equal(u32(aux["inv_perm"]), ref["inv"]), "inv"
+    assert np.array_equal(u32(aux["counts"]), ref["counts"]), "counts"
+    assert np.array_equal(u32(aux["offsets"]), ref["offsets"]), "offsets"
+    err = rel_err(out.float().cpu().numpy(), ref["out"])
+    assert err <= TOL, f"max|d|/rms = {err}"
+    return err, dev, ref
+
+
+@pytest.mark.parametrize("T", [1, 2, 3, 7])
+@pytest.mark.parametrize("E,k", [(2, 1), (2, 2), (8, 1), (8, 2)])
+def test_tiny_exhaustive(pkg, O, T, E, k):
+    check_block(pkg, O, make_block(T, 128, E, 64, k, seed=T * 10 + E + k))
+
+
+@pytest.fixture(scope="module")
+def config0():
+    """BASELINE.json configs[0]: hidden 2048, 128 experts, top-8 renormalised, inter 768, 4-bit, 64 tokens."""
+    return make_block(64, 2048, 128, 768, 8, seed=0)
+
+
+def test_config0_block(pkg, O, config0):
+    err, dev, ref = check_block(pkg, O, config0)
+    # the un-fused route through the op surface gives the same routing and, within tolerance, the same output
+    x = bf16_cuda(config0["x"])
+    idx, sc, lg = pkg.nn.router_topk(x, dev.gate_weight, 8, return_logits=True)
+    assert np.array_equal(u32(idx), ref["idx"])
+    p = pkg.ops.softmax_axis(lg, -1, True)
+    neg = (-p.float()).bfloat16()
+    part = pkg.ops.argpartition_axis(neg, 7, -1)[:, :8].contiguous()
+    assert np.array_equal(u32(part), ref["idx"])       # argpartition(-p, k-1)[:, :k] is the same selection
+    yk = dev.switch_mlp.forward(x, idx)
+    ref_yk = O.switch_glu(config0["x"], ref["idx"], config0["gate"], config0["up"], config0["down"])
+    assert rel_err(yk.float().cpu().numpy(), ref_yk) <= TOL
+
+
+@pytest.mark.parametrize("T", [1, 4, 16])
+def test_decode_sweep(pkg, O, config0, T):
+    # BASELINE.json configs[1], decode points (64 is test_config0_block): same weights, fewer tokens
+    blk = dict(config0)
+    blk["x"] = config0["x"][:T].copy()
+    blk["T"] = T
+    check_block(pkg, O, blk)
+
+
+@pytest.mark.parametrize("T", [200, 1500])
+def test_more_rows_per_expert(pkg, O, T):
+    # experts own more than eight rows: the wide (32 rows per pass) variant and multi-pass loop
+    check_block(pkg, O, make_block(T, 256, 8, 128, 2, seed=T))
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_mixtral_style_skewed(pkg, O, bits):
+    # BASELINE.json configs[4] scaled down: 8 experts, top-2, softmax over the selected logits,
+    # Zipf(1.2) logit bias; ragged segments including empty experts
+    blk = make_block(300, 512, 8, 1024, 2, bits=bits, seed=11, zipf_bias=True)
+    err, dev, ref = check_block(pkg, O, blk, mode=1, renorm=False)
+    assert ref["counts"].max() > 3 * max(1, ref["counts"].min())
+
+
+def test_no_renorm_and_ties(pkg, O):
+    blk = make_block(50, 256, 16, 128, 4, seed=21)
+    blk["wr"][7] = blk["wr"][3]          # exact ties between two experts on every token
+    blk["wr"][9] = blk["wr"][3]
+    check_block(pkg, O, blk, mode=0, renorm=False)
+    check_block(pkg, O, blk, mode=1, renorm=False)
+
+
+def test_empty_input(pkg, O):
+    blk = make_block(4, 128, 4, 64, 2, seed=1)
+    dev = to_device(pkg, blk)
+    out = dev.forward(torch.empty((0, 128), dtype=torch.bfloat16, device="cuda"))
+    assert tuple(out.shape) == (0, 128)
+    perm, inv, counts, offsets = pkg.ops.moe_permute(torch.empty(0, dtype=torch.int32, device="cuda"), 4)
+    pkg.default_context().check()
+    assert counts.sum().item() == 0 and offsets.tolist() == [0] * 5
+
+
+@pytest.mark.parametrize("n,E", [(1, 1), (1000, 128), (1024, 7), (1025, 128), (65536, 128), (100003, 256), (32768, 8)])
+def test_permute_bit_exact(pkg, O, n, E):
+    rng = np.random.default_rng(n + E)
+    p = rng.random(E) ** 3
+    idx = rng.choice(E, size=n, p=p / p.sum()).astype(np.uint32)
+    perm, inv, counts, offsets = pkg.ops.moe_permute(torch.from_numpy(idx.view(np.int32)).cuda(), E)
+    pkg.default_context().check()
+    rp, ri, rc, ro = O.permute(idx, E)
+    assert np.array_equal(u32(perm), rp) and np.array_equal(u32(inv), ri)
+    assert np.array_equal(u32(counts), rc) and np.array_equal(u32(offsets), ro)
+
+
+def test_router_large_bit_exact(pkg, O):
+    # prefill-sized router: all three logit-kernel tilings against the oracle
+    rng = np.random.default_rng(5)
+    H, E, k = 2048, 128, 8
+    wr = O.round_bf16((rng.standard_normal((E, H)) * 0.02).astype(np.float32))
+    for T in (3, 100, 1000):
+        x = O.round_bf16(rng.standard_normal((T, H)).astype(np.float32))
+        ridx, rsc, rlg = O.router(x, wr, k, return_logits=True)
+        idx, sc, lg = pkg.nn.router_topk(bf16_cuda(x), bf16_cuda(wr), k, return_logits=True)
+        assert np.array_equal(lg.float().cpu().numpy(), rlg)
+        assert np.array_equal(u32(idx), ridx) and np.array_equal(sc.float().cpu().numpy(), rsc)
+
+
+def test_bad_config_is_rejected(pkg):
+    blk = make_block(4, 128, 4, 64, 2, seed=1)
+    dev = to_device(pkg, blk)
+    with pytest.raises(pkg.B200Error):
+        dev.forward(torch.zeros((4, 64), dtype=torch.bfloat16, device="cuda"))   # wrong hidden size
+    with pytest.raises(pkg.B200Error):
+        pkg.nn.router_topk(torch.zeros((4, 128), dtype=torch.bfloat16, device="cuda"),
+                           torch.zeros((4, 128), dtype=torch.bfloat16, device="cuda"), 5)  # top_k > experts

@@ -1,0 +1,163 @@
+"""GPU: every op of the reference surface, through the C ABI, against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import bf16_cuda, rel_err, u32
+
+pytestmark = pytest.mark.gpu
+
+
+def np_i32(a):
+    return torch.from_numpy(np.ascontiguousarray(a).view(np.int32)).cuda()
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+@pytest.mark.parametrize("gs", [32, 64, 128])
+@pytest.mark.parametrize("bf16", [True, False])
+def test_quantize_bit_exact(pkg, O, bits, gs, bf16):
+    rng = np.random.default_rng(bits * 100 + gs)
+    w = (rng.standard_normal((3, 37, 256)) * 0.02).astype(np.float32)
+    w[0, 0, :gs] = 0.0           # constant group
+    w[0, 1, :gs] = np.abs(w[0, 1, :gs])  # one-signed group
+    if bf16:
+        w = O.round_bf16(w)
+    wq, s, b = O.quantize(w, gs, bits, bf16_params=bf16)
+    wt = torch.from_numpy(w).cuda()
+    dq, ds, db = pkg.ops.quantize(wt.bfloat16() if bf16 else wt, gs, bits)
+    assert np.array_equal(u32(dq), wq)
+    assert np.array_equal(ds.float().cpu().numpy(), s) and np.array_equal(db.float().cpu().numpy(), b)
+    wh = O.dequantize(wq, s, b, gs, bits)
+    dh = pkg.ops.dequantize(dq, ds, db, gs, bits).float().cpu().numpy()
+    assert np.array_equal(dh, O.round_bf16(wh) if bf16 else wh)
+
+
+def test_quantize_reference_case(pkg):
+    # mlx-rs/src/ops/quantization.rs:297-315 through the CUDA path
+    x = (torch.ones(128, 1) * torch.arange(512, dtype=torch.float32)[None]).cuda()
+    for bits in (2, 4, 8):
+        wq, s, b = pkg.ops.quantize(x, 128, bits)
+        assert tuple(wq.shape) == (128, 512 * bits // 32) and tuple(s.shape) == (128, 4) == tuple(b.shape)
+        xh = pkg.ops.dequantize(wq, s, b, 128, bits)
+        assert (x - xh).abs().max().item() <= 127.0 / (1 << bits)
+
+
+def test_quantize_rejects_bad_arguments(pkg):
+    x = torch.zeros(4, 100, device="cuda")
+    with pytest.raises(pkg.B200Error):
+        pkg.ops.quantize(x, 64, 4)          # last axis not a multiple of the group size
+    with pytest.raises(pkg.B200Error):
+        pkg.ops.quantize(torch.zeros(4, 128, device="cuda"), 64, 3)
+    with pytest.raises(pkg.B200Error):
+        pkg.ops.quantize(torch.zeros(128, device="cuda"), 64, 4)   # 1-D input
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("shape", [(32, 128, 128), (1, 2048, 768), (7, 768, 2048), (100, 64, 40)])
+def test_quantized_matmul_transposed(pkg, O, bits, shape):
+    m, k, n = shape
+    rng = np.random.default_rng(m + n)
+    x = O.round_bf16((rng.standard_normal((m, k)) / np.sqrt(k)).astype(np.float32))
+    w = O.round_bf16((rng.standard_normal((n, k)) / np.sqrt(k)).astype(np.float32))
+    wq, s, b = O.quantize(w, 64, bits)
+    ref = O.quantized_matmul(x, wq, s, b, True, 64, bits)
+    got = pkg.ops.quantized_matmul(bf16_cuda(x), np_i32(wq), bf16_cuda(s), bf16_cuda(b), True, 64, bits)
+    pkg.default_context().check()
+    assert tuple(got.shape) == (m, n)
+    assert rel_err(got.float().cpu().numpy(), ref) <= 1e-2   # one bf16 rounding of the output
+
+
+def test_quantized_matmul_reference_case(pkg, O):
+    # mlx-rs/src/ops/quantization.rs:317-342 (transpose = false): equals x @ dequantize(w)
+    rng = np.random.default_rng(0)
+    m, n, k = 32, 128, 128
+    x = O.round_bf16((rng.standard_normal((m, k)) / np.sqrt(k)).astype(np.float32))
+    w = O.round_bf16((rng.standard_normal((k, n)) / np.sqrt(k)).astype(np.float32))
+    wq, s, b = pkg.ops.quantize(bf16_cuda(w), 64, 4)
+    wh = pkg.ops.dequantize(wq, s, b, 64, 4).float().cpu().numpy()
+    got = pkg.ops.quantized_matmul(bf16_cuda(x), wq, s, b, False, 64, 4).float().cpu().numpy()
+    assert np.abs(got - x @ wh).max() < 1e-2
+    ref = O.quantized_matmul(x, u32(wq), s.float().cpu().numpy(), b.float().cpu().numpy(), False, 64, 4)
+    assert np.abs(got - ref).max() < 1e-2
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_gather_qmm_reference_cases(pkg, O, bits):
+    # mlx-rs/src/ops/quantization.rs:344-423: gather_qmm == gather_mm on the dequantized, transposed weights
+    rng = np.random.default_rng(0)
+    m, n, k = 32, 64, 64
+    w = O.round_bf16(rng.standard_normal((3, n, k)).astype(np.float32))
+    wq, s, b = O.quantize(w, 64, bits)
+    wh_t = np.swapaxes(O.dequantize(wq, s, b, 64, bits), -1, -2).copy()
+    rhs = np.array([2, 1], np.uint32)
+    for bx, lhs in ((1, [0, 0]), (5, [0, 2])):
+        x = O.round_bf16(rng.standard_normal((bx, m, k)).astype(np.float32))
+        lhs = np.array(lhs, np.uint32)
+        c1 = O.gather_mm(x, wh_t, lhs, rhs)
+        c2 = pkg.ops.gather_qmm(bf16_cuda(x), np_i32(wq), bf16_cuda(s), bf16_cuda(b), np_i32(lhs), np_i32(rhs), True,
+                                64, bits)
+        pkg.default_context().check()
+        assert tuple(c2.shape) == (2, m, n)
+        assert rel_err(c2.float().cpu().numpy(), c1) <= 1e-2
+
+
+def test_gather_qmm_switch_linear_shape(pkg, O):
+    # the shape a SwitchLinear issues: x [n,1,K], unsorted expert ids, no lhs
+    rng = np.random.default_rng(2)
+    n_idx, K, N, E = 300, 256, 192, 16
+    x = O.round_bf16(rng.standard_normal((n_idx, 1, K)).astype(np.float32))
+    w = O.round_bf16((rng.standard_normal((E, N, K)) * 0.05).astype(np.float32))
+    wq, s, b = O.quantize(w)
+    rhs = rng.integers(0, E, n_idx).astype(np.uint32)
+    ref = O.gather_qmm(x, wq, s, b, None, rhs)
+    got = pkg.ops.gather_qmm(bf16_cuda(x), np_i32(wq), bf16_cuda(s), bf16_cuda(b), None, np_i32(rhs))
+    pkg.default_context().check()
+    assert rel_err(got.float().cpu().numpy(), ref) <= 1e-2
+    with pytest.raises(pkg.B200Error):
+        pkg.ops.gather_qmm(bf16_cuda(x), np_i32(wq), bf16_cuda(s), bf16_cuda(b), None, np_i32(rhs), transpose=False)
+    bad = rhs.copy()
+    bad[3] = E + 2                      # out-of-range expert: reported at the next check, nothing written for it
+    pkg.ops.gather_qmm(bf16_cuda(x), np_i32(wq), bf16_cuda(s), bf16_cuda(b), None, np_i32(bad))
+    with pytest.raises(pkg.B200Error):
+        pkg.default_context().check()
+    pkg.default_context().check()       # the status word is cleared once reported
+
+
+@pytest.mark.parametrize("cols", [8, 128, 200, 256])
+def test_softmax_argpartition_take(pkg, O, cols):
+    rng = np.random.default_rng(cols)
+    a = O.round_bf16(rng.standard_normal((57, cols)).astype(np.float32) * 2)
+    a[:, 3] = a[:, 1]                   # ties
+    da = bf16_cuda(a)
+    p = pkg.ops.softmax_axis(da, -1, True).float().cpu().numpy()
+    assert np.array_equal(p, O.f64_to_bf16(O.softmax(a)))
+    kth = min(7, cols - 1)
+    part = pkg.ops.argpartition_axis(da, kth, -1)
+    full = O.argpartition(a, kth)
+    got = u32(part)
+    assert np.array_equal(got[:, :kth + 1], full[:, :kth + 1])
+    for r in range(a.shape[0]):
+        assert sorted(got[r].tolist()) == list(range(cols))
+        assert a[r, got[r, kth + 1:]].min(initial=np.inf) >= a[r, got[r, kth]]
+    taken = pkg.ops.take_along_axis(da, part[:, :kth + 1].contiguous(), -1).float().cpu().numpy()
+    assert np.array_equal(taken, O.take_along_axis(a, full[:, :kth + 1]))
+    with pytest.raises(pkg.B200Error):
+        pkg.ops.argpartition_axis(da, cols, -1)       # kth out of range (mlx-rs/src/ops/sort.rs:266-298)
+    pkg.ops.take_along_axis(da, torch.full((57, 1), cols, dtype=torch.int32, device="cuda"), -1)
+    with pytest.raises(pkg.B200Error):
+        pkg.default_context().check()
+
+
+def test_rms_norm_and_residual(pkg, O):
+    rng = np.random.default_rng(9)
+    x = O.round_bf16(rng.standard_normal((33, 2048)).astype(np.float32))
+    r = O.round_bf16(rng.standard_normal((33, 2048)).astype(np.float32))
+    w = O.round_bf16(rng.standard_normal(2048).astype(np.float32))
+    got = pkg.ops.rms_norm(bf16_cuda(x), bf16_cuda(w), 1e-6).float().cpu().numpy()
+    assert rel_err(got, O.rms_norm(x, w, 1e-6)) <= 1e-2
+    got1 = pkg.ops.rms_norm(bf16_cuda(x), None, 1e-6).float().cpu().numpy()
+    assert rel_err(got1, O.rms_norm(x, None, 1e-6)) <= 1e-2
+    s, n = pkg.ops.add_rms_norm(bf16_cuda(x), bf16_cuda(r), None, 1e-6)
+    sref = O.round_bf16(x + r)
+    assert np.array_equal(s.float().cpu().numpy(), sref)
+    assert rel_err(n.float().cpu().numpy(), O.rms_norm(sref, None, 1e-6)) <= 1e-2
