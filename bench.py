@@ -1,0 +1,320 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized MoE block (BASELINE.json metric: MoE layer tokens/s, 4-bit
+Qwen3-30B-A3B shape; % of roofline).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--impl ours|reference]
+
+One step = one forward of the block over one batch of T synthetic tokens (seeded random
+weights quantized with the library's own quantize kernel; there are no checkpoints here).
+Prints ONE JSON line.  `value` is timed with the inputs resident in HBM, `e2e` through the
+public API with host buffers (H2D of x and D2H of the output inside the timed region).
+L2 is flushed between timed iterations (a 512 MB buffer is overwritten), and every iteration is
+timed with its own pair of CUDA events on the launching stream.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPE = dict(hidden=2048, inter=768, n_experts=128, top_k=8, bits=4, group_size=64)  # Qwen3-30B-A3B MoE layer
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+SWEEP = (1, 4, 16, 64, 512, 2048, 8192)  # BASELINE.json configs[1]
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm=float(d["hbm_gbs"]), tensor=float(d["bf16_tflops"]), source="measured")
+    return dict(hbm=6650.0, tensor=1590.0, source="fallback")
+
+
+def expert_bytes(H, I, bits, gs=64):
+    """Packed weight + scale + bias bytes of one expert's three matrices."""
+    return 3 * (H * I * bits // 8 + 2 * (H * I // gs) * 2)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device, self.proc = device, None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.device)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        self.lines = []
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                out, _ = self.proc.communicate(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+                out, _ = self.proc.communicate()
+            self.lines = [l for l in out.splitlines() if l.strip()]
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for l in self.lines:
+            f = [c.strip() for c in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["unsampled"])
+        # "under load" = samples in the upper half of what was seen (idle samples bracket the region)
+        hi = [s for s in sm if s >= 0.5 * max(sm)]
+        return dict(sm_mhz=statistics.median(hi), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+
+
+def build_block(pkg, torch, seed, shape, device):
+    """Seeded random-init weights of the named architecture, quantized on the GPU by the library."""
+    H, I, E = shape["hidden"], shape["inter"], shape["n_experts"]
+    g = torch.Generator(device=device).manual_seed(seed)
+    lin = []
+    for r, c in ((I, H), (I, H), (H, I)):
+        w = (torch.randn(E, r, c, generator=g, device=device, dtype=torch.float32) * 0.02).bfloat16()
+        lin.append(pkg.nn.QuantizedSwitchLinear.from_weight(w, shape["group_size"], shape["bits"]))
+        del w
+    wr = (torch.randn(E, H, generator=g, device=device, dtype=torch.float32) * 0.02).bfloat16()
+    return pkg.nn.MoeBlock(wr, pkg.nn.SwitchGlu(*lin), shape["top_k"], True, 0)
+
+
+def time_steps(torch, fn, steps, warmup, flush):
+    """-> list of per-step milliseconds (CUDA events on the current stream, L2 flushed in between)."""
+    for _ in range(warmup):
+        flush()
+        fn()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in evs:
+        flush()
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    return [a.elapsed_time(b) for a, b in evs]
+
+
+def cpu_baseline(T_sample, shape, seed, reps_budget_s=15.0):
+    """Times the CPU oracle (a port: the reference's MLX CPU path cannot be built here) on the
+    host cores: a block of `T_sample` tokens over a bounded number of experts' worth of work."""
+    import numpy as np
+    import torch
+    from oracle import oracle as O
+    H, I, E, k = shape["hidden"], shape["inter"], shape["n_experts"], shape["top_k"]
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(T_sample, H, generator=g).bfloat16().float().numpy()
+    wr = (torch.randn(E, H, generator=g) * 0.02).bfloat16().float().numpy()
+    q = []
+    for r, c in ((I, H), (I, H), (H, I)):
+        # one expert's random weights tiled over all experts: the arithmetic per token is identical
+        # and the host spends its time on the timed work, not on drawing 600 M normals
+        w1 = (torch.randn(8, r, c, generator=g) * 0.02).bfloat16().float().numpy()
+        w = np.tile(w1, (E // 8, 1, 1))
+        q.append(O.quantize(w, shape["group_size"], shape["bits"]))
+    O.moe_block(x, wr, q[0], q[1], q[2], k)  # warm-up
+    t0, n = time.perf_counter(), 0
+    while True:
+        O.moe_block(x, wr, q[0], q[1], q[2], k)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt > reps_budget_s or n >= 50:
+            break
+    return dict(value=T_sample * n / dt, unit=UNIT, cores=O.num_threads(), kind="port",
+                sample=f"{n} forwards of a {T_sample}-token block, {dt:.1f} s, OpenMP on all host threads; "
+                       "weights are 8 distinct random experts tiled to 128")
+
+
+def run_reference(args):
+    """Reference arm: the CPU oracle (port of the reference semantics; the reference itself is a
+    Rust binding over an absent MLX and cannot be built) on all host threads, same config."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    T = args.tokens
+    T_sample = min(T, 256)
+    per_step = []
+    base = None
+    for i in range(args.warmup + args.steps):
+        base = cpu_baseline(T_sample, SHAPE, args.seed, reps_budget_s=max(2.0, 40.0 / (args.warmup + args.steps)))
+        if i >= args.warmup:
+            per_step.append(base["value"])
+    v = statistics.mean(per_step)
+    line = dict(metric=METRIC, value=v, unit=UNIT, n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
+                ms_per_step=1e3 * T / v, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32",
+                data="synthetic", impl="reference",
+                config=dict(workload=workload_name(T), tokens=T, **SHAPE),
+                cpu_baseline=dict(value=v, unit=UNIT, cores=base["cores"], kind="port", sample=base["sample"]),
+                e2e=dict(value=v, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line))
+
+
+def workload_name(T):
+    return f"configs[1] point T={T}: Qwen3-30B-A3B MoE layer (H2048 E128 top-8 I768, 4-bit g64), bf16 N(0,1) tokens"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--tokens", type=int, default=8192, help="tokens per step per GPU (configs[1] sweep point)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import __graft_entry__ as ge
+    pkg = ge.load_package()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = measured_peaks()
+    T = args.tokens
+    H, I, E, k, bits = (SHAPE[n] for n in ("hidden", "inter", "n_experts", "top_k", "bits"))
+
+    if world > 1:
+        from importlib import import_module
+        ep = import_module("mlx_rs_b200.ep")
+        return ep.bench_main(args, pkg, SHAPE, peaks, METRIC, UNIT, workload_name)
+
+    ctx = pkg.default_context()
+    block = build_block(pkg, torch, args.seed, SHAPE, dev)
+    ctx.reserve(block.config, max(T, max(SWEEP)))
+    flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+
+    def flush():
+        flush_buf.fill_(1)
+
+    g = torch.Generator(device=dev).manual_seed(args.seed + 1)
+
+    def point(Tp, steps, warmup, profile):
+        x = torch.randn(Tp, H, generator=g, device=dev, dtype=torch.float32).bfloat16()
+        out_holder = {}
+
+        def step():
+            out_holder["o"] = block.forward(x)
+        l0 = ctx.launch_count()
+        ms = time_steps(torch, step, steps, warmup, flush)
+        launches = (ctx.launch_count() - l0) // (steps + warmup)
+        res = dict(tokens=Tp, ms_per_step=statistics.mean(ms), ms_min=min(ms), launches_per_step=launches)
+        res["tokens_per_s"] = Tp / (res["ms_per_step"] * 1e-3)
+        # routing actually taken -> algorithmic bytes of this batch
+        _, aux = block.forward(x, return_aux=True)
+        counts = aux["counts"].cpu()
+        n_act = int((counts > 0).sum())
+        res["active_experts"] = n_act
+        we = expert_bytes(H, I, bits)
+        res["block_bytes"] = n_act * we + E * H * 2 + 2 * Tp * H * 2
+        res["block_flops"] = Tp * (k * 3 * 2 * H * I + 2 * H * E)
+        res["block_gbs"] = res["block_bytes"] / (res["ms_per_step"] * 1e-3) / 1e9
+        res["block_tflops"] = res["block_flops"] / (res["ms_per_step"] * 1e-3) / 1e12
+        if profile:
+            ctx.set_profiling(True)
+            stage = {n: [] for n in ctx.STAGES}
+            for _ in range(max(3, steps)):
+                flush()
+                block.forward(x)
+                for n, v in ctx.stage_ms().items():
+                    stage[n].append(v)
+            ctx.set_profiling(False)
+            res["stage_ms"] = {n: statistics.mean(v) for n, v in stage.items()}
+            gu_ms = res["stage_ms"]["gate_up"]
+            gu_bytes = n_act * (we * 2 // 3) + Tp * k * H * 2 + Tp * k * I * 2
+            gu_flops = Tp * k * 2 * 2 * H * I
+            res["gate_up"] = dict(ms=gu_ms, bytes=gu_bytes, flops=gu_flops, gbs=gu_bytes / (gu_ms * 1e-3) / 1e9,
+                                  tflops=gu_flops / (gu_ms * 1e-3) / 1e12)
+        return res, x
+
+    with ClockSampler(local) as clk:
+        main_res, x_main = point(T, args.steps, args.warmup, True)
+    clocks = clk.summary()
+
+    # end to end through the public API with host buffers
+    xh = x_main.cpu().pin_memory()
+    oh = torch.empty_like(xh).pin_memory()
+    xd = torch.empty_like(x_main)
+
+    def e2e_step():
+        xd.copy_(xh, non_blocking=True)
+        o = block.forward(xd)
+        oh.copy_(o, non_blocking=True)
+    e2e_ms = time_steps(torch, e2e_step, args.steps, args.warmup, flush)
+    e2e = dict(value=T / (statistics.mean(e2e_ms) * 1e-3), unit=UNIT, h2d_bytes_per_step=xh.numel() * 2,
+               d2h_bytes_per_step=oh.numel() * 2)
+
+    sweep = []
+    if not args.no_sweep:
+        for Tp in SWEEP:
+            if Tp == T:
+                r = main_res
+            else:
+                r, _ = point(Tp, max(5, min(args.steps, 10)), 3, True)
+            gu = r["gate_up"]
+            decode = Tp < 1024
+            sweep.append(dict(tokens=Tp, tokens_per_s=r["tokens_per_s"], ms=r["ms_per_step"],
+                              active_experts=r["active_experts"], launches=r["launches_per_step"],
+                              block_frac_hbm=r["block_gbs"] / peaks["hbm"], block_frac_tensor=r["block_tflops"] / peaks["tensor"],
+                              gate_up_ms=gu["ms"], gate_up_frac=(gu["gbs"] / peaks["hbm"]) if decode else (gu["tflops"] / peaks["tensor"]),
+                              bound="hbm" if decode else "tensor", stage_ms=r["stage_ms"]))
+
+    gu = main_res["gate_up"]
+    if T < 1024:
+        roof = dict(bound="hbm", achieved=gu["gbs"], peak=peaks["hbm"], unit="GB/s", frac=gu["gbs"] / peaks["hbm"])
+    else:
+        roof = dict(bound="tensor", achieved=gu["tflops"], peak=peaks["tensor"], unit="TFLOP/s",
+                    frac=gu["tflops"] / peaks["tensor"])
+    roof.update(kernel="gate+up grouped quantized GEMM (dominant)", peak_source=peaks["source"], traffic=None,
+                kernel_ms=gu["ms"], algorithmic_bytes=gu["bytes"], algorithmic_flops=gu["flops"])
+
+    base = None if args.no_cpu_baseline else cpu_baseline(min(T, 256), SHAPE, args.seed)
+    line = dict(metric=METRIC, value=main_res["tokens_per_s"], unit=UNIT, n_gpus=1, steps=args.steps, warmup=args.warmup,
+                ms_per_step=main_res["ms_per_step"], higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+                data="synthetic",
+                config=dict(workload=workload_name(T), tokens=T, l2="flushed between iterations (512 MB overwrite)",
+                            parallelism="single GPU", **SHAPE),
+                roofline=roof, cpu_baseline=base, e2e=e2e, gpu_launches=main_res["launches_per_step"] * args.steps,
+                clocks=clocks, block=dict(active_experts=main_res["active_experts"], gbs=main_res["block_gbs"],
+                                          tflops=main_res["block_tflops"], stage_ms=main_res["stage_ms"]),
+                sweep=sweep)
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

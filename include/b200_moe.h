@@ -98,6 +98,14 @@ int b200_ctx_reserve(b200_ctx* ctx, const b200_moe_config* cfg, int64_t max_toke
 int b200_ctx_check(b200_ctx* ctx, void* stream);
 /* Number of kernels launched through this context so far. */
 int64_t b200_ctx_launch_count(const b200_ctx* ctx);
+/* Stage timing of b200_moe_block_forward (the library's stand-in for a profiler hook; the
+ * reference has none).  While enabled, an event is recorded on the call's stream between the
+ * stages; b200_ctx_stage_ms waits for the last profiled call and returns the milliseconds of
+ * its stages in this order: router logits, softmax/top-k, permutation, gate+up product,
+ * down product, combine. */
+#define B200_N_STAGES 6
+int b200_ctx_set_profiling(b200_ctx* ctx, int enable);
+int b200_ctx_stage_ms(b200_ctx* ctx, float* ms, int n);
 
 /* ---- op surface of the reference -------------------------------------------------------- */
 

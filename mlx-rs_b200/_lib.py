@@ -38,6 +38,8 @@ EXPORTS = {
     "b200_ctx_reserve": (C.c_int, [C.c_void_p, C.POINTER(MoeConfig), C.c_int64]),
     "b200_ctx_check": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200_ctx_launch_count": (C.c_int64, [C.c_void_p]),
+    "b200_ctx_set_profiling": (C.c_int, [C.c_void_p, C.c_int]),
+    "b200_ctx_stage_ms": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.c_int]),
     "b200_quantize": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_void_p,
                                 C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200_dequantize": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64,
@@ -122,6 +124,17 @@ class Context:
 
     def check(self):
         check(lib().b200_ctx_check(self._h, stream_ptr()))
+
+    STAGES = ("router_logits", "route_topk", "permute", "gate_up", "down", "combine")
+
+    def set_profiling(self, on):
+        check(lib().b200_ctx_set_profiling(self._h, int(bool(on))))
+
+    def stage_ms(self):
+        """Milliseconds of each stage of the last profiled MoeBlock.forward (waits for it)."""
+        buf = (C.c_float * len(self.STAGES))()
+        check(lib().b200_ctx_stage_ms(self._h, buf, len(self.STAGES)))
+        return dict(zip(self.STAGES, [float(v) for v in buf]))
 
     def launch_count(self):
         return int(lib().b200_ctx_launch_count(self._h))

@@ -35,8 +35,14 @@ struct b200_ctx {
   size_t ws_used = 0;           // bump pointer of the call in progress
   int* err = nullptr;           // device status word
   int64_t launches = 0;
+  bool profiling = false;       // record an event after every stage of the block forward
+  cudaEvent_t ev[B200_N_STAGES + 1] = {};
+  bool ev_valid = false;
 
   void begin() { ws_used = 0; }
+  void mark(int i, cudaStream_t st) {
+    if (profiling) cudaEventRecord(ev[i], st);
+  }
   // Bump-allocates from the arena; returns null when it does not fit (caller grows first).
   void* take(size_t bytes) {
     size_t off = (ws_used + 255) & ~size_t(255);
@@ -70,7 +76,7 @@ static size_t block_scratch_bytes(const b200_moe_config& cfg, int64_t T) {
   b += al(sizeof(uint32_t) * (E + 1)) * 3 + al(16);  // counts, offsets, active, n_active
   b += al(sizeof(uint32_t) * permute_scratch_words(n, (int)E));
   b += al(sizeof(uint16_t) * n * cfg.inter);         // h
-  b += al(sizeof(uint16_t) * n * cfg.hidden);        // per-assignment outputs
+  b += al(sizeof(float) * n * cfg.hidden);           // per-assignment outputs (float32)
   return b + 4096;
 }
 
@@ -138,6 +144,8 @@ int b200_ctx_destroy(b200_ctx* c) {
   cudaDeviceSynchronize();
   if (c->ws) cudaFree(c->ws);
   if (c->err) cudaFree(c->err);
+  for (auto& e : c->ev)
+    if (e) cudaEventDestroy(e);
   delete c;
   return 0;
 }
@@ -162,6 +170,24 @@ int b200_ctx_check(b200_ctx* c, void* stream) {
 }
 
 int64_t b200_ctx_launch_count(const b200_ctx* c) { return c ? c->launches : 0; }
+
+int b200_ctx_set_profiling(b200_ctx* c, int enable) {
+  CTX_ENTER(c);
+  if (enable && !c->ev[0])
+    for (auto& e : c->ev) B200_CUDA(cudaEventCreate(&e));
+  c->profiling = enable != 0;
+  c->ev_valid = false;
+  return 0;
+}
+
+int b200_ctx_stage_ms(b200_ctx* c, float* ms, int n) {
+  CTX_ENTER(c);
+  B200_REQUIRE(ms != nullptr && n >= B200_N_STAGES, "ms must hold B200_N_STAGES floats");
+  B200_REQUIRE(c->profiling && c->ev_valid, "no profiled b200_moe_block_forward call to report");
+  B200_CUDA(cudaEventSynchronize(c->ev[B200_N_STAGES]));
+  for (int i = 0; i < B200_N_STAGES; ++i) B200_CUDA(cudaEventElapsedTime(&ms[i], c->ev[i], c->ev[i + 1]));
+  return 0;
+}
 
 // ---- plain ops ----------------------------------------------------------------------------------
 
@@ -414,6 +440,7 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
   }
   launch_permute(idx, n, E, perm, inv, counts, offsets, active, n_active, chunk, c->err, st);
   LAUNCHED(c, permute_launches(n));
+  c->mark(3, st);
   const int max_active = (int)(E < n ? E : n);
 
   GroupedArgs gu{};
@@ -435,6 +462,7 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
   gu.K = cfg.hidden;
   gu.N = cfg.inter;
   if (run_grouped(c, gu, 2, cfg.bits, max_active, n, st)) return 1;
+  c->mark(4, st);
 
   GroupedArgs dn{};
   dn.x = h;
@@ -449,9 +477,12 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
   dn.dst_perm = 1;
   dn.row_scale = scores;
   dn.out = yk;
+  dn.out_f32 = scores != nullptr;  // weighted rows stay float32 until the combine; SwitchGlu's own output is bf16
   dn.K = cfg.inter;
   dn.N = cfg.hidden;
-  return run_grouped(c, dn, 1, cfg.bits, max_active, n, st);
+  if (run_grouped(c, dn, 1, cfg.bits, max_active, n, st)) return 1;
+  c->mark(5, st);
+  return 0;
 }
 
 static int check_params(const b200_moe_params* p, bool need_router) {
@@ -487,19 +518,24 @@ int b200_moe_block_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_m
   void* logits = c->take(sizeof(uint16_t) * T * cfg->n_experts);
   uint32_t* idx = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
   void* scores = c->take(sizeof(uint16_t) * n);
-  void* yk = c->take(sizeof(uint16_t) * n * cfg->hidden);
+  void* yk = c->take(sizeof(float) * n * cfg->hidden);
   B200_REQUIRE(logits && idx && scores && yk, "scratch arena too small");
   if (aux) {
     if (aux->logits) logits = aux->logits;
     if (aux->indices) idx = aux->indices;
     if (aux->scores) scores = aux->scores;
   }
+  c->mark(0, st);
   launch_router_logits(x, params->router_weight, params->router_logit_bias, logits, (int)T, cfg->hidden, cfg->n_experts, st);
+  c->mark(1, st);
   launch_route_topk(logits, (int)T, cfg->n_experts, cfg->top_k, cfg->router_mode, cfg->norm_topk_prob, idx, scores,
                     nullptr, st);
+  c->mark(2, st);
   LAUNCHED(c, 2);
   if (experts_forward(c, *cfg, *params, x, idx, scores, T, yk, aux, st)) return 1;
   if (launch_combine(yk, T, cfg->top_k, cfg->hidden, out, st)) return 1;
+  c->mark(6, st);
+  c->ev_valid = c->profiling;
   LAUNCHED(c, 1);
   return 0;
 }

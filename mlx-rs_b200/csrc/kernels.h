@@ -22,7 +22,8 @@ struct GroupedArgs {
   int src_div;
   int dst_perm;               // 0: out row = sorted position, 1: out row = perm[p]
   const void* row_scale;      // bf16, indexed by out row; may be null
-  void* out;                  // bf16 [rows, N]
+  void* out;                  // [rows, N], bf16 or float32
+  int out_f32;                // 1: float32 output (no rounding before the k-way combine)
   int K, N;
 };
 

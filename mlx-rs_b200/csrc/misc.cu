@@ -110,34 +110,32 @@ int launch_dequantize(const uint32_t* wq, const void* scales, const void* biases
   return 0;
 }
 
-// combine: out[t, c] = bf16( sum_j float(yk[t, j, c]) ), j ascending (sum_axis(-2),
-// mlx-rs/src/ops/reduction.rs:260-275; the routing weights were applied by the producer).
-__global__ void combine_kernel(const uint4* __restrict__ yk, int64_t T, int k, int64_t H8, uint4* __restrict__ out) {
+// combine: out[t, c] = bf16( sum_j yk[t, j, c] ), j ascending, float32 throughout (sum_axis(-2),
+// mlx-rs/src/ops/reduction.rs:260-275; the routing weights were applied by the producer, whose
+// float32 results are summed here without an intermediate rounding).
+__global__ void combine_kernel(const float4* __restrict__ yk, int64_t T, int k, int64_t H4, uint2* __restrict__ out) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= T * H8) return;
-  const int64_t t = i / H8, c = i % H8;
-  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (i >= T * H4) return;
+  const int64_t t = i / H4, c = i % H4;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int j = 0; j < k; ++j) {
-    const uint4 v = __ldg(&yk[(t * k + j) * H8 + c]);
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      acc[2 * q] += __uint_as_float(u[q] << 16);
-      acc[2 * q + 1] += __uint_as_float(u[q] & 0xffff0000u);
-    }
+    const float4 v = __ldg(&yk[(t * k + j) * H4 + c]);
+    acc.x += v.x;
+    acc.y += v.y;
+    acc.z += v.z;
+    acc.w += v.w;
   }
-  uint4 o;
-  uint32_t* ou = &o.x;
-#pragma unroll
-  for (int q = 0; q < 4; ++q) ou[q] = f32_to_bf16_bits(acc[2 * q]) | (f32_to_bf16_bits(acc[2 * q + 1]) << 16);
+  uint2 o;
+  o.x = f32_to_bf16_bits(acc.x) | (f32_to_bf16_bits(acc.y) << 16);
+  o.y = f32_to_bf16_bits(acc.z) | (f32_to_bf16_bits(acc.w) << 16);
   out[i] = o;
 }
 
 int launch_combine(const void* yk, int64_t T, int k, int64_t H, void* out, cudaStream_t st) {
   if (T == 0) return 0;
-  B200_REQUIRE(H % 8 == 0, "hidden size must be a multiple of 8");
-  int64_t n = T * (H / 8);
-  combine_kernel<<<cdiv(n, 256), 256, 0, st>>>(static_cast<const uint4*>(yk), T, k, H / 8, static_cast<uint4*>(out));
+  B200_REQUIRE(H % 4 == 0, "hidden size must be a multiple of 4");
+  int64_t n = T * (H / 4);
+  combine_kernel<<<cdiv(n, 256), 256, 0, st>>>(static_cast<const float4*>(yk), T, k, H / 4, static_cast<uint2*>(out));
   return 0;
 }
 

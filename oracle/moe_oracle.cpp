@@ -91,9 +91,11 @@ int orc_num_threads() {
 }
 
 void orc_f32_to_bf16(const float* in, int64_t n, uint16_t* out) {
+#pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < n; ++i) out[i] = f32_to_bf16_bits(in[i]);
 }
 void orc_bf16_to_f32(const uint16_t* in, int64_t n, float* out) {
+#pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < n; ++i) out[i] = bf16_bits_to_f32(in[i]);
 }
 void orc_f64_to_bf16(const double* in, int64_t n, uint16_t* out) {
@@ -409,14 +411,16 @@ int orc_permute(const uint32_t* idx, int64_t n, int64_t E, uint32_t* perm, uint3
 //   idx     [T,k]   expert of each assignment;   scores [T,k] (null: no combine, y_k written)
 //   gate/up [E,I,H/epw] + scales/biases [E,I,H/gs];  down [E,H,I/epw] + [E,H,I/gs]
 //   out     [T,H]   (combined)   or   y_k [T,k,H] when scores == null
-// Rounding points: h = bf16(silu(g) * u) and the final output are rounded to bf16;
-// `round_every_op` != 0 additionally rounds g, u, silu(g), y, s*y and the running sum, which
-// is the literal op-by-op dataflow of a bf16 graph (mlx-rs/src/nn/activation.rs:876-880,
-// mlx-rs/src/ops/reduction.rs:260-275).
+// Rounding points: h = bf16(silu(g) * u) always; the final output is rounded to bf16 when
+// `round_out` != 0 and left as the float32 accumulation otherwise (the tolerance of the parity
+// tests is tighter than one bf16 ulp of a large output, so they compare with the unrounded
+// value).  `round_every_op` != 0 additionally rounds g, u, silu(g), y, s*y and the running
+// sum, which is the literal op-by-op dataflow of a bf16 graph
+// (mlx-rs/src/nn/activation.rs:876-880, mlx-rs/src/ops/reduction.rs:260-275).
 int orc_switch_glu(const float* x, int64_t T, int64_t H, int64_t E, int64_t I, int k, const uint32_t* idx,
                    const float* scores, const uint32_t* gq, const float* gs_, const float* gb,
                    const uint32_t* uq, const float* us, const float* ub, const uint32_t* dq, const float* ds,
-                   const float* db, int gs, int bits, int round_every_op, float* out) {
+                   const float* db, int gs, int bits, int round_every_op, int round_out, float* out) {
   const int epw = elems_per_word(bits);
   const int64_t n = T * k;
   std::vector<uint32_t> perm(n), inv(n), counts(E), offsets(E + 1);
@@ -455,7 +459,7 @@ int orc_switch_glu(const float* x, int64_t T, int64_t H, int64_t E, int64_t I, i
     }
   }
   if (!scores) {
-    for (int64_t i = 0; i < n * H; ++i) out[i] = round_bf16(yk[i]);
+    for (int64_t i = 0; i < n * H; ++i) out[i] = round_out ? round_bf16(yk[i]) : yk[i];
     return 0;
   }
 #pragma omp parallel for schedule(static)
@@ -471,7 +475,7 @@ int orc_switch_glu(const float* x, int64_t T, int64_t H, int64_t E, int64_t I, i
           acc += v;
         }
       }
-      out[t * H + c] = round_bf16(acc);
+      out[t * H + c] = round_out ? round_bf16(acc) : acc;
     }
   return 0;
 }

@@ -225,9 +225,10 @@ def permute(idx, n_experts):
     return perm, inv, counts, offsets
 
 
-def switch_glu(x, idx, gate, up, down, scores=None, group_size=64, bits=4, round_every_op=False):
+def switch_glu(x, idx, gate, up, down, scores=None, group_size=64, bits=4, round_every_op=False, round_out=True):
     """gate/up/down are (wq, scales, biases) triples.  -> [T,H] when `scores` is given
-    (weighted combine), else the per-assignment outputs [T,k,H]."""
+    (weighted combine), else the per-assignment outputs [T,k,H].  `round_out=False` returns
+    the float32 accumulation without the final bf16 rounding."""
     x, idx = _f32(x), _u32(idx)
     T, H = x.shape
     k = idx.shape[-1]
@@ -241,7 +242,7 @@ def switch_glu(x, idx, gate, up, down, scores=None, group_size=64, bits=4, round
                               _p(idx, C.c_uint32), _p(sc, C.c_float), _p(gq, C.c_uint32), _p(gs_, C.c_float),
                               _p(gb, C.c_float), _p(uq, C.c_uint32), _p(us, C.c_float), _p(ub, C.c_float),
                               _p(dq, C.c_uint32), _p(ds, C.c_float), _p(db, C.c_float), group_size, bits,
-                              int(round_every_op), _p(out, C.c_float))
+                              int(round_every_op), int(round_out), _p(out, C.c_float))
     if rc:
         raise IndexError("switch_glu: expert index out of range")
     return out
@@ -249,8 +250,10 @@ def switch_glu(x, idx, gate, up, down, scores=None, group_size=64, bits=4, round
 
 def moe_block(x, wr, gate, up, down, top_k, mode=0, renorm=True, logit_bias=None, group_size=64, bits=4,
               round_every_op=False):
-    """Whole block -> dict(out, idx, scores, perm, inv, counts, offsets)."""
+    """Whole block -> dict(out, out_f32, idx, scores, perm, inv, counts, offsets); `out_f32` is the
+    float32 accumulation before the final bf16 rounding, `out` its bf16 rounding."""
     idx, sc = router(x, wr, top_k, mode, renorm, logit_bias)
     perm, inv, counts, offsets = permute(idx, np.shape(wr)[0])
-    out = switch_glu(x, idx, gate, up, down, sc, group_size, bits, round_every_op)
-    return dict(out=out, idx=idx, scores=sc, perm=perm, inv=inv, counts=counts, offsets=offsets)
+    out32 = switch_glu(x, idx, gate, up, down, sc, group_size, bits, round_every_op, round_out=False)
+    return dict(out=round_bf16(out32), out_f32=out32, idx=idx, scores=sc, perm=perm, inv=inv, counts=counts,
+                offsets=offsets)
