@@ -177,6 +177,22 @@ int b200_router_topk(b200_ctx* ctx, const b200_moe_config* cfg, const void* x, c
 int b200_moe_permute(b200_ctx* ctx, const uint32_t* indices, int64_t n, int n_experts, uint32_t* perm, uint32_t* inv_perm,
                      uint32_t* counts, uint32_t* offsets, void* stream);
 
+/* Allocation-free variant of b200_moe_permute.  It has no counterpart in the reference (whose
+ * arrays are always allocated by MLX); it exists for callers of THIS library that must not
+ * trigger a device allocation: a server that gave all device memory to its own pool at start-up,
+ * or a token loop that cannot afford the device-wide synchronisation cudaMalloc/cudaFree imply.
+ * Same arguments and results as b200_moe_permute, but no context: the scratch memory is a fixed
+ * 258 KB __device__ array inside the library (held by every GPU that loads it, until exit).
+ * Limit: ceil(n/1024) * n_experts <= 65536 (e.g. n <= 524288 at 128 experts); larger problems
+ * are rejected with an error.  The call performs no cudaMalloc/cudaFree and uses no allocating
+ * library routine.  Its first call on a device resolves the array's device address
+ * (cudaGetSymbolAddress) and should therefore happen before any stream capture begins.  All
+ * calls share the one array and it keeps the previous call's contents (the call clears what
+ * has to start at zero): calls whose kernels overlap on the GPU - two streams, two threads -
+ * race on it, so serialise them.  Expert indices >= n_experts are skipped, not reported. */
+int b200_moe_permute_static(const uint32_t* indices, int64_t n, int n_experts, uint32_t* perm, uint32_t* inv_perm,
+                            uint32_t* counts, uint32_t* offsets, void* stream);
+
 /* SwitchGLU forward: (x bf16 [T, H], indices [T, k]) -> out bf16 [T, k, H],
  * out[t, j] = down_e( silu(gate_e(x_t)) * up_e(x_t) ), e = indices[t, j]. */
 int b200_switch_glu_forward(b200_ctx* ctx, const b200_moe_config* cfg, const b200_moe_params* params, const void* x,

@@ -62,6 +62,8 @@ EXPORTS = {
                                    C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200_moe_permute": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                    C.c_void_p, C.c_void_p]),
+    "b200_moe_permute_static": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                          C.c_void_p, C.c_void_p]),
     "b200_switch_glu_forward": (C.c_int, [C.c_void_p, C.POINTER(MoeConfig), C.POINTER(MoeParams), C.c_void_p, C.c_void_p,
                                           C.c_int64, C.c_void_p, C.c_void_p]),
     "b200_moe_block_forward": (C.c_int, [C.c_void_p, C.POINTER(MoeConfig), C.POINTER(MoeParams), C.c_void_p, C.c_int64,

@@ -180,4 +180,62 @@ int launch_permute(const uint32_t* idx, int64_t n, int E, uint32_t* perm, uint32
 
 size_t permute_scratch_words(int64_t n, int E) { return (size_t)cdiv(n, kChunk) * E; }
 
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant of the token -> expert sort.
+//
+// b200_moe_permute needs scratch in global memory (the chunk table, the list of active
+// experts) and takes it from the context's arena, which is grown with cudaMalloc.  Some
+// callers cannot live with that: a serving process that hands all of the device's memory to
+// its own pool at start-up (so a later cudaMalloc by a library fails or fragments the pool),
+// or a latency-critical token loop that must never hit the implicit device-wide
+// synchronisation of cudaMalloc / cudaFree.  For them the same kernels run here on a scratch
+// area that is part of the library image: a file-scope __device__ array of fixed size.  Every
+// GPU that loads the library carries these 258 KB until the process exits.
+//
+// In host code the array's name is only a host-side handle, not a device address, so the
+// address is looked up once per device with cudaGetSymbolAddress (with that device current)
+// and cached; kernels receive that pointer.
+// ---------------------------------------------------------------------------------------
+constexpr int kStaticTableWords = 1 << 16;  // chunk table capacity: ceil(n/1024) * n_experts <= 65536
+constexpr int kStaticTailWords = 512;       // active list (<= 257), n_active, status word
+static __device__ __align__(256) uint32_t g_permute_static_scratch[kStaticTableWords + kStaticTailWords];
+
+constexpr int kMaxDevices = 64;
+static uint32_t* g_static_scratch_addr[kMaxDevices] = {};
+
 }  // namespace b200
+
+extern "C" int b200_moe_permute_static(const uint32_t* indices, int64_t n, int n_experts, uint32_t* perm,
+                                       uint32_t* inv_perm, uint32_t* counts, uint32_t* offsets, void* stream) {
+  using namespace b200;
+  B200_REQUIRE(n_experts > 0 && n_experts <= 256, "n_experts must be in 1..256");
+  B200_REQUIRE(n >= 0 && n < (int64_t(1) << 31), "bad assignment count");
+  B200_REQUIRE(counts && offsets, "counts and offsets are required");
+  B200_REQUIRE(n == 0 || (indices && perm && inv_perm), "null tensor");
+  B200_REQUIRE(permute_scratch_words(n, n_experts) <= (size_t)kStaticTableWords,
+               "problem exceeds the static scratch: ceil(n/1024) * n_experts must not exceed 65536 "
+               "(use b200_moe_permute, which allocates, for larger inputs)");
+  int dev = -1;
+  B200_CUDA(cudaGetDevice(&dev));
+  B200_REQUIRE(dev >= 0 && dev < kMaxDevices, "device ordinal out of range");
+  if (!g_static_scratch_addr[dev]) {  // set-up on the first call on this device
+    uint32_t* ptr = nullptr;
+    B200_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_permute_static_scratch));
+    B200_REQUIRE(ptr != nullptr, "cudaGetSymbolAddress returned a null address");
+    g_static_scratch_addr[dev] = ptr;
+  }
+  uint32_t* base = g_static_scratch_addr[dev];
+  uint32_t* active = base + kStaticTableWords;
+  uint32_t* n_active = active + 260;
+  int* status = reinterpret_cast<int*>(active + 264);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left.  The chunk table, the active list and
+  // n_active are fully rewritten by the kernels before they are read; only the status word is
+  // written conditionally, so it is the one thing that has to be cleared.
+  B200_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
+  launch_permute(indices, n, n_experts, perm, inv_perm, counts, offsets, active, n_active, base, status, st);
+  cudaError_t le = cudaGetLastError();
+  if (le != cudaSuccess) B200_FAIL(std::string("kernel launch failed: ") + cudaGetErrorString(le));
+  return 0;
+}

@@ -153,3 +153,26 @@ def moe_permute(indices, n_experts, ctx=None):
     L.check(L.lib().b200_moe_permute(_ctx(ctx), L.ptr(indices), n, n_experts, L.ptr(perm), L.ptr(inv), L.ptr(counts),
                                      L.ptr(offsets), L.stream_ptr()))
     return perm, inv, counts, offsets
+
+
+def moe_permute_static(indices, n_experts):
+    """moe_permute without any device allocation by the library (no context either): the scratch is
+    a fixed array inside libb200moe.so.  For callers whose memory pool owns the whole device or whose
+    token loop must not meet cudaMalloc's device-wide synchronisation.  The outputs are allocated
+    HERE by torch for convenience; a caller that cannot allocate passes its own buffers to the C
+    entry point `b200_moe_permute_static`.  Limit: ceil(n/1024) * n_experts <= 65536."""
+    _cuda(indices)
+    n = indices.numel()
+    dev = indices.device
+    perm = torch.empty(n, dtype=torch.int32, device=dev)
+    inv = torch.empty(n, dtype=torch.int32, device=dev)
+    counts = torch.empty(n_experts, dtype=torch.int32, device=dev)
+    offsets = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
+    moe_permute_static_into(indices, n_experts, perm, inv, counts, offsets)
+    return perm, inv, counts, offsets
+
+
+def moe_permute_static_into(indices, n_experts, perm, inv, counts, offsets):
+    """The C entry point itself, on caller-provided buffers: nothing is allocated."""
+    L.check(L.lib().b200_moe_permute_static(L.ptr(indices), indices.numel(), n_experts, L.ptr(perm), L.ptr(inv),
+                                            L.ptr(counts), L.ptr(offsets), L.stream_ptr()))
