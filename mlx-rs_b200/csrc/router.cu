@@ -12,6 +12,8 @@
 // of the bf16 operands (accumulated in float64: products of two bf16 numbers are exact in
 // float64 and the sum carries ~2^-53 relative error, far below half a bf16 ulp), the
 // probability is the exact softmax of those bf16 logits.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -116,15 +118,111 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const __nv_bfloat16*
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Warp-per-expert variant for token counts that cannot fill the GPU with 64x64 tiles.
+// CTA = 8 warps = 8 experts against TT tokens whose rows are staged once in shared memory as
+// raw bf16.  A lane loads 8 consecutive weights per 128-bit load (all loads of a row are issued
+// before the first use), converts them to float64 with integer re-biasing, and accumulates one
+// float64 sum per token; a butterfly reduction over the lanes finishes each dot product.
+// ---------------------------------------------------------------------------------------
+template <int TT>
+__global__ void __launch_bounds__(256) router_logits_warp_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                 const __nv_bfloat16* __restrict__ w,
+                                                                 const float* __restrict__ logit_bias,
+                                                                 __nv_bfloat16* __restrict__ logits, int T, int H, int E) {
+  extern __shared__ __align__(16) unsigned char rsm[];  // [TT][H] bf16
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int t0 = blockIdx.y * TT;
+  const int e = blockIdx.x * 8 + warp;
+  const int nvec = H / 8;  // 128-bit vectors per row
+  // stage the token rows (zero rows past T)
+  for (int i = tid; i < TT * nvec; i += 256) {
+    int r = i / nvec, c = i % nvec;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t0 + r < T) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + r) * H) + c);
+    reinterpret_cast<uint4*>(rsm)[i] = v;
+  }
+  __syncthreads();
+  if (e >= E) return;
+  double acc[TT];
+#pragma unroll
+  for (int j = 0; j < TT; ++j) acc[j] = 0.0;
+  const uint4* wrow = reinterpret_cast<const uint4*>(w + (size_t)e * H);
+  constexpr int UN = 4;  // row vectors in flight per lane
+  for (int c0 = lane; c0 < nvec; c0 += 32 * UN) {
+    uint4 wv[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      int c = c0 + 32 * u;
+      wv[u] = (c < nvec) ? __ldg(wrow + c) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      int c = c0 + 32 * u;
+      if (c >= nvec) break;
+      const uint32_t wu[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+      double wd[8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        wd[2 * q] = bf16_bits_to_f64(wu[q] & 0xffffu);
+        wd[2 * q + 1] = bf16_bits_to_f64(wu[q] >> 16);
+      }
+#pragma unroll
+      for (int j = 0; j < TT; ++j) {
+        const uint4 xv = reinterpret_cast<const uint4*>(rsm)[j * nvec + c];
+        const uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          acc[j] = fma(bf16_bits_to_f64(xu[q] & 0xffffu), wd[2 * q], acc[j]);
+          acc[j] = fma(bf16_bits_to_f64(xu[q] >> 16), wd[2 * q + 1], acc[j]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < TT; ++j) {
+    double s = acc[j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0 && t0 + j < T) {
+      uint32_t bits = f64_to_bf16_bits(s);
+      if (logit_bias) bits = f32_to_bf16_bits(bf16_bits_to_f32(bits) + logit_bias[e]);
+      logits[(size_t)(t0 + j) * E + e] = __ushort_as_bfloat16((unsigned short)bits);
+    }
+  }
+}
+
+template <int TT>
+static int launch_router_warp(const __nv_bfloat16* xp, const __nv_bfloat16* wp, const float* logit_bias,
+                              __nv_bfloat16* lp, int T, int H, int E, cudaStream_t st) {
+  size_t smem = (size_t)TT * H * 2;
+  auto kern = router_logits_warp_kernel<TT>;
+  static size_t attr_bytes = 0;
+  if (smem > 48 * 1024 && smem > attr_bytes) {
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_bytes = smem;
+  }
+  dim3 grid(cdiv(E, 8), cdiv(T, TT));
+  kern<<<grid, 256, smem, st>>>(xp, wp, logit_bias, lp, T, H, E);
+  return 0;
+}
+
 int launch_router_logits(const void* x, const void* w, const float* logit_bias, void* logits, int T, int H, int E,
                          cudaStream_t st) {
   auto xp = static_cast<const __nv_bfloat16*>(x);
   auto wp = static_cast<const __nv_bfloat16*>(w);
   auto lp = static_cast<__nv_bfloat16*>(logits);
-  if (T <= 4) {
-    dim3 grid(cdiv(E, 16), T);
-    router_logits_kernel<1, 1, 4><<<grid, 256, 0, st>>>(xp, wp, logit_bias, lp, T, H, E);
-  } else if (T <= 256) {
+  static const int force = [] {
+    const char* v = getenv("B200_ROUTER_KERNEL");  // "warp" / "tile": development override
+    return !v ? 0 : (v[0] == 'w' ? 1 : 2);
+  }();
+  const bool warp_ok = (H % 8 == 0) && ((size_t)8 * H * 2 <= 200 * 1024);
+  const bool use_warp = force ? (force == 1 && warp_ok) : (warp_ok && T < 2048);
+  if (use_warp) {
+    if (T <= 4) return launch_router_warp<1>(xp, wp, logit_bias, lp, T, H, E, st);
+    return launch_router_warp<8>(xp, wp, logit_bias, lp, T, H, E, st);
+  }
+  if (T <= 256) {
     dim3 grid(cdiv(E, 16), cdiv(T, 8));
     router_logits_kernel<4, 2, 4><<<grid, 256, 0, st>>>(xp, wp, logit_bias, lp, T, H, E);
   } else {
