@@ -78,6 +78,7 @@ typedef struct {
   uint32_t* counts;   /* [E]      assignments per expert */
   uint32_t* offsets;  /* [E+1]    exclusive prefix sum of counts */
   void* logits;       /* [T, E]   bf16 router logits */
+  float* out_f32;     /* [T, H]   the block output before its final rounding to bf16 (out == bf16(out_f32)) */
 } b200_moe_aux;
 
 /* ---- library / context ----------------------------------------------------------------- */
@@ -103,6 +104,12 @@ int64_t b200_ctx_launch_count(const b200_ctx* ctx);
  * stages; b200_ctx_stage_ms waits for the last profiled call and returns the milliseconds of
  * its stages in this order: router logits, softmax/top-k, permutation, gate+up product,
  * down product, combine. */
+/* Which grouped-product kernel the routed block uses: AUTO picks the memory-bound kernel while
+ * experts own few rows and the tcgen05 tensor-core kernel beyond that (when the shape allows
+ * it: inter % 128 == 0, hidden % 256 == 0); the other two values pin the choice (TENSOR_CORE
+ * still falls back when the shape does not allow it). */
+enum { B200_QMM_AUTO = 0, B200_QMM_SMALL = 1, B200_QMM_TENSOR_CORE = 2 };
+int b200_ctx_set_qmm_path(b200_ctx* ctx, int path);
 #define B200_N_STAGES 6
 int b200_ctx_set_profiling(b200_ctx* ctx, int enable);
 int b200_ctx_stage_ms(b200_ctx* ctx, float* ms, int n);

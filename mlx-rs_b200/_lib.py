@@ -26,7 +26,8 @@ class MoeParams(C.Structure):
 
 
 class MoeAux(C.Structure):
-    _fields_ = [(n, C.c_void_p) for n in ("indices", "scores", "perm", "inv_perm", "counts", "offsets", "logits")]
+    _fields_ = [(n, C.c_void_p) for n in ("indices", "scores", "perm", "inv_perm", "counts", "offsets", "logits",
+                                            "out_f32")]
 
 
 EXPORTS = {
@@ -38,6 +39,7 @@ EXPORTS = {
     "b200_ctx_reserve": (C.c_int, [C.c_void_p, C.POINTER(MoeConfig), C.c_int64]),
     "b200_ctx_check": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200_ctx_launch_count": (C.c_int64, [C.c_void_p]),
+    "b200_ctx_set_qmm_path": (C.c_int, [C.c_void_p, C.c_int]),
     "b200_ctx_set_profiling": (C.c_int, [C.c_void_p, C.c_int]),
     "b200_ctx_stage_ms": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.c_int]),
     "b200_quantize": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_void_p,
@@ -128,6 +130,12 @@ class Context:
         check(lib().b200_ctx_check(self._h, stream_ptr()))
 
     STAGES = ("router_logits", "route_topk", "permute", "gate_up", "down", "combine")
+
+    QMM_AUTO, QMM_SMALL, QMM_TENSOR_CORE = 0, 1, 2
+
+    def set_qmm_path(self, path):
+        """Pin the grouped-product kernel (QMM_SMALL / QMM_TENSOR_CORE) or let the library choose (QMM_AUTO)."""
+        check(lib().b200_ctx_set_qmm_path(self._h, int(path)))
 
     def set_profiling(self, on):
         check(lib().b200_ctx_set_profiling(self._h, int(bool(on))))

@@ -1,5 +1,6 @@
 // C ABI of the library (see include/b200_moe.h): argument validation, scratch management and
 // the composition of kernels behind every entry point.  No kernel lives here.
+#include <cstdlib>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -35,6 +36,7 @@ struct b200_ctx {
   size_t ws_used = 0;           // bump pointer of the call in progress
   int* err = nullptr;           // device status word
   int64_t launches = 0;
+  int qmm_path = B200_QMM_AUTO;
   bool profiling = false;       // record an event after every stage of the block forward
   cudaEvent_t ev[B200_N_STAGES + 1] = {};
   bool ev_valid = false;
@@ -77,6 +79,9 @@ static size_t block_scratch_bytes(const b200_moe_config& cfg, int64_t T) {
   b += al(sizeof(uint32_t) * permute_scratch_words(n, (int)E));
   b += al(sizeof(uint16_t) * n * cfg.inter);         // h
   b += al(sizeof(float) * n * cfg.hidden);           // per-assignment outputs (float32)
+  b += al(sizeof(uint16_t) * n * cfg.hidden);        // rows gathered into expert order, fp16 (tensor-core path)
+  b += al(sizeof(uint16_t) * n * cfg.inter) + 2 * al(sizeof(float) * n);  // fp16 copy of h, row scales
+  b += al(sizeof(uint32_t) * prefill_tile_words(n, (int)E)) * 3 + al(16);
   return b + 4096;
 }
 
@@ -170,6 +175,13 @@ int b200_ctx_check(b200_ctx* c, void* stream) {
 }
 
 int64_t b200_ctx_launch_count(const b200_ctx* c) { return c ? c->launches : 0; }
+
+int b200_ctx_set_qmm_path(b200_ctx* c, int path) {
+  CTX_ENTER(c);
+  B200_REQUIRE(path == B200_QMM_AUTO || path == B200_QMM_SMALL || path == B200_QMM_TENSOR_CORE, "unknown path");
+  c->qmm_path = path;
+  return 0;
+}
 
 int b200_ctx_set_profiling(b200_ctx* c, int enable) {
   CTX_ENTER(c);
@@ -416,6 +428,14 @@ int b200_moe_permute(b200_ctx* c, const uint32_t* indices, int64_t n, int E, uin
   return 0;
 }
 
+// Which grouped-product kernel a block of n assignments over at most `max_active` experts uses.
+static bool use_tensor_core_path(const b200_ctx* c, const b200_moe_config& cfg, int64_t n, int max_active) {
+  if (!prefill_shape_ok(cfg.hidden, cfg.inter, 2) || !prefill_shape_ok(cfg.inter, cfg.hidden, 1)) return false;
+  if (c->qmm_path == B200_QMM_SMALL) return false;
+  if (c->qmm_path == B200_QMM_TENSOR_CORE) return true;
+  return n / (max_active > 0 ? max_active : 1) >= 48;
+}
+
 // Shared tail of switch_glu_forward and moe_block_forward: permute, gate/up, down.
 // `scores` null: unweighted per-assignment outputs go to `yk` ([T*k, H]).
 static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_moe_params& p, const void* x,
@@ -440,8 +460,29 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
   }
   launch_permute(idx, n, E, perm, inv, counts, offsets, active, n_active, chunk, c->err, st);
   LAUNCHED(c, permute_launches(n));
-  c->mark(3, st);
   const int max_active = (int)(E < n ? E : n);
+
+  // Regime: the tensor-core path once experts own enough rows to fill 128-row tiles.
+  const bool tc = use_tensor_core_path(c, cfg, n, max_active);
+  uint32_t *tile_expert = nullptr, *tile_row0 = nullptr, *tile_rows = nullptr, *n_row_tiles = nullptr;
+  void *xs = nullptr, *h16 = nullptr;
+  float *rs_x = nullptr, *rs_h = nullptr;
+  if (tc) {
+    const size_t tw = prefill_tile_words(n, E);
+    tile_expert = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
+    tile_row0 = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
+    tile_rows = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
+    n_row_tiles = static_cast<uint32_t*>(c->take(16));
+    xs = c->take(sizeof(uint16_t) * n * cfg.hidden);
+    h16 = c->take(sizeof(uint16_t) * n * cfg.inter);
+    rs_x = static_cast<float*>(c->take(sizeof(float) * n));
+    rs_h = static_cast<float*>(c->take(sizeof(float) * n));
+    B200_REQUIRE(tile_expert && tile_row0 && tile_rows && n_row_tiles && xs && h16 && rs_x && rs_h,
+                 "scratch arena too small");
+    launch_build_row_tiles(counts, offsets, E, tile_expert, tile_row0, tile_rows, n_row_tiles, st);
+    LAUNCHED(c, 1);
+  }
+  c->mark(3, st);
 
   GroupedArgs gu{};
   gu.x = x;
@@ -461,7 +502,16 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
   gu.out = h;
   gu.K = cfg.hidden;
   gu.N = cfg.inter;
-  if (run_grouped(c, gu, 2, cfg.bits, max_active, n, st)) return 1;
+  if (tc) {
+    // rows gathered into expert order, converted to row-normalised fp16, in the k order the 4-bit unpack produces
+    launch_prepare_rows(x, perm, cfg.top_k, n, cfg.hidden, cfg.bits == 4, xs, rs_x, st);
+    if (launch_grouped_qmm_tc(xs, rs_x, n, gu, 2, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, c->err,
+                              st))
+      return 1;
+    LAUNCHED(c, 2);
+  } else if (run_grouped(c, gu, 2, cfg.bits, max_active, n, st)) {
+    return 1;
+  }
   c->mark(4, st);
 
   GroupedArgs dn{};
@@ -480,7 +530,16 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
   dn.out_f32 = scores != nullptr;  // weighted rows stay float32 until the combine; SwitchGlu's own output is bf16
   dn.K = cfg.inter;
   dn.N = cfg.hidden;
-  if (run_grouped(c, dn, 1, cfg.bits, max_active, n, st)) return 1;
+  if (tc) {
+    // h was written (bf16-rounded) already in unpack order; only the fp16 conversion remains
+    launch_prepare_rows(h, nullptr, 1, n, cfg.inter, 0, h16, rs_h, st);
+    if (launch_grouped_qmm_tc(h16, rs_h, n, dn, 1, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, c->err,
+                              st))
+      return 1;
+    LAUNCHED(c, 2);
+  } else if (run_grouped(c, dn, 1, cfg.bits, max_active, n, st)) {
+    return 1;
+  }
   c->mark(5, st);
   return 0;
 }
@@ -533,7 +592,7 @@ int b200_moe_block_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_m
   c->mark(2, st);
   LAUNCHED(c, 2);
   if (experts_forward(c, *cfg, *params, x, idx, scores, T, yk, aux, st)) return 1;
-  if (launch_combine(yk, T, cfg->top_k, cfg->hidden, out, st)) return 1;
+  if (launch_combine(yk, T, cfg->top_k, cfg->hidden, out, aux ? aux->out_f32 : nullptr, st)) return 1;
   c->mark(6, st);
   c->ev_valid = c->profiling;
   LAUNCHED(c, 1);

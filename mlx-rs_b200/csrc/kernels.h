@@ -46,12 +46,23 @@ size_t permute_scratch_words(int64_t n, int E);
 // qmm_decode.cu
 int launch_grouped_qmm_small(const GroupedArgs& a, int nmat, int bits, int max_active, int64_t rows, cudaStream_t st);
 
+// qmm_prefill.cu (tcgen05 path)
+size_t prefill_tile_words(int64_t rows, int E);
+bool prefill_shape_ok(int K, int N, int nmat);
+int launch_build_row_tiles(const uint32_t* counts, const uint32_t* offsets, int E, uint32_t* tile_expert,
+                           uint32_t* tile_row0, uint32_t* tile_rows, uint32_t* n_row_tiles, cudaStream_t st);
+int launch_prepare_rows(const void* x, const uint32_t* perm, int src_div, int64_t n_rows, int K, int permute8, void* xs,
+                        float* row_scale, cudaStream_t st);
+int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows, const GroupedArgs& g, int nmat, int bits, const uint32_t* tile_expert,
+                          const uint32_t* tile_row0, const uint32_t* tile_rows, const uint32_t* n_row_tiles, int E,
+                          int* err, cudaStream_t st);
+
 // misc.cu
 int launch_quantize(const void* w, int is_bf16, int64_t rows, int64_t K, int gs, int bits, uint32_t* wq, void* scales,
                     void* biases, cudaStream_t st);
 int launch_dequantize(const uint32_t* wq, const void* scales, const void* biases, int is_bf16, int64_t rows, int64_t K,
                       int gs, int bits, void* out, cudaStream_t st);
-int launch_combine(const void* yk, int64_t T, int k, int64_t H, void* out, cudaStream_t st);
+int launch_combine(const void* yk, int64_t T, int k, int64_t H, void* out, void* out_f32, cudaStream_t st);
 int launch_rms_norm(const void* x, const void* residual, const void* weight, float eps, int64_t rows, int64_t cols,
                     void* out, void* sum_out, cudaStream_t st);
 int launch_add(const void* a, const void* b, int64_t n, void* out, cudaStream_t st);

@@ -113,7 +113,8 @@ int launch_dequantize(const uint32_t* wq, const void* scales, const void* biases
 // combine: out[t, c] = bf16( sum_j yk[t, j, c] ), j ascending, float32 throughout (sum_axis(-2),
 // mlx-rs/src/ops/reduction.rs:260-275; the routing weights were applied by the producer, whose
 // float32 results are summed here without an intermediate rounding).
-__global__ void combine_kernel(const float4* __restrict__ yk, int64_t T, int k, int64_t H4, uint2* __restrict__ out) {
+__global__ void combine_kernel(const float4* __restrict__ yk, int64_t T, int k, int64_t H4, uint2* __restrict__ out,
+                               float4* __restrict__ out_f32) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= T * H4) return;
   const int64_t t = i / H4, c = i % H4;
@@ -129,13 +130,15 @@ __global__ void combine_kernel(const float4* __restrict__ yk, int64_t T, int k, 
   o.x = f32_to_bf16_bits(acc.x) | (f32_to_bf16_bits(acc.y) << 16);
   o.y = f32_to_bf16_bits(acc.z) | (f32_to_bf16_bits(acc.w) << 16);
   out[i] = o;
+  if (out_f32) out_f32[i] = acc;  // the sum before its rounding to bf16
 }
 
-int launch_combine(const void* yk, int64_t T, int k, int64_t H, void* out, cudaStream_t st) {
+int launch_combine(const void* yk, int64_t T, int k, int64_t H, void* out, void* out_f32, cudaStream_t st) {
   if (T == 0) return 0;
   B200_REQUIRE(H % 4 == 0, "hidden size must be a multiple of 4");
   int64_t n = T * (H / 4);
-  combine_kernel<<<cdiv(n, 256), 256, 0, st>>>(static_cast<const float4*>(yk), T, k, H / 4, static_cast<uint2*>(out));
+  combine_kernel<<<cdiv(n, 256), 256, 0, st>>>(static_cast<const float4*>(yk), T, k, H / 4, static_cast<uint2*>(out),
+                                               static_cast<float4*>(out_f32));
   return 0;
 }
 

@@ -1,0 +1,649 @@
+// Grouped quantized expert GEMM for the dense (prefill) regime: tcgen05 tensor cores with
+// TMEM accumulators, A tiles staged by TMA, B tiles dequantised into shared memory.
+//
+// Same contract as the memory-bound kernel (gather_qmm with sorted rows,
+// mlx-rs/src/ops/quantization.rs:160-230, with the SiLU-gate and routing-weight epilogues
+// fused), chosen when experts own many rows.  Per CTA (persistent over a tile list):
+//
+//   tile    = 128 rows of one expert's segment  x  256 accumulator columns
+//             (NMAT = 2: 128 gate features + the same 128 up features; NMAT = 1: 256 features)
+//   K loop  = blocks of 64 (= one quantisation group), 4 UMMA instructions m128 n256 k16 each
+//   A       = activations [rows, K] fp16, one TMA tile load (128 x 64, 128-byte swizzle) per block
+//   B       = one thread per accumulator column reads that weight row's 32 (4-bit) or 64 (8-bit)
+//             packed bytes plus its scale and bias, forms w_hat = fp16(scale*q + bias) with one
+//             fused multiply-add per pair, and writes the row's 128 bytes in the same swizzled
+//             K-major layout TMA produces.  fp16 (11 significant bits) rather than bf16 (8) keeps
+//             the dequantisation error an order of magnitude below the output tolerance; its
+//             narrow exponent range is handled by scaling every weight row by a power of two
+//             (exact) chosen from the row's largest |bias| + qmax*|scale|, undone per accumulator
+//             column in the epilogue.  kind::f16 wants both operands in one format, so A is
+//             converted to fp16 too, each row scaled by its own power of two (undone per
+//             accumulator row in the epilogue).
+//   D       = float32 in tensor memory, two accumulator stages (2 x 256 columns) so that the
+//             epilogue of tile i overlaps the main loop of tile i+1
+//
+// Warp roles (14 warps): 0-3 epilogue (one TMEM lane quarter each), 4-11 dequantisation,
+// 12 TMA producer, 13 MMA issuer (also owns the TMEM allocation).  Stages hand over through
+// mbarriers; every wait is bounded by a 2 s timer after which the CTA sets a status word, drops
+// out of its loops, releases its tensor memory and returns.
+//
+// 4-bit codes are unpacked pairwise (elements j and j+4 of a word land in one bf16x2), so a
+// row's k order inside each group of eight is [0,4,1,5,2,6,3,7]; the A operand is written in
+// that same order by its producer (the row gather for gate/up, the gate/up epilogue for down),
+// which leaves every dot product unchanged.  No load in this file uses cluster multicast.
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace b200 {
+
+namespace {
+
+constexpr int BM = 128, BK = 64, NCOL = 256;
+constexpr int STAGES = 4, ACC_STAGES = 2;
+constexpr int A_BYTES = BM * BK * 2;      // 16 KB
+constexpr int B_BYTES = NCOL * BK * 2;    // 32 KB
+constexpr int N_EPI = 128, N_DEQ = 256;
+constexpr int N_THREADS = N_EPI + N_DEQ + 64;  // + TMA warp + MMA warp
+constexpr int CS_BUFS = 4;                // column-scale buffers (tiles in flight between dequantisation and epilogue)
+constexpr int SMEM_BYTES = 1024 + STAGES * (A_BYTES + B_BYTES) + 256 + CS_BUFS * NCOL * 4;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait: false when the abort flag is up or the time limit has passed.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((it & 31u) == 31u) {
+      if (*abort_flag) return false;
+      uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+               : "memory");
+}
+// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3fffu);        // start address
+  d |= (uint64_t)1 << 16;                         // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                         // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                         // SWIZZLE_128B
+  return d;
+}
+// kind::f16, A = B = fp16 (format 0), D = f32 (format 1), both operands K-major, M = 128, N = 256
+constexpr uint32_t kIdesc = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(NCOL >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+struct PrefillArgs {
+  const uint32_t* w[2];
+  const void* scales[2];
+  const void* biases[2];
+  const uint32_t* tile_expert;  // per row tile: expert
+  const uint32_t* tile_row0;    // first sorted position of the tile
+  const uint32_t* tile_rows;    // valid rows (<= 128)
+  const uint32_t* n_row_tiles;  // device scalar
+  const uint32_t* perm;         // sorted position -> flat assignment index
+  int dst_perm;                 // out row = perm[p] instead of p
+  const float* a_row_scale;     // by sorted position: the power of two each A row was divided by
+  const void* row_scale;        // bf16 by out row, or null
+  void* out;
+  int out_f32;
+  int K, N;                     // reduction length, output features per matrix
+  int* err;
+};
+
+// dequantise 8 codes of one 4-bit word -> 16 bytes of fp16 (k order [0,4,1,5,2,6,3,7]).
+// OR-ing a nibble into the mantissa of 1024.0 gives 1024+q (low nibbles) or 1024+16q (nibbles
+// taken in place at bits 4..7); both are brought back to q exactly before the affine step.
+__device__ __forceinline__ uint4 deq_word4(uint32_t w, __half2 s2, __half2 b2) {
+  const __half2 k1024 = __floats2half2_rn(1024.f, 1024.f);
+  const __half2 k16th = __floats2half2_rn(0.0625f, 0.0625f), km64 = __floats2half2_rn(-64.f, -64.f);
+  uint4 o;
+  uint32_t* ou = &o.x;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t v = w >> (8 * h);
+    uint32_t lo = (v & 0x000f000fu) | 0x64006400u;  // (1024 + q_j,     1024 + q_{j+4}),     j = 2h
+    uint32_t hi = (v & 0x00f000f0u) | 0x64006400u;  // (1024 + 16 q_j', 1024 + 16 q_{j'+4}), j' = 2h+1
+    __half2 q0 = __hsub2(*reinterpret_cast<__half2*>(&lo), k1024);
+    __half2 q1 = __hfma2(*reinterpret_cast<__half2*>(&hi), k16th, km64);
+    __half2 v0 = __hfma2(q0, s2, b2), v1 = __hfma2(q1, s2, b2);
+    ou[2 * h] = *reinterpret_cast<uint32_t*>(&v0);
+    ou[2 * h + 1] = *reinterpret_cast<uint32_t*>(&v1);
+  }
+  return o;
+}
+// dequantise 8 codes of two 8-bit words -> 16 bytes of fp16 (natural k order)
+__device__ __forceinline__ uint4 deq_word8(uint32_t w0, uint32_t w1, __half2 s2, __half2 b2) {
+  const __half2 k1024 = __floats2half2_rn(1024.f, 1024.f);
+  uint4 o;
+  uint32_t* ou = &o.x;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t w = j < 2 ? w0 : w1;
+    int b = (j & 1) * 2;
+    uint32_t m = __byte_perm(w, 0x64646464u, 0x4040 | ((b + 1) << 8) | b);  // (1024 + q_b, 1024 + q_{b+1})
+    __half2 v = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&m), k1024), s2, b2);
+    ou[j] = *reinterpret_cast<uint32_t*>(&v);
+  }
+  return o;
+}
+
+template <int BITS, int NMAT>
+__global__ void __launch_bounds__(N_THREADS, 1)
+grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, PrefillArgs p) {
+  constexpr int FEAT = (NMAT == 2) ? 128 : 256;  // output features per tile
+  constexpr int WPB = BK * BITS / 32;            // packed words per row per K block (8 or 16)
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* a_st = smem;
+  unsigned char* b_st = smem + STAGES * A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES));
+  // bars: full[4], empty[4], tmem_full[2], tmem_empty[2], then tmem base + abort flag
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
+  float* colscale = reinterpret_cast<float*>(smem + STAGES * (A_BYTES + B_BYTES) + 256);  // [CS_BUFS][NCOL]
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (4 + s); };
+  auto tfull_bar = [&](int a) { return bar0 + 8u * (8 + a); };
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (10 + a); };
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int KB = p.K / BK;
+  const int n_col_tiles = p.N / FEAT;
+  const int wrow = p.K * BITS / 32;  // packed words per weight row
+  const int G = p.K / 64;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), N_DEQ + 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < ACC_STAGES; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), N_EPI);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 13) {  // whole warp: allocate all 512 tensor-memory columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = (int)(*p.n_row_tiles) * n_col_tiles;
+
+  if (warp < 4) {
+    // ------------------------------- epilogue -------------------------------------------
+    int acc = 0, acc_phase = 0, tcount = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
+      const int rt = tile / n_col_tiles, ct = tile % n_col_tiles;
+      const float* cs = colscale + (tcount % CS_BUFS) * NCOL;
+      const uint32_t row0 = p.tile_row0[rt];
+      const int rows = (int)p.tile_rows[rt];
+      const int r = warp * 32 + lane;  // accumulator row = TMEM lane
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) break;
+      tc_fence_after();
+      const bool row_ok = r < rows;
+      const uint32_t sp = row0 + r;
+      const uint32_t dst = row_ok ? (p.dst_perm ? p.perm[sp] : sp) : 0u;
+      const float ar = row_ok ? p.a_row_scale[sp] : 1.0f;
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * NCOL);
+      if constexpr (NMAT == 2) {
+#pragma unroll 1
+        for (int c = 0; c < 128; c += 32) {
+          uint32_t g[32], u[32];
+          tmem_ld32(lane_addr + c, g);
+          tmem_ld32(lane_addr + 128 + c, u);
+          tmem_ld_wait();
+          if (row_ok) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              float h[8];
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                float gv = __uint_as_float(g[i + q]) * (cs[c + i + q] * ar), uv = __uint_as_float(u[i + q]) * (cs[128 + c + i + q] * ar);
+                h[q] = gv / (1.0f + __expf(-gv)) * uv;
+              }
+              if constexpr (BITS == 4) {  // the consumer (down projection) reads k in [0,4,1,5,2,6,3,7] order
+                packed[i / 2 + 0] = f32_to_bf16_bits(h[0]) | (f32_to_bf16_bits(h[4]) << 16);
+                packed[i / 2 + 1] = f32_to_bf16_bits(h[1]) | (f32_to_bf16_bits(h[5]) << 16);
+                packed[i / 2 + 2] = f32_to_bf16_bits(h[2]) | (f32_to_bf16_bits(h[6]) << 16);
+                packed[i / 2 + 3] = f32_to_bf16_bits(h[3]) | (f32_to_bf16_bits(h[7]) << 16);
+              } else {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  packed[i / 2 + q] = f32_to_bf16_bits(h[2 * q]) | (f32_to_bf16_bits(h[2 * q + 1]) << 16);
+              }
+            }
+            uint4* o = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)dst * p.N + ct * FEAT + c);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) o[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+          }
+        }
+      } else {
+        const float sc = ar * ((row_ok && p.row_scale)
+                                   ? bf16_bits_to_f32(static_cast<const unsigned short*>(p.row_scale)[dst])
+                                   : 1.0f);
+#pragma unroll 1
+        for (int c = 0; c < 256; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(lane_addr + c, v);
+          tmem_ld_wait();
+          if (row_ok) {
+            if (p.out_f32) {
+              float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.out) + (size_t)dst * p.N + ct * FEAT + c);
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                o[q] = make_float4(__uint_as_float(v[4 * q]) * cs[c + 4 * q] * sc,
+                                   __uint_as_float(v[4 * q + 1]) * cs[c + 4 * q + 1] * sc,
+                                   __uint_as_float(v[4 * q + 2]) * cs[c + 4 * q + 2] * sc,
+                                   __uint_as_float(v[4 * q + 3]) * cs[c + 4 * q + 3] * sc);
+            } else {
+              uint4* o = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)dst * p.N + ct * FEAT + c);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  w[j] = f32_to_bf16_bits(__uint_as_float(v[8 * q + 2 * j]) * cs[c + 8 * q + 2 * j] * sc) |
+                         (f32_to_bf16_bits(__uint_as_float(v[8 * q + 2 * j + 1]) * cs[c + 8 * q + 2 * j + 1] * sc) << 16);
+                o[q] = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(tempty_bar(acc));
+      if (++acc == ACC_STAGES) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  } else if (warp < 12) {
+    // ------------------------------- B dequantisation --------------------------------------
+    const int col = tid - N_EPI;  // accumulator column = B tile row, 0..255
+    const int mt = (NMAT == 2) ? (col >> 7) : 0;
+    const int fcol = (NMAT == 2) ? (col & 127) : col;
+    const uint32_t sw = (uint32_t)(col & 7);
+    const uint32_t row_off = (uint32_t)(col >> 3) * 1024u + (uint32_t)(col & 7) * 128u;
+    int s = 0, phase = 0, tcount = 0;
+    constexpr float kQmax = (BITS == 4) ? 15.f : 255.f;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
+      const int rt = tile / n_col_tiles, ct = tile % n_col_tiles;
+      const int e = (int)p.tile_expert[rt];
+      const size_t wr = (size_t)e * p.N + (size_t)ct * FEAT + fcol;
+      const uint32_t* wp = p.w[mt] + wr * wrow;
+      const unsigned short* sp = static_cast<const unsigned short*>(p.scales[mt]) + wr * G;
+      const unsigned short* bp = static_cast<const unsigned short*>(p.biases[mt]) + wr * G;
+      // power-of-two normalisation of this weight row for fp16: largest |w_hat| lands in [2^13, 2^14)
+      float mx = 0.f;
+      for (int g = 0; g < G; ++g)
+        mx = fmaxf(mx, fabsf(bf16_bits_to_f32(__ldg(bp + g))) + kQmax * fabsf(bf16_bits_to_f32(__ldg(sp + g))));
+      int ex = (mx > 0.f && mx < 3.0e38f) ? (ilogbf(mx) - 13) : 0;
+      ex = max(-100, min(100, ex));
+      const float down_f = ldexpf(1.0f, -ex);
+      colscale[(tcount % CS_BUFS) * NCOL + col] = ldexpf(1.0f, ex);
+      uint4 nx[WPB / 4];
+#pragma unroll
+      for (int q = 0; q < WPB / 4; ++q) nx[q] = ldg_nc_v4(wp + 4 * q);
+      unsigned short ns = __ldg(sp), nb = __ldg(bp);
+      bool dead = false;
+      for (int kb = 0; kb < KB; ++kb) {
+        uint4 cur[WPB / 4];
+#pragma unroll
+        for (int q = 0; q < WPB / 4; ++q) cur[q] = nx[q];
+        const unsigned short cs = ns, cb = nb;
+        if (kb + 1 < KB) {
+#pragma unroll
+          for (int q = 0; q < WPB / 4; ++q) nx[q] = ldg_nc_v4(wp + (size_t)(kb + 1) * WPB + 4 * q);
+          ns = __ldg(sp + kb + 1);
+          nb = __ldg(bp + kb + 1);
+        }
+        if (!mbar_wait(empty_bar(s), phase ^ 1, abort_flag)) {
+          dead = true;
+          break;
+        }
+        const __half2 s2 = __float2half2_rn(bf16_bits_to_f32(cs) * down_f);
+        const __half2 b2 = __float2half2_rn(bf16_bits_to_f32(cb) * down_f);
+        unsigned char* dst = b_st + (size_t)s * B_BYTES + row_off;
+        const uint32_t* cw = &cur[0].x;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint4 o;
+          if constexpr (BITS == 4)
+            o = deq_word4(cw[c], s2, b2);
+          else
+            o = deq_word8(cw[2 * c], cw[2 * c + 1], s2, b2);
+          *reinterpret_cast<uint4*>(dst + (((uint32_t)c ^ sw) << 4)) = o;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(full_bar(s));
+        if (++s == STAGES) {
+          s = 0;
+          phase ^= 1;
+        }
+      }
+      if (dead) break;
+    }
+  } else if (warp == 12) {
+    // ------------------------------- TMA producer (A) ---------------------------------------
+    if (lane == 0) {
+      int s = 0, phase = 0;
+      bool dead = false;
+      for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
+        const int rt = tile / n_col_tiles;
+        const int row0 = (int)p.tile_row0[rt];
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(empty_bar(s), phase ^ 1, abort_flag)) {
+            dead = true;
+            break;
+          }
+          mbar_arrive_expect_tx(full_bar(s), A_BYTES);
+          tma_load_2d(smem_u32(a_st + (size_t)s * A_BYTES), &tmap_a, full_bar(s), kb * BK, row0);
+          if (++s == STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------- MMA issuer ----------------------------------------------
+    if (lane == 0) {
+      int s = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool dead = false;
+      for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * NCOL);
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(full_bar(s), phase, abort_flag)) {
+            dead = true;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(a_st + (size_t)s * A_BYTES), b_addr = smem_u32(b_st + (size_t)s * B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma_bf16(d_tmem, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), (kb | k) ? 1u : 0u);
+          umma_commit(empty_bar(s));  // the stage is free once these MMAs have read it
+          if (++s == STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+        if (dead) break;
+        umma_commit(tfull_bar(acc));  // accumulator complete
+        if (++acc == ACC_STAGES) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+    __syncwarp();
+  }
+
+  // ------------------------------- teardown ------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (tid == 0) atomicExch(p.err, 3);
+    __nanosleep(200000);  // let copies and MMAs that are still in flight land before the CTA goes away
+  }
+  if (warp == 13) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
+  }
+}
+
+// ---- helpers: row-tile map and the permuted row gather ----------------------------------------
+__global__ void __launch_bounds__(256) build_row_tiles_kernel(const uint32_t* __restrict__ counts,
+                                                              const uint32_t* __restrict__ offsets, int E,
+                                                              uint32_t* __restrict__ tile_expert,
+                                                              uint32_t* __restrict__ tile_row0,
+                                                              uint32_t* __restrict__ tile_rows,
+                                                              uint32_t* __restrict__ n_row_tiles) {
+  __shared__ uint32_t pre[257];
+  const int e = threadIdx.x;
+  const uint32_t c = (e < E) ? counts[e] : 0u;
+  const uint32_t nt = (c + BM - 1) / BM;
+  pre[e + 1] = nt;
+  if (e == 0) pre[0] = 0;
+  __syncthreads();
+  if (e == 0) {
+    for (int i = 1; i <= 256; ++i) pre[i] += pre[i - 1];
+    *n_row_tiles = pre[256];
+  }
+  __syncthreads();
+  if (e < E) {
+    const uint32_t base = pre[e], o = offsets[e];
+    for (uint32_t i = 0; i < nt; ++i) {
+      tile_expert[base + i] = (uint32_t)e;
+      tile_row0[base + i] = o + i * BM;
+      tile_rows[base + i] = min((uint32_t)BM, c - i * BM);
+    }
+  }
+}
+
+// A-operand preparation, one warp per row: xs[p, :] = fp16( x[src(p), :] * 2^-e_p ) where 2^e_p
+// (written to row_scale[p]) brings the row's largest magnitude into [2^14, 2^15); optionally each
+// aligned group of eight elements is stored as [0,4,1,5,2,6,3,7] (the order 4-bit codes unpack in).
+// The scaling is exact (bf16 has fewer significant bits than fp16) unless an element is more
+// than 2^28 below the row maximum.
+__global__ void __launch_bounds__(256) prepare_rows_kernel(const uint4* __restrict__ x, const uint32_t* __restrict__ perm,
+                                                           int src_div, int64_t n_rows, int vec_per_row, int permute8,
+                                                           uint4* __restrict__ xs, float* __restrict__ row_scale) {
+  const int lane = threadIdx.x & 31;
+  const int64_t r = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  const uint32_t src = perm ? perm[r] / (uint32_t)src_div : (uint32_t)r;
+  const uint4* xr = x + (size_t)src * vec_per_row;
+  uint32_t mxbits = 0;  // max over |x| as bf16 bit patterns (monotonic for non-negative floats)
+  for (int c = lane; c < vec_per_row; c += 32) {
+    const uint4 v = __ldg(xr + c);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) mxbits = max(mxbits, max(u[q] & 0x7fffu, (u[q] >> 16) & 0x7fffu));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mxbits = max(mxbits, __shfl_xor_sync(0xffffffffu, mxbits, o));
+  const float mx = bf16_bits_to_f32(mxbits);
+  int ex = (mx > 0.f && mx < 3.0e38f) ? (ilogbf(mx) - 14) : 0;
+  ex = max(-100, min(100, ex));
+  const float f = ldexpf(1.0f, -ex);
+  if (lane == 0) row_scale[r] = ldexpf(1.0f, ex);
+  for (int c = lane; c < vec_per_row; c += 32) {
+    const uint4 v = __ldg(xr + c);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+    uint32_t hh[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      __half2 h2 = __floats2half2_rn(__uint_as_float(u[q] << 16) * f, __uint_as_float(u[q] & 0xffff0000u) * f);
+      hh[q] = *reinterpret_cast<uint32_t*>(&h2);
+    }
+    uint4 o = make_uint4(hh[0], hh[1], hh[2], hh[3]);
+    if (permute8) {
+      o.x = __byte_perm(hh[0], hh[2], 0x5410);
+      o.y = __byte_perm(hh[0], hh[2], 0x7632);
+      o.z = __byte_perm(hh[1], hh[3], 0x5410);
+      o.w = __byte_perm(hh[1], hh[3], 0x7632);
+    }
+    xs[(size_t)r * vec_per_row + c] = o;
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+}  // namespace
+
+size_t prefill_tile_words(int64_t rows, int E) { return (size_t)(rows / BM + E + 1); }
+
+bool prefill_shape_ok(int K, int N, int nmat) { return K % 64 == 0 && N % (nmat == 2 ? 128 : 256) == 0; }
+
+int launch_build_row_tiles(const uint32_t* counts, const uint32_t* offsets, int E, uint32_t* tile_expert,
+                           uint32_t* tile_row0, uint32_t* tile_rows, uint32_t* n_row_tiles, cudaStream_t st) {
+  build_row_tiles_kernel<<<1, 256, 0, st>>>(counts, offsets, E, tile_expert, tile_row0, tile_rows, n_row_tiles);
+  return 0;
+}
+
+int launch_prepare_rows(const void* x, const uint32_t* perm, int src_div, int64_t n_rows, int K, int permute8, void* xs,
+                        float* row_scale, cudaStream_t st) {
+  if (n_rows == 0) return 0;
+  prepare_rows_kernel<<<cdiv(n_rows, 8), 256, 0, st>>>(static_cast<const uint4*>(x), perm, src_div, n_rows, K / 8,
+                                                       permute8, static_cast<uint4*>(xs), row_scale);
+  return 0;
+}
+
+// a: activations [rows, K] fp16 (rows scaled by 1/a_row_scale) in the k order the weights are unpacked in.
+int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows, const GroupedArgs& g, int nmat, int bits, const uint32_t* tile_expert,
+                          const uint32_t* tile_row0, const uint32_t* tile_rows, const uint32_t* n_row_tiles, int E,
+                          int* err, cudaStream_t st) {
+  if (rows == 0) return 0;
+  B200_REQUIRE(prefill_shape_ok(g.K, g.N, nmat), "shape not supported by the tensor-core path");
+  EncodeTiledFn enc = encode_fn();
+  B200_REQUIRE(enc != nullptr, "cuTensorMapEncodeTiled is not available from the driver");
+  CUtensorMap tmap;
+  cuuint64_t dims[2] = {(cuuint64_t)g.K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)g.K * 2};
+  cuuint32_t box[2] = {BK, BM};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult cr = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(a), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200_REQUIRE(cr == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed (the activation buffer must be 16-byte aligned)");
+
+  PrefillArgs p{};
+  for (int i = 0; i < 2; ++i) {
+    p.w[i] = g.w[i];
+    p.scales[i] = g.scales[i];
+    p.biases[i] = g.biases[i];
+  }
+  p.tile_expert = tile_expert;
+  p.tile_row0 = tile_row0;
+  p.tile_rows = tile_rows;
+  p.n_row_tiles = n_row_tiles;
+  p.perm = g.perm;
+  p.dst_perm = g.dst_perm;
+  p.a_row_scale = a_row_scale;
+  p.row_scale = g.row_scale;
+  p.out = g.out;
+  p.out_f32 = g.out_f32;
+  p.K = g.K;
+  p.N = g.N;
+  p.err = err;
+
+  static int n_sm = 0;
+  if (!n_sm) {
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    B200_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const int feat = nmat == 2 ? 128 : 256;
+  const int64_t max_tiles = (int64_t)prefill_tile_words(rows, E) * (g.N / feat);
+  const int grid = (int)(max_tiles < n_sm ? max_tiles : n_sm);
+
+#define B200_TC_LAUNCH(BITSV, NMATV)                                                                          \
+  do {                                                                                                        \
+    auto kern = grouped_qmm_tc_kernel<BITSV, NMATV>;                                                          \
+    static bool attr = false;                                                                                 \
+    if (!attr) {                                                                                              \
+      B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));         \
+      attr = true;                                                                                            \
+    }                                                                                                         \
+    kern<<<grid, N_THREADS, SMEM_BYTES, st>>>(tmap, p);                                                       \
+  } while (0)
+  if (bits == 4 && nmat == 2)
+    B200_TC_LAUNCH(4, 2);
+  else if (bits == 4 && nmat == 1)
+    B200_TC_LAUNCH(4, 1);
+  else if (bits == 8 && nmat == 2)
+    B200_TC_LAUNCH(8, 2);
+  else if (bits == 8 && nmat == 1)
+    B200_TC_LAUNCH(8, 1);
+  else
+    B200_FAIL("bits must be 4 or 8");
+#undef B200_TC_LAUNCH
+  return 0;
+}
+
+}  // namespace b200

@@ -102,9 +102,10 @@ class MoeBlock:
                        inv_perm=torch.empty(n, dtype=torch.int32, device=dev),
                        counts=torch.empty(E, dtype=torch.int32, device=dev),
                        offsets=torch.empty(E + 1, dtype=torch.int32, device=dev),
-                       logits=torch.empty((T, E), dtype=torch.bfloat16, device=dev))
+                       logits=torch.empty((T, E), dtype=torch.bfloat16, device=dev),
+                       out_f32=torch.empty(x.shape, dtype=torch.float32, device=dev))
             aux_c = L.MoeAux(*[aux[n_].data_ptr() for n_ in ("indices", "scores", "perm", "inv_perm", "counts",
-                                                             "offsets", "logits")])
+                                                             "offsets", "logits", "out_f32")])
         L.check(L.lib().b200_moe_block_forward(ops._ctx(self.ctx), C.byref(self._cfg), C.byref(self._params), L.ptr(x),
                                                T, L.ptr(out), C.byref(aux_c) if aux_c is not None else None,
                                                L.stream_ptr()))

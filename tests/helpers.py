@@ -43,3 +43,13 @@ def rel_err(got, ref):
     """max|delta| / rms(reference): the tolerance of the north star is 2e-2 on this quantity."""
     ref = np.asarray(ref, dtype=np.float64)
     return float(np.abs(np.asarray(got, dtype=np.float64) - ref).max() / max(np.sqrt((ref ** 2).mean()), 1e-30))
+
+
+def close_up_to_bf16_rounding(got, ref, tol):
+    """|got - ref| <= tol * rms(ref) + one bf16 rounding of ref (half an ulp is at most 2^-9 |ref|):
+    for results that only exist as bf16 (an output of magnitude 8 rms carries a rounding error of
+    up to 3 % of rms by itself, more than the tolerance)."""
+    ref = np.asarray(ref, dtype=np.float64)
+    got = np.asarray(got, dtype=np.float64)
+    rms = max(np.sqrt((ref ** 2).mean()), 1e-30)
+    return bool(np.all(np.abs(got - ref) <= tol * rms + 2.0 ** -8 * np.abs(ref)))

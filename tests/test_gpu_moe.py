@@ -1,12 +1,16 @@
 """GPU: the routed block through the C ABI against the CPU oracle.
 
 Bars (BASELINE.json): top-k indices, permutation and per-expert counts bit-exact; layer output
-max|delta| <= 2e-2 * rms(oracle output)."""
+max|delta| <= 2e-2 * rms(oracle output) with float32 accumulation.  The output bar is checked on
+the float32 result the block produces right before its final rounding (aux `out_f32`) against the
+oracle's float32 result, and the bf16 output must equal the rounding of that value exactly: one
+bf16 ulp of an output of magnitude 8 rms is 6 % of rms, so no bf16 tensor can be compared at
+2e-2 * rms directly."""
 import numpy as np
 import pytest
 import torch
 
-from tests.helpers import bf16_cuda, make_block, rel_err, to_device, u32
+from tests.helpers import bf16_cuda, close_up_to_bf16_rounding, make_block, rel_err, to_device, u32
 
 pytestmark = pytest.mark.gpu
 TOL = 2e-2
@@ -24,7 +28,12 @@ def check_block(pkg, O, blk, mode=0, renorm=True):
     assert np.array_equal(u32(aux["inv_perm"]), ref["inv"]), "inv"
     assert np.array_equal(u32(aux["counts"]), ref["counts"]), "counts"
     assert np.array_equal(u32(aux["offsets"]), ref["offsets"]), "offsets"
-    err = rel_err(out.float().cpu().numpy(), ref["out_f32"])
+    # the bar applies to the float32 result; the bf16 output must be exactly its rounding
+    got32 = aux["out_f32"].cpu().numpy()
+    err = rel_err(got32, ref["out_f32"])
+    assert np.array_equal(out.float().cpu().numpy(), O.round_bf16(got32)), "bf16 output is not the rounding of out_f32"
+    print(f"[parity] T={blk['T']} H={blk['H']} E={blk['E']} I={blk['I']} k={blk['k']} bits={blk['bits']} mode={mode}: "
+          f"max|d|/rms = {err:.4f}")
     assert err <= TOL, f"max|d|/rms = {err}"
     return err, dev, ref
 
@@ -53,7 +62,7 @@ def test_config0_block(pkg, O, config0):
     assert np.array_equal(u32(part), ref["idx"])       # argpartition(-p, k-1)[:, :k] is the same selection
     yk = dev.switch_mlp.forward(x, idx)
     ref_yk = O.switch_glu(config0["x"], ref["idx"], config0["gate"], config0["up"], config0["down"], round_out=False)
-    assert rel_err(yk.float().cpu().numpy(), ref_yk) <= TOL
+    assert close_up_to_bf16_rounding(yk.float().cpu().numpy(), ref_yk, TOL)
 
 
 @pytest.mark.parametrize("T", [1, 4, 16])
@@ -65,19 +74,40 @@ def test_decode_sweep(pkg, O, config0, T):
     check_block(pkg, O, blk)
 
 
+@pytest.fixture(params=["small", "tensor_core"])
+def qmm_path(request, pkg):
+    """Runs a test once per grouped-product kernel (memory-bound mma.sync / tcgen05) and restores AUTO."""
+    ctx = pkg.default_context()
+    ctx.set_qmm_path(ctx.QMM_SMALL if request.param == "small" else ctx.QMM_TENSOR_CORE)
+    yield request.param
+    ctx.set_qmm_path(ctx.QMM_AUTO)
+
+
 @pytest.mark.parametrize("T", [200, 1500])
-def test_more_rows_per_expert(pkg, O, T):
-    # experts own more than eight rows: the wide (32 rows per pass) variant and multi-pass loop
+def test_more_rows_per_expert(pkg, O, T, qmm_path):
+    # experts own many rows: wide/multi-pass variant of the small kernel; ragged 128-row tiles of the tcgen05 kernel
     check_block(pkg, O, make_block(T, 256, 8, 128, 2, seed=T))
 
 
 @pytest.mark.parametrize("bits", [4, 8])
-def test_mixtral_style_skewed(pkg, O, bits):
+def test_mixtral_style_skewed(pkg, O, bits, qmm_path):
     # BASELINE.json configs[4] scaled down: 8 experts, top-2, softmax over the selected logits,
     # Zipf(1.2) logit bias; ragged segments including empty experts
     blk = make_block(300, 512, 8, 1024, 2, bits=bits, seed=11, zipf_bias=True)
     err, dev, ref = check_block(pkg, O, blk, mode=1, renorm=False)
     assert ref["counts"].max() > 3 * max(1, ref["counts"].min())
+
+
+def test_prefill_512_tokens_config0_shape(pkg, O, config0, qmm_path):
+    # BASELINE.json configs[1] prefill point T=512 on the config-0 weights, both kernels
+    blk = dict(config0)
+    g = torch.Generator().manual_seed(7)
+    blk["x"] = torch.randn(512, 2048, generator=g).bfloat16().float().numpy()
+    blk["T"] = 512
+    err, dev, ref = check_block(pkg, O, blk)
+    yk = dev.switch_mlp.forward(bf16_cuda(blk["x"]), torch.from_numpy(ref["idx"].view(np.int32)).cuda())
+    ref_yk = O.switch_glu(blk["x"], ref["idx"], blk["gate"], blk["up"], blk["down"], round_out=False)
+    assert close_up_to_bf16_rounding(yk.float().cpu().numpy(), ref_yk, TOL)
 
 
 def test_no_renorm_and_ties(pkg, O):
