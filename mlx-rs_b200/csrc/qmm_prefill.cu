@@ -9,8 +9,11 @@
 //             (NMAT = 2: 128 gate features + the same 128 up features; NMAT = 1: 256 features)
 //   K loop  = blocks of 64 (= one quantisation group), 4 UMMA instructions m128 n256 k16 each
 //   A       = activations [rows, K] fp16, one TMA tile load (128 x 64, 128-byte swizzle) per block
-//   B       = one thread per accumulator column reads that weight row's 32 (4-bit) or 64 (8-bit)
-//             packed bytes plus its scale and bias, forms w_hat = fp16(scale*q + bias) with one
+//   W       = the packed weights of the tile's 256 accumulator columns, 128 bytes per row (four
+//             4-bit or two 8-bit K blocks) per TMA stage: per-lane loads of 32 bytes from 256
+//             different rows cost the L1 a cycle per row, bulk tensor copies do not
+//   B       = one thread per accumulator column reads its row's 32 (4-bit) or 64 (8-bit) packed
+//             bytes from the W stage plus its scale and bias, forms w_hat = fp16(scale*q + bias) with one
 //             fused multiply-add per pair, and writes the row's 128 bytes in the same swizzled
 //             K-major layout TMA produces.  fp16 (11 significant bits) rather than bf16 (8) keeps
 //             the dequantisation error an order of magnitude below the output tolerance; its
@@ -22,8 +25,8 @@
 //   D       = float32 in tensor memory, two accumulator stages (2 x 256 columns) so that the
 //             epilogue of tile i overlaps the main loop of tile i+1
 //
-// Warp roles (14 warps): 0-3 epilogue (one TMEM lane quarter each), 4-11 dequantisation,
-// 12 TMA producer, 13 MMA issuer (also owns the TMEM allocation).  Stages hand over through
+// Warp roles (15 warps): 0-3 epilogue (one TMEM lane quarter each), 4-11 dequantisation,
+// 12 TMA producer for A, 13 MMA issuer (also owns the TMEM allocation), 14 TMA producer for W.  Stages hand over through
 // mbarriers; every wait is bounded by a 2 s timer after which the CTA sets a status word, drops
 // out of its loops, releases its tensor memory and returns.
 //
@@ -42,13 +45,15 @@ namespace b200 {
 namespace {
 
 constexpr int BM = 128, BK = 64, NCOL = 256;
-constexpr int STAGES = 4, ACC_STAGES = 2;
+constexpr int STAGES = 3, ACC_STAGES = 2, W_STAGES = 2;
 constexpr int A_BYTES = BM * BK * 2;      // 16 KB
 constexpr int B_BYTES = NCOL * BK * 2;    // 32 KB
 constexpr int N_EPI = 128, N_DEQ = 256;
-constexpr int N_THREADS = N_EPI + N_DEQ + 64;  // + TMA warp + MMA warp
+constexpr int W_BYTES = NCOL * 128;       // 32 KB: 128 packed bytes of each of the 256 weight rows
+constexpr int N_THREADS = N_EPI + N_DEQ + 96;  // + TMA(A) warp + MMA warp + TMA(W) warp
 constexpr int CS_BUFS = 4;                // column-scale buffers (tiles in flight between dequantisation and epilogue)
-constexpr int SMEM_BYTES = 1024 + STAGES * (A_BYTES + B_BYTES) + 256 + CS_BUFS * NCOL * 4;
+constexpr int RING_BYTES = STAGES * (A_BYTES + B_BYTES) + W_STAGES * W_BYTES;
+constexpr int SMEM_BYTES = 1024 + RING_BYTES + 256 + CS_BUFS * NCOL * 4;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -189,28 +194,32 @@ __device__ __forceinline__ uint4 deq_word8(uint32_t w0, uint32_t w1, __half2 s2,
 
 template <int BITS, int NMAT>
 __global__ void __launch_bounds__(N_THREADS, 1)
-grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, PrefillArgs p) {
+grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w0,
+                      const __grid_constant__ CUtensorMap tmap_w1, PrefillArgs p) {
   constexpr int FEAT = (NMAT == 2) ? 128 : 256;  // output features per tile
   constexpr int WPB = BK * BITS / 32;            // packed words per row per K block (8 or 16)
+  constexpr int KPS = 32 / WPB;                  // K blocks covered by one W stage (4 or 2)
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* a_st = smem;
   unsigned char* b_st = smem + STAGES * A_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES));
-  // bars: full[4], empty[4], tmem_full[2], tmem_empty[2], then tmem base + abort flag
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
-  float* colscale = reinterpret_cast<float*>(smem + STAGES * (A_BYTES + B_BYTES) + 256);  // [CS_BUFS][NCOL]
+  unsigned char* w_st = b_st + STAGES * B_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + RING_BYTES);
+  // bars: full[4], empty[4], tmem_full[2], tmem_empty[2], w_full[2], w_empty[2], then tmem base + abort flag
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
+  float* colscale = reinterpret_cast<float*>(smem + RING_BYTES + 256);  // [CS_BUFS][NCOL]
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (4 + s); };
   auto tfull_bar = [&](int a) { return bar0 + 8u * (8 + a); };
   auto tempty_bar = [&](int a) { return bar0 + 8u * (10 + a); };
+  auto wfull_bar = [&](int s) { return bar0 + 8u * (12 + s); };
+  auto wempty_bar = [&](int s) { return bar0 + 8u * (14 + s); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int KB = p.K / BK;
   const int n_col_tiles = p.N / FEAT;
-  const int wrow = p.K * BITS / 32;  // packed words per weight row
   const int G = p.K / 64;
 
   if (tid == 0) {
@@ -221,6 +230,10 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, PrefillArgs p)
     for (int a = 0; a < ACC_STAGES; ++a) {
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), N_EPI);
+    }
+    for (int w = 0; w < W_STAGES; ++w) {
+      mbar_init(wfull_bar(w), 1);
+      mbar_init(wempty_bar(w), N_DEQ);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -331,38 +344,87 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, PrefillArgs p)
     const int fcol = (NMAT == 2) ? (col & 127) : col;
     const uint32_t sw = (uint32_t)(col & 7);
     const uint32_t row_off = (uint32_t)(col >> 3) * 1024u + (uint32_t)(col & 7) * 128u;
-    int s = 0, phase = 0, tcount = 0;
+    int s = 0, phase = 0, tcount = 0, ws = 0, wphase = 0;
     constexpr float kQmax = (BITS == 4) ? 15.f : 255.f;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
       const int rt = tile / n_col_tiles, ct = tile % n_col_tiles;
       const int e = (int)p.tile_expert[rt];
       const size_t wr = (size_t)e * p.N + (size_t)ct * FEAT + fcol;
-      const uint32_t* wp = p.w[mt] + wr * wrow;
       const unsigned short* sp = static_cast<const unsigned short*>(p.scales[mt]) + wr * G;
       const unsigned short* bp = static_cast<const unsigned short*>(p.biases[mt]) + wr * G;
       // power-of-two normalisation of this weight row for fp16: largest |w_hat| lands in [2^13, 2^14)
+      // (all loads of the row's scales and biases are issued before the first use: one round trip)
       float mx = 0.f;
-      for (int g = 0; g < G; ++g)
-        mx = fmaxf(mx, fabsf(bf16_bits_to_f32(__ldg(bp + g))) + kQmax * fabsf(bf16_bits_to_f32(__ldg(sp + g))));
+      if ((G & 7) == 0) {
+        for (int g0 = 0; g0 < G; g0 += 32) {
+          uint4 sv[4], bv[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const bool ok = g0 + 8 * q < G;
+            sv[q] = ok ? __ldg(reinterpret_cast<const uint4*>(sp + g0) + q) : make_uint4(0, 0, 0, 0);
+            bv[q] = ok ? __ldg(reinterpret_cast<const uint4*>(bp + g0) + q) : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t su[4] = {sv[q].x, sv[q].y, sv[q].z, sv[q].w}, bu[4] = {bv[q].x, bv[q].y, bv[q].z, bv[q].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              mx = fmaxf(mx, fabsf(__uint_as_float(bu[j] << 16)) + kQmax * fabsf(__uint_as_float(su[j] << 16)));
+              mx = fmaxf(mx, fabsf(__uint_as_float(bu[j] & 0xffff0000u)) + kQmax * fabsf(__uint_as_float(su[j] & 0xffff0000u)));
+            }
+          }
+        }
+      } else {
+#pragma unroll 4
+        for (int g = 0; g < G; ++g)
+          mx = fmaxf(mx, fabsf(bf16_bits_to_f32(__ldg(bp + g))) + kQmax * fabsf(bf16_bits_to_f32(__ldg(sp + g))));
+      }
+      // pull the first lines of the next tile's weight row, scales and biases into L2 meanwhile
+      {
+        const int ntile = tile + gridDim.x;
+        if (ntile < total_tiles) {
+          const int nrt = ntile / n_col_tiles, nct = ntile % n_col_tiles;
+          const size_t nwr = (size_t)p.tile_expert[nrt] * p.N + (size_t)nct * FEAT + fcol;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const unsigned short*>(p.scales[mt]) + nwr * G));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const unsigned short*>(p.biases[mt]) + nwr * G));
+        }
+      }
       int ex = (mx > 0.f && mx < 3.0e38f) ? (ilogbf(mx) - 13) : 0;
       ex = max(-100, min(100, ex));
       const float down_f = ldexpf(1.0f, -ex);
       colscale[(tcount % CS_BUFS) * NCOL + col] = ldexpf(1.0f, ex);
-      uint4 nx[WPB / 4];
-#pragma unroll
-      for (int q = 0; q < WPB / 4; ++q) nx[q] = ldg_nc_v4(wp + 4 * q);
-      unsigned short ns = __ldg(sp), nb = __ldg(bp);
+      // scale / bias: four K blocks' worth per 8-byte load, fetched one chunk ahead
+      const bool sb_vec = (G & 3) == 0;
+      uint2 s_cur = make_uint2(0, 0), b_cur = s_cur, s_nxt = s_cur, b_nxt = s_cur;
+      if (sb_vec) {
+        s_nxt = __ldg(reinterpret_cast<const uint2*>(sp));
+        b_nxt = __ldg(reinterpret_cast<const uint2*>(bp));
+      }
+      const int bx = col >> 7, rr = col & 127;
+      const uint32_t w_row_off = (uint32_t)bx * 16384u + (uint32_t)(rr >> 3) * 1024u + (uint32_t)(rr & 7) * 128u;
       bool dead = false;
       for (int kb = 0; kb < KB; ++kb) {
-        uint4 cur[WPB / 4];
-#pragma unroll
-        for (int q = 0; q < WPB / 4; ++q) cur[q] = nx[q];
-        const unsigned short cs = ns, cb = nb;
-        if (kb + 1 < KB) {
-#pragma unroll
-          for (int q = 0; q < WPB / 4; ++q) nx[q] = ldg_nc_v4(wp + (size_t)(kb + 1) * WPB + 4 * q);
-          ns = __ldg(sp + kb + 1);
-          nb = __ldg(bp + kb + 1);
+        const int kin = kb % KPS;
+        if (kin == 0 && !mbar_wait(wfull_bar(ws), wphase, abort_flag)) {
+          dead = true;
+          break;
+        }
+        unsigned short cs, cb;
+        if (sb_vec) {
+          if ((kb & 3) == 0) {
+            s_cur = s_nxt;
+            b_cur = b_nxt;
+            if (kb + 4 < G) {
+              s_nxt = __ldg(reinterpret_cast<const uint2*>(sp + kb + 4));
+              b_nxt = __ldg(reinterpret_cast<const uint2*>(bp + kb + 4));
+            }
+          }
+          const uint32_t sw2 = (kb & 2) ? s_cur.y : s_cur.x, bw2 = (kb & 2) ? b_cur.y : b_cur.x;
+          cs = (unsigned short)((kb & 1) ? (sw2 >> 16) : (sw2 & 0xffffu));
+          cb = (unsigned short)((kb & 1) ? (bw2 >> 16) : (bw2 & 0xffffu));
+        } else {
+          cs = __ldg(sp + kb);
+          cb = __ldg(bp + kb);
         }
         if (!mbar_wait(empty_bar(s), phase ^ 1, abort_flag)) {
           dead = true;
@@ -370,6 +432,11 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, PrefillArgs p)
         }
         const __half2 s2 = __float2half2_rn(bf16_bits_to_f32(cs) * down_f);
         const __half2 b2 = __float2half2_rn(bf16_bits_to_f32(cb) * down_f);
+        const unsigned char* wsrc = w_st + (size_t)ws * W_BYTES + w_row_off;
+        uint4 cur[WPB / 4];
+#pragma unroll
+        for (int q = 0; q < WPB / 4; ++q)
+          cur[q] = *reinterpret_cast<const uint4*>(wsrc + (((uint32_t)(kin * (WPB / 4) + q) ^ sw) << 4));
         unsigned char* dst = b_st + (size_t)s * B_BYTES + row_off;
         const uint32_t* cw = &cur[0].x;
 #pragma unroll
@@ -386,6 +453,13 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, PrefillArgs p)
         if (++s == STAGES) {
           s = 0;
           phase ^= 1;
+        }
+        if (kin == KPS - 1 || kb == KB - 1) {  // this thread is done with the W stage
+          mbar_arrive(wempty_bar(ws));
+          if (++ws == W_STAGES) {
+            ws = 0;
+            wphase ^= 1;
+          }
         }
       }
       if (dead) break;
@@ -413,7 +487,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, PrefillArgs p)
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp == 13) {
     // ------------------------------- MMA issuer ----------------------------------------------
     if (lane == 0) {
       int s = 0, phase = 0, acc = 0, acc_phase = 0;
@@ -443,6 +517,37 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, PrefillArgs p)
         if (++acc == ACC_STAGES) {
           acc = 0;
           acc_phase ^= 1;
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------- TMA producer (packed weights) ---------------------------
+    if (lane == 0) {
+      int ws = 0, wphase = 0;
+      bool dead = false;
+      const int n_wst = (KB + KPS - 1) / KPS;
+      for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
+        const int rt = tile / n_col_tiles, ct = tile % n_col_tiles;
+        const int row_base = (int)p.tile_expert[rt] * p.N + ct * FEAT;
+        for (int wk = 0; wk < n_wst; ++wk) {
+          if (!mbar_wait(wempty_bar(ws), wphase ^ 1, abort_flag)) {
+            dead = true;
+            break;
+          }
+          mbar_arrive_expect_tx(wfull_bar(ws), W_BYTES);
+          const uint32_t dst = smem_u32(w_st + (size_t)ws * W_BYTES);
+          if constexpr (NMAT == 2) {
+            tma_load_2d(dst, &tmap_w0, wfull_bar(ws), wk * 32, row_base);
+            tma_load_2d(dst + 16384, &tmap_w1, wfull_bar(ws), wk * 32, row_base);
+          } else {
+            tma_load_2d(dst, &tmap_w0, wfull_bar(ws), wk * 32, row_base);
+            tma_load_2d(dst + 16384, &tmap_w0, wfull_bar(ws), wk * 32, row_base + 128);
+          }
+          if (++ws == W_STAGES) {
+            ws = 0;
+            wphase ^= 1;
+          }
         }
       }
     }
@@ -591,6 +696,18 @@ int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   B200_REQUIRE(cr == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed (the activation buffer must be 16-byte aligned)");
+  // packed weights as [E*N rows, K*bits/32 words] uint32; one box = 128 rows x 128 bytes
+  CUtensorMap tmap_w[2];
+  for (int i = 0; i < nmat; ++i) {
+    cuuint64_t wd[2] = {(cuuint64_t)g.K * bits / 32, (cuuint64_t)E * g.N};
+    cuuint64_t ws_[1] = {(cuuint64_t)g.K * bits / 8};
+    cuuint32_t wb[2] = {32, 128};
+    cr = enc(&tmap_w[i], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(g.w[i]), wd, ws_, wb, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    B200_REQUIRE(cr == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed for the packed weights (16-byte alignment required)");
+  }
+  if (nmat == 1) tmap_w[1] = tmap_w[0];
 
   PrefillArgs p{};
   for (int i = 0; i < 2; ++i) {
@@ -630,7 +747,7 @@ int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows,
       B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));         \
       attr = true;                                                                                            \
     }                                                                                                         \
-    kern<<<grid, N_THREADS, SMEM_BYTES, st>>>(tmap, p);                                                       \
+    kern<<<grid, N_THREADS, SMEM_BYTES, st>>>(tmap, tmap_w[0], tmap_w[1], p);                                                       \
   } while (0)
   if (bits == 4 && nmat == 2)
     B200_TC_LAUNCH(4, 2);
