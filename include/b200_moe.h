@@ -159,6 +159,13 @@ int b200_argpartition_axis(b200_ctx* ctx, const void* a, int64_t rows, int64_t c
 int b200_take_along_axis(b200_ctx* ctx, const void* a, int64_t rows, int64_t cols, const uint32_t* indices, int64_t icols,
                          void* out, void* stream);
 
+/* take_axis(x, indices / div, 0) for rows of bf16: out[p, :] = x[indices[p] / div, :]
+ * (take_axis, mlx-rs/src/ops/indexing/mod.rs:374-401, composed with floor_divide,
+ * mlx-rs/src/ops/arithmetic.rs:401 - the "x[order // k]" step of the token sort).
+ * x [x_rows, cols], indices [n_rows], cols a multiple of 8. */
+int b200_take_rows(b200_ctx* ctx, const void* x, const uint32_t* indices, uint32_t div, int64_t n_rows, int64_t x_rows,
+                   int64_t cols, void* out, void* stream);
+
 /* fast::rms_norm(x, weight, eps); mlx-rs/src/fast.rs:178-205.  bf16 [rows, cols]; weight
  * bf16 [cols] or NULL for ones. */
 int b200_rms_norm(b200_ctx* ctx, const void* x, const void* weight, float eps, int64_t rows, int64_t cols, void* out,
@@ -199,6 +206,14 @@ int b200_moe_permute(b200_ctx* ctx, const uint32_t* indices, int64_t n, int n_ex
  * race on it, so serialise them.  Expert indices >= n_experts are skipped, not reported. */
 int b200_moe_permute_static(const uint32_t* indices, int64_t n, int n_experts, uint32_t* perm, uint32_t* inv_perm,
                             uint32_t* counts, uint32_t* offsets, void* stream);
+
+/* Weighted un-sort and combine of expert outputs held in sorted order (the return path of the
+ * expert-parallel exchange): out[t, :] = bf16( sum_j scores[t, j] * y_sorted[inv_perm[t*k + j], :] )
+ * in float32, j ascending (take with the inverse order + multiply + sum_axis(-2),
+ * mlx-rs/src/ops/reduction.rs:260-275).  y_sorted bf16 [T*k, hidden]; out_f32 (optional) receives
+ * the sum before rounding. */
+int b200_moe_combine(b200_ctx* ctx, const void* y_sorted, const uint32_t* inv_perm, const void* scores, int64_t T,
+                     int top_k, int64_t hidden, void* out, float* out_f32, void* stream);
 
 /* SwitchGLU forward: (x bf16 [T, H], indices [T, k]) -> out bf16 [T, k, H],
  * out[t, j] = down_e( silu(gate_e(x_t)) * up_e(x_t) ), e = indices[t, j]. */

@@ -363,6 +363,27 @@ int b200_take_along_axis(b200_ctx* c, const void* a, int64_t rows, int64_t cols,
   return 0;
 }
 
+int b200_take_rows(b200_ctx* c, const void* x, const uint32_t* indices, uint32_t div, int64_t n_rows, int64_t x_rows,
+                   int64_t cols, void* out, void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(div >= 1, "div must be at least 1");
+  B200_REQUIRE(n_rows >= 0 && x_rows >= 0 && cols > 0 && cols % 8 == 0, "cols must be a positive multiple of 8");
+  B200_REQUIRE(n_rows == 0 || (x && indices && out), "null tensor");
+  launch_take_rows(x, indices, div, n_rows, x_rows, cols, out, c->err, static_cast<cudaStream_t>(stream));
+  LAUNCHED(c, n_rows ? 1 : 0);
+  return 0;
+}
+
+int b200_moe_combine(b200_ctx* c, const void* y_sorted, const uint32_t* inv_perm, const void* scores, int64_t T, int top_k,
+                     int64_t hidden, void* out, float* out_f32, void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(T >= 0 && top_k > 0 && hidden > 0 && hidden % 4 == 0, "bad shape");
+  B200_REQUIRE(T == 0 || (y_sorted && inv_perm && scores && out), "null tensor");
+  launch_gather_combine(y_sorted, inv_perm, scores, T, top_k, hidden, out, out_f32, static_cast<cudaStream_t>(stream));
+  LAUNCHED(c, T ? 1 : 0);
+  return 0;
+}
+
 int b200_rms_norm(b200_ctx* c, const void* x, const void* weight, float eps, int64_t rows, int64_t cols, void* out,
                   void* stream) {
   CTX_ENTER(c);

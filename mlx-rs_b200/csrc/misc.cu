@@ -142,6 +142,68 @@ int launch_combine(const void* yk, int64_t T, int k, int64_t H, void* out, void*
   return 0;
 }
 
+// take_axis(x, indices / div, axis=0) for rows of 2-byte elements (mlx-rs/src/ops/indexing/mod.rs:374-401
+// composed with floor_divide, mlx-rs/src/ops/arithmetic.rs:401): out[p, :] = x[indices[p] / div, :].
+__global__ void take_rows_kernel(const uint4* __restrict__ x, const uint32_t* __restrict__ indices, uint32_t div,
+                                 int64_t n_rows, int64_t x_rows, int vec_per_row, uint4* __restrict__ out,
+                                 int* __restrict__ err) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_rows * vec_per_row) return;
+  const int64_t r = i / vec_per_row;
+  const int c = (int)(i % vec_per_row);
+  const uint32_t src = indices[r] / div;
+  if (src >= x_rows) {
+    *err = 1;
+    out[i] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  out[i] = __ldg(x + (size_t)src * vec_per_row + c);
+}
+
+int launch_take_rows(const void* x, const uint32_t* indices, uint32_t div, int64_t n_rows, int64_t x_rows, int64_t cols,
+                     void* out, int* err, cudaStream_t st) {
+  if (n_rows == 0) return 0;
+  int64_t n = n_rows * (cols / 8);
+  take_rows_kernel<<<cdiv(n, 256), 256, 0, st>>>(static_cast<const uint4*>(x), indices, div, n_rows, x_rows,
+                                                 (int)(cols / 8), static_cast<uint4*>(out), err);
+  return 0;
+}
+
+// Weighted un-sort + combine for expert outputs that arrive as bf16 rows in sorted order
+// (expert-parallel return path): out[t, :] = bf16( sum_j score[t, j] * y[inv[t*k + j], :] ),
+// float32 accumulation, j ascending (take with the inverse order, multiply, sum_axis(-2)).
+__global__ void gather_combine_kernel(const uint2* __restrict__ y, const uint32_t* __restrict__ inv,
+                                      const unsigned short* __restrict__ scores, int64_t T, int k, int64_t H4,
+                                      uint2* __restrict__ out, float4* __restrict__ out_f32) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * H4) return;
+  const int64_t t = i / H4, c = i % H4;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int j = 0; j < k; ++j) {
+    const float s = bf16_bits_to_f32(scores[t * k + j]);
+    const uint2 v = __ldg(&y[(size_t)inv[t * k + j] * H4 + c]);
+    acc.x += s * __uint_as_float(v.x << 16);
+    acc.y += s * __uint_as_float(v.x & 0xffff0000u);
+    acc.z += s * __uint_as_float(v.y << 16);
+    acc.w += s * __uint_as_float(v.y & 0xffff0000u);
+  }
+  uint2 o;
+  o.x = f32_to_bf16_bits(acc.x) | (f32_to_bf16_bits(acc.y) << 16);
+  o.y = f32_to_bf16_bits(acc.z) | (f32_to_bf16_bits(acc.w) << 16);
+  out[i] = o;
+  if (out_f32) out_f32[i] = acc;
+}
+
+int launch_gather_combine(const void* y, const uint32_t* inv, const void* scores, int64_t T, int k, int64_t H, void* out,
+                          void* out_f32, cudaStream_t st) {
+  if (T == 0) return 0;
+  int64_t n = T * (H / 4);
+  gather_combine_kernel<<<cdiv(n, 256), 256, 0, st>>>(static_cast<const uint2*>(y), inv,
+                                                      static_cast<const unsigned short*>(scores), T, k, H / 4,
+                                                      static_cast<uint2*>(out), static_cast<float4*>(out_f32));
+  return 0;
+}
+
 // Residual add + RMSNorm (fast::rms_norm, mlx-rs/src/fast.rs:178-205; residual wiring as in
 // mlx-lm/src/models/qwen3.rs:310-325).  s = bf16(x + residual) is written to sum_out (when
 // given) and the norm is taken over that rounded sum: out = w * s * rsqrt(mean(s^2) + eps).

@@ -192,6 +192,106 @@ __global__ void __launch_bounds__(256) router_logits_warp_kernel(const __nv_bflo
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Large token counts: float64 tensor-core variant.  CTA = 8 warps over TT tokens x 128 experts;
+// a warp owns 32 tokens x TT/2 experts as 8x8 accumulator tiles of mma.sync m8n8k4 (f64), the
+// operands being converted to float64 once per 32-wide K chunk while they are staged in shared
+// memory (row-major, rows padded by 32 bytes so that fragment loads spread over all banks).
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void dmma_884(double (&c)[2], double a, double b) {
+  asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+               : "+d"(c[0]), "+d"(c[1])
+               : "d"(a), "d"(b));
+}
+
+template <int TT>
+__global__ void __launch_bounds__(256) router_logits_dmma_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                 const __nv_bfloat16* __restrict__ w,
+                                                                 const float* __restrict__ logit_bias,
+                                                                 __nv_bfloat16* __restrict__ logits, int T, int H, int E) {
+  constexpr int KC = 32, LD = KC + 4, TE = 128;
+  constexpr int WE = TT / 2;       // experts per warp
+  constexpr int NE = WE / 8;       // expert tiles per warp
+  constexpr int TW = TT / 32;      // warps along tokens
+  extern __shared__ __align__(16) unsigned char dsm[];
+  double* xs = reinterpret_cast<double*>(dsm);  // [TT][LD]
+  double* ws = xs + TT * LD;                     // [TE][LD]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wt = warp % TW, we = warp / TW;
+  const int t0 = blockIdx.x * TT, e0 = blockIdx.y * TE;
+  const int r = lane >> 2, kq = lane & 3;
+
+  double acc[4][NE][2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < NE; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+
+  for (int k0 = 0; k0 < H; k0 += KC) {
+    // stage + convert: one 128-bit load = 8 consecutive k of one row
+    for (int i = tid; i < (TT + TE) * (KC / 8); i += 256) {
+      const int row = i / (KC / 8), c = i % (KC / 8);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (k0 + c * 8 < H) {
+        if (row < TT) {
+          if (t0 + row < T) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + row) * H + k0) + c);
+        } else if (e0 + row - TT < E) {
+          v = __ldg(reinterpret_cast<const uint4*>(w + (size_t)(e0 + row - TT) * H + k0) + c);
+        }
+      }
+      double* d = (row < TT ? xs + row * LD : ws + (row - TT) * LD) + c * 8;
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        d[2 * q] = bf16_bits_to_f64(u[q] & 0xffffu);
+        d[2 * q + 1] = bf16_bits_to_f64(u[q] >> 16);
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < KC; kk += 4) {
+      double a[4], b[NE];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = xs[(wt * 32 + i * 8 + r) * LD + kk + kq];
+#pragma unroll
+      for (int j = 0; j < NE; ++j) b[j] = ws[(we * WE + j * 8 + r) * LD + kk + kq];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < NE; ++j) dmma_884(acc[i][j], a[i], b[j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < NE; ++j)
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int t = t0 + wt * 32 + i * 8 + r, e = e0 + we * WE + j * 8 + kq * 2 + q;
+        if (t < T && e < E) {
+          uint32_t bits = f64_to_bf16_bits(acc[i][j][q]);
+          if (logit_bias) bits = f32_to_bf16_bits(bf16_bits_to_f32(bits) + logit_bias[e]);
+          logits[(size_t)t * E + e] = __ushort_as_bfloat16((unsigned short)bits);
+        }
+      }
+}
+
+template <int TT>
+static int launch_router_dmma(const __nv_bfloat16* xp, const __nv_bfloat16* wp, const float* logit_bias,
+                              __nv_bfloat16* lp, int T, int H, int E, cudaStream_t st) {
+  constexpr size_t smem = sizeof(double) * (TT + 128) * 36;
+  auto kern = router_logits_dmma_kernel<TT>;
+  static bool attr = false;
+  if (!attr) {
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr = true;
+  }
+  dim3 grid(cdiv(T, TT), cdiv(E, 128));
+  kern<<<grid, 256, smem, st>>>(xp, wp, logit_bias, lp, T, H, E);
+  return 0;
+}
+
 template <int TT>
 static int launch_router_warp(const __nv_bfloat16* xp, const __nv_bfloat16* wp, const float* logit_bias,
                               __nv_bfloat16* lp, int T, int H, int E, cudaStream_t st) {
@@ -213,11 +313,16 @@ int launch_router_logits(const void* x, const void* w, const float* logit_bias, 
   auto wp = static_cast<const __nv_bfloat16*>(w);
   auto lp = static_cast<__nv_bfloat16*>(logits);
   static const int force = [] {
-    const char* v = getenv("B200_ROUTER_KERNEL");  // "warp" / "tile": development override
-    return !v ? 0 : (v[0] == 'w' ? 1 : 2);
+    const char* v = getenv("B200_ROUTER_KERNEL");  // "warp" / "tile" / "dmma": development override
+    return !v ? 0 : (v[0] == 'w' ? 1 : (v[0] == 't' ? 2 : 3));
   }();
   const bool warp_ok = (H % 8 == 0) && ((size_t)8 * H * 2 <= 200 * 1024);
-  const bool use_warp = force ? (force == 1 && warp_ok) : (warp_ok && T < 2048);
+  const bool dmma_ok = (H % 8 == 0);
+  if (dmma_ok && (force == 3 || (!force && T >= 1024))) {
+    if (T >= 6144) return launch_router_dmma<64>(xp, wp, logit_bias, lp, T, H, E, st);
+    return launch_router_dmma<32>(xp, wp, logit_bias, lp, T, H, E, st);
+  }
+  const bool use_warp = force ? (force == 1 && warp_ok) : warp_ok;
   if (use_warp) {
     if (T <= 4) return launch_router_warp<1>(xp, wp, logit_bias, lp, T, H, E, st);
     return launch_router_warp<8>(xp, wp, logit_bias, lp, T, H, E, st);

@@ -155,6 +155,28 @@ def moe_permute(indices, n_experts, ctx=None):
     return perm, inv, counts, offsets
 
 
+def take_rows(x, indices, div=1, ctx=None):
+    """take_axis(x, indices // div, axis=0) for a 2-D bf16 tensor -> [len(indices), cols]."""
+    _cuda(x, indices)
+    _req(x.dim() == 2 and x.element_size() == 2, "take_rows: 2-D tensor of 2-byte elements")
+    out = torch.empty((indices.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    L.check(L.lib().b200_take_rows(_ctx(ctx), L.ptr(x), L.ptr(indices), int(div), indices.numel(), x.shape[0], x.shape[1],
+                                   L.ptr(out), L.stream_ptr()))
+    return out
+
+
+def moe_combine(y_sorted, inv_perm, scores, return_f32=False, ctx=None):
+    """out[t] = sum_j scores[t, j] * y_sorted[inv_perm[t*k + j]] (float32 accumulation) -> bf16 [T, H]."""
+    _cuda(y_sorted, inv_perm, scores)
+    T, k = scores.shape
+    H = y_sorted.shape[-1]
+    out = torch.empty((T, H), dtype=torch.bfloat16, device=y_sorted.device)
+    o32 = torch.empty((T, H), dtype=torch.float32, device=y_sorted.device) if return_f32 else None
+    L.check(L.lib().b200_moe_combine(_ctx(ctx), L.ptr(y_sorted), L.ptr(inv_perm), L.ptr(scores), T, k, H, L.ptr(out),
+                                     L.ptr(o32), L.stream_ptr()))
+    return (out, o32) if return_f32 else out
+
+
 def moe_permute_static(indices, n_experts):
     """moe_permute without any device allocation by the library (no context either): the scratch is
     a fixed array inside libb200moe.so.  For callers whose memory pool owns the whole device or whose

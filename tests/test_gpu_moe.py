@@ -145,7 +145,7 @@ def test_router_large_bit_exact(pkg, O):
     rng = np.random.default_rng(5)
     H, E, k = 2048, 128, 8
     wr = O.round_bf16((rng.standard_normal((E, H)) * 0.02).astype(np.float32))
-    for T in (3, 100, 1000):
+    for T in (3, 100, 1000, 1500, 6200):
         x = O.round_bf16(rng.standard_normal((T, H)).astype(np.float32))
         ridx, rsc, rlg = O.router(x, wr, k, return_logits=True)
         idx, sc, lg = pkg.nn.router_topk(bf16_cuda(x), bf16_cuda(wr), k, return_logits=True)
