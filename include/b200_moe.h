@@ -110,6 +110,11 @@ int64_t b200_ctx_launch_count(const b200_ctx* ctx);
  * still falls back when the shape does not allow it). */
 enum { B200_QMM_AUTO = 0, B200_QMM_SMALL = 1, B200_QMM_TENSOR_CORE = 2 };
 int b200_ctx_set_qmm_path(b200_ctx* ctx, int path);
+/* Diagnostic: synchronises the device and copies the first n (<= 64) 32-bit words of the
+ * context's status buffer to HOST memory.  Word 0 is the status b200_ctx_check reports; words
+ * 16.. hold the tensor-core kernel's self-timing (kilo-cycles per role and wait) when the
+ * environment variable B200_TC_DEBUG has bit 5 set. */
+int b200_ctx_debug_words(b200_ctx* ctx, int32_t* host_out, int n);
 #define B200_N_STAGES 6
 int b200_ctx_set_profiling(b200_ctx* ctx, int enable);
 int b200_ctx_stage_ms(b200_ctx* ctx, float* ms, int n);

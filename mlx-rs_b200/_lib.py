@@ -39,6 +39,7 @@ EXPORTS = {
     "b200_ctx_reserve": (C.c_int, [C.c_void_p, C.POINTER(MoeConfig), C.c_int64]),
     "b200_ctx_check": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200_ctx_launch_count": (C.c_int64, [C.c_void_p]),
+    "b200_ctx_debug_words": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int]),
     "b200_ctx_set_qmm_path": (C.c_int, [C.c_void_p, C.c_int]),
     "b200_ctx_set_profiling": (C.c_int, [C.c_void_p, C.c_int]),
     "b200_ctx_stage_ms": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.c_int]),
@@ -134,6 +135,11 @@ class Context:
         check(lib().b200_ctx_check(self._h, stream_ptr()))
 
     STAGES = ("router_logits", "route_topk", "permute", "gate_up", "down", "combine")
+
+    def debug_words(self, n=64):
+        buf = (C.c_int32 * n)()
+        check(lib().b200_ctx_debug_words(self._h, buf, n))
+        return list(buf)
 
     QMM_AUTO, QMM_SMALL, QMM_TENSOR_CORE = 0, 1, 2
 

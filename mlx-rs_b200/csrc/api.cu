@@ -176,6 +176,14 @@ int b200_ctx_check(b200_ctx* c, void* stream) {
 
 int64_t b200_ctx_launch_count(const b200_ctx* c) { return c ? c->launches : 0; }
 
+int b200_ctx_debug_words(b200_ctx* c, int32_t* host_out, int n) {
+  CTX_ENTER(c);
+  B200_REQUIRE(host_out != nullptr && n > 0 && n <= 64, "n must be in 1..64");
+  B200_CUDA(cudaDeviceSynchronize());
+  B200_CUDA(cudaMemcpy(host_out, c->err, sizeof(int32_t) * n, cudaMemcpyDeviceToHost));
+  return 0;
+}
+
 int b200_ctx_set_qmm_path(b200_ctx* c, int path) {
   CTX_ENTER(c);
   B200_REQUIRE(path == B200_QMM_AUTO || path == B200_QMM_SMALL || path == B200_QMM_TENSOR_CORE, "unknown path");

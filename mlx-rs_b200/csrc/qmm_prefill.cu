@@ -37,6 +37,8 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -45,15 +47,16 @@ namespace b200 {
 namespace {
 
 constexpr int BM = 128, BK = 64, NCOL = 256;
-constexpr int STAGES = 3, ACC_STAGES = 2, W_STAGES = 2;
+constexpr int A_STAGES = 4, STAGES = 2, ACC_STAGES = 2, W_STAGES = 2;  // STAGES = dequantised-B stages
 constexpr int A_BYTES = BM * BK * 2;      // 16 KB
 constexpr int B_BYTES = NCOL * BK * 2;    // 32 KB
 constexpr int N_EPI = 128, N_DEQ = 256;
 constexpr int W_BYTES = NCOL * 128;       // 32 KB: 128 packed bytes of each of the 256 weight rows
 constexpr int N_THREADS = N_EPI + N_DEQ + 96;  // + TMA(A) warp + MMA warp + TMA(W) warp
 constexpr int CS_BUFS = 4;                // column-scale buffers (tiles in flight between dequantisation and epilogue)
-constexpr int RING_BYTES = STAGES * (A_BYTES + B_BYTES) + W_STAGES * W_BYTES;
-constexpr int SMEM_BYTES = 1024 + RING_BYTES + 256 + CS_BUFS * NCOL * 4;
+constexpr int RING_BYTES = A_STAGES * A_BYTES + STAGES * B_BYTES + W_STAGES * W_BYTES;
+constexpr int STG_LD = 36;                // floats per staged row: 16-byte aligned, quarter-warps hit distinct banks
+constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512 + CS_BUFS * NCOL * 4 + 4 * 32 * STG_LD * 4;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -71,6 +74,31 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// One arrival per warp: every lane has finished its part (and, where the async proxy will read
+// the data, executed its own proxy fence) before lane 0 signals.  256 individual arrivals on one
+// barrier serialise in shared memory and dominate a K block.
+__device__ __forceinline__ void mbar_arrive_warp(uint32_t bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
+// Self-timing (diagnostic, enabled by bit 5 of PrefillArgs::debug): CTA 0 accumulates the
+// cycles each role spends in each of its waits and writes them to the status buffer.
+struct RoleTimer {
+  long long acc[4] = {0, 0, 0, 0};
+  long long t0 = 0;
+  bool on;
+  __device__ explicit RoleTimer(bool enable) : on(enable) {}
+  __device__ __forceinline__ void start() {
+    if (on) t0 = clock64();
+  }
+  __device__ __forceinline__ void stop(int i) {
+    if (on) acc[i] += clock64() - t0;
+  }
+  __device__ void flush(int* dst) {
+    if (on)
+      for (int i = 0; i < 4; ++i) dst[i] = (int)(acc[i] >> 10);
+  }
+};
 // Bounded wait: false when the abort flag is up or the time limit has passed.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   uint64_t t0 = 0;
@@ -153,6 +181,7 @@ struct PrefillArgs {
   int out_f32;
   int K, N;                     // reduction length, output features per matrix
   int* err;
+  int debug;                    // development: 1 = skip the dequantisation work, 2 = skip the MMAs
 };
 
 // dequantise 8 codes of one 4-bit word -> 16 bytes of fp16 (k order [0,4,1,5,2,6,3,7]).
@@ -202,16 +231,19 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* a_st = smem;
-  unsigned char* b_st = smem + STAGES * A_BYTES;
+  unsigned char* b_st = smem + A_STAGES * A_BYTES;
   unsigned char* w_st = b_st + STAGES * B_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + RING_BYTES);
   // bars: full[4], empty[4], tmem_full[2], tmem_empty[2], w_full[2], w_empty[2], then tmem base + abort flag
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
-  float* colscale = reinterpret_cast<float*>(smem + RING_BYTES + 256);  // [CS_BUFS][NCOL]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 33);
+  float* colscale = reinterpret_cast<float*>(smem + RING_BYTES + 512);  // [CS_BUFS][NCOL]
+  float* stage_buf = colscale + CS_BUFS * NCOL;  // 4 warps x [32][STG_LD]
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (4 + s); };
+  auto afull_bar = [&](int s) { return bar0 + 8u * (16 + s); };
+  auto aempty_bar = [&](int s) { return bar0 + 8u * (24 + s); };
   auto tfull_bar = [&](int a) { return bar0 + 8u * (8 + a); };
   auto tempty_bar = [&](int a) { return bar0 + 8u * (10 + a); };
   auto wfull_bar = [&](int s) { return bar0 + 8u * (12 + s); };
@@ -224,16 +256,20 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), N_DEQ + 1);
+      mbar_init(full_bar(s), N_DEQ / 32);
       mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < A_STAGES; ++s) {
+      mbar_init(afull_bar(s), 1);
+      mbar_init(aempty_bar(s), 1);
     }
     for (int a = 0; a < ACC_STAGES; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), N_EPI);
+      mbar_init(tempty_bar(a), N_EPI / 32);
     }
     for (int w = 0; w < W_STAGES; ++w) {
       mbar_init(wfull_bar(w), 1);
-      mbar_init(wempty_bar(w), N_DEQ);
+      mbar_init(wempty_bar(w), N_DEQ / 32);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -250,51 +286,78 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 
   if (warp < 4) {
     // ------------------------------- epilogue -------------------------------------------
+    // A thread owns one accumulator row (its TMEM lane).  Results go through a per-warp staging
+    // buffer (32 rows x 32 columns, float32) so that global stores are coalesced: a store
+    // instruction then covers whole 64/128-byte row segments instead of 32 different lines.
     int acc = 0, acc_phase = 0, tcount = 0;
+    RoleTimer tm((p.debug & 32) && blockIdx.x == 0 && tid == 0);
+    const long long t_begin = clock64();
+    float* stg = stage_buf + warp * (32 * STG_LD);
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
       const int rt = tile / n_col_tiles, ct = tile % n_col_tiles;
       const float* cs = colscale + (tcount % CS_BUFS) * NCOL;
+      tm.start();
       const uint32_t row0 = p.tile_row0[rt];
       const int rows = (int)p.tile_rows[rt];
       const int r = warp * 32 + lane;  // accumulator row = TMEM lane
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) break;
+      tm.stop(0);
+      tm.start();
       tc_fence_after();
       const bool row_ok = r < rows;
       const uint32_t sp = row0 + r;
-      const uint32_t dst = row_ok ? (p.dst_perm ? p.perm[sp] : sp) : 0u;
+      const uint32_t dst = row_ok ? (p.dst_perm ? p.perm[sp] : sp) : 0xffffffffu;  // 0xffffffff: row not stored
       const float ar = row_ok ? p.a_row_scale[sp] : 1.0f;
       const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * NCOL);
       if constexpr (NMAT == 2) {
 #pragma unroll 1
         for (int c = 0; c < 128; c += 32) {
           uint32_t g[32], u[32];
+          tm.stop(3);
+          tm.start();
           tmem_ld32(lane_addr + c, g);
           tmem_ld32(lane_addr + 128 + c, u);
           tmem_ld_wait();
-          if (row_ok) {
-            uint32_t packed[16];
+          tm.stop(1);
+          tm.start();
+          __syncwarp();  // the previous chunk's readers are done with the staging buffer
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              float h[8];
+          for (int i = 0; i < 32; i += 4) {
+            const float4 cg = *reinterpret_cast<const float4*>(cs + c + i);
+            const float4 cu = *reinterpret_cast<const float4*>(cs + 128 + c + i);
+            const float cgs[4] = {cg.x, cg.y, cg.z, cg.w}, cus[4] = {cu.x, cu.y, cu.z, cu.w};
+            float h[4];
 #pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                float gv = __uint_as_float(g[i + q]) * (cs[c + i + q] * ar), uv = __uint_as_float(u[i + q]) * (cs[128 + c + i + q] * ar);
-                h[q] = gv / (1.0f + __expf(-gv)) * uv;
-              }
-              if constexpr (BITS == 4) {  // the consumer (down projection) reads k in [0,4,1,5,2,6,3,7] order
-                packed[i / 2 + 0] = f32_to_bf16_bits(h[0]) | (f32_to_bf16_bits(h[4]) << 16);
-                packed[i / 2 + 1] = f32_to_bf16_bits(h[1]) | (f32_to_bf16_bits(h[5]) << 16);
-                packed[i / 2 + 2] = f32_to_bf16_bits(h[2]) | (f32_to_bf16_bits(h[6]) << 16);
-                packed[i / 2 + 3] = f32_to_bf16_bits(h[3]) | (f32_to_bf16_bits(h[7]) << 16);
-              } else {
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                  packed[i / 2 + q] = f32_to_bf16_bits(h[2 * q]) | (f32_to_bf16_bits(h[2 * q + 1]) << 16);
-              }
+            for (int q = 0; q < 4; ++q) {
+              const float gv = __uint_as_float(g[i + q]) * (cgs[q] * ar), uv = __uint_as_float(u[i + q]) * (cus[q] * ar);
+              h[q] = gv / (1.0f + __expf(-gv)) * uv;
             }
-            uint4* o = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)dst * p.N + ct * FEAT + c);
+            *reinterpret_cast<float4*>(stg + lane * STG_LD + i) = make_float4(h[0], h[1], h[2], h[3]);
+          }
+          __syncwarp();
+          tm.stop(2);
+          tm.start();
+          // 4 lanes per row (8 columns = 16 bytes of bf16 each), 8 rows per store instruction
 #pragma unroll
-            for (int q = 0; q < 4; ++q) o[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+          for (int it = 0; it < 4; ++it) {
+            const int rr = it * 8 + (lane >> 2), cg8 = (lane & 3) * 8;
+            const uint32_t d = __shfl_sync(0xffffffffu, dst, rr);
+            const float4 v0 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8);
+            const float4 v1 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8 + 4);
+            uint4 o;
+            if constexpr (BITS == 4) {  // the consumer (down projection) reads k in [0,4,1,5,2,6,3,7] order
+              o.x = f32_to_bf16_bits(v0.x) | (f32_to_bf16_bits(v1.x) << 16);
+              o.y = f32_to_bf16_bits(v0.y) | (f32_to_bf16_bits(v1.y) << 16);
+              o.z = f32_to_bf16_bits(v0.z) | (f32_to_bf16_bits(v1.z) << 16);
+              o.w = f32_to_bf16_bits(v0.w) | (f32_to_bf16_bits(v1.w) << 16);
+            } else {
+              o.x = f32_to_bf16_bits(v0.x) | (f32_to_bf16_bits(v0.y) << 16);
+              o.y = f32_to_bf16_bits(v0.z) | (f32_to_bf16_bits(v0.w) << 16);
+              o.z = f32_to_bf16_bits(v1.x) | (f32_to_bf16_bits(v1.y) << 16);
+              o.w = f32_to_bf16_bits(v1.z) | (f32_to_bf16_bits(v1.w) << 16);
+            }
+            if (d != 0xffffffffu)
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)d * p.N + ct * FEAT + c + cg8) = o;
           }
         }
       } else {
@@ -306,37 +369,60 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           uint32_t v[32];
           tmem_ld32(lane_addr + c, v);
           tmem_ld_wait();
-          if (row_ok) {
-            if (p.out_f32) {
-              float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.out) + (size_t)dst * p.N + ct * FEAT + c);
+          __syncwarp();
 #pragma unroll
-              for (int q = 0; q < 8; ++q)
-                o[q] = make_float4(__uint_as_float(v[4 * q]) * cs[c + 4 * q] * sc,
-                                   __uint_as_float(v[4 * q + 1]) * cs[c + 4 * q + 1] * sc,
-                                   __uint_as_float(v[4 * q + 2]) * cs[c + 4 * q + 2] * sc,
-                                   __uint_as_float(v[4 * q + 3]) * cs[c + 4 * q + 3] * sc);
-            } else {
-              uint4* o = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)dst * p.N + ct * FEAT + c);
+          for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<float4*>(stg + lane * STG_LD + i) =
+                make_float4(__uint_as_float(v[i]) * sc, __uint_as_float(v[i + 1]) * sc, __uint_as_float(v[i + 2]) * sc,
+                            __uint_as_float(v[i + 3]) * sc);
+          __syncwarp();
+          if (p.out_f32) {
+            // 8 lanes per row (4 columns = 16 bytes each): a 128-byte line per row, 4 rows per instruction
+            const int c4 = (lane & 7) * 4;
+            const float4 cc = *reinterpret_cast<const float4*>(cs + c + c4);
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint32_t w[4];
+            for (int it = 0; it < 8; ++it) {
+              const int rr = it * 4 + (lane >> 3);
+              const uint32_t d = __shfl_sync(0xffffffffu, dst, rr);
+              float4 x4 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + c4);
+              x4.x *= cc.x;
+              x4.y *= cc.y;
+              x4.z *= cc.z;
+              x4.w *= cc.w;
+              if (d != 0xffffffffu)
+                *reinterpret_cast<float4*>(static_cast<float*>(p.out) + (size_t)d * p.N + ct * FEAT + c + c4) = x4;
+            }
+          } else {
+            const int cg8 = (lane & 3) * 8;
+            const float4 c0 = *reinterpret_cast<const float4*>(cs + c + cg8);
+            const float4 c1 = *reinterpret_cast<const float4*>(cs + c + cg8 + 4);
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                  w[j] = f32_to_bf16_bits(__uint_as_float(v[8 * q + 2 * j]) * cs[c + 8 * q + 2 * j] * sc) |
-                         (f32_to_bf16_bits(__uint_as_float(v[8 * q + 2 * j + 1]) * cs[c + 8 * q + 2 * j + 1] * sc) << 16);
-                o[q] = make_uint4(w[0], w[1], w[2], w[3]);
-              }
+            for (int it = 0; it < 4; ++it) {
+              const int rr = it * 8 + (lane >> 2);
+              const uint32_t d = __shfl_sync(0xffffffffu, dst, rr);
+              const float4 v0 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8);
+              const float4 v1 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8 + 4);
+              uint4 o;
+              o.x = f32_to_bf16_bits(v0.x * c0.x) | (f32_to_bf16_bits(v0.y * c0.y) << 16);
+              o.y = f32_to_bf16_bits(v0.z * c0.z) | (f32_to_bf16_bits(v0.w * c0.w) << 16);
+              o.z = f32_to_bf16_bits(v1.x * c1.x) | (f32_to_bf16_bits(v1.y * c1.y) << 16);
+              o.w = f32_to_bf16_bits(v1.z * c1.z) | (f32_to_bf16_bits(v1.w * c1.w) << 16);
+              if (d != 0xffffffffu)
+                *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)d * p.N + ct * FEAT + c + cg8) = o;
             }
           }
         }
       }
       tc_fence_before();
-      mbar_arrive(tempty_bar(acc));
+      mbar_arrive_warp(tempty_bar(acc), lane);
+      tm.stop(3);
       if (++acc == ACC_STAGES) {
         acc = 0;
         acc_phase ^= 1;
       }
     }
+    (void)t_begin;
+    tm.flush(p.err + 16 + (NMAT == 1 ? 24 : 0));
   } else if (warp < 12) {
     // ------------------------------- B dequantisation --------------------------------------
     const int col = tid - N_EPI;  // accumulator column = B tile row, 0..255
@@ -345,6 +431,8 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const uint32_t sw = (uint32_t)(col & 7);
     const uint32_t row_off = (uint32_t)(col >> 3) * 1024u + (uint32_t)(col & 7) * 128u;
     int s = 0, phase = 0, tcount = 0, ws = 0, wphase = 0;
+    RoleTimer tm((p.debug & 32) && blockIdx.x == 0 && tid == N_EPI);
+    const long long t_begin = clock64();
     constexpr float kQmax = (BITS == 4) ? 15.f : 255.f;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
       const int rt = tile / n_col_tiles, ct = tile % n_col_tiles;
@@ -355,20 +443,26 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       // power-of-two normalisation of this weight row for fp16: largest |w_hat| lands in [2^13, 2^14)
       // (all loads of the row's scales and biases are issued before the first use: one round trip)
       float mx = 0.f;
-      if ((G & 7) == 0) {
+      const bool sb_vec = (G & 3) == 0;
+      uint2 s_first = make_uint2(0, 0), b_first = s_first;
+      if (sb_vec) {
         for (int g0 = 0; g0 < G; g0 += 32) {
-          uint4 sv[4], bv[4];
+          uint2 sv[8], bv[8];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const bool ok = g0 + 8 * q < G;
-            sv[q] = ok ? __ldg(reinterpret_cast<const uint4*>(sp + g0) + q) : make_uint4(0, 0, 0, 0);
-            bv[q] = ok ? __ldg(reinterpret_cast<const uint4*>(bp + g0) + q) : make_uint4(0, 0, 0, 0);
+          for (int q = 0; q < 8; ++q) {
+            const bool ok = g0 + 4 * q < G;
+            sv[q] = ok ? __ldg(reinterpret_cast<const uint2*>(sp + g0) + q) : make_uint2(0, 0);
+            bv[q] = ok ? __ldg(reinterpret_cast<const uint2*>(bp + g0) + q) : make_uint2(0, 0);
+          }
+          if (g0 == 0) {
+            s_first = sv[0];
+            b_first = bv[0];
           }
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint32_t su[4] = {sv[q].x, sv[q].y, sv[q].z, sv[q].w}, bu[4] = {bv[q].x, bv[q].y, bv[q].z, bv[q].w};
+          for (int q = 0; q < 8; ++q) {
+            const uint32_t su[2] = {sv[q].x, sv[q].y}, bu[2] = {bv[q].x, bv[q].y};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < 2; ++j) {
               mx = fmaxf(mx, fabsf(__uint_as_float(bu[j] << 16)) + kQmax * fabsf(__uint_as_float(su[j] << 16)));
               mx = fmaxf(mx, fabsf(__uint_as_float(bu[j] & 0xffff0000u)) + kQmax * fabsf(__uint_as_float(su[j] & 0xffff0000u)));
             }
@@ -394,21 +488,18 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       const float down_f = ldexpf(1.0f, -ex);
       colscale[(tcount % CS_BUFS) * NCOL + col] = ldexpf(1.0f, ex);
       // scale / bias: four K blocks' worth per 8-byte load, fetched one chunk ahead
-      const bool sb_vec = (G & 3) == 0;
-      uint2 s_cur = make_uint2(0, 0), b_cur = s_cur, s_nxt = s_cur, b_nxt = s_cur;
-      if (sb_vec) {
-        s_nxt = __ldg(reinterpret_cast<const uint2*>(sp));
-        b_nxt = __ldg(reinterpret_cast<const uint2*>(bp));
-      }
+      uint2 s_cur = make_uint2(0, 0), b_cur = s_cur, s_nxt = s_first, b_nxt = b_first;
       const int bx = col >> 7, rr = col & 127;
       const uint32_t w_row_off = (uint32_t)bx * 16384u + (uint32_t)(rr >> 3) * 1024u + (uint32_t)(rr & 7) * 128u;
       bool dead = false;
       for (int kb = 0; kb < KB; ++kb) {
         const int kin = kb % KPS;
+        tm.start();
         if (kin == 0 && !mbar_wait(wfull_bar(ws), wphase, abort_flag)) {
           dead = true;
           break;
         }
+        tm.stop(0);
         unsigned short cs, cb;
         if (sb_vec) {
           if ((kb & 3) == 0) {
@@ -426,9 +517,27 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           cs = __ldg(sp + kb);
           cb = __ldg(bp + kb);
         }
+        tm.start();
         if (!mbar_wait(empty_bar(s), phase ^ 1, abort_flag)) {
           dead = true;
           break;
+        }
+        tm.stop(0);
+        tm.start();
+        if (p.debug & 1) {
+          mbar_arrive_warp(full_bar(s), lane);
+          if (++s == STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
+          if (kin == KPS - 1 || kb == KB - 1) {
+            mbar_arrive_warp(wempty_bar(ws), lane);
+            if (++ws == W_STAGES) {
+              ws = 0;
+              wphase ^= 1;
+            }
+          }
+          continue;
         }
         const __half2 s2 = __float2half2_rn(bf16_bits_to_f32(cs) * down_f);
         const __half2 b2 = __float2half2_rn(bf16_bits_to_f32(cb) * down_f);
@@ -448,68 +557,97 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             o = deq_word8(cw[2 * c], cw[2 * c + 1], s2, b2);
           *reinterpret_cast<uint4*>(dst + (((uint32_t)c ^ sw) << 4)) = o;
         }
+        tm.stop(1);
+        tm.start();
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive(full_bar(s));
+        mbar_arrive_warp(full_bar(s), lane);
         if (++s == STAGES) {
           s = 0;
           phase ^= 1;
         }
-        if (kin == KPS - 1 || kb == KB - 1) {  // this thread is done with the W stage
-          mbar_arrive(wempty_bar(ws));
+        if (kin == KPS - 1 || kb == KB - 1) {  // this warp is done with the W stage
+          mbar_arrive_warp(wempty_bar(ws), lane);
           if (++ws == W_STAGES) {
             ws = 0;
             wphase ^= 1;
           }
         }
+        tm.stop(2);
       }
       if (dead) break;
     }
+    tm.acc[3] = clock64() - t_begin;
+    tm.flush(p.err + 20 + (NMAT == 1 ? 24 : 0));
   } else if (warp == 12) {
     // ------------------------------- TMA producer (A) ---------------------------------------
     if (lane == 0) {
       int s = 0, phase = 0;
       bool dead = false;
+      RoleTimer tm((p.debug & 32) && blockIdx.x == 0);
+      const long long t_begin = clock64();
       for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
         const int rt = tile / n_col_tiles;
         const int row0 = (int)p.tile_row0[rt];
         for (int kb = 0; kb < KB; ++kb) {
-          if (!mbar_wait(empty_bar(s), phase ^ 1, abort_flag)) {
+          tm.start();
+          if (!mbar_wait(aempty_bar(s), phase ^ 1, abort_flag)) {
             dead = true;
             break;
           }
-          mbar_arrive_expect_tx(full_bar(s), A_BYTES);
-          tma_load_2d(smem_u32(a_st + (size_t)s * A_BYTES), &tmap_a, full_bar(s), kb * BK, row0);
-          if (++s == STAGES) {
+          tm.stop(0);
+          mbar_arrive_expect_tx(afull_bar(s), A_BYTES);
+          tma_load_2d(smem_u32(a_st + (size_t)s * A_BYTES), &tmap_a, afull_bar(s), kb * BK, row0);
+          if (++s == A_STAGES) {
             s = 0;
             phase ^= 1;
           }
         }
       }
+      tm.acc[3] = clock64() - t_begin;
+      tm.flush(p.err + 24 + (NMAT == 1 ? 24 : 0));
     }
     __syncwarp();
   } else if (warp == 13) {
     // ------------------------------- MMA issuer ----------------------------------------------
     if (lane == 0) {
-      int s = 0, phase = 0, acc = 0, acc_phase = 0;
+      int s = 0, phase = 0, sa = 0, aphase = 0, acc = 0, acc_phase = 0;
       bool dead = false;
+      RoleTimer tm((p.debug & 32) && blockIdx.x == 0);
+      const long long t_begin = clock64();
       for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
+        tm.start();
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag)) break;
+        tm.stop(2);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * NCOL);
         for (int kb = 0; kb < KB; ++kb) {
+          tm.start();
+          if (!mbar_wait(afull_bar(sa), aphase, abort_flag)) {
+            dead = true;
+            break;
+          }
+          tm.stop(0);
+          tm.start();
           if (!mbar_wait(full_bar(s), phase, abort_flag)) {
             dead = true;
             break;
           }
+          tm.stop(1);
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(a_st + (size_t)s * A_BYTES), b_addr = smem_u32(b_st + (size_t)s * B_BYTES);
+          const uint32_t a_addr = smem_u32(a_st + (size_t)sa * A_BYTES), b_addr = smem_u32(b_st + (size_t)s * B_BYTES);
+          if (!(p.debug & 2))
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
             umma_bf16(d_tmem, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), (kb | k) ? 1u : 0u);
-          umma_commit(empty_bar(s));  // the stage is free once these MMAs have read it
+          umma_commit(aempty_bar(sa));  // both stages are free once these MMAs have read them
+          umma_commit(empty_bar(s));
           if (++s == STAGES) {
             s = 0;
             phase ^= 1;
+          }
+          if (++sa == A_STAGES) {
+            sa = 0;
+            aphase ^= 1;
           }
         }
         if (dead) break;
@@ -519,6 +657,8 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           acc_phase ^= 1;
         }
       }
+      tm.acc[3] = clock64() - t_begin;
+      tm.flush(p.err + 28 + (NMAT == 1 ? 24 : 0));
     }
     __syncwarp();
   } else {
@@ -527,14 +667,18 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       int ws = 0, wphase = 0;
       bool dead = false;
       const int n_wst = (KB + KPS - 1) / KPS;
+      RoleTimer tm((p.debug & 32) && blockIdx.x == 0);
+      const long long t_begin = clock64();
       for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
         const int rt = tile / n_col_tiles, ct = tile % n_col_tiles;
         const int row_base = (int)p.tile_expert[rt] * p.N + ct * FEAT;
         for (int wk = 0; wk < n_wst; ++wk) {
+          tm.start();
           if (!mbar_wait(wempty_bar(ws), wphase ^ 1, abort_flag)) {
             dead = true;
             break;
           }
+          tm.stop(0);
           mbar_arrive_expect_tx(wfull_bar(ws), W_BYTES);
           const uint32_t dst = smem_u32(w_st + (size_t)ws * W_BYTES);
           if constexpr (NMAT == 2) {
@@ -550,6 +694,8 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
         }
       }
+      tm.acc[3] = clock64() - t_begin;
+      tm.flush(p.err + 32 + (NMAT == 1 ? 24 : 0));
     }
     __syncwarp();
   }
@@ -728,6 +874,10 @@ int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows,
   p.K = g.K;
   p.N = g.N;
   p.err = err;
+  {
+    static const int dbg = [] { const char* v = getenv("B200_TC_DEBUG"); return v ? atoi(v) : 0; }();
+    p.debug = dbg;
+  }
 
   static int n_sm = 0;
   if (!n_sm) {
