@@ -42,54 +42,58 @@ def expert_bytes(H, I, bits, gs=64):
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons through NVML (read-only) in a thread while the timed
+    region runs; falls back to `nvidia-smi -lms` when NVML is not importable."""
+    NAMES = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
-    def __init__(self, device):
-        self.device, self.proc = device, None
+    def __init__(self, device, period_s=0.01):
+        self.device, self.period = device, period_s
+        self.sm, self.reasons, self.max_mhz = [], set(), None
+        self._stop, self._thr, self.proc = None, None, None
+
+    def _run(self, nv, h):
+        while not self._stop.is_set():
+            try:
+                self.sm.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(h) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for bit, name in self.NAMES.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.device)], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+            import threading
+            import pynvml as nv
+            nv.nvmlInit()
+            # NVML enumerates physical GPUs; honour CUDA_VISIBLE_DEVICES when it lists indices
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            idx = self.device
+            if vis and all(v.strip().isdigit() for v in vis.split(",")):
+                idx = int(vis.split(",")[self.device])
+            h = nv.nvmlDeviceGetHandleByIndex(idx)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            self._stop = threading.Event()
+            self._thr = threading.Thread(target=self._run, args=(nv, h), daemon=True)
+            self._thr.start()
+        except Exception:
+            self._thr = None
         return self
 
     def __exit__(self, *a):
-        self.lines = []
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                out, _ = self.proc.communicate(timeout=5)
-            except subprocess.TimeoutExpired:
-                self.proc.kill()
-                out, _ = self.proc.communicate()
-            self.lines = [l for l in out.splitlines() if l.strip()]
+        if self._thr is not None:
+            self._stop.set()
+            self._thr.join(timeout=2)
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for l in self.lines:
-            f = [c.strip() for c in l.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for n, v in zip(names, f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        if not sm:
-            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["unsampled"])
-        # "under load" = samples in the upper half of what was seen (idle samples bracket the region)
-        hi = [s for s in sm if s >= 0.5 * max(sm)]
-        return dict(sm_mhz=statistics.median(hi), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        if not self.sm:
+            return dict(sm_mhz=None, sm_max_mhz=self.max_mhz, reasons=["unsampled"])
+        hi = [s for s in self.sm if s >= 0.5 * max(self.sm)]   # idle samples bracket the region
+        return dict(sm_mhz=statistics.median(hi), sm_max_mhz=self.max_mhz, reasons=sorted(self.reasons),
+                    samples=len(self.sm))
 
 
 def build_block(pkg, torch, seed, shape, device):

@@ -462,14 +462,14 @@ static bool use_tensor_core_path(const b200_ctx* c, const b200_moe_config& cfg, 
   if (!prefill_shape_ok(cfg.hidden, cfg.inter, 2) || !prefill_shape_ok(cfg.inter, cfg.hidden, 1)) return false;
   if (c->qmm_path == B200_QMM_SMALL) return false;
   if (c->qmm_path == B200_QMM_TENSOR_CORE) return true;
-  return n / (max_active > 0 ? max_active : 1) >= 48;
+  return n / (max_active > 0 ? max_active : 1) >= 24;
 }
 
 // Shared tail of switch_glu_forward and moe_block_forward: permute, gate/up, down.
 // `scores` null: unweighted per-assignment outputs go to `yk` ([T*k, H]).
 static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_moe_params& p, const void* x,
                            const uint32_t* idx, const void* scores, int64_t T, void* yk, const b200_moe_aux* aux,
-                           cudaStream_t st) {
+                           cudaStream_t st, bool* yk_is_bf16 = nullptr) {
   const int64_t n = T * cfg.top_k;
   const int E = cfg.n_experts;
   uint32_t* perm = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
@@ -556,7 +556,11 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
   dn.dst_perm = 1;
   dn.row_scale = scores;
   dn.out = yk;
-  dn.out_f32 = scores != nullptr;  // weighted rows stay float32 until the combine; SwitchGlu's own output is bf16
+  // weighted rows stay float32 until the combine (storing them as bf16 halves the traffic of the
+  // tensor-core path's epilogue but triples its error against the 2e-2 bar: measured 0.017 at
+  // T=512); SwitchGlu's own output is bf16
+  dn.out_f32 = scores != nullptr;
+  if (yk_is_bf16) *yk_is_bf16 = !dn.out_f32;
   dn.K = cfg.inter;
   dn.N = cfg.hidden;
   if (tc) {
@@ -620,8 +624,9 @@ int b200_moe_block_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_m
                     nullptr, st);
   c->mark(2, st);
   LAUNCHED(c, 2);
-  if (experts_forward(c, *cfg, *params, x, idx, scores, T, yk, aux, st)) return 1;
-  if (launch_combine(yk, T, cfg->top_k, cfg->hidden, out, aux ? aux->out_f32 : nullptr, st)) return 1;
+  bool yk_bf16 = false;
+  if (experts_forward(c, *cfg, *params, x, idx, scores, T, yk, aux, st, &yk_bf16)) return 1;
+  if (launch_combine(yk, yk_bf16, T, cfg->top_k, cfg->hidden, out, aux ? aux->out_f32 : nullptr, st)) return 1;
   c->mark(6, st);
   c->ev_valid = c->profiling;
   LAUNCHED(c, 1);

@@ -62,7 +62,7 @@ int launch_quantize(const void* w, int is_bf16, int64_t rows, int64_t K, int gs,
                     void* biases, cudaStream_t st);
 int launch_dequantize(const uint32_t* wq, const void* scales, const void* biases, int is_bf16, int64_t rows, int64_t K,
                       int gs, int bits, void* out, cudaStream_t st);
-int launch_combine(const void* yk, int64_t T, int k, int64_t H, void* out, void* out_f32, cudaStream_t st);
+int launch_combine(const void* yk, int yk_bf16, int64_t T, int k, int64_t H, void* out, void* out_f32, cudaStream_t st);
 int launch_take_rows(const void* x, const uint32_t* indices, uint32_t div, int64_t n_rows, int64_t x_rows, int64_t cols,
                      void* out, int* err, cudaStream_t st);
 int launch_gather_combine(const void* y, const uint32_t* inv, const void* scores, int64_t T, int k, int64_t H, void* out,

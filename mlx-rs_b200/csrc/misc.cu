@@ -133,8 +133,37 @@ __global__ void combine_kernel(const float4* __restrict__ yk, int64_t T, int k, 
   if (out_f32) out_f32[i] = acc;  // the sum before its rounding to bf16
 }
 
-int launch_combine(const void* yk, int64_t T, int k, int64_t H, void* out, void* out_f32, cudaStream_t st) {
+// Same sum over bf16 inputs (the tensor-core path stores its weighted rows as bf16 to halve the
+// traffic of its write-bound epilogue).
+__global__ void combine_bf16_kernel(const uint2* __restrict__ yk, int64_t T, int k, int64_t H4, uint2* __restrict__ out,
+                                    float4* __restrict__ out_f32) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * H4) return;
+  const int64_t t = i / H4, c = i % H4;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int j = 0; j < k; ++j) {
+    const uint2 v = __ldg(&yk[(t * k + j) * H4 + c]);
+    acc.x += __uint_as_float(v.x << 16);
+    acc.y += __uint_as_float(v.x & 0xffff0000u);
+    acc.z += __uint_as_float(v.y << 16);
+    acc.w += __uint_as_float(v.y & 0xffff0000u);
+  }
+  uint2 o;
+  o.x = f32_to_bf16_bits(acc.x) | (f32_to_bf16_bits(acc.y) << 16);
+  o.y = f32_to_bf16_bits(acc.z) | (f32_to_bf16_bits(acc.w) << 16);
+  out[i] = o;
+  if (out_f32) out_f32[i] = acc;
+}
+
+int launch_combine(const void* yk, int yk_bf16, int64_t T, int k, int64_t H, void* out, void* out_f32, cudaStream_t st) {
   if (T == 0) return 0;
+  if (yk_bf16) {
+    B200_REQUIRE(H % 4 == 0, "hidden size must be a multiple of 4");
+    int64_t n4 = T * (H / 4);
+    combine_bf16_kernel<<<cdiv(n4, 256), 256, 0, st>>>(static_cast<const uint2*>(yk), T, k, H / 4,
+                                                       static_cast<uint2*>(out), static_cast<float4*>(out_f32));
+    return 0;
+  }
   B200_REQUIRE(H % 4 == 0, "hidden size must be a multiple of 4");
   int64_t n = T * (H / 4);
   combine_kernel<<<cdiv(n, 256), 256, 0, st>>>(static_cast<const float4*>(yk), T, k, H / 4, static_cast<uint2*>(out),

@@ -46,17 +46,19 @@ namespace b200 {
 
 namespace {
 
-constexpr int BM = 128, BK = 64, NCOL = 256;
-constexpr int A_STAGES = 4, STAGES = 2, ACC_STAGES = 2, W_STAGES = 2;  // STAGES = dequantised-B stages
-constexpr int A_BYTES = BM * BK * 2;      // 16 KB
-constexpr int B_BYTES = NCOL * BK * 2;    // 32 KB
-constexpr int N_EPI = 128, N_DEQ = 256;
-constexpr int W_BYTES = NCOL * 128;       // 32 KB: 128 packed bytes of each of the 256 weight rows
-constexpr int N_THREADS = N_EPI + N_DEQ + 96;  // + TMA(A) warp + MMA warp + TMA(W) warp
+constexpr int BM = 128, BMT = 256, BK = 64, NCOL = 256;  // BMT: rows per tile = two 128-row accumulators sharing B
+constexpr int A_STAGES = 3, STAGES = 2, W_STAGES = 2;    // STAGES = dequantised-B stages
+constexpr int A_BYTES = BM * BK * 2;                     // 16 KB per 128-row sub-tile
+constexpr int A_STAGE_BYTES = 2 * A_BYTES;               // both sub-tiles of a K block
+constexpr int B_BYTES = NCOL * BK * 2;                   // 32 KB
+constexpr int W_BYTES = NCOL * 64;                       // 16 KB: 64 packed bytes of each of the 256 weight rows
+constexpr int N_EPI = 256, N_DEQ = 256;
+constexpr int WARP_TMA_A = (N_EPI + N_DEQ) / 32, WARP_MMA = WARP_TMA_A + 1, WARP_TMA_W = WARP_TMA_A + 2;
+constexpr int N_THREADS = N_EPI + N_DEQ + 96;            // + TMA(A) warp + MMA warp + TMA(W) warp
 constexpr int CS_BUFS = 4;                // column-scale buffers (tiles in flight between dequantisation and epilogue)
-constexpr int RING_BYTES = A_STAGES * A_BYTES + STAGES * B_BYTES + W_STAGES * W_BYTES;
-constexpr int STG_LD = 36;                // floats per staged row: 16-byte aligned, quarter-warps hit distinct banks
-constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512 + CS_BUFS * NCOL * 4 + 4 * 32 * STG_LD * 4;
+constexpr int RING_BYTES = A_STAGES * A_STAGE_BYTES + STAGES * B_BYTES + W_STAGES * W_BYTES;
+constexpr int STG_LD = 20;                // floats per staged row (16 + 4): 16-byte aligned, quarter-warps hit distinct banks
+constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512 + CS_BUFS * NCOL * 4 + (N_EPI / 32) * 32 * STG_LD * 4;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -161,6 +163,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -227,27 +238,28 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                       const __grid_constant__ CUtensorMap tmap_w1, PrefillArgs p) {
   constexpr int FEAT = (NMAT == 2) ? 128 : 256;  // output features per tile
   constexpr int WPB = BK * BITS / 32;            // packed words per row per K block (8 or 16)
-  constexpr int KPS = 32 / WPB;                  // K blocks covered by one W stage (4 or 2)
+  constexpr int KPS = 16 / WPB;                  // K blocks covered by one W stage (2 or 1)
+  constexpr int CPK = WPB / 4;                   // 16-byte chunks of a row per K block (2 or 4)
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* a_st = smem;
-  unsigned char* b_st = smem + A_STAGES * A_BYTES;
+  unsigned char* b_st = smem + A_STAGES * A_STAGE_BYTES;
   unsigned char* w_st = b_st + STAGES * B_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + RING_BYTES);
-  // bars: full[4], empty[4], tmem_full[2], tmem_empty[2], w_full[2], w_empty[2], then tmem base + abort flag
+  // bars: b_full[4] 0.., b_empty[4] 4.., tmem_full 8, tmem_empty 9, w_full[2] 12.., w_empty[2] 14..,
+  //       a_full[8] 16.., a_empty[8] 24.., then tmem base + abort flag
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 33);
   float* colscale = reinterpret_cast<float*>(smem + RING_BYTES + 512);  // [CS_BUFS][NCOL]
-  float* stage_buf = colscale + CS_BUFS * NCOL;  // 4 warps x [32][STG_LD]
+  float* stage_buf = colscale + CS_BUFS * NCOL;                          // N_EPI/32 warps x [32][STG_LD]
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (4 + s); };
-  auto afull_bar = [&](int s) { return bar0 + 8u * (16 + s); };
-  auto aempty_bar = [&](int s) { return bar0 + 8u * (24 + s); };
-  auto tfull_bar = [&](int a) { return bar0 + 8u * (8 + a); };
-  auto tempty_bar = [&](int a) { return bar0 + 8u * (10 + a); };
+  const uint32_t tfull_bar = bar0 + 8u * 8, tempty_bar = bar0 + 8u * 9;
   auto wfull_bar = [&](int s) { return bar0 + 8u * (12 + s); };
   auto wempty_bar = [&](int s) { return bar0 + 8u * (14 + s); };
+  auto afull_bar = [&](int s) { return bar0 + 8u * (16 + s); };
+  auto aempty_bar = [&](int s) { return bar0 + 8u * (24 + s); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int KB = p.K / BK;
@@ -263,10 +275,8 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       mbar_init(afull_bar(s), 1);
       mbar_init(aempty_bar(s), 1);
     }
-    for (int a = 0; a < ACC_STAGES; ++a) {
-      mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), N_EPI / 32);
-    }
+    mbar_init(tfull_bar, 1);
+    mbar_init(tempty_bar, N_EPI / 32);
     for (int w = 0; w < W_STAGES; ++w) {
       mbar_init(wfull_bar(w), 1);
       mbar_init(wempty_bar(w), N_DEQ / 32);
@@ -274,7 +284,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 13) {  // whole warp: allocate all 512 tensor-memory columns
+  if (warp == WARP_MMA) {  // whole warp: allocate all 512 tensor-memory columns
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
@@ -284,14 +294,15 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const uint32_t tmem_base = *tmem_slot;
   const int total_tiles = (int)(*p.n_row_tiles) * n_col_tiles;
 
-  if (warp < 4) {
+  if (warp < N_EPI / 32) {
     // ------------------------------- epilogue -------------------------------------------
-    // A thread owns one accumulator row (its TMEM lane).  Results go through a per-warp staging
-    // buffer (32 rows x 32 columns, float32) so that global stores are coalesced: a store
-    // instruction then covers whole 64/128-byte row segments instead of 32 different lines.
-    int acc = 0, acc_phase = 0, tcount = 0;
+    // Warps 0-3 drain accumulator 0 (rows 0..127 of the tile), warps 4-7 accumulator 1 (rows
+    // 128..255); a thread owns one accumulator row (its TMEM lane).  Results pass through a
+    // per-warp staging buffer (32 rows x 16 columns, float32) so that a global store instruction
+    // covers whole row segments instead of 32 different lines.
+    const int sub = warp >> 2, q4 = warp & 3;
+    int tphase = 0, tcount = 0;
     RoleTimer tm((p.debug & 32) && blockIdx.x == 0 && tid == 0);
-    const long long t_begin = clock64();
     float* stg = stage_buf + warp * (32 * STG_LD);
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
       const int rt = tile / n_col_tiles, ct = tile % n_col_tiles;
@@ -299,141 +310,142 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       tm.start();
       const uint32_t row0 = p.tile_row0[rt];
       const int rows = (int)p.tile_rows[rt];
-      const int r = warp * 32 + lane;  // accumulator row = TMEM lane
-      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) break;
-      tm.stop(0);
-      tm.start();
-      tc_fence_after();
+      const int r = sub * 128 + q4 * 32 + lane;  // row of the tile
       const bool row_ok = r < rows;
       const uint32_t sp = row0 + r;
       const uint32_t dst = row_ok ? (p.dst_perm ? p.perm[sp] : sp) : 0xffffffffu;  // 0xffffffff: row not stored
       const float ar = row_ok ? p.a_row_scale[sp] : 1.0f;
-      const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * NCOL);
-      if constexpr (NMAT == 2) {
+      if (!mbar_wait(tfull_bar, tphase, abort_flag)) break;
+      tphase ^= 1;
+      tm.stop(0);
+      tm.start();
+      tc_fence_after();
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(sub * NCOL);
+      if (sub * 128 < rows) {  // (warp-uniform) this accumulator holds rows of the tile
+        if constexpr (NMAT == 2) {
+          uint32_t g[16], u[16];
+          tmem_ld16(lane_addr, g);
+          tmem_ld16(lane_addr + 128, u);
 #pragma unroll 1
-        for (int c = 0; c < 128; c += 32) {
-          uint32_t g[32], u[32];
-          tm.stop(3);
-          tm.start();
-          tmem_ld32(lane_addr + c, g);
-          tmem_ld32(lane_addr + 128 + c, u);
-          tmem_ld_wait();
-          tm.stop(1);
-          tm.start();
-          __syncwarp();  // the previous chunk's readers are done with the staging buffer
+          for (int c = 0; c < 128; c += 16) {
+            tmem_ld_wait();
+            __syncwarp();  // the previous chunk's readers are done with the staging buffer
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 cg = *reinterpret_cast<const float4*>(cs + c + i);
-            const float4 cu = *reinterpret_cast<const float4*>(cs + 128 + c + i);
-            const float cgs[4] = {cg.x, cg.y, cg.z, cg.w}, cus[4] = {cu.x, cu.y, cu.z, cu.w};
-            float h[4];
+            for (int i = 0; i < 16; i += 4) {
+              const float4 cg = *reinterpret_cast<const float4*>(cs + c + i);
+              const float4 cu = *reinterpret_cast<const float4*>(cs + 128 + c + i);
+              const float cgs[4] = {cg.x, cg.y, cg.z, cg.w}, cus[4] = {cu.x, cu.y, cu.z, cu.w};
+              float h[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const float gv = __uint_as_float(g[i + q]) * (cgs[q] * ar), uv = __uint_as_float(u[i + q]) * (cus[q] * ar);
-              h[q] = gv / (1.0f + __expf(-gv)) * uv;
+              for (int q = 0; q < 4; ++q) {
+                const float gv = __uint_as_float(g[i + q]) * (cgs[q] * ar), uv = __uint_as_float(u[i + q]) * (cus[q] * ar);
+                h[q] = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
+              }
+              *reinterpret_cast<float4*>(stg + lane * STG_LD + i) = make_float4(h[0], h[1], h[2], h[3]);
             }
-            *reinterpret_cast<float4*>(stg + lane * STG_LD + i) = make_float4(h[0], h[1], h[2], h[3]);
-          }
-          __syncwarp();
-          tm.stop(2);
-          tm.start();
-          // 4 lanes per row (8 columns = 16 bytes of bf16 each), 8 rows per store instruction
-#pragma unroll
-          for (int it = 0; it < 4; ++it) {
-            const int rr = it * 8 + (lane >> 2), cg8 = (lane & 3) * 8;
-            const uint32_t d = __shfl_sync(0xffffffffu, dst, rr);
-            const float4 v0 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8);
-            const float4 v1 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8 + 4);
-            uint4 o;
-            if constexpr (BITS == 4) {  // the consumer (down projection) reads k in [0,4,1,5,2,6,3,7] order
-              o.x = f32_to_bf16_bits(v0.x) | (f32_to_bf16_bits(v1.x) << 16);
-              o.y = f32_to_bf16_bits(v0.y) | (f32_to_bf16_bits(v1.y) << 16);
-              o.z = f32_to_bf16_bits(v0.z) | (f32_to_bf16_bits(v1.z) << 16);
-              o.w = f32_to_bf16_bits(v0.w) | (f32_to_bf16_bits(v1.w) << 16);
-            } else {
-              o.x = f32_to_bf16_bits(v0.x) | (f32_to_bf16_bits(v0.y) << 16);
-              o.y = f32_to_bf16_bits(v0.z) | (f32_to_bf16_bits(v0.w) << 16);
-              o.z = f32_to_bf16_bits(v1.x) | (f32_to_bf16_bits(v1.y) << 16);
-              o.w = f32_to_bf16_bits(v1.z) | (f32_to_bf16_bits(v1.w) << 16);
+            if (c + 16 < 128) {  // next chunk's accumulators travel while this one is stored
+              tmem_ld16(lane_addr + c + 16, g);
+              tmem_ld16(lane_addr + 128 + c + 16, u);
             }
-            if (d != 0xffffffffu)
-              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)d * p.N + ct * FEAT + c + cg8) = o;
-          }
-        }
-      } else {
-        const float sc = ar * ((row_ok && p.row_scale)
-                                   ? bf16_bits_to_f32(static_cast<const unsigned short*>(p.row_scale)[dst])
-                                   : 1.0f);
-#pragma unroll 1
-        for (int c = 0; c < 256; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(lane_addr + c, v);
-          tmem_ld_wait();
-          __syncwarp();
+            __syncwarp();
+            // 2 lanes per row (8 columns = 16 bytes of bf16 each), 16 rows per store instruction
 #pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            *reinterpret_cast<float4*>(stg + lane * STG_LD + i) =
-                make_float4(__uint_as_float(v[i]) * sc, __uint_as_float(v[i + 1]) * sc, __uint_as_float(v[i + 2]) * sc,
-                            __uint_as_float(v[i + 3]) * sc);
-          __syncwarp();
-          if (p.out_f32) {
-            // 8 lanes per row (4 columns = 16 bytes each): a 128-byte line per row, 4 rows per instruction
-            const int c4 = (lane & 7) * 4;
-            const float4 cc = *reinterpret_cast<const float4*>(cs + c + c4);
-#pragma unroll
-            for (int it = 0; it < 8; ++it) {
-              const int rr = it * 4 + (lane >> 3);
-              const uint32_t d = __shfl_sync(0xffffffffu, dst, rr);
-              float4 x4 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + c4);
-              x4.x *= cc.x;
-              x4.y *= cc.y;
-              x4.z *= cc.z;
-              x4.w *= cc.w;
-              if (d != 0xffffffffu)
-                *reinterpret_cast<float4*>(static_cast<float*>(p.out) + (size_t)d * p.N + ct * FEAT + c + c4) = x4;
-            }
-          } else {
-            const int cg8 = (lane & 3) * 8;
-            const float4 c0 = *reinterpret_cast<const float4*>(cs + c + cg8);
-            const float4 c1 = *reinterpret_cast<const float4*>(cs + c + cg8 + 4);
-#pragma unroll
-            for (int it = 0; it < 4; ++it) {
-              const int rr = it * 8 + (lane >> 2);
+            for (int it = 0; it < 2; ++it) {
+              const int rr = it * 16 + (lane >> 1), cg8 = (lane & 1) * 8;
               const uint32_t d = __shfl_sync(0xffffffffu, dst, rr);
               const float4 v0 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8);
               const float4 v1 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8 + 4);
               uint4 o;
-              o.x = f32_to_bf16_bits(v0.x * c0.x) | (f32_to_bf16_bits(v0.y * c0.y) << 16);
-              o.y = f32_to_bf16_bits(v0.z * c0.z) | (f32_to_bf16_bits(v0.w * c0.w) << 16);
-              o.z = f32_to_bf16_bits(v1.x * c1.x) | (f32_to_bf16_bits(v1.y * c1.y) << 16);
-              o.w = f32_to_bf16_bits(v1.z * c1.z) | (f32_to_bf16_bits(v1.w * c1.w) << 16);
+              if constexpr (BITS == 4) {  // the consumer (down projection) reads k in [0,4,1,5,2,6,3,7] order
+                o.x = f32_to_bf16_bits(v0.x) | (f32_to_bf16_bits(v1.x) << 16);
+                o.y = f32_to_bf16_bits(v0.y) | (f32_to_bf16_bits(v1.y) << 16);
+                o.z = f32_to_bf16_bits(v0.z) | (f32_to_bf16_bits(v1.z) << 16);
+                o.w = f32_to_bf16_bits(v0.w) | (f32_to_bf16_bits(v1.w) << 16);
+              } else {
+                o.x = f32_to_bf16_bits(v0.x) | (f32_to_bf16_bits(v0.y) << 16);
+                o.y = f32_to_bf16_bits(v0.z) | (f32_to_bf16_bits(v0.w) << 16);
+                o.z = f32_to_bf16_bits(v1.x) | (f32_to_bf16_bits(v1.y) << 16);
+                o.w = f32_to_bf16_bits(v1.z) | (f32_to_bf16_bits(v1.w) << 16);
+              }
               if (d != 0xffffffffu)
                 *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)d * p.N + ct * FEAT + c + cg8) = o;
+            }
+          }
+        } else {
+          const float sc = ar * ((row_ok && p.row_scale)
+                                     ? bf16_bits_to_f32(static_cast<const unsigned short*>(p.row_scale)[dst])
+                                     : 1.0f);
+          uint32_t v[16];
+          tmem_ld16(lane_addr, v);
+#pragma unroll 1
+          for (int c = 0; c < 256; c += 16) {
+            tmem_ld_wait();
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 16; i += 4)
+              *reinterpret_cast<float4*>(stg + lane * STG_LD + i) =
+                  make_float4(__uint_as_float(v[i]) * sc, __uint_as_float(v[i + 1]) * sc, __uint_as_float(v[i + 2]) * sc,
+                              __uint_as_float(v[i + 3]) * sc);
+            if (c + 16 < 256) tmem_ld16(lane_addr + c + 16, v);
+            __syncwarp();
+            if (p.out_f32) {
+              // 4 lanes per row (4 columns = 16 bytes each): 64 bytes per row, 8 rows per instruction
+              const int c4 = (lane & 3) * 4;
+              const float4 cc = *reinterpret_cast<const float4*>(cs + c + c4);
+#pragma unroll
+              for (int it = 0; it < 4; ++it) {
+                const int rr = it * 8 + (lane >> 2);
+                const uint32_t d = __shfl_sync(0xffffffffu, dst, rr);
+                float4 x4 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + c4);
+                x4.x *= cc.x;
+                x4.y *= cc.y;
+                x4.z *= cc.z;
+                x4.w *= cc.w;
+                if (d != 0xffffffffu)
+                  *reinterpret_cast<float4*>(static_cast<float*>(p.out) + (size_t)d * p.N + ct * FEAT + c + c4) = x4;
+              }
+            } else {
+              const int cg8 = (lane & 1) * 8;
+              const float4 c0 = *reinterpret_cast<const float4*>(cs + c + cg8);
+              const float4 c1 = *reinterpret_cast<const float4*>(cs + c + cg8 + 4);
+#pragma unroll
+              for (int it = 0; it < 2; ++it) {
+                const int rr = it * 16 + (lane >> 1);
+                const uint32_t d = __shfl_sync(0xffffffffu, dst, rr);
+                const float4 v0 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8);
+                const float4 v1 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8 + 4);
+                uint4 o;
+                o.x = f32_to_bf16_bits(v0.x * c0.x) | (f32_to_bf16_bits(v0.y * c0.y) << 16);
+                o.y = f32_to_bf16_bits(v0.z * c0.z) | (f32_to_bf16_bits(v0.w * c0.w) << 16);
+                o.z = f32_to_bf16_bits(v1.x * c1.x) | (f32_to_bf16_bits(v1.y * c1.y) << 16);
+                o.w = f32_to_bf16_bits(v1.z * c1.z) | (f32_to_bf16_bits(v1.w * c1.w) << 16);
+                if (d != 0xffffffffu)
+                  *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)d * p.N + ct * FEAT + c + cg8) = o;
+              }
             }
           }
         }
       }
       tc_fence_before();
-      mbar_arrive_warp(tempty_bar(acc), lane);
-      tm.stop(3);
-      if (++acc == ACC_STAGES) {
-        acc = 0;
-        acc_phase ^= 1;
-      }
+      mbar_arrive_warp(tempty_bar, lane);
+      tm.stop(1);
     }
-    (void)t_begin;
     tm.flush(p.err + 16 + (NMAT == 1 ? 24 : 0));
-  } else if (warp < 12) {
+  } else if (warp < (N_EPI + N_DEQ) / 32) {
     // ------------------------------- B dequantisation --------------------------------------
     const int col = tid - N_EPI;  // accumulator column = B tile row, 0..255
     const int mt = (NMAT == 2) ? (col >> 7) : 0;
     const int fcol = (NMAT == 2) ? (col & 127) : col;
     const uint32_t sw = (uint32_t)(col & 7);
     const uint32_t row_off = (uint32_t)(col >> 3) * 1024u + (uint32_t)(col & 7) * 128u;
+    // W stage: two boxes of 128 rows x 64 bytes, 64-byte swizzle (16-byte chunk index ^ (row/2 % 4))
+    const int bx = col >> 7, rr = col & 127;
+    const uint32_t w_row_off = (uint32_t)bx * 8192u + (uint32_t)rr * 64u;
+    const uint32_t wsw = (uint32_t)((rr >> 1) & 3);
     int s = 0, phase = 0, tcount = 0, ws = 0, wphase = 0;
+    constexpr float kQmax = (BITS == 4) ? 15.f : 255.f;
     RoleTimer tm((p.debug & 32) && blockIdx.x == 0 && tid == N_EPI);
     const long long t_begin = clock64();
-    constexpr float kQmax = (BITS == 4) ? 15.f : 255.f;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
       const int rt = tile / n_col_tiles, ct = tile % n_col_tiles;
       const int e = (int)p.tile_expert[rt];
@@ -473,7 +485,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         for (int g = 0; g < G; ++g)
           mx = fmaxf(mx, fabsf(bf16_bits_to_f32(__ldg(bp + g))) + kQmax * fabsf(bf16_bits_to_f32(__ldg(sp + g))));
       }
-      // pull the first lines of the next tile's weight row, scales and biases into L2 meanwhile
+      // pull the first lines of the next tile's scales and biases into L2 meanwhile
       {
         const int ntile = tile + gridDim.x;
         if (ntile < total_tiles) {
@@ -483,14 +495,14 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const unsigned short*>(p.biases[mt]) + nwr * G));
         }
       }
-      int ex = (mx > 0.f && mx < 3.0e38f) ? (ilogbf(mx) - 13) : 0;
+      // exponent of mx straight from its bits (mx is a finite non-negative float here)
+      int ex = 0;
+      if (mx > 0.f && mx < 3.0e38f) ex = (int)((__float_as_uint(mx) >> 23) & 0xffu) - 127 - 13;
       ex = max(-100, min(100, ex));
-      const float down_f = ldexpf(1.0f, -ex);
-      colscale[(tcount % CS_BUFS) * NCOL + col] = ldexpf(1.0f, ex);
+      const float down_f = __uint_as_float((uint32_t)(127 - ex) << 23);
+      colscale[(tcount % CS_BUFS) * NCOL + col] = __uint_as_float((uint32_t)(127 + ex) << 23);
       // scale / bias: four K blocks' worth per 8-byte load, fetched one chunk ahead
       uint2 s_cur = make_uint2(0, 0), b_cur = s_cur, s_nxt = s_first, b_nxt = b_first;
-      const int bx = col >> 7, rr = col & 127;
-      const uint32_t w_row_off = (uint32_t)bx * 16384u + (uint32_t)(rr >> 3) * 1024u + (uint32_t)(rr & 7) * 128u;
       bool dead = false;
       for (int kb = 0; kb < KB; ++kb) {
         const int kin = kb % KPS;
@@ -499,7 +511,6 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           dead = true;
           break;
         }
-        tm.stop(0);
         unsigned short cs, cb;
         if (sb_vec) {
           if ((kb & 3) == 0) {
@@ -517,7 +528,6 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           cs = __ldg(sp + kb);
           cb = __ldg(bp + kb);
         }
-        tm.start();
         if (!mbar_wait(empty_bar(s), phase ^ 1, abort_flag)) {
           dead = true;
           break;
@@ -542,10 +552,10 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const __half2 s2 = __float2half2_rn(bf16_bits_to_f32(cs) * down_f);
         const __half2 b2 = __float2half2_rn(bf16_bits_to_f32(cb) * down_f);
         const unsigned char* wsrc = w_st + (size_t)ws * W_BYTES + w_row_off;
-        uint4 cur[WPB / 4];
+        uint4 cur[CPK];
 #pragma unroll
-        for (int q = 0; q < WPB / 4; ++q)
-          cur[q] = *reinterpret_cast<const uint4*>(wsrc + (((uint32_t)(kin * (WPB / 4) + q) ^ sw) << 4));
+        for (int q = 0; q < CPK; ++q)
+          cur[q] = *reinterpret_cast<const uint4*>(wsrc + (((uint32_t)(kin * CPK + q) ^ wsw) << 4));
         unsigned char* dst = b_st + (size_t)s * B_BYTES + row_off;
         const uint32_t* cw = &cur[0].x;
 #pragma unroll
@@ -578,7 +588,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     }
     tm.acc[3] = clock64() - t_begin;
     tm.flush(p.err + 20 + (NMAT == 1 ? 24 : 0));
-  } else if (warp == 12) {
+  } else if (warp == WARP_TMA_A) {
     // ------------------------------- TMA producer (A) ---------------------------------------
     if (lane == 0) {
       int s = 0, phase = 0;
@@ -588,6 +598,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
         const int rt = tile / n_col_tiles;
         const int row0 = (int)p.tile_row0[rt];
+        const int n_sub = ((int)p.tile_rows[rt] > BM) ? 2 : 1;
         for (int kb = 0; kb < KB; ++kb) {
           tm.start();
           if (!mbar_wait(aempty_bar(s), phase ^ 1, abort_flag)) {
@@ -595,8 +606,10 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             break;
           }
           tm.stop(0);
-          mbar_arrive_expect_tx(afull_bar(s), A_BYTES);
-          tma_load_2d(smem_u32(a_st + (size_t)s * A_BYTES), &tmap_a, afull_bar(s), kb * BK, row0);
+          mbar_arrive_expect_tx(afull_bar(s), n_sub * A_BYTES);
+          const uint32_t dst = smem_u32(a_st + (size_t)s * A_STAGE_BYTES);
+          tma_load_2d(dst, &tmap_a, afull_bar(s), kb * BK, row0);
+          if (n_sub == 2) tma_load_2d(dst + A_BYTES, &tmap_a, afull_bar(s), kb * BK, row0 + BM);
           if (++s == A_STAGES) {
             s = 0;
             phase ^= 1;
@@ -607,19 +620,21 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       tm.flush(p.err + 24 + (NMAT == 1 ? 24 : 0));
     }
     __syncwarp();
-  } else if (warp == 13) {
+  } else if (warp == WARP_MMA) {
     // ------------------------------- MMA issuer ----------------------------------------------
     if (lane == 0) {
-      int s = 0, phase = 0, sa = 0, aphase = 0, acc = 0, acc_phase = 0;
+      int s = 0, phase = 0, sa = 0, aphase = 0, tphase = 0;
       bool dead = false;
       RoleTimer tm((p.debug & 32) && blockIdx.x == 0);
       const long long t_begin = clock64();
       for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
+        const int rt = tile / n_col_tiles;
+        const int n_sub = ((int)p.tile_rows[rt] > BM) ? 2 : 1;
         tm.start();
-        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag)) break;
+        if (!mbar_wait(tempty_bar, tphase ^ 1, abort_flag)) break;
+        tphase ^= 1;
         tm.stop(2);
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * NCOL);
         for (int kb = 0; kb < KB; ++kb) {
           tm.start();
           if (!mbar_wait(afull_bar(sa), aphase, abort_flag)) {
@@ -634,11 +649,15 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
           tm.stop(1);
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(a_st + (size_t)sa * A_BYTES), b_addr = smem_u32(b_st + (size_t)s * B_BYTES);
-          if (!(p.debug & 2))
+          const uint32_t a_addr = smem_u32(a_st + (size_t)sa * A_STAGE_BYTES), b_addr = smem_u32(b_st + (size_t)s * B_BYTES);
+          if (!(p.debug & 2)) {
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma_bf16(d_tmem, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), (kb | k) ? 1u : 0u);
+            for (int k = 0; k < BK / 16; ++k) {
+              const uint64_t bd = umma_desc(b_addr + k * 32);
+              umma_bf16(tmem_base, umma_desc(a_addr + k * 32), bd, (kb | k) ? 1u : 0u);
+              if (n_sub == 2) umma_bf16(tmem_base + NCOL, umma_desc(a_addr + A_BYTES + k * 32), bd, (kb | k) ? 1u : 0u);
+            }
+          }
           umma_commit(aempty_bar(sa));  // both stages are free once these MMAs have read them
           umma_commit(empty_bar(s));
           if (++s == STAGES) {
@@ -651,11 +670,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
         }
         if (dead) break;
-        umma_commit(tfull_bar(acc));  // accumulator complete
-        if (++acc == ACC_STAGES) {
-          acc = 0;
-          acc_phase ^= 1;
-        }
+        umma_commit(tfull_bar);  // accumulators complete
       }
       tm.acc[3] = clock64() - t_begin;
       tm.flush(p.err + 28 + (NMAT == 1 ? 24 : 0));
@@ -682,11 +697,11 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           mbar_arrive_expect_tx(wfull_bar(ws), W_BYTES);
           const uint32_t dst = smem_u32(w_st + (size_t)ws * W_BYTES);
           if constexpr (NMAT == 2) {
-            tma_load_2d(dst, &tmap_w0, wfull_bar(ws), wk * 32, row_base);
-            tma_load_2d(dst + 16384, &tmap_w1, wfull_bar(ws), wk * 32, row_base);
+            tma_load_2d(dst, &tmap_w0, wfull_bar(ws), wk * 16, row_base);
+            tma_load_2d(dst + 8192, &tmap_w1, wfull_bar(ws), wk * 16, row_base);
           } else {
-            tma_load_2d(dst, &tmap_w0, wfull_bar(ws), wk * 32, row_base);
-            tma_load_2d(dst + 16384, &tmap_w0, wfull_bar(ws), wk * 32, row_base + 128);
+            tma_load_2d(dst, &tmap_w0, wfull_bar(ws), wk * 16, row_base);
+            tma_load_2d(dst + 8192, &tmap_w0, wfull_bar(ws), wk * 16, row_base + 128);
           }
           if (++ws == W_STAGES) {
             ws = 0;
@@ -707,7 +722,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     if (tid == 0) atomicExch(p.err, 3);
     __nanosleep(200000);  // let copies and MMAs that are still in flight land before the CTA goes away
   }
-  if (warp == 13) {
+  if (warp == WARP_MMA) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
   }
@@ -723,7 +738,7 @@ __global__ void __launch_bounds__(256) build_row_tiles_kernel(const uint32_t* __
   __shared__ uint32_t pre[257];
   const int e = threadIdx.x;
   const uint32_t c = (e < E) ? counts[e] : 0u;
-  const uint32_t nt = (c + BM - 1) / BM;
+  const uint32_t nt = (c + BMT - 1) / BMT;
   pre[e + 1] = nt;
   if (e == 0) pre[0] = 0;
   __syncthreads();
@@ -736,8 +751,8 @@ __global__ void __launch_bounds__(256) build_row_tiles_kernel(const uint32_t* __
     const uint32_t base = pre[e], o = offsets[e];
     for (uint32_t i = 0; i < nt; ++i) {
       tile_expert[base + i] = (uint32_t)e;
-      tile_row0[base + i] = o + i * BM;
-      tile_rows[base + i] = min((uint32_t)BM, c - i * BM);
+      tile_row0[base + i] = o + i * BMT;
+      tile_rows[base + i] = min((uint32_t)BMT, c - i * BMT);
     }
   }
 }
@@ -807,7 +822,7 @@ static EncodeTiledFn encode_fn() {
 
 }  // namespace
 
-size_t prefill_tile_words(int64_t rows, int E) { return (size_t)(rows / BM + E + 1); }
+size_t prefill_tile_words(int64_t rows, int E) { return (size_t)(rows / BMT + E + 1); }
 
 bool prefill_shape_ok(int K, int N, int nmat) { return K % 64 == 0 && N % (nmat == 2 ? 128 : 256) == 0; }
 
@@ -842,14 +857,14 @@ int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   B200_REQUIRE(cr == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed (the activation buffer must be 16-byte aligned)");
-  // packed weights as [E*N rows, K*bits/32 words] uint32; one box = 128 rows x 128 bytes
+  // packed weights as [E*N rows, K*bits/32 words] uint32; one box = 128 rows x 64 bytes
   CUtensorMap tmap_w[2];
   for (int i = 0; i < nmat; ++i) {
     cuuint64_t wd[2] = {(cuuint64_t)g.K * bits / 32, (cuuint64_t)E * g.N};
     cuuint64_t ws_[1] = {(cuuint64_t)g.K * bits / 8};
-    cuuint32_t wb[2] = {32, 128};
+    cuuint32_t wb[2] = {16, 128};
     cr = enc(&tmap_w[i], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(g.w[i]), wd, ws_, wb, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     B200_REQUIRE(cr == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed for the packed weights (16-byte alignment required)");
   }
