@@ -193,7 +193,7 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
-    ap.add_argument("--qmm-path", default="auto", choices=["auto", "small", "tensor_core"],
+    ap.add_argument("--qmm-path", default="auto", choices=["auto", "small", "stream", "tensor_core"],
                     help="pin the grouped-product kernel (default: the library chooses)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -221,7 +221,7 @@ def main():
         return ep.bench_main(args, pkg, SHAPE, peaks, METRIC, UNIT, workload_name)
 
     ctx = pkg.default_context()
-    ctx.set_qmm_path(dict(auto=ctx.QMM_AUTO, small=ctx.QMM_SMALL, tensor_core=ctx.QMM_TENSOR_CORE)[args.qmm_path])
+    ctx.set_qmm_path(dict(auto=ctx.QMM_AUTO, small=ctx.QMM_SMALL, stream=ctx.QMM_STREAM, tensor_core=ctx.QMM_TENSOR_CORE)[args.qmm_path])
     block = build_block(pkg, torch, args.seed, SHAPE, dev)
     ctx.reserve(block.config, max(T, max(SWEEP)))
     flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)

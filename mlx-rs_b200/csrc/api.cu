@@ -186,7 +186,8 @@ int b200_ctx_debug_words(b200_ctx* c, int32_t* host_out, int n) {
 
 int b200_ctx_set_qmm_path(b200_ctx* c, int path) {
   CTX_ENTER(c);
-  B200_REQUIRE(path == B200_QMM_AUTO || path == B200_QMM_SMALL || path == B200_QMM_TENSOR_CORE, "unknown path");
+  B200_REQUIRE(path == B200_QMM_AUTO || path == B200_QMM_SMALL || path == B200_QMM_TENSOR_CORE || path == B200_QMM_STREAM,
+               "unknown path");
   c->qmm_path = path;
   return 0;
 }
@@ -247,6 +248,12 @@ int b200_dequantize(b200_ctx* c, const uint32_t* wq, const void* scales, const v
 // Shared by quantized_matmul, gather_qmm and the block: run one grouped product.
 static int run_grouped(b200_ctx* c, GroupedArgs& a, int nmat, int bits, int max_active, int64_t rows, cudaStream_t st) {
   if (rows == 0) return 0;
+  // memory-bound regime: the TMA-streamed kernel where its shape rules hold, else the first-generation one
+  if (c->qmm_path != B200_QMM_SMALL && a.n_experts > 0 && stream_shape_ok(a.K, a.N, nmat, bits)) {
+    if (launch_grouped_qmm_stream(a, nmat, bits, a.n_experts, max_active, rows, c->err, st)) return 1;
+    LAUNCHED(c, 1);
+    return 0;
+  }
   if (launch_grouped_qmm_small(a, nmat, bits, max_active, rows, st)) return 1;
   LAUNCHED(c, 1);
   return 0;
@@ -286,6 +293,7 @@ int b200_quantized_matmul(b200_ctx* c, const void* x, const uint32_t* w, const v
   a.out = out;
   a.K = (int)K;
   a.N = (int)N;
+  a.n_experts = 1;
   return run_grouped(c, a, 1, bits, 1, M, st);
 }
 
@@ -338,6 +346,7 @@ int b200_gather_qmm(b200_ctx* c, const void* x, const uint32_t* w, const void* s
   a.out = out;
   a.K = (int)K;
   a.N = (int)N;
+  a.n_experts = (int)E;
   return run_grouped(c, a, 1, bits, (int)(E < n ? E : n), n, st);
 }
 
@@ -460,7 +469,7 @@ int b200_moe_permute(b200_ctx* c, const uint32_t* indices, int64_t n, int E, uin
 // Which grouped-product kernel a block of n assignments over at most `max_active` experts uses.
 static bool use_tensor_core_path(const b200_ctx* c, const b200_moe_config& cfg, int64_t n, int max_active) {
   if (!prefill_shape_ok(cfg.hidden, cfg.inter, 2) || !prefill_shape_ok(cfg.inter, cfg.hidden, 1)) return false;
-  if (c->qmm_path == B200_QMM_SMALL) return false;
+  if (c->qmm_path == B200_QMM_SMALL || c->qmm_path == B200_QMM_STREAM) return false;
   if (c->qmm_path == B200_QMM_TENSOR_CORE) return true;
   return n / (max_active > 0 ? max_active : 1) >= 24;
 }
@@ -531,6 +540,7 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
   gu.out = h;
   gu.K = cfg.hidden;
   gu.N = cfg.inter;
+  gu.n_experts = E;
   if (tc) {
     // rows gathered into expert order, converted to row-normalised fp16, in the k order the 4-bit unpack produces
     launch_prepare_rows(x, perm, cfg.top_k, n, cfg.hidden, cfg.bits == 4, xs, rs_x, st);
@@ -563,6 +573,7 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
   if (yk_is_bf16) *yk_is_bf16 = !dn.out_f32;
   dn.K = cfg.inter;
   dn.N = cfg.hidden;
+  dn.n_experts = E;
   if (tc) {
     // h was written (bf16-rounded) already in unpack order; only the fp16 conversion remains
     launch_prepare_rows(h, nullptr, 1, n, cfg.inter, 0, h16, rs_h, st);

@@ -25,6 +25,7 @@ struct GroupedArgs {
   void* out;                  // [rows, N], bf16 or float32
   int out_f32;                // 1: float32 output (no rounding before the k-way combine)
   int K, N;
+  int n_experts;              // number of stacked weight matrices
 };
 
 // router.cu
@@ -45,6 +46,11 @@ size_t permute_scratch_words(int64_t n, int E);
 
 // qmm_decode.cu
 int launch_grouped_qmm_small(const GroupedArgs& a, int nmat, int bits, int max_active, int64_t rows, cudaStream_t st);
+
+// qmm_stream.cu (memory-bound regime, TMA-streamed weights)
+bool stream_shape_ok(int K, int N, int nmat, int bits);
+int launch_grouped_qmm_stream(const GroupedArgs& g, int nmat, int bits, int n_experts, int max_active, int64_t rows,
+                              int* err, cudaStream_t st);
 
 // qmm_prefill.cu (tcgen05 path)
 size_t prefill_tile_words(int64_t rows, int E);

@@ -66,6 +66,19 @@ def test_config0_block(pkg, O, config0):
 
 
 @pytest.mark.parametrize("T", [1, 4, 16])
+def test_decode_sweep_first_generation_kernel(pkg, O, config0, T):
+    ctx = pkg.default_context()
+    ctx.set_qmm_path(ctx.QMM_SMALL)
+    try:
+        blk = dict(config0)
+        blk["x"] = config0["x"][:T].copy()
+        blk["T"] = T
+        check_block(pkg, O, blk)
+    finally:
+        ctx.set_qmm_path(ctx.QMM_AUTO)
+
+
+@pytest.mark.parametrize("T", [1, 4, 16])
 def test_decode_sweep(pkg, O, config0, T):
     # BASELINE.json configs[1], decode points (64 is test_config0_block): same weights, fewer tokens
     blk = dict(config0)
@@ -74,11 +87,12 @@ def test_decode_sweep(pkg, O, config0, T):
     check_block(pkg, O, blk)
 
 
-@pytest.fixture(params=["small", "tensor_core"])
+@pytest.fixture(params=["small", "stream", "tensor_core"])
 def qmm_path(request, pkg):
-    """Runs a test once per grouped-product kernel (memory-bound mma.sync / tcgen05) and restores AUTO."""
+    """Runs a test once per grouped-product kernel (register-load mma.sync / TMA-streamed mma.sync / tcgen05)
+    and restores AUTO."""
     ctx = pkg.default_context()
-    ctx.set_qmm_path(ctx.QMM_SMALL if request.param == "small" else ctx.QMM_TENSOR_CORE)
+    ctx.set_qmm_path(dict(small=ctx.QMM_SMALL, stream=ctx.QMM_STREAM, tensor_core=ctx.QMM_TENSOR_CORE)[request.param])
     yield request.param
     ctx.set_qmm_path(ctx.QMM_AUTO)
 
