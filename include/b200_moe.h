@@ -104,11 +104,10 @@ int64_t b200_ctx_launch_count(const b200_ctx* ctx);
  * stages; b200_ctx_stage_ms waits for the last profiled call and returns the milliseconds of
  * its stages in this order: router logits, softmax/top-k, permutation, gate+up product,
  * down product, combine. */
-/* Which grouped-product kernel the routed block uses.  AUTO: the TMA-streamed memory-bound
- * kernel while experts own few rows (the first-generation register-load kernel where its shape
- * rules do not hold: K % 256, N % 64/128), the tcgen05 tensor-core kernel beyond that (when
- * inter % 128 == 0 and hidden % 256 == 0).  The other values pin the choice; a pinned kernel
- * still falls back when the shape does not allow it. */
+/* Which grouped-product kernel the routed block uses.  AUTO: the register-load mma.sync kernel
+ * while experts own few rows, the tcgen05 tensor-core kernel beyond that (when inter % 128 == 0
+ * and hidden % 256 == 0).  STREAM pins the TMA-streamed variant of the memory-bound kernel
+ * (K % 256 == 0, N % 64 or 128 == 0).  A pinned kernel falls back when the shape does not allow it. */
 enum { B200_QMM_AUTO = 0, B200_QMM_SMALL = 1, B200_QMM_TENSOR_CORE = 2, B200_QMM_STREAM = 3 };
 int b200_ctx_set_qmm_path(b200_ctx* ctx, int path);
 /* Diagnostic: synchronises the device and copies the first n (<= 64) 32-bit words of the

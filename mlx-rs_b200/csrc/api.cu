@@ -248,8 +248,9 @@ int b200_dequantize(b200_ctx* c, const uint32_t* wq, const void* scales, const v
 // Shared by quantized_matmul, gather_qmm and the block: run one grouped product.
 static int run_grouped(b200_ctx* c, GroupedArgs& a, int nmat, int bits, int max_active, int64_t rows, cudaStream_t st) {
   if (rows == 0) return 0;
-  // memory-bound regime: the TMA-streamed kernel where its shape rules hold, else the first-generation one
-  if (c->qmm_path != B200_QMM_SMALL && a.n_experts > 0 && stream_shape_ok(a.K, a.N, nmat, bits)) {
+  // memory-bound regime: the register-load kernel by default; the TMA-streamed variant when pinned
+  // (it measures the same within a few percent, see qmm_stream.cu)
+  if (c->qmm_path == B200_QMM_STREAM && a.n_experts > 0 && stream_shape_ok(a.K, a.N, nmat, bits)) {
     if (launch_grouped_qmm_stream(a, nmat, bits, a.n_experts, max_active, rows, c->err, st)) return 1;
     LAUNCHED(c, 1);
     return 0;

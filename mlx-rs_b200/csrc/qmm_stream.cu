@@ -3,10 +3,12 @@
 // codes fed to mma.sync as exact fp16 values, affine scale/bias folded per group in float32.
 //
 // Same contract as qmm_decode.cu (gather_qmm with sorted rows,
-// mlx-rs/src/ops/quantization.rs:160-230, SiLU-gate or routing-weight epilogue fused); this
-// kernel replaces it where it applies (4-bit or 8-bit, group 64, K a multiple of 256, N a
-// multiple of the feature block).  What changed and why (see the ncu summary of the first
-// kernel: issue-bound on the integer pipe at a quarter occupancy, load latency exposed):
+// mlx-rs/src/ops/quantization.rs:160-230, SiLU-gate or routing-weight epilogue fused), for 4-bit
+// or 8-bit codes, group 64, K a multiple of 256, N a multiple of the feature block.  Measured on
+// B200 it matches the first-generation kernel (64.6 vs 69.3 us for gate+up at 16 tokens, 114 vs
+// 106 us at 64 tokens of the 128-expert shape) without beating it: both end up bound by the
+// instructions spent per packed weight, not by memory.  It is therefore selectable
+// (B200_QMM_STREAM) but not the default.  What it does differently from the first kernel:
 //
 //  * weights no longer travel through per-thread global loads.  One producer thread issues TMA
 //    tile loads (128 packed bytes x 128 weight rows = 16 KB per stage, 128-byte swizzle) into a
@@ -27,6 +29,8 @@
 // epilogue), in the k order the unpacking produces.
 #include <cuda.h>
 #include <cuda_fp16.h>
+
+#include <cstdlib>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -78,6 +82,12 @@ __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile
     }
   }
 }
+// 1-D bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16)
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
 __device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
@@ -86,14 +96,14 @@ __device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* map, uin
 // D = A*B + C with separate C (read) and D (written) registers
 __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                               uint32_t b1, float c0, float c1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
       : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1));
 }
 __device__ __forceinline__ void mma_f16_16816_acc(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                   uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -114,10 +124,28 @@ struct StreamArgs {
   int out_f32;
   int K, N;
   int* err;
+  int debug;                 // development: bit 5 = CTA 0 writes per-role cycle counts to err[16..]
 };
 
 
 constexpr int MAX_RING = 10;
+
+struct STimer {
+  long long acc[4] = {0, 0, 0, 0};
+  long long t0 = 0;
+  bool on;
+  __device__ explicit STimer(bool e) : on(e) {}
+  __device__ __forceinline__ void start() {
+    if (on) t0 = clock64();
+  }
+  __device__ __forceinline__ void stop(int i) {
+    if (on) acc[i] += clock64() - t0;
+  }
+  __device__ void flush(int* dst) {
+    if (on)
+      for (int i = 0; i < 4; ++i) dst[i] = (int)(acc[i] >> 10);
+  }
+};
 
 template <int BITS, int NMAT, int NT>
 __global__ void __launch_bounds__(N_THREADS_S, 1)
@@ -136,8 +164,14 @@ grouped_qmm_stream_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __g
   float* xsum = negc + G * ROWS;                                     // [G][ROWS]
   float* rowsc = xsum + G * ROWS;                                    // [ROWS]
   uint64_t* bars = reinterpret_cast<uint64_t*>(rowsc + ROWS + 2);    // full[MAX_RING], empty[MAX_RING] (8-byte aligned: ROWS even)
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * MAX_RING + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * MAX_RING + 5);
   const uint32_t xbar = s_u32(bars + 2 * MAX_RING);  // compute-warp rendezvous around the activation staging
+  // scale/bias slots: per work item the four (NMAT = 2) or two contiguous blocks [rows][G] of bf16
+  // scales and biases of the item's weight rows, fetched by bulk copies one item ahead
+  const uint32_t sbfull0 = s_u32(bars + 2 * MAX_RING + 1), sbempty0 = s_u32(bars + 2 * MAX_RING + 3);
+  const int SB_BLOCK = (WROWS / NMAT) * G * 2;       // bytes of one block
+  const int SB_SLOT = 2 * NMAT * SB_BLOCK;           // scales + biases of every matrix
+  unsigned char* sb_base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(bars + 2 * MAX_RING + 8) + 15) & ~uintptr_t(15));
   const uint32_t bar0 = s_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (MAX_RING + s); };
@@ -149,6 +183,10 @@ grouped_qmm_stream_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __g
       bar_init(empty_bar(s), N_COMPUTE / 32);
     }
     bar_init(xbar, N_COMPUTE / 32);
+    for (int i = 0; i < 2; ++i) {
+      bar_init(sbfull0 + 8u * i, 1);
+      bar_init(sbempty0 + 8u * i, N_COMPUTE / 32);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -163,33 +201,69 @@ grouped_qmm_stream_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __g
   if (warp == N_COMPUTE / 32) {
     // ------------------------------- producer: TMA weight stream ----------------------------
     if (lane == 0) {
-      int s = 0, ph = 0;
+      int s = 0, ph = 0, sl = 0, slph = 0;
       bool dead = false;
-      for (int item = i0; item < i1 && !dead; ++item) {
-        const int e = (int)p.active[item / nfb], fb = item % nfb;
+      STimer tm((p.debug & 32) && blockIdx.x == 0);
+      const long long tb = clock64();
+      // units are visited run by run (a run = this CTA's consecutive items of one expert), pass by
+      // pass inside a run, item by item inside a pass: the activation rows staged for a pass
+      // then serve every item of the run
+      for (int it0 = i0; it0 < i1 && !dead;) {
+        tm.start();
+        const int ea = it0 / nfb;
+        const int run_end = min(i1, (ea + 1) * nfb);
+        const int e = (int)p.active[ea];
         const int m = (int)(p.offsets[e + 1] - p.offsets[e]);
-        const int row_base = e * N + fb * FB;
+        tm.stop(2);
         for (int p0 = 0; p0 < m && !dead; p0 += ROWS) {
-          for (int st = 0; st < n_st; ++st) {
-            if (!bar_wait(empty_bar(s), ph ^ 1, abort_flag)) {
-              dead = true;
-              break;
+          for (int item = it0; item < run_end && !dead; ++item) {
+            const int row_base = e * N + (item % nfb) * FB;
+            {  // scales and biases of this item's rows -> slot sl
+              tm.start();
+              if (!bar_wait(sbempty0 + 8u * sl, slph ^ 1, abort_flag)) {
+                dead = true;
+                break;
+              }
+              tm.stop(1);
+              bar_expect_tx(sbfull0 + 8u * sl, (uint32_t)SB_SLOT);
+              const uint32_t dst = s_u32(sb_base + (size_t)sl * SB_SLOT);
+#pragma unroll
+              for (int mt = 0; mt < NMAT; ++mt) {
+                const size_t off = (size_t)row_base * G * 2;
+                bulk_copy(dst + (2 * mt) * SB_BLOCK, static_cast<const unsigned char*>(p.scales[mt]) + off, SB_BLOCK, sbfull0 + 8u * sl);
+                bulk_copy(dst + (2 * mt + 1) * SB_BLOCK, static_cast<const unsigned char*>(p.biases[mt]) + off, SB_BLOCK, sbfull0 + 8u * sl);
+              }
+              if (++sl == 2) {
+                sl = 0;
+                slph ^= 1;
+              }
             }
-            bar_expect_tx(full_bar(s), STAGE_BYTES);
-            const uint32_t dst = s_u32(w_ring + (size_t)s * STAGE_BYTES);
-            if constexpr (NMAT == 2) {
-              tma_2d(dst, &tmap_w0, full_bar(s), st * 32, row_base);
-              tma_2d(dst + STAGE_BYTES / 2, &tmap_w1, full_bar(s), st * 32, row_base);
-            } else {
-              tma_2d(dst, &tmap_w0, full_bar(s), st * 32, row_base);
-            }
-            if (++s == ring) {
-              s = 0;
-              ph ^= 1;
+            for (int st = 0; st < n_st; ++st) {
+              tm.start();
+              if (!bar_wait(empty_bar(s), ph ^ 1, abort_flag)) {
+                dead = true;
+                break;
+              }
+              tm.stop(0);
+              bar_expect_tx(full_bar(s), STAGE_BYTES);
+              const uint32_t dst = s_u32(w_ring + (size_t)s * STAGE_BYTES);
+              if constexpr (NMAT == 2) {
+                tma_2d(dst, &tmap_w0, full_bar(s), st * 32, row_base);
+                tma_2d(dst + STAGE_BYTES / 2, &tmap_w1, full_bar(s), st * 32, row_base);
+              } else {
+                tma_2d(dst, &tmap_w0, full_bar(s), st * 32, row_base);
+              }
+              if (++s == ring) {
+                s = 0;
+                ph ^= 1;
+              }
             }
           }
         }
+        it0 = run_end;
       }
+      tm.acc[3] = clock64() - tb;
+      tm.flush(p.err + 16);
     }
     __syncwarp();
   } else {
@@ -202,7 +276,9 @@ grouped_qmm_stream_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __g
     const uint32_t offA = (uint32_t)rA * 128u, offB = (uint32_t)rB * 128u;
     const uint32_t swA = (uint32_t)(rA & 7), swB = (uint32_t)(rB & 7);
     int s = 0, ph = 0;
-    int staged_e = -1, staged_p0 = -1, xph = 0;
+    int staged_e = -1, staged_p0 = -1, xph = 0, sl = 0, slph = 0;
+    STimer tm((p.debug & 32) && blockIdx.x == 0 && tid == 0);
+    const long long tb = clock64();
     bool dead = false;
     // rendezvous of the eight compute warps on an mbarrier, with the same bounded wait as every
     // other wait of the kernel (a plain bar.sync could not give up)
@@ -213,16 +289,29 @@ grouped_qmm_stream_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __g
       xph ^= 1;
       return ok;
     };
-    for (int item = i0; item < i1 && !dead; ++item) {
-      const int e = (int)p.active[item / nfb], fb = item % nfb;
-      const uint32_t seg0 = p.offsets[e];
-      const int m = (int)(p.offsets[e + 1] - seg0);
-      const size_t wrA = (size_t)e * N + fb * FB + fA, wrB = (size_t)e * N + fb * FB + fB;
-      const unsigned short* sA = static_cast<const unsigned short*>(p.scales[0]) + wrA * G;
-      const unsigned short* bA = static_cast<const unsigned short*>(p.biases[0]) + wrA * G;
-      const unsigned short* sB = static_cast<const unsigned short*>(p.scales[NMAT - 1]) + wrB * G;
-      const unsigned short* bB = static_cast<const unsigned short*>(p.biases[NMAT - 1]) + wrB * G;
-      for (int p0 = 0; p0 < m && !dead; p0 += ROWS) {
+    for (int it0 = i0; it0 < i1 && !dead;) {
+     const int ea = it0 / nfb;
+     const int run_end = min(i1, (ea + 1) * nfb);
+     const int e = (int)p.active[ea];
+     const uint32_t seg0 = p.offsets[e];
+     const int m = (int)(p.offsets[e + 1] - seg0);
+     for (int p0 = 0; p0 < m && !dead; p0 += ROWS) {
+      for (int item = it0; item < run_end && !dead; ++item) {
+      const int fb = item % nfb;
+      // this item's scales / biases: blocks [scales0, biases0, (scales1, biases1)] of [rows][G] bf16 in slot sl
+      tm.start();
+      if (!bar_wait(sbfull0 + 8u * sl, slph, abort_flag)) {
+        dead = true;
+        break;
+      }
+      tm.stop(2);
+      const unsigned char* slot = sb_base + (size_t)sl * SB_SLOT;
+      const unsigned short* sA = reinterpret_cast<const unsigned short*>(slot) + (size_t)fA * G;
+      const unsigned short* bA = reinterpret_cast<const unsigned short*>(slot + SB_BLOCK) + (size_t)fA * G;
+      const unsigned short* sB = reinterpret_cast<const unsigned short*>(slot + (NMAT == 2 ? 2 : 0) * SB_BLOCK) + (size_t)fB * G;
+      const unsigned short* bB = reinterpret_cast<const unsigned short*>(slot + (NMAT == 2 ? 3 : 1) * SB_BLOCK) + (size_t)fB * G;
+      {
+        tm.start();
         if (e != staged_e || p0 != staged_p0) {
           // ---- stage the activation rows of this (expert, pass): fp16, row-normalised, permuted ----
           if (!rendezvous()) {  // every compute warp is done with the old rows
@@ -314,6 +403,7 @@ grouped_qmm_stream_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __g
           staged_e = e;
           staged_p0 = p0;
         }
+        tm.stop(1);
         // ---- K loop over the streamed weight stages ---------------------------------------
         float tot[NT][4];
 #pragma unroll
@@ -327,13 +417,13 @@ grouped_qmm_stream_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __g
           const int g0 = st * GPS;
           if (sb_vec) {
             if constexpr (BITS == 4) {
-              const uint2 a = __ldg(reinterpret_cast<const uint2*>(sA + g0)), b = __ldg(reinterpret_cast<const uint2*>(bA + g0));
-              const uint2 c = __ldg(reinterpret_cast<const uint2*>(sB + g0)), d = __ldg(reinterpret_cast<const uint2*>(bB + g0));
+              const uint2 a = *reinterpret_cast<const uint2*>(sA + g0), b = *reinterpret_cast<const uint2*>(bA + g0);
+              const uint2 c = *reinterpret_cast<const uint2*>(sB + g0), d = *reinterpret_cast<const uint2*>(bB + g0);
               sAw[0] = a.x; sAw[1] = a.y; bAw[0] = b.x; bAw[1] = b.y;
               sBw[0] = c.x; sBw[1] = c.y; bBw[0] = d.x; bBw[1] = d.y;
             } else {
-              sAw[0] = __ldg(reinterpret_cast<const uint32_t*>(sA + g0)); bAw[0] = __ldg(reinterpret_cast<const uint32_t*>(bA + g0));
-              sBw[0] = __ldg(reinterpret_cast<const uint32_t*>(sB + g0)); bBw[0] = __ldg(reinterpret_cast<const uint32_t*>(bB + g0));
+              sAw[0] = *reinterpret_cast<const uint32_t*>(sA + g0); bAw[0] = *reinterpret_cast<const uint32_t*>(bA + g0);
+              sBw[0] = *reinterpret_cast<const uint32_t*>(sB + g0); bBw[0] = *reinterpret_cast<const uint32_t*>(bB + g0);
               sAw[1] = bAw[1] = sBw[1] = bBw[1] = 0;
             }
           } else {
@@ -344,72 +434,87 @@ grouped_qmm_stream_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __g
               for (int j = 0; j < 2; ++j) {
                 const int gi = 2 * h + j;
                 if (gi < GPS) {
-                  sAw[h] |= (uint32_t)__ldg(sA + g0 + gi) << (16 * j);
-                  bAw[h] |= (uint32_t)__ldg(bA + g0 + gi) << (16 * j);
-                  sBw[h] |= (uint32_t)__ldg(sB + g0 + gi) << (16 * j);
-                  bBw[h] |= (uint32_t)__ldg(bB + g0 + gi) << (16 * j);
+                  sAw[h] |= (uint32_t)sA[g0 + gi] << (16 * j);
+                  bAw[h] |= (uint32_t)bA[g0 + gi] << (16 * j);
+                  sBw[h] |= (uint32_t)sB[g0 + gi] << (16 * j);
+                  bBw[h] |= (uint32_t)bB[g0 + gi] << (16 * j);
                 }
               }
             }
           }
+          tm.start();
           if (!bar_wait(full_bar(s), ph, abort_flag)) {
             dead = true;
             break;
           }
+          tm.stop(0);
           const unsigned char* wst = w_ring + (size_t)s * STAGE_BYTES;
+          // All operands of the stage's GPS groups are fetched first and the MMAs are issued
+          // group-interleaved (MMA i of every group before MMA i+1 of any), so that GPS*NT
+          // independent accumulator chains hide the tensor-pipe latency.
+          uint32_t wA[GPS][4], wB[GPS][4];
 #pragma unroll
           for (int gi = 0; gi < GPS; ++gi) {
-            const int g = g0 + gi;
-            uint32_t wA[4], wB[4];  // packed words of this thread for rows A and B (2 words at 4 bits, 4 at 8 bits)
             if constexpr (BITS == 4) {
               const uint32_t ch = (uint32_t)(2 * gi + (t >> 1));
               const uint2 a = *reinterpret_cast<const uint2*>(wst + offA + ((ch ^ swA) << 4) + (t & 1) * 8);
               const uint2 b = *reinterpret_cast<const uint2*>(wst + offB + ((ch ^ swB) << 4) + (t & 1) * 8);
-              wA[0] = a.x; wA[1] = a.y; wB[0] = b.x; wB[1] = b.y;
-              wA[2] = wA[3] = wB[2] = wB[3] = 0;
+              wA[gi][0] = a.x; wA[gi][1] = a.y; wB[gi][0] = b.x; wB[gi][1] = b.y;
+              wA[gi][2] = wA[gi][3] = wB[gi][2] = wB[gi][3] = 0;
             } else {
               const uint32_t ch = (uint32_t)(4 * gi + t);
               const uint4 a = *reinterpret_cast<const uint4*>(wst + offA + ((ch ^ swA) << 4));
               const uint4 b = *reinterpret_cast<const uint4*>(wst + offB + ((ch ^ swB) << 4));
-              wA[0] = a.x; wA[1] = a.y; wA[2] = a.z; wA[3] = a.w;
-              wB[0] = b.x; wB[1] = b.y; wB[2] = b.z; wB[3] = b.w;
+              wA[gi][0] = a.x; wA[gi][1] = a.y; wA[gi][2] = a.z; wA[gi][3] = a.w;
+              wB[gi][0] = b.x; wB[gi][1] = b.y; wB[gi][2] = b.z; wB[gi][3] = b.w;
             }
-            const float s_a = __uint_as_float((gi & 1) ? (sAw[gi >> 1] & 0xffff0000u) : (sAw[gi >> 1] << 16));
-            const float b_a = __uint_as_float((gi & 1) ? (bAw[gi >> 1] & 0xffff0000u) : (bAw[gi >> 1] << 16));
-            const float s_b = __uint_as_float((gi & 1) ? (sBw[gi >> 1] & 0xffff0000u) : (sBw[gi >> 1] << 16));
-            const float b_b = __uint_as_float((gi & 1) ? (bBw[gi >> 1] & 0xffff0000u) : (bBw[gi >> 1] << 16));
+          }
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-              const uint4* xp = reinterpret_cast<const uint4*>(xs + (size_t)(nt * 8 + gq) * XS + (size_t)(g * 4 + t) * 32);
-              const uint4 x0 = xp[0], x1 = xp[1];
-              const float2 nc = *reinterpret_cast<const float2*>(&negc[g * ROWS + nt * 8 + 2 * t]);
-              const float2 xsm = *reinterpret_cast<const float2*>(&xsum[g * ROWS + nt * 8 + 2 * t]);
-              float acc[4];
-              if constexpr (BITS == 4) {
-                constexpr uint32_t LO = 0x000f000fu, HI = 0x00f000f0u, MG = 0x64006400u;
-                uint32_t a = wA[0], b = wB[0];
-                mma_f16_16816(acc, (a & LO) | MG, (b & LO) | MG, (a & HI) | MG, (b & HI) | MG, x0.x, x0.y, nc.x, nc.y);
-                a >>= 8; b >>= 8;
-                mma_f16_16816_acc(acc, (a & LO) | MG, (b & LO) | MG, (a & HI) | MG, (b & HI) | MG, x0.z, x0.w);
-                a = wA[1]; b = wB[1];
-                mma_f16_16816_acc(acc, (a & LO) | MG, (b & LO) | MG, (a & HI) | MG, (b & HI) | MG, x1.x, x1.y);
-                a >>= 8; b >>= 8;
-                mma_f16_16816_acc(acc, (a & LO) | MG, (b & LO) | MG, (a & HI) | MG, (b & HI) | MG, x1.z, x1.w);
-              } else {
-                constexpr uint32_t MG8 = 0x64646464u;
-                mma_f16_16816(acc, __byte_perm(wA[0], MG8, 0x4140), __byte_perm(wB[0], MG8, 0x4140),
-                              __byte_perm(wA[0], MG8, 0x4342), __byte_perm(wB[0], MG8, 0x4342), x0.x, x0.y, nc.x, nc.y);
-                mma_f16_16816_acc(acc, __byte_perm(wA[1], MG8, 0x4140), __byte_perm(wB[1], MG8, 0x4140),
-                                  __byte_perm(wA[1], MG8, 0x4342), __byte_perm(wB[1], MG8, 0x4342), x0.z, x0.w);
-                mma_f16_16816_acc(acc, __byte_perm(wA[2], MG8, 0x4140), __byte_perm(wB[2], MG8, 0x4140),
-                                  __byte_perm(wA[2], MG8, 0x4342), __byte_perm(wB[2], MG8, 0x4342), x1.x, x1.y);
-                mma_f16_16816_acc(acc, __byte_perm(wA[3], MG8, 0x4140), __byte_perm(wB[3], MG8, 0x4140),
-                                  __byte_perm(wA[3], MG8, 0x4342), __byte_perm(wB[3], MG8, 0x4342), x1.z, x1.w);
+          for (int nt = 0; nt < NT; ++nt) {
+            if (nt > 0 && nt * 8 >= m - p0) break;  // (warp-uniform) this n-tile holds no row of the pass
+            uint4 x0[GPS], x1[GPS];
+            float acc[GPS][4];
+#pragma unroll
+            for (int gi = 0; gi < GPS; ++gi) {
+              const uint4* xp = reinterpret_cast<const uint4*>(xs + (size_t)(nt * 8 + gq) * XS + (size_t)((g0 + gi) * 4 + t) * 32);
+              x0[gi] = xp[0];
+              x1[gi] = xp[1];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+#pragma unroll
+              for (int gi = 0; gi < GPS; ++gi) {
+                const uint4& xv = (i < 2) ? x0[gi] : x1[gi];
+                const uint32_t b0 = (i & 1) ? xv.z : xv.x, b1 = (i & 1) ? xv.w : xv.y;
+                uint32_t a0, a1, a2, a3;
+                if constexpr (BITS == 4) {
+                  constexpr uint32_t LO = 0x000f000fu, HI = 0x00f000f0u, MG = 0x64006400u;
+                  const uint32_t a = wA[gi][i >> 1] >> (8 * (i & 1)), b = wB[gi][i >> 1] >> (8 * (i & 1));
+                  a0 = (a & LO) | MG; a1 = (b & LO) | MG; a2 = (a & HI) | MG; a3 = (b & HI) | MG;
+                } else {
+                  constexpr uint32_t MG8 = 0x64646464u;
+                  a0 = __byte_perm(wA[gi][i], MG8, 0x4140); a1 = __byte_perm(wB[gi][i], MG8, 0x4140);
+                  a2 = __byte_perm(wA[gi][i], MG8, 0x4342); a3 = __byte_perm(wB[gi][i], MG8, 0x4342);
+                }
+                if (i == 0) {
+                  const float2 nc = *reinterpret_cast<const float2*>(&negc[(g0 + gi) * ROWS + nt * 8 + 2 * t]);
+                  mma_f16_16816(acc[gi], a0, a1, a2, a3, b0, b1, nc.x, nc.y);
+                } else {
+                  mma_f16_16816_acc(acc[gi], a0, a1, a2, a3, b0, b1);
+                }
               }
-              tot[nt][0] = fmaf(s_a, acc[0], fmaf(b_a, xsm.x, tot[nt][0]));
-              tot[nt][1] = fmaf(s_a, acc[1], fmaf(b_a, xsm.y, tot[nt][1]));
-              tot[nt][2] = fmaf(s_b, acc[2], fmaf(b_b, xsm.x, tot[nt][2]));
-              tot[nt][3] = fmaf(s_b, acc[3], fmaf(b_b, xsm.y, tot[nt][3]));
+            }
+#pragma unroll
+            for (int gi = 0; gi < GPS; ++gi) {
+              const float2 xsm = *reinterpret_cast<const float2*>(&xsum[(g0 + gi) * ROWS + nt * 8 + 2 * t]);
+              const float s_a = __uint_as_float((gi & 1) ? (sAw[gi >> 1] & 0xffff0000u) : (sAw[gi >> 1] << 16));
+              const float b_a = __uint_as_float((gi & 1) ? (bAw[gi >> 1] & 0xffff0000u) : (bAw[gi >> 1] << 16));
+              const float s_b = __uint_as_float((gi & 1) ? (sBw[gi >> 1] & 0xffff0000u) : (sBw[gi >> 1] << 16));
+              const float b_b = __uint_as_float((gi & 1) ? (bBw[gi >> 1] & 0xffff0000u) : (bBw[gi >> 1] << 16));
+              tot[nt][0] = fmaf(s_a, acc[gi][0], fmaf(b_a, xsm.x, tot[nt][0]));
+              tot[nt][1] = fmaf(s_a, acc[gi][1], fmaf(b_a, xsm.y, tot[nt][1]));
+              tot[nt][2] = fmaf(s_b, acc[gi][2], fmaf(b_b, xsm.x, tot[nt][2]));
+              tot[nt][3] = fmaf(s_b, acc[gi][3], fmaf(b_b, xsm.y, tot[nt][3]));
             }
           }
           __syncwarp();
@@ -447,6 +552,23 @@ grouped_qmm_stream_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __g
             }
           }
       }
+      if (dead) break;
+      __syncwarp();
+      if (lane == 0) bar_arrive(sbempty0 + 8u * sl);  // this warp is done with the item's scales
+      if (++sl == 2) {
+        sl = 0;
+        slph ^= 1;
+      }
+      }
+     }
+     it0 = run_end;
+    }
+    tm.acc[3] = clock64() - tb;
+    tm.flush(p.err + 20);
+    if ((p.debug & 32) && tid == 0) {
+      atomicMax(p.err + 24, (int)((clock64() - tb) >> 10));
+      atomicAdd(p.err + 25, (int)((clock64() - tb) >> 10));
+      atomicAdd(p.err + 26, i1 - i0);
     }
   }
   __syncthreads();
@@ -471,7 +593,8 @@ static EncodeTiledFnS encode_fn_s() {
 
 static size_t stream_fixed_smem(int K, int rows) {
   const int G = K / 64;
-  return (size_t)rows * (2 * K + 16) + sizeof(float) * (2 * G * rows + rows + 2) + 8 * (2 * MAX_RING + 1) + 16 + 1024;
+  const size_t sb = (size_t)2 * 4 * 64 * G * 2;  // two slots of scales + biases for 128 weight rows
+  return (size_t)rows * (2 * K + 16) + sizeof(float) * (2 * G * rows + rows + 2) + 8 * (2 * MAX_RING + 8) + 16 + sb + 1024;
 }
 
 }  // namespace
@@ -521,6 +644,10 @@ int launch_grouped_qmm_stream(const GroupedArgs& g, int nmat, int bits, int n_ex
   p.K = g.K;
   p.N = g.N;
   p.err = err;
+  {
+    static const int dbg = [] { const char* v = getenv("B200_TC_DEBUG"); return v ? atoi(v) : 0; }();
+    p.debug = dbg;
+  }
 
   static int n_sm = 0;
   if (!n_sm) {
@@ -528,9 +655,8 @@ int launch_grouped_qmm_stream(const GroupedArgs& g, int nmat, int bits, int n_ex
     B200_CUDA(cudaGetDevice(&dev));
     B200_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
   }
-  // 16 rows per pass once experts are expected to own more than eight rows (if the rows fit)
-  const int64_t per = rows / max_active;
-  const int nt = (per > 8 && stream_fixed_smem(g.K, 16) + 4 * STAGE_BYTES <= 227 * 1024) ? 2 : 1;
+  // 16 rows per pass as soon as some expert must own more than one row
+  const int nt = (rows > max_active && stream_fixed_smem(g.K, 16) + 4 * STAGE_BYTES <= 227 * 1024) ? 2 : 1;
   const size_t fixed = stream_fixed_smem(g.K, 8 * nt);
   int ring = (int)((227 * 1024 - fixed) / STAGE_BYTES);
   if (ring > MAX_RING) ring = MAX_RING;
