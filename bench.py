@@ -193,6 +193,8 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
+                    help="replay the step from a CUDA graph (auto: for steps of at most 1024 tokens)")
     ap.add_argument("--qmm-path", default="auto", choices=["auto", "small", "stream", "tensor_core"],
                     help="pin the grouped-product kernel (default: the library chooses)")
     args = ap.parse_args()
@@ -235,12 +237,30 @@ def main():
         x = torch.randn(Tp, H, generator=g, device=dev, dtype=torch.float32).bfloat16()
         out_holder = {}
 
-        def step():
+        def eager_step():
             out_holder["o"] = block.forward(x)
         l0 = ctx.launch_count()
+        eager_step()
+        launches = ctx.launch_count() - l0
+        # Decode-sized steps are launch-bound when driven call by call from Python; like a serving
+        # loop would, the timed step replays a CUDA graph of the same library call (same kernels,
+        # same inputs resident in HBM).  Prefill-sized steps run eagerly.
+        use_graph = args.graph == "on" or (args.graph == "auto" and Tp <= 1024)
+        step = eager_step
+        if use_graph:
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    eager_step()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                eager_step()
+            step = graph.replay
         ms = time_steps(torch, step, steps, warmup, flush)
-        launches = (ctx.launch_count() - l0) // (steps + warmup)
-        res = dict(tokens=Tp, ms_per_step=statistics.mean(ms), ms_min=min(ms), launches_per_step=launches)
+        res = dict(tokens=Tp, ms_per_step=statistics.mean(ms), ms_min=min(ms), launches_per_step=launches,
+                   cuda_graph=use_graph)
         res["tokens_per_s"] = Tp / (res["ms_per_step"] * 1e-3)
         # routing actually taken -> algorithmic bytes of this batch
         _, aux = block.forward(x, return_aux=True)
@@ -295,7 +315,7 @@ def main():
                 r, _ = point(Tp, max(5, min(args.steps, 10)), 3, True)
             gu = r["gate_up"]
             decode = Tp < 1024
-            sweep.append(dict(tokens=Tp, tokens_per_s=r["tokens_per_s"], ms=r["ms_per_step"],
+            sweep.append(dict(tokens=Tp, tokens_per_s=r["tokens_per_s"], ms=r["ms_per_step"], cuda_graph=r["cuda_graph"],
                               active_experts=r["active_experts"], launches=r["launches_per_step"],
                               block_frac_hbm=r["block_gbs"] / peaks["hbm"], block_frac_tensor=r["block_tflops"] / peaks["tensor"],
                               gate_up_ms=gu["ms"], gate_up_frac=(gu["gbs"] / peaks["hbm"]) if decode else (gu["tflops"] / peaks["tensor"]),
@@ -315,7 +335,7 @@ def main():
                 ms_per_step=main_res["ms_per_step"], higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
                 data="synthetic",
                 config=dict(workload=workload_name(T), tokens=T, l2="flushed between iterations (512 MB overwrite)",
-                            parallelism="single GPU", **SHAPE),
+                            parallelism="single GPU", cuda_graph=main_res["cuda_graph"], **SHAPE),
                 roofline=roof, cpu_baseline=base, e2e=e2e, gpu_launches=main_res["launches_per_step"] * args.steps,
                 clocks=clocks, block=dict(active_experts=main_res["active_experts"], gbs=main_res["block_gbs"],
                                           tflops=main_res["block_tflops"], stage_ms=main_res["stage_ms"]),

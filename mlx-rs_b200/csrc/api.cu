@@ -470,6 +470,11 @@ int b200_moe_permute(b200_ctx* c, const uint32_t* indices, int64_t n, int E, uin
 // Which grouped-product kernel a block of n assignments over at most `max_active` experts uses.
 static bool use_tensor_core_path(const b200_ctx* c, const b200_moe_config& cfg, int64_t n, int max_active) {
   if (!prefill_shape_ok(cfg.hidden, cfg.inter, 2) || !prefill_shape_ok(cfg.inter, cfg.hidden, 1)) return false;
+  // the memory-bound kernels stage eight activation rows of length K in shared memory; beyond
+  // that (e.g. the 14336-wide down projection of a Mixtral-shaped layer) only the tensor-core
+  // kernel, which streams activations by TMA, applies
+  const int kmax = cfg.hidden > cfg.inter ? cfg.hidden : cfg.inter;
+  if ((size_t)8 * (2 * kmax + 16) + sizeof(float) * (kmax / 64) * 8 > 220 * 1024) return true;
   if (c->qmm_path == B200_QMM_SMALL || c->qmm_path == B200_QMM_STREAM) return false;
   if (c->qmm_path == B200_QMM_TENSOR_CORE) return true;
   return n / (max_active > 0 ? max_active : 1) >= 24;

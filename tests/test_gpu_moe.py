@@ -124,6 +124,22 @@ def test_prefill_512_tokens_config0_shape(pkg, O, config0, qmm_path):
     assert close_up_to_bf16_rounding(yk.float().cpu().numpy(), ref_yk, TOL)
 
 
+def test_config3_shape_reduced_experts(pkg, O, qmm_path):
+    # BASELINE.json configs[3] (Qwen3-235B-A22B layer: hidden 4096, inter 1536, top-8 renormalised, 4-bit)
+    # with 16 of its 128 experts so that the CPU oracle finishes in seconds; 300 tokens
+    check_block(pkg, O, make_block(300, 4096, 16, 1536, 8, seed=33))
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("T", [3, 400])
+def test_config4_shape_reduced_experts(pkg, O, bits, T):
+    # BASELINE.json configs[4] (Mixtral layer: hidden 4096, inter 14336, top-2 of 8, softmax over the
+    # selected, Zipf(1.2) skew) with 4 experts; K = 14336 in the down projection exceeds what the
+    # memory-bound kernels can stage, so both token counts run on the tensor-core kernel
+    blk = make_block(T, 4096, 4, 14336, 2, bits=bits, seed=44 + T, zipf_bias=True)
+    check_block(pkg, O, blk, mode=1, renorm=False)
+
+
 def test_no_renorm_and_ties(pkg, O):
     blk = make_block(50, 256, 16, 128, 4, seed=21)
     blk["wr"][7] = blk["wr"][3]          # exact ties between two experts on every token
