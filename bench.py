@@ -183,8 +183,81 @@ def workload_name(T):
     return f"configs[1] point T={T}: Qwen3-30B-A3B MoE layer (H2048 E128 top-8 I768, 4-bit g64), bf16 N(0,1) tokens"
 
 
+def run_stack(args, pkg, torch, dev, peaks):
+    """BASELINE.json configs[2]: 48 pre-RMSNorm MoE blocks with residuals, a 2048-token prefill followed
+    by 256 single-token decode steps (each step feeds the previous output row back in).  One bench
+    step = the whole sequence.  The decode step (48 layers, ~390 kernels) is replayed from a CUDA graph."""
+    import statistics as st
+    n_layers, t_prefill, n_decode = args.layers, 2048, 256
+    H = SHAPE["hidden"]
+    ctx = pkg.default_context()
+    blocks = [build_block(pkg, torch, args.seed + l, SHAPE, dev) for l in range(n_layers)]
+    stack = pkg.nn.MoeStack(blocks, eps=1e-6)
+    ctx.reserve(blocks[0].config, t_prefill)
+    g = torch.Generator(device=dev).manual_seed(args.seed + 99)
+    xp = torch.randn(t_prefill, H, generator=g, device=dev, dtype=torch.float32).bfloat16()
+    xd = torch.zeros(1, H, dtype=torch.bfloat16, device=dev)
+    holder = {}
+
+    def decode_step():
+        holder["o"] = stack.forward(xd)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        decode_step()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        decode_step()
+
+    def sequence():
+        out = stack.forward(xp)
+        xd.copy_(out[-1:])
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(n_decode):
+            graph.replay()
+            xd.copy_(holder["o"])
+        ev1.record()
+        return ev0, ev1
+    for _ in range(max(1, args.warmup // 3)):
+        sequence()
+    torch.cuda.synchronize()
+    tot, dec = [], []
+    l0 = ctx.launch_count()
+    with ClockSampler(dev.index or 0) as clk:
+        for _ in range(args.steps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            e0, e1 = sequence()
+            b.record()
+            torch.cuda.synchronize()
+            tot.append(a.elapsed_time(b))
+            dec.append(e0.elapsed_time(e1))
+    ms, dms = st.mean(tot), st.mean(dec)
+    we = expert_bytes(H, SHAPE["inter"], SHAPE["bits"])
+    dec_bytes = n_layers * (SHAPE["top_k"] * we + SHAPE["n_experts"] * H * 2)
+    line = dict(metric=METRIC, value=(t_prefill + n_decode) / (ms * 1e-3), unit=UNIT, n_gpus=1, steps=args.steps,
+                warmup=args.warmup, ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+                data="synthetic",
+                config=dict(workload=f"configs[2]: {n_layers} x (RMSNorm eps 1e-6 + MoE block + residual), 2048-token prefill "
+                                     "then 256 decode steps", l2="working set 16 GB per pass, far larger than L2",
+                            parallelism="single GPU", cuda_graph="decode steps", **SHAPE),
+                prefill=dict(tokens=t_prefill, ms=ms - dms, tokens_per_s=t_prefill / ((ms - dms) * 1e-3)),
+                decode=dict(steps=n_decode, ms_per_token=dms / n_decode, tokens_per_s=n_decode / (dms * 1e-3),
+                            hbm_gbs=dec_bytes / (dms / n_decode * 1e-3) / 1e9,
+                            frac_hbm=dec_bytes / (dms / n_decode * 1e-3) / 1e9 / peaks["hbm"]),
+                roofline=dict(bound="hbm", achieved=dec_bytes / (dms / n_decode * 1e-3) / 1e9, peak=peaks["hbm"], unit="GB/s",
+                              frac=dec_bytes / (dms / n_decode * 1e-3) / 1e9 / peaks["hbm"], traffic=None,
+                              peak_source=peaks["source"], kernel="whole 48-layer decode step (all kernels)"),
+                cpu_baseline=None, e2e=None, gpu_launches=ctx.launch_count() - l0, clocks=clk.summary())
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="layer", choices=["layer", "stack"],
+                    help="layer: one MoE layer (configs[1], the metric's config); stack: configs[2]")
+    ap.add_argument("--layers", type=int, default=48)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
@@ -222,6 +295,8 @@ def main():
         ep = import_module("mlx_rs_b200.ep")
         return ep.bench_main(args, pkg, SHAPE, peaks, METRIC, UNIT, workload_name)
 
+    if args.workload == "stack":
+        return run_stack(args, pkg, torch, dev, peaks)
     ctx = pkg.default_context()
     ctx.set_qmm_path(dict(auto=ctx.QMM_AUTO, small=ctx.QMM_SMALL, stream=ctx.QMM_STREAM, tensor_core=ctx.QMM_TENSOR_CORE)[args.qmm_path])
     block = build_block(pkg, torch, args.seed, SHAPE, dev)

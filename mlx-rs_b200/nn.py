@@ -125,3 +125,27 @@ def router_topk(x, gate_weight, top_k, router_mode=ROUTER_SOFTMAX_TOPK, norm_top
     L.check(L.lib().b200_router_topk(ops._ctx(ctx), C.byref(cfg), L.ptr(x), L.ptr(gate_weight), L.ptr(logit_bias), T,
                                      L.ptr(idx), L.ptr(sc), L.ptr(lg), L.stream_ptr()))
     return (idx, sc, lg) if return_logits else (idx, sc)
+
+
+class MoeStack:
+    """A stack of pre-norm MoE blocks with residual connections and no attention (BASELINE.json
+    configs[2]): per layer  h <- h + block(rms_norm(h, weight, eps)), the wiring of a transformer
+    block's MLP half (mlx-lm/src/models/qwen3.rs:310-325) with the MLP replaced by the routed block.
+    The residual add of layer l is fused with the norm of layer l+1 (one kernel)."""
+
+    def __init__(self, blocks, norm_weights=None, eps=1e-6, ctx=None):
+        self.blocks, self.eps, self.ctx = list(blocks), eps, ctx
+        self.norm_weights = list(norm_weights) if norm_weights is not None else [None] * len(self.blocks)
+
+    def forward(self, x):
+        h = x
+        y = None
+        for blk, w in zip(self.blocks, self.norm_weights):
+            if y is None:
+                normed = ops.rms_norm(h, w, self.eps, ctx=self.ctx)
+            else:
+                h, normed = ops.add_rms_norm(h, y, w, self.eps, ctx=self.ctx)
+            y = blk.forward(normed)
+        out = torch.empty_like(h)
+        L.check(L.lib().b200_add(ops._ctx(self.ctx), L.ptr(h), L.ptr(y), h.numel(), L.ptr(out), L.stream_ptr()))
+        return out

@@ -191,3 +191,22 @@ def test_bad_config_is_rejected(pkg):
     with pytest.raises(pkg.B200Error):
         pkg.nn.router_topk(torch.zeros((4, 128), dtype=torch.bfloat16, device="cuda"),
                            torch.zeros((4, 128), dtype=torch.bfloat16, device="cuda"), 5)  # top_k > experts
+
+
+def test_stack_of_blocks_with_norm_and_residual(pkg, O):
+    # BASELINE.json configs[2] scaled down: 3 pre-RMSNorm (eps 1e-6, unit weight) MoE blocks with residuals
+    T, H, E, I, k = 40, 256, 8, 128, 2
+    blks = [make_block(T, H, E, I, k, seed=100 + l) for l in range(3)]
+    h = blks[0]["x"].copy()
+    for b in blks:                                   # oracle: bf16 tensor between ops, float32 inside
+        normed = O.round_bf16(O.rms_norm(h, None, 1e-6))
+        y = O.moe_block(normed, b["wr"], b["gate"], b["up"], b["down"], k)["out"]
+        h = O.round_bf16(h + y)
+    stack = pkg.nn.MoeStack([to_device(pkg, b) for b in blks], eps=1e-6)
+    got = stack.forward(bf16_cuda(blks[0]["x"])).float().cpu().numpy()
+    pkg.default_context().check()
+    # a last-bit difference in one layer's output can flip a near-tie in the next layer's routing,
+    # which changes that token's output discontinuously: judge token by token
+    rms = np.sqrt((h.astype(np.float64) ** 2).mean())
+    ok = np.all(np.abs(got - h) <= TOL * rms + 2.0 ** -7 * np.abs(h), axis=1)
+    assert ok.mean() >= 0.9, f"only {ok.mean():.2f} of the tokens agree"
