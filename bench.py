@@ -268,6 +268,9 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the step from a CUDA graph (auto: for steps of at most 1024 tokens)")
+    ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: peer = the library's dispatch/combine kernels over mapped peer memory; "
+                         "nccl = torch.distributed all-to-all-v (the baseline it is measured against)")
     ap.add_argument("--qmm-path", default="auto", choices=["auto", "small", "stream", "tensor_core"],
                     help="pin the grouped-product kernel (default: the library chooses)")
     args = ap.parse_args()
@@ -293,7 +296,7 @@ def main():
     if world > 1:
         from importlib import import_module
         ep = import_module("mlx_rs_b200.ep")
-        return ep.bench_main(args, pkg, SHAPE, peaks, METRIC, UNIT, workload_name)
+        return ep.bench_main(args, pkg, SHAPE, peaks, METRIC, UNIT, workload_name, ClockSampler)
 
     if args.workload == "stack":
         return run_stack(args, pkg, torch, dev, peaks)

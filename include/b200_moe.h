@@ -225,6 +225,45 @@ int b200_moe_combine(b200_ctx* ctx, const void* y_sorted, const uint32_t* inv_pe
 int b200_switch_glu_forward(b200_ctx* ctx, const b200_moe_config* cfg, const b200_moe_params* params, const void* x,
                             const uint32_t* indices, int64_t T, void* out, void* stream);
 
+/* SwitchGLU over rows that are already grouped by expert: rows bf16 [n, H] with counts[e] consecutive
+ * rows for expert e (device array, sum == n); out bf16 [n, H] in the same order.  The sorted-input
+ * case of SwitchGlu::forward (mlx-lm/src/models/switch_layers.rs, gather_qmm with sorted_indices)
+ * without the sort; used on the rows a rank receives in the expert-parallel exchange. */
+int b200_switch_glu_sorted(b200_ctx* ctx, const b200_moe_config* cfg, const b200_moe_params* params, const void* rows,
+                           const uint32_t* counts, int64_t n, void* out, void* stream);
+
+/* ---- expert parallelism over peer memory --------------------------------------------------------
+ * None of the b200_ep_* entry points has a counterpart in the reference, which has no distributed
+ * layer.  One process per GPU; rank r owns experts [r*E/G, (r+1)*E/G).  Every rank allocates two
+ * exchange buffers of capacity_rows x hidden bf16 (arriving rows, expert outputs) with
+ * b200_ep_buffer_alloc, passes the 64-byte handles to its peers by any host channel, and maps
+ * theirs with b200_ep_buffer_open.  Row numbering on the owning rank: by local expert, then by
+ * source rank, then in the source's sorted order.  No kernel here waits on another GPU: the
+ * caller orders the phases with stream-ordered collectives that every rank joins
+ * (all-gather of the counts -> layout -> dispatch -> barrier -> b200_switch_glu_sorted ->
+ * barrier -> combine; the next step's all-gather keeps buffers from being overwritten early). */
+#define B200_EP_HANDLE_BYTES 64
+int b200_ep_buffer_alloc(b200_ctx* ctx, size_t bytes, void** ptr, unsigned char* handle);
+int b200_ep_buffer_open(b200_ctx* ctx, const unsigned char* handle, void** ptr);
+int b200_ep_buffer_close(b200_ctx* ctx, void* ptr);
+int b200_ep_buffer_free(b200_ctx* ctx, void* ptr);
+/* all_counts [n_ranks, n_experts] (rows rank s routes to expert e, on the device) ->
+ * dst_row0 [n_experts]: row on the owner of e where this rank's rows of e start;
+ * local_counts [n_experts / n_ranks]: rows arriving here per local expert. */
+int b200_ep_layout(b200_ctx* ctx, const uint32_t* all_counts, int n_ranks, int n_experts, int rank, uint32_t capacity_rows,
+                   uint32_t* dst_row0, uint32_t* local_counts, void* stream);
+/* Gather into expert order fused with the send: sorted position j (assignment perm[j], token
+ * perm[j] / top_k, expert indices[perm[j]]) is stored into the owner's rows buffer
+ * peer_rows[owner] (host array of n_ranks device pointers, own entry local). */
+int b200_ep_dispatch(b200_ctx* ctx, const void* x, const uint32_t* indices, const uint32_t* perm, const uint32_t* offsets,
+                     const uint32_t* dst_row0, int64_t n, int top_k, int64_t hidden, int n_experts, int n_ranks,
+                     void* const* peer_rows, uint32_t capacity_rows, void* stream);
+/* Return fused with the weighted combine: out[t, :] = bf16( sum_j scores[t, j] * y_owner[row(t, j), :] ),
+ * float32 accumulation, j ascending, read from the owners' output buffers peer_y. */
+int b200_ep_combine(b200_ctx* ctx, void* const* peer_y, const uint32_t* indices, const uint32_t* inv_perm,
+                    const uint32_t* offsets, const uint32_t* dst_row0, const void* scores, int64_t T, int top_k,
+                    int64_t hidden, int n_experts, int n_ranks, uint32_t capacity_rows, void* out, void* stream);
+
 /* MoE block forward: x bf16 [T, H] -> out bf16 [T, H]; aux may be NULL. */
 int b200_moe_block_forward(b200_ctx* ctx, const b200_moe_config* cfg, const b200_moe_params* params, const void* x,
                            int64_t T, void* out, const b200_moe_aux* aux, void* stream);

@@ -60,6 +60,19 @@ EXPORTS = {
                                  C.c_void_p, C.c_void_p]),
     "b200_moe_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int64,
                                    C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200_switch_glu_sorted": (C.c_int, [C.c_void_p, C.POINTER(MoeConfig), C.POINTER(MoeParams), C.c_void_p, C.c_void_p,
+                                         C.c_int64, C.c_void_p, C.c_void_p]),
+    "b200_ep_buffer_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
+    "b200_ep_buffer_open": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]),
+    "b200_ep_buffer_close": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b200_ep_buffer_free": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b200_ep_layout": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_void_p, C.c_void_p,
+                                 C.c_void_p]),
+    "b200_ep_dispatch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                   C.c_int, C.c_int64, C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_uint32, C.c_void_p]),
+    "b200_ep_combine": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                  C.c_void_p, C.c_int64, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_uint32, C.c_void_p,
+                                  C.c_void_p]),
     "b200_rms_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int64, C.c_int64, C.c_void_p,
                                 C.c_void_p]),
     "b200_add_rms_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int64, C.c_int64,

@@ -1,6 +1,7 @@
 // C ABI of the library (see include/b200_moe.h): argument validation, scratch management and
 // the composition of kernels behind every entry point.  No kernel lives here.
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -169,7 +170,10 @@ int b200_ctx_check(b200_ctx* c, void* stream) {
   B200_CUDA(cudaMemcpy(&h, c->err, sizeof(int), cudaMemcpyDeviceToHost));
   if (h != 0) {
     B200_CUDA(cudaMemset(c->err, 0, sizeof(int)));
-    B200_FAIL(h == 2 ? "an expert index was out of range" : "a gather index was out of range");
+    B200_FAIL(h == 2   ? "an expert index was out of range"
+              : h == 3 ? "a rank would receive more rows than its exchange buffers hold"
+              : h == 4 ? "an expert-parallel routing table was inconsistent"
+                       : "a gather index was out of range");
   }
   return 0;
 }
@@ -480,6 +484,14 @@ static bool use_tensor_core_path(const b200_ctx* c, const b200_moe_config& cfg, 
   return n / (max_active > 0 ? max_active : 1) >= 24;
 }
 
+// Gate/up and down products over rows that are grouped by expert (offsets/active/n_active describe
+// the groups).  `perm` non-null: source row of sorted position p is perm[p] / src_div and the output
+// row is perm[p] (un-sorted on the fly); `perm` null: rows are already in expert order and stay so.
+static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_moe_params& p, const void* x,
+                          const uint32_t* perm, int src_div, const uint32_t* counts, const uint32_t* offsets,
+                          const uint32_t* active, const uint32_t* n_active, int64_t n, const void* scores, void* yk,
+                          cudaStream_t st, bool* yk_is_bf16);
+
 // Shared tail of switch_glu_forward and moe_block_forward: permute, gate/up, down.
 // `scores` null: unweighted per-assignment outputs go to `yk` ([T*k, H]).
 static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_moe_params& p, const void* x,
@@ -494,8 +506,7 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
   uint32_t* active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
   uint32_t* n_active = static_cast<uint32_t*>(c->take(16));
   uint32_t* chunk = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * permute_scratch_words(n, E)));
-  void* h = c->take(sizeof(uint16_t) * n * cfg.inter);
-  B200_REQUIRE(perm && inv && counts && offsets && active && n_active && chunk && h, "scratch arena too small");
+  B200_REQUIRE(perm && inv && counts && offsets && active && n_active && chunk, "scratch arena too small");
   if (aux) {
     if (aux->perm) perm = aux->perm;
     if (aux->inv_perm) inv = aux->inv_perm;
@@ -504,6 +515,16 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
   }
   launch_permute(idx, n, E, perm, inv, counts, offsets, active, n_active, chunk, c->err, st);
   LAUNCHED(c, permute_launches(n));
+  return experts_sorted(c, cfg, p, x, perm, cfg.top_k, counts, offsets, active, n_active, n, scores, yk, st, yk_is_bf16);
+}
+
+static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_moe_params& p, const void* x,
+                          const uint32_t* perm, int src_div, const uint32_t* counts, const uint32_t* offsets,
+                          const uint32_t* active, const uint32_t* n_active, int64_t n, const void* scores, void* yk,
+                          cudaStream_t st, bool* yk_is_bf16) {
+  const int E = cfg.n_experts;
+  void* h = c->take(sizeof(uint16_t) * n * cfg.inter);
+  B200_REQUIRE(h, "scratch arena too small");
   const int max_active = (int)(E < n ? E : n);
 
   // Regime: the tensor-core path once experts own enough rows to fill 128-row tiles.
@@ -540,8 +561,8 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
   gu.active = active;
   gu.n_active = n_active;
   gu.perm = perm;
-  gu.src_mode = kSrcPermDiv;
-  gu.src_div = cfg.top_k;
+  gu.src_mode = perm ? kSrcPermDiv : kSrcIdent;
+  gu.src_div = src_div;
   gu.dst_perm = 0;
   gu.out = h;
   gu.K = cfg.hidden;
@@ -549,7 +570,7 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
   gu.n_experts = E;
   if (tc) {
     // rows gathered into expert order, converted to row-normalised fp16, in the k order the 4-bit unpack produces
-    launch_prepare_rows(x, perm, cfg.top_k, n, cfg.hidden, cfg.bits == 4, xs, rs_x, st);
+    launch_prepare_rows(x, perm, perm ? src_div : 1, n, cfg.hidden, cfg.bits == 4, xs, rs_x, st);
     if (launch_grouped_qmm_tc(xs, rs_x, n, gu, 2, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, c->err,
                               st))
       return 1;
@@ -569,7 +590,7 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
   dn.n_active = n_active;
   dn.perm = perm;
   dn.src_mode = kSrcIdent;
-  dn.dst_perm = 1;
+  dn.dst_perm = perm ? 1 : 0;
   dn.row_scale = scores;
   dn.out = yk;
   // weighted rows stay float32 until the combine (storing them as bf16 halves the traffic of the
@@ -646,6 +667,124 @@ int b200_moe_block_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_m
   if (launch_combine(yk, yk_bf16, T, cfg->top_k, cfg->hidden, out, aux ? aux->out_f32 : nullptr, st)) return 1;
   c->mark(6, st);
   c->ev_valid = c->profiling;
+  LAUNCHED(c, 1);
+  return 0;
+}
+
+// ---- expert-parallel exchange over peer memory ----------------------------------------------------
+
+int b200_switch_glu_sorted(b200_ctx* c, const b200_moe_config* cfg, const b200_moe_params* params, const void* rows,
+                           const uint32_t* counts, int64_t n, void* out, void* stream) {
+  CTX_ENTER(c);
+  if (check_cfg(cfg) || check_params(params, false)) return 1;
+  B200_REQUIRE(n >= 0 && n < (int64_t(1) << 31), "bad row count");
+  if (n == 0) return 0;
+  B200_REQUIRE(rows && counts && out, "null tensor");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  b200_moe_config one = *cfg;
+  one.top_k = 1;  // n rows, one assignment each
+  if (ctx_grow(c, block_scratch_bytes(one, n))) return 1;
+  const int E = cfg->n_experts;
+  uint32_t* offsets = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  uint32_t* active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  uint32_t* n_active = static_cast<uint32_t*>(c->take(16));
+  B200_REQUIRE(offsets && active && n_active, "scratch arena too small");
+  launch_segments_from_counts(counts, E, offsets, active, n_active, st);
+  LAUNCHED(c, 1);
+  return experts_sorted(c, one, *params, rows, nullptr, 1, counts, offsets, active, n_active, n, nullptr, out, st, nullptr);
+}
+
+int b200_ep_buffer_alloc(b200_ctx* c, size_t bytes, void** ptr, unsigned char* handle) {
+  CTX_ENTER(c);
+  B200_REQUIRE(ptr && handle && bytes > 0, "bad arguments");
+  static_assert(sizeof(cudaIpcMemHandle_t) == B200_EP_HANDLE_BYTES, "handle size");
+  void* p = nullptr;
+  B200_CUDA(cudaMalloc(&p, bytes));
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    B200_FAIL(std::string("cudaIpcGetMemHandle -> ") + cudaGetErrorString(e));
+  }
+  memcpy(handle, &h, sizeof(h));
+  *ptr = p;
+  return 0;
+}
+
+int b200_ep_buffer_open(b200_ctx* c, const unsigned char* handle, void** ptr) {
+  CTX_ENTER(c);
+  B200_REQUIRE(ptr && handle, "bad arguments");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  B200_CUDA(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return 0;
+}
+
+int b200_ep_buffer_close(b200_ctx* c, void* ptr) {
+  CTX_ENTER(c);
+  if (ptr) B200_CUDA(cudaIpcCloseMemHandle(ptr));
+  return 0;
+}
+
+int b200_ep_buffer_free(b200_ctx* c, void* ptr) {
+  CTX_ENTER(c);
+  if (ptr) {
+    B200_CUDA(cudaDeviceSynchronize());
+    B200_CUDA(cudaFree(ptr));
+  }
+  return 0;
+}
+
+static int fill_peers(EpPeers& pe, void* const* peers, int G) {
+  B200_REQUIRE(peers != nullptr && G >= 1 && G <= kEpMaxRanks, "between 1 and 16 ranks");
+  for (int i = 0; i < kEpMaxRanks; ++i) pe.p[i] = i < G ? peers[i] : nullptr;
+  for (int i = 0; i < G; ++i) B200_REQUIRE(pe.p[i] != nullptr, "a peer buffer pointer is null");
+  return 0;
+}
+
+int b200_ep_layout(b200_ctx* c, const uint32_t* all_counts, int n_ranks, int n_experts, int rank, uint32_t capacity_rows,
+                   uint32_t* dst_row0, uint32_t* local_counts, void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(all_counts && dst_row0 && local_counts, "null tensor");
+  B200_REQUIRE(n_ranks >= 1 && n_ranks <= kEpMaxRanks && rank >= 0 && rank < n_ranks, "bad rank");
+  B200_REQUIRE(n_experts > 0 && n_experts % n_ranks == 0, "experts must divide evenly over the ranks");
+  launch_ep_layout(all_counts, n_ranks, n_experts, rank, capacity_rows, dst_row0, local_counts, c->err,
+                   static_cast<cudaStream_t>(stream));
+  LAUNCHED(c, 1);
+  return 0;
+}
+
+int b200_ep_dispatch(b200_ctx* c, const void* x, const uint32_t* indices, const uint32_t* perm, const uint32_t* offsets,
+                     const uint32_t* dst_row0, int64_t n, int top_k, int64_t hidden, int n_experts, int n_ranks,
+                     void* const* peer_rows, uint32_t capacity_rows, void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(n >= 0 && n < (int64_t(1) << 31) && top_k > 0, "bad row count");
+  B200_REQUIRE(hidden > 0 && hidden % 8 == 0, "hidden must be a multiple of 8");
+  B200_REQUIRE(n_experts > 0 && n_ranks > 0 && n_experts % n_ranks == 0, "experts must divide evenly over the ranks");
+  EpPeers pe;
+  if (fill_peers(pe, peer_rows, n_ranks)) return 1;
+  if (n == 0) return 0;
+  B200_REQUIRE(x && indices && perm && offsets && dst_row0, "null tensor");
+  launch_ep_dispatch(x, indices, perm, offsets, dst_row0, n, top_k, hidden, n_experts, n_ranks, pe, capacity_rows, c->err,
+                     static_cast<cudaStream_t>(stream));
+  LAUNCHED(c, 1);
+  return 0;
+}
+
+int b200_ep_combine(b200_ctx* c, void* const* peer_y, const uint32_t* indices, const uint32_t* inv_perm,
+                    const uint32_t* offsets, const uint32_t* dst_row0, const void* scores, int64_t T, int top_k,
+                    int64_t hidden, int n_experts, int n_ranks, uint32_t capacity_rows, void* out, void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(T >= 0 && top_k > 0 && T * top_k < (int64_t(1) << 31), "bad token count");
+  B200_REQUIRE(hidden > 0 && hidden % 8 == 0, "hidden must be a multiple of 8");
+  B200_REQUIRE(n_experts > 0 && n_ranks > 0 && n_experts % n_ranks == 0, "experts must divide evenly over the ranks");
+  EpPeers pe;
+  if (fill_peers(pe, peer_y, n_ranks)) return 1;
+  if (T == 0) return 0;
+  B200_REQUIRE(indices && inv_perm && offsets && dst_row0 && scores && out, "null tensor");
+  if (launch_ep_combine(pe, indices, inv_perm, offsets, dst_row0, scores, T, top_k, hidden, n_experts, n_ranks,
+                        capacity_rows, out, c->err, static_cast<cudaStream_t>(stream)))
+    return 1;
   LAUNCHED(c, 1);
   return 0;
 }

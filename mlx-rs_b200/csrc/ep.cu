@@ -1,0 +1,201 @@
+// Expert-parallel exchange over peer memory (one process per GPU, all GPUs of one NVSwitch node).
+//
+// The reference has no distributed layer; these kernels exist because the routed block shards
+// naturally by expert.  Rank r owns the contiguous experts [r*Eg, (r+1)*Eg).  Every rank holds two
+// exchange buffers that its peers map (CUDA IPC): `rows` (tokens arriving for its experts) and
+// `y` (its experts' outputs).  Both use the same row numbering on the owning rank:
+//
+//     [local expert 0: rows from rank 0 | rank 1 | ... ][local expert 1: ...] ...
+//
+// so arriving rows are already grouped by expert and the grouped products run on them in place.
+//   dispatch : the gather into expert order and the send are one kernel - each sorted row is read
+//              from this rank's tokens and stored straight into the owner's `rows` buffer
+//              (plain 16-byte peer stores over NVLink).
+//   combine  : the return and the weighted k-way sum are one kernel - each token reads its k
+//              expert outputs straight out of the owners' `y` buffers (peer loads) and
+//              accumulates in float32.
+// Neither kernel waits on another GPU.  Ordering between ranks comes from stream-ordered
+// collectives issued by the host layer between the phases (a kernel's peer stores are complete
+// when it ends; a collective that every rank joins after that kernel cannot finish anywhere
+// before all of those kernels have ended).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace b200 {
+
+// ---- segment tables from per-expert counts ------------------------------------------------
+__global__ void segments_from_counts_kernel(const uint32_t* __restrict__ counts, int E, uint32_t* __restrict__ offsets,
+                                            uint32_t* __restrict__ active, uint32_t* __restrict__ n_active) {
+  if (threadIdx.x != 0) return;
+  uint32_t run = 0, na = 0;
+  for (int e = 0; e < E; ++e) {
+    offsets[e] = run;
+    const uint32_t c = counts[e];
+    if (c) active[na++] = e;
+    run += c;
+  }
+  offsets[E] = run;
+  *n_active = na;
+}
+
+int launch_segments_from_counts(const uint32_t* counts, int E, uint32_t* offsets, uint32_t* active, uint32_t* n_active,
+                                cudaStream_t st) {
+  segments_from_counts_kernel<<<1, 32, 0, st>>>(counts, E, offsets, active, n_active);
+  return 0;
+}
+
+// ---- where this rank's rows land on their owners ---------------------------------------------
+// all_counts[s*E + e] = rows that rank s routes to expert e.  For this rank (`rank`):
+//   dst_row0[e]     = row, in the buffers of the rank that owns e, of this rank's first row of e
+//   local_counts[l] = rows arriving here for local expert l (summed over sources)
+// *err is set when a rank would receive more than `capacity` rows.
+__global__ void ep_layout_kernel(const uint32_t* __restrict__ all_counts, int G, int E, int rank, uint32_t capacity,
+                                 uint32_t* __restrict__ dst_row0, uint32_t* __restrict__ local_counts,
+                                 int* __restrict__ err) {
+  const int Eg = E / G;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int d = e / Eg, first = d * Eg;
+    uint32_t row = 0;
+    for (int f = first; f < e; ++f)
+      for (int s = 0; s < G; ++s) row += all_counts[s * E + f];
+    for (int s = 0; s < rank; ++s) row += all_counts[s * E + e];
+    dst_row0[e] = row;
+    if (row + all_counts[rank * E + e] > capacity) *err = 3;
+    if (d == rank) {
+      uint32_t c = 0;
+      for (int s = 0; s < G; ++s) c += all_counts[s * E + e];
+      local_counts[e - first] = c;
+    }
+  }
+}
+
+int launch_ep_layout(const uint32_t* all_counts, int G, int E, int rank, uint32_t capacity, uint32_t* dst_row0,
+                     uint32_t* local_counts, int* err, cudaStream_t st) {
+  ep_layout_kernel<<<1, 256, 0, st>>>(all_counts, G, E, rank, capacity, dst_row0, local_counts, err);
+  return 0;
+}
+
+// ---- dispatch: gather into expert order + store to the owning rank ----------------------------
+// Sorted position j holds assignment a = perm[j] (token a / k, expert idx[a]).
+__global__ void __launch_bounds__(256) ep_dispatch_kernel(const uint4* __restrict__ x, const uint32_t* __restrict__ idx,
+                                                          const uint32_t* __restrict__ perm,
+                                                          const uint32_t* __restrict__ offsets,
+                                                          const uint32_t* __restrict__ dst_row0, int64_t n, uint32_t k,
+                                                          int vec_per_row, int E, int Eg, EpPeers peers,
+                                                          uint32_t capacity, int* __restrict__ err) {
+  for (int64_t j = blockIdx.x; j < n; j += gridDim.x) {
+    const uint32_t a = perm[j];
+    if (a >= n) {
+      if (threadIdx.x == 0) *err = 4;
+      continue;
+    }
+    const uint32_t e = idx[a];
+    if (e >= (uint32_t)E) {
+      if (threadIdx.x == 0) *err = 4;
+      continue;
+    }
+    const uint32_t row = dst_row0[e] + (uint32_t)j - offsets[e];
+    if (row >= capacity) {
+      if (threadIdx.x == 0) *err = 3;
+      continue;
+    }
+    const uint4* src = x + (size_t)(a / k) * vec_per_row;
+    uint4* dst = static_cast<uint4*>(peers.p[e / Eg]) + (size_t)row * vec_per_row;
+    for (int c = threadIdx.x; c < vec_per_row; c += blockDim.x) dst[c] = __ldg(src + c);
+  }
+}
+
+int launch_ep_dispatch(const void* x, const uint32_t* idx, const uint32_t* perm, const uint32_t* offsets,
+                       const uint32_t* dst_row0, int64_t n, int k, int64_t H, int E, int G, const EpPeers& peers,
+                       uint32_t capacity, int* err, cudaStream_t st) {
+  if (n == 0) return 0;
+  const int grid = (int)(n < 148 * 16 ? n : 148 * 16);
+  ep_dispatch_kernel<<<grid, 256, 0, st>>>(static_cast<const uint4*>(x), idx, perm, offsets, dst_row0, n, (uint32_t)k,
+                                           (int)(H / 8), E, E / G, peers, capacity, err);
+  return 0;
+}
+
+// ---- combine: read the k expert outputs from their owners + weighted sum ------------------------
+// out[t, :] = bf16( sum_j score[t, j] * y_owner(idx[t,j])[row(t, j), :] ), float32 accumulation, j ascending.
+__device__ __forceinline__ uint4 ld_cg_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+constexpr int kEpMaxTopK = 32;
+
+__global__ void __launch_bounds__(256) ep_combine_kernel(EpPeers peers, const uint32_t* __restrict__ idx,
+                                                         const uint32_t* __restrict__ inv,
+                                                         const uint32_t* __restrict__ offsets,
+                                                         const uint32_t* __restrict__ dst_row0,
+                                                         const unsigned short* __restrict__ scores, int64_t T, int k,
+                                                         int vec_per_row, int E, int Eg, uint32_t capacity,
+                                                         uint4* __restrict__ out, int* __restrict__ err) {
+  __shared__ const uint4* s_row[kEpMaxTopK];
+  __shared__ float s_w[kEpMaxTopK];
+  for (int64_t t = blockIdx.x; t < T; t += gridDim.x) {
+    __syncthreads();
+    if (threadIdx.x < k) {
+      const int64_t a = t * k + threadIdx.x;
+      const uint32_t e = idx[a];
+      const uint4* ptr = nullptr;
+      if (e < (uint32_t)E) {
+        const uint32_t row = dst_row0[e] + inv[a] - offsets[e];
+        if (row < capacity) ptr = static_cast<const uint4*>(peers.p[e / Eg]) + (size_t)row * vec_per_row;
+      }
+      if (!ptr) *err = 4;
+      s_row[threadIdx.x] = ptr;
+      s_w[threadIdx.x] = bf16_bits_to_f32(scores[a]);
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < vec_per_row; c += blockDim.x) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      int j = 0;
+      for (; j + 4 <= k; j += 4) {  // four peer loads in flight per thread
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = s_row[j + u] ? ld_cg_v4(s_row[j + u] + c) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float s = s_w[j + u];
+          const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            acc[2 * q] += s * __uint_as_float(w[q] << 16);
+            acc[2 * q + 1] += s * __uint_as_float(w[q] & 0xffff0000u);
+          }
+        }
+      }
+      for (; j < k; ++j) {
+        const uint4 v = s_row[j] ? ld_cg_v4(s_row[j] + c) : make_uint4(0, 0, 0, 0);
+        const float s = s_w[j];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          acc[2 * q] += s * __uint_as_float(w[q] << 16);
+          acc[2 * q + 1] += s * __uint_as_float(w[q] & 0xffff0000u);
+        }
+      }
+      uint4 o;
+      o.x = f32_to_bf16_bits(acc[0]) | (f32_to_bf16_bits(acc[1]) << 16);
+      o.y = f32_to_bf16_bits(acc[2]) | (f32_to_bf16_bits(acc[3]) << 16);
+      o.z = f32_to_bf16_bits(acc[4]) | (f32_to_bf16_bits(acc[5]) << 16);
+      o.w = f32_to_bf16_bits(acc[6]) | (f32_to_bf16_bits(acc[7]) << 16);
+      out[(size_t)t * vec_per_row + c] = o;
+    }
+  }
+}
+
+int launch_ep_combine(const EpPeers& peers, const uint32_t* idx, const uint32_t* inv, const uint32_t* offsets,
+                      const uint32_t* dst_row0, const void* scores, int64_t T, int k, int64_t H, int E, int G,
+                      uint32_t capacity, void* out, int* err, cudaStream_t st) {
+  if (T == 0) return 0;
+  B200_REQUIRE(k <= kEpMaxTopK, "top_k above 32");
+  const int grid = (int)(T < 148 * 16 ? T : 148 * 16);
+  ep_combine_kernel<<<grid, 256, 0, st>>>(peers, idx, inv, offsets, dst_row0, static_cast<const unsigned short*>(scores), T,
+                                          k, (int)(H / 8), E, E / G, capacity, static_cast<uint4*>(out), err);
+  return 0;
+}
+
+}  // namespace b200

@@ -83,4 +83,21 @@ int launch_dense_segments(uint32_t* counts, uint32_t* offsets, uint32_t* active,
 int launch_expand_indices(const uint32_t* lhs, const uint32_t* rhs, int64_t n_idx, int M, uint32_t* flat_expert,
                           uint32_t* flat_src, cudaStream_t st);
 
+
+// ep.cu (expert-parallel exchange over peer memory)
+constexpr int kEpMaxRanks = 16;
+struct EpPeers {
+  void* p[kEpMaxRanks];       // the same exchange buffer on every rank, indexed by rank (own entry = local pointer)
+};
+int launch_segments_from_counts(const uint32_t* counts, int E, uint32_t* offsets, uint32_t* active, uint32_t* n_active,
+                                cudaStream_t st);
+int launch_ep_layout(const uint32_t* all_counts, int G, int E, int rank, uint32_t capacity, uint32_t* dst_row0,
+                     uint32_t* local_counts, int* err, cudaStream_t st);
+int launch_ep_dispatch(const void* x, const uint32_t* idx, const uint32_t* perm, const uint32_t* offsets,
+                       const uint32_t* dst_row0, int64_t n, int k, int64_t H, int E, int G, const EpPeers& peers,
+                       uint32_t capacity, int* err, cudaStream_t st);
+int launch_ep_combine(const EpPeers& peers, const uint32_t* idx, const uint32_t* inv, const uint32_t* offsets,
+                      const uint32_t* dst_row0, const void* scores, int64_t T, int k, int64_t H, int E, int G,
+                      uint32_t capacity, void* out, int* err, cudaStream_t st);
+
 }  // namespace b200

@@ -10,12 +10,20 @@ a rank are already grouped by destination, so one forward is
           -> local SwitchGLU on the received rows -> combine all-to-all-v back
           -> weighted un-sort + k-way sum on the source rank.
 
-torch.distributed (NCCL over NVLink on GPUs, gloo on CPU in the tests) is the transport; the
-compute steps go through a small backend object so that the exchange protocol can be tested on
-CPU ranks.  Returned rows travel as bf16 (one rounding per expert output more than the
-single-GPU path, which keeps the weighted rows in float32).
+Two transports:
+
+* `PeerExpertParallelMoe` (the product path on GPUs): each rank maps its peers' exchange buffers
+  (CUDA IPC) and the library's own kernels move the rows - the gather into expert order stores
+  straight into the owner's buffer, the weighted combine reads the expert outputs straight out of
+  the owners' buffers.  NCCL carries only the [G, E] count table and two one-word barriers.
+* `ExpertParallelMoe`: torch.distributed all-to-all-v (NCCL on GPUs, gloo on CPU in the tests); the
+  compute steps go through a small backend object so that the exchange protocol can be tested on
+  CPU ranks.  It is the baseline the peer-memory path is measured against.
+
+Returned rows travel as bf16 in both (one rounding per expert output more than the single-GPU
+path, which keeps the weighted rows in float32).
 """
-import statistics
+import ctypes as C
 
 import torch
 import torch.distributed as dist
@@ -97,6 +105,121 @@ class ExpertParallelMoe:
         return out
 
 
+def layout_tables(all_counts, rank):
+    """Host mirror of b200_ep_layout (numpy/torch CPU ints): (dst_row0 [E], local_counts [E/G])."""
+    G, E = all_counts.shape
+    Eg = E // G
+    c = all_counts.to(torch.int64).cpu()
+    per_expert = c.sum(dim=0)                                   # rows arriving for every expert
+    dst_row0 = torch.zeros(E, dtype=torch.int64)
+    for e in range(E):
+        first = (e // Eg) * Eg
+        dst_row0[e] = per_expert[first:e].sum() + c[:rank, e].sum()
+    return dst_row0.to(torch.int32), per_expert[rank * Eg:(rank + 1) * Eg].to(torch.int32)
+
+
+class PeerBuffers:
+    """This rank's two exchange buffers (arriving rows, expert outputs; capacity_rows x hidden bf16
+    each) and the mapped addresses of every peer's.  Collective: every rank of `group` constructs it."""
+
+    def __init__(self, pkg, hidden, capacity_rows, group=None, ctx=None):
+        from . import _lib as L
+        self.L, self.ctx = L, (ctx or L.default_context())
+        self.group, self.hidden, self.capacity = group, hidden, int(capacity_rows)
+        self.rank, self.G = dist.get_rank(group), dist.get_world_size(group)
+        nbytes = self.capacity * hidden * 2
+        self.own, handles = [], []
+        for _ in range(2):
+            p = C.c_void_p()
+            h = C.create_string_buffer(64)
+            L.check(L.lib().b200_ep_buffer_alloc(self.ctx.handle, nbytes, C.byref(p), h))
+            self.own.append(p.value)
+            handles.append(bytes(h.raw))
+        gathered = [None] * self.G
+        dist.all_gather_object(gathered, handles, group=group)
+        self.rows_ptrs, self.y_ptrs, self._opened = [], [], []
+        for r in range(self.G):
+            for which, lst in ((0, self.rows_ptrs), (1, self.y_ptrs)):
+                if r == self.rank:
+                    lst.append(self.own[which])
+                else:
+                    p = C.c_void_p()
+                    L.check(L.lib().b200_ep_buffer_open(self.ctx.handle, gathered[r][which], C.byref(p)))
+                    lst.append(p.value)
+                    self._opened.append(p.value)
+        dist.barrier(group=group)
+
+    def close(self):
+        """Collective: unmap the peers' buffers, then (after every rank has) free this rank's."""
+        torch.cuda.synchronize()
+        for p in self._opened:
+            self.L.check(self.L.lib().b200_ep_buffer_close(self.ctx.handle, C.c_void_p(p)))
+        self._opened = []
+        dist.barrier(group=self.group)
+        for p in self.own:
+            self.L.check(self.L.lib().b200_ep_buffer_free(self.ctx.handle, C.c_void_p(p)))
+        self.own = []
+
+
+class PeerExpertParallelMoe:
+    """One forward = route -> sort -> all-gather of the counts -> dispatch kernel (peer stores) ->
+    barrier -> SwitchGLU on the arrived rows in place -> barrier -> combine kernel (peer loads).
+    The barriers are one-word all-reduces: stream-ordered, so no kernel of this library ever waits
+    on another GPU.  The next forward's all-gather is what keeps a fast rank from overwriting
+    buffers that a slow rank still reads."""
+
+    def __init__(self, pkg, gate_weight, local_switch_mlp, n_experts, top_k, buffers, norm_topk_prob=True,
+                 router_mode=0, router_logit_bias=None, ctx=None):
+        self.pkg, self.ctx, self.buf = pkg, ctx, buffers
+        self.gate_weight, self.mlp = gate_weight, local_switch_mlp
+        self.E, self.k = n_experts, top_k
+        self.norm, self.mode, self.bias = norm_topk_prob, router_mode, router_logit_bias
+        self.group, self.G, self.rank = buffers.group, buffers.G, buffers.rank
+        if n_experts % self.G:
+            raise ValueError("the number of experts must be divisible by the number of ranks")
+        dev = gate_weight.device
+        self._flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._all_counts = torch.empty((self.G, n_experts), dtype=torch.int32, device=dev)
+        self._rows_view = _device_view(buffers.own[0], buffers.capacity, buffers.hidden, dev)
+        self._y_view = _device_view(buffers.own[1], buffers.capacity, buffers.hidden, dev)
+        self.last = {}
+
+    def _barrier(self):
+        dist.all_reduce(self._flag, group=self.group)
+
+    def forward(self, x):
+        ops, E, k, G, cap = self.pkg.ops, self.E, self.k, self.G, self.buf.capacity
+        Eg = E // G
+        idx, scores = self.pkg.nn.router_topk(x, self.gate_weight, k, self.mode, self.norm, self.bias, ctx=self.ctx)
+        perm, inv, counts, offsets = ops.moe_permute(idx.reshape(-1), E, ctx=self.ctx)
+        dist.all_gather_into_tensor(self._all_counts.view(-1), counts, group=self.group)
+        dst_row0, local_counts = ops.ep_layout(self._all_counts, self.rank, cap, ctx=self.ctx)
+        table = self._all_counts.cpu().to(torch.int64)                 # the one host synchronisation of the step
+        arriving = table.view(G, G, Eg).sum(dim=(0, 2))
+        if int(arriving.max()) > cap:
+            raise self.pkg.B200Error(f"a rank would receive {int(arriving.max())} rows; the exchange buffers hold {cap}")
+        n_recv = int(arriving[self.rank])
+        ops.ep_dispatch(x, idx, perm, offsets, dst_row0, self.buf.rows_ptrs, cap, E, ctx=self.ctx)
+        self._barrier()
+        if n_recv:
+            self.mlp.forward_sorted(self._rows_view, local_counts, n_recv, out=self._y_view)
+        self._barrier()
+        out = ops.ep_combine(self.buf.y_ptrs, idx, inv, offsets, dst_row0, scores, x.shape[-1], cap, E, ctx=self.ctx)
+        mine = table[self.rank].view(G, Eg)
+        self.last = dict(idx=idx, scores=scores, perm=perm, counts=counts, recv_rows=n_recv,
+                         sent_rows=int(mine.sum() - mine[self.rank].sum()))
+        return out
+
+
+def _device_view(address, rows, cols, device):
+    """A torch bf16 [rows, cols] view of device memory the library allocated (no ownership)."""
+    class _Holder:
+        pass
+    h = _Holder()
+    h.__cuda_array_interface__ = dict(shape=(rows, cols), typestr="<i2", data=(int(address), False), version=3)
+    return torch.as_tensor(h, device=device).view(torch.bfloat16)
+
+
 def shard_switch_mlp(pkg, switch_mlp, rank, world):
     """The contiguous expert shard of a SwitchGlu for `rank` (views, no copy)."""
     E = switch_mlp.n_experts
@@ -108,7 +231,7 @@ def shard_switch_mlp(pkg, switch_mlp, rank, world):
     return pkg.nn.SwitchGlu(cut(switch_mlp.gate_proj), cut(switch_mlp.up_proj), cut(switch_mlp.down_proj))
 
 
-def bench_main(args, pkg, shape, peaks, metric, unit, workload_name):
+def bench_main(args, pkg, shape, peaks, metric, unit, workload_name, clock_sampler):
     """bench.py for N > 1: weak scaling, `--tokens` tokens per GPU, experts sharded E/N per GPU.
     Timing: barrier + synchronize, per-step CUDA events, max over ranks."""
     import json
@@ -130,8 +253,14 @@ def bench_main(args, pkg, shape, peaks, metric, unit, workload_name):
         lin.append(pkg.nn.QuantizedSwitchLinear.from_weight(w, shape["group_size"], shape["bits"]))
         del w
     mlp = pkg.nn.SwitchGlu(*lin)
-    be = B200Backend(pkg, wr, mlp, k)
-    ep = ExpertParallelMoe(be, E, k)
+    bufs = None
+    if args.ep_transport == "peer":
+        # every rank can at worst receive every assignment of every rank; 2x the balanced load is
+        # what this benchmark's random routing needs, and what a deployment would size by policy
+        bufs = PeerBuffers(pkg, H, min(T * k * world, 2 * T * k + 4096))
+        ep = PeerExpertParallelMoe(pkg, wr, mlp, E, k, bufs)
+    else:
+        ep = ExpertParallelMoe(B200Backend(pkg, wr, mlp, k), E, k)
     gx = torch.Generator(device=dev).manual_seed(args.seed + 2000 + rank)
     x = torch.randn(T, H, generator=gx, device=dev, dtype=torch.float32).bfloat16()
     flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
@@ -156,7 +285,8 @@ def bench_main(args, pkg, shape, peaks, metric, unit, workload_name):
         return ms.item() / steps
 
     l0 = ctx.launch_count()
-    ms = timed(lambda: ep.forward(x), args.steps, args.warmup)
+    with clock_sampler(local) as clk:
+        ms = timed(lambda: ep.forward(x), args.steps, args.warmup)
     launches = (ctx.launch_count() - l0) // (args.steps + args.warmup) * args.steps
     xh = x.cpu().pin_memory()
     oh = torch.empty_like(xh).pin_memory()
@@ -176,7 +306,9 @@ def bench_main(args, pkg, shape, peaks, metric, unit, workload_name):
                     dtype="bf16", data="synthetic",
                     config=dict(workload=workload_name(T) + f" per GPU, {Eg} experts per GPU", tokens_per_gpu=T,
                                 l2="flushed between iterations (512 MB overwrite)",
-                                parallelism=f"ep{world} (NCCL all-to-all-v dispatch + combine)", **shape),
+                                parallelism=f"ep{world} (" + ("dispatch/combine kernels over mapped peer memory"
+                                                              if bufs else "NCCL all-to-all-v dispatch + combine") + ")",
+                                **shape),
                     roofline=dict(bound="tensor", achieved=flops / (ms * 1e-3) / 1e12 / world, peak=peaks["tensor"],
                                   unit="TFLOP/s", frac=flops / (ms * 1e-3) / 1e12 / world / peaks["tensor"],
                                   traffic=None, peak_source=peaks["source"],
@@ -184,8 +316,11 @@ def bench_main(args, pkg, shape, peaks, metric, unit, workload_name):
                     cpu_baseline=None,
                     e2e=dict(value=total / (e2e_ms * 1e-3), unit=unit, h2d_bytes_per_step=xh.numel() * 2 * world,
                              d2h_bytes_per_step=oh.numel() * 2 * world),
-                    gpu_launches=launches,
+                    gpu_launches=launches, clocks=clk.summary(),
                     exchange=dict(rows_sent_off_rank_per_step=sent.item(), bytes_each_way=sent.item() * H * 2))
         print(json.dumps(line))
+    ctx.check()
+    if bufs is not None:
+        bufs.close()
     dist.barrier()
     dist.destroy_process_group()

@@ -72,6 +72,20 @@ class SwitchGlu:
         return out
 
 
+    def forward_sorted(self, rows, counts, n=None, out=None):
+        """SwitchGLU over rows already grouped by expert (counts[e] consecutive rows each): the
+        sorted-input case, without the sort.  `out` may be a preallocated [n, hidden] bf16 buffer."""
+        ops._cuda(rows, counts)
+        ops._req(rows.dtype == torch.bfloat16 and counts.dtype == torch.int32, "forward_sorted: bf16 rows, int32 counts")
+        n = rows.shape[0] if n is None else n
+        if out is None:
+            out = torch.empty((n, self.hidden), dtype=rows.dtype, device=rows.device)
+        cfg, params = self._cfg(1), self._params()
+        L.check(L.lib().b200_switch_glu_sorted(ops._ctx(self.ctx), C.byref(cfg), C.byref(params), L.ptr(rows),
+                                               L.ptr(counts), n, L.ptr(out), L.stream_ptr()))
+        return out
+
+
 class MoeBlock:
     """gate (router Linear, weight [E,H] bf16) + switch_mlp (SwitchGlu)."""
 

@@ -7,6 +7,8 @@ take_along_axis: mlx-rs/src/ops/indexing/mod.rs:424-453; rms_norm: mlx-rs/src/fa
 Tensors are torch CUDA tensors (torch only holds the memory).  Index tensors are int32 (same
 bits as the reference's uint32 for every valid index).  Calls are eager and stream-ordered.
 """
+import ctypes as C
+
 import torch
 
 from . import _lib as L
@@ -175,6 +177,45 @@ def moe_combine(y_sorted, inv_perm, scores, return_f32=False, ctx=None):
     L.check(L.lib().b200_moe_combine(_ctx(ctx), L.ptr(y_sorted), L.ptr(inv_perm), L.ptr(scores), T, k, H, L.ptr(out),
                                      L.ptr(o32), L.stream_ptr()))
     return (out, o32) if return_f32 else out
+
+
+def _ptr_array(ptrs):
+    arr = (C.c_void_p * len(ptrs))(*[int(v) for v in ptrs])
+    return arr
+
+
+def ep_layout(all_counts, rank, capacity_rows, ctx=None):
+    """all_counts int32 [G, E] (rows rank s routes to expert e) -> (dst_row0 [E], local_counts [E/G]):
+    where this rank's rows of each expert start in the owner's exchange buffers, and how many rows
+    arrive here per local expert."""
+    _cuda(all_counts)
+    G, E = all_counts.shape
+    dst_row0 = torch.empty(E, dtype=torch.int32, device=all_counts.device)
+    local_counts = torch.empty(E // G, dtype=torch.int32, device=all_counts.device)
+    L.check(L.lib().b200_ep_layout(_ctx(ctx), L.ptr(all_counts), G, E, rank, capacity_rows, L.ptr(dst_row0),
+                                   L.ptr(local_counts), L.stream_ptr()))
+    return dst_row0, local_counts
+
+
+def ep_dispatch(x, indices, perm, offsets, dst_row0, peer_rows, capacity_rows, n_experts, ctx=None):
+    """Store every sorted row of this rank into the rows buffer of the rank that owns its expert
+    (peer_rows: device addresses of all ranks' buffers, own entry included)."""
+    _cuda(x, indices, perm, offsets, dst_row0)
+    k = indices.shape[-1]
+    L.check(L.lib().b200_ep_dispatch(_ctx(ctx), L.ptr(x), L.ptr(indices), L.ptr(perm), L.ptr(offsets), L.ptr(dst_row0),
+                                     perm.numel(), k, x.shape[-1], n_experts, len(peer_rows), _ptr_array(peer_rows),
+                                     capacity_rows, L.stream_ptr()))
+
+
+def ep_combine(peer_y, indices, inv_perm, offsets, dst_row0, scores, hidden, capacity_rows, n_experts, ctx=None):
+    """out[t] = bf16(sum_j scores[t, j] * y row of assignment (t, j) read from its owner's buffer)."""
+    _cuda(indices, inv_perm, offsets, dst_row0, scores)
+    T, k = scores.shape
+    out = torch.empty((T, hidden), dtype=torch.bfloat16, device=scores.device)
+    L.check(L.lib().b200_ep_combine(_ctx(ctx), _ptr_array(peer_y), L.ptr(indices), L.ptr(inv_perm), L.ptr(offsets),
+                                    L.ptr(dst_row0), L.ptr(scores), T, k, hidden, n_experts, len(peer_y), capacity_rows,
+                                    L.ptr(out), L.stream_ptr()))
+    return out
 
 
 def moe_permute_static(indices, n_experts):

@@ -107,3 +107,31 @@ def test_helpers_for_split_sizes_and_local_ids():
     assert ep.split_sizes(counts) == [3, 3]
     assert ep.local_expert_ids(counts).tolist() == [0, 0, 2, 1, 1, 1]
     assert ep.local_expert_ids(torch.zeros((2, 3), dtype=torch.int32)).numel() == 0
+
+
+def test_peer_layout_tables_tile_every_receive_buffer():
+    """Host mirror of the peer-memory layout: the segments that all ranks write into one owner's
+    buffer are disjoint, gap-free, grouped by local expert and, within an expert, ordered by source."""
+    import __graft_entry__ as ge
+    from importlib import import_module
+    ge.load_package()
+    ep = import_module("mlx_rs_b200.ep")
+    rng = np.random.default_rng(0)
+    G, E = 4, 16
+    Eg = E // G
+    counts = rng.integers(0, 7, size=(G, E))
+    counts[:, 5] = 0                                    # an expert nobody picked
+    t = torch.from_numpy(counts.astype(np.int32))
+    tables = [ep.layout_tables(t, r) for r in range(G)]
+    for d in range(G):
+        segs = []
+        for el in range(Eg):
+            e = d * Eg + el
+            for s in range(G):
+                segs.append((int(tables[s][0][e]), int(counts[s, e]), el, s))
+        pos = 0
+        for start, length, el, s in segs:                # already in (expert, source) order
+            assert start == pos
+            pos += length
+        assert pos == counts[:, d * Eg:(d + 1) * Eg].sum()
+        assert np.array_equal(tables[d][1].numpy(), counts[:, d * Eg:(d + 1) * Eg].sum(axis=0))

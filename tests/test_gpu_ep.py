@@ -13,7 +13,7 @@ from tests.helpers import make_block
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, cfg, ret):
+def _worker(rank, world, port, cfg, transport, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -26,8 +26,13 @@ def _worker(rank, world, port, cfg, ret):
         blk = make_block(**cfg)
         full = to_device(pkg, blk)
         mlp = ep.shard_switch_mlp(pkg, full.switch_mlp, rank, world)
-        moe = ep.ExpertParallelMoe(ep.B200Backend(pkg, full.gate_weight, mlp, blk["k"]), blk["E"], blk["k"])
         T = blk["T"]
+        bufs = None
+        if transport == "peer":
+            bufs = ep.PeerBuffers(pkg, blk["H"], T * blk["k"])
+            moe = ep.PeerExpertParallelMoe(pkg, full.gate_weight, mlp, blk["E"], blk["k"], bufs)
+        else:
+            moe = ep.ExpertParallelMoe(ep.B200Backend(pkg, full.gate_weight, mlp, blk["k"]), blk["E"], blk["k"])
         lo, hi = rank * T // world, (rank + 1) * T // world
         x = torch.from_numpy(blk["x"][lo:hi]).bfloat16().cuda()
         for _ in range(2):                      # twice: scratch reuse across calls
@@ -35,6 +40,8 @@ def _worker(rank, world, port, cfg, ret):
         pkg.default_context().check()
         ret[rank] = dict(out=out.float().cpu().numpy(), idx=moe.last["idx"].cpu().numpy().view(np.uint32),
                          counts=moe.last["counts"].cpu().numpy().view(np.uint32), lo=lo, hi=hi)
+        if bufs is not None:
+            bufs.close()
     finally:
         dist.destroy_process_group()
 
@@ -47,13 +54,14 @@ def _free_port():
 
 @pytest.mark.parametrize("cfg", [dict(T=96, H=256, E=8, I=128, k=2, seed=3),
                                  dict(T=700, H=512, E=16, I=256, k=4, seed=5)])
-def test_expert_parallel_two_gpus(O, cfg):
+@pytest.mark.parametrize("transport", ["nccl", "peer"])
+def test_expert_parallel_two_gpus(O, cfg, transport):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = 2
     with mp.Manager() as m:
         ret = m.dict()
-        mp.spawn(_worker, args=(world, _free_port(), cfg, ret), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, _free_port(), cfg, transport, ret), nprocs=world, join=True)
         ret = dict(ret)
     blk = make_block(**cfg)
     ref = O.moe_block(blk["x"], blk["wr"], blk["gate"], blk["up"], blk["down"], blk["k"])

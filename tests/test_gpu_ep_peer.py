@@ -1,0 +1,69 @@
+"""GPU (one device): the peer-memory expert-parallel kernels with G ranks emulated one after another on
+a single GPU - every "peer" buffer is a local allocation, and since none of these kernels waits on
+another, running the ranks' phases in sequence is the same computation as G processes."""
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import make_block, to_device
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("cfg,G", [(dict(T=96, H=256, E=8, I=128, k=2, seed=3), 2),
+                                   (dict(T=700, H=512, E=16, I=256, k=4, seed=5), 4),
+                                   (dict(T=2400, H=512, E=8, I=256, k=2, seed=9), 2)])   # tensor-core regime
+def test_peer_exchange_emulated_ranks(pkg, O, cfg, G):
+    from importlib import import_module
+    ep = import_module("mlx_rs_b200.ep")
+    ops, dev = pkg.ops, torch.device("cuda", 0)
+    blk = make_block(**cfg)
+    full = to_device(pkg, blk)
+    T, E, k, H = blk["T"], blk["E"], blk["k"], blk["H"]
+    Eg = E // G
+    cap = T * k
+    rows_buf = [torch.zeros((cap, H), dtype=torch.bfloat16, device=dev) for _ in range(G)]
+    y_buf = [torch.zeros((cap, H), dtype=torch.bfloat16, device=dev) for _ in range(G)]
+    rows_ptrs, y_ptrs = [b.data_ptr() for b in rows_buf], [b.data_ptr() for b in y_buf]
+    mlps = [ep.shard_switch_mlp(pkg, full.switch_mlp, r, G) for r in range(G)]
+    xs, routed = [], []
+    for r in range(G):
+        lo, hi = r * T // G, (r + 1) * T // G
+        x = torch.from_numpy(blk["x"][lo:hi]).bfloat16().to(dev)
+        idx, scores = pkg.nn.router_topk(x, full.gate_weight, k, 0, True, None)
+        perm, inv, counts, offsets = ops.moe_permute(idx.reshape(-1), E)
+        xs.append(x)
+        routed.append((idx, scores, perm, inv, counts, offsets))
+    all_counts = torch.stack([rt[4] for rt in routed]).contiguous()
+    tables = []
+    for r in range(G):
+        dst_row0, local_counts = ops.ep_layout(all_counts, r, cap)
+        want_row0, want_counts = ep.layout_tables(all_counts, r)
+        assert torch.equal(dst_row0.cpu(), want_row0) and torch.equal(local_counts.cpu(), want_counts)
+        tables.append((dst_row0, local_counts))
+    for r in range(G):      # phase 1 on every rank, then the barrier
+        idx, scores, perm, inv, counts, offsets = routed[r]
+        ops.ep_dispatch(xs[r], idx, perm, offsets, tables[r][0], rows_ptrs, cap, E)
+    for r in range(G):      # phase 2
+        n_recv = int(tables[r][1].sum())
+        if n_recv:
+            mlps[r].forward_sorted(rows_buf[r], tables[r][1], n_recv, out=y_buf[r])
+    ref = O.moe_block(blk["x"], blk["wr"], blk["gate"], blk["up"], blk["down"], k)
+    rms = np.sqrt((ref["out_f32"] ** 2).mean())
+    for r in range(G):      # phase 3
+        idx, scores, perm, inv, counts, offsets = routed[r]
+        out = ops.ep_combine(y_ptrs, idx, inv, offsets, tables[r][0], scores, H, cap, E)
+        pkg.default_context().check()
+        lo, hi = r * T // G, (r + 1) * T // G
+        assert np.array_equal(idx.cpu().numpy().view(np.uint32), ref["idx"][lo:hi])
+        d = np.abs(out.float().cpu().numpy() - ref["out_f32"][lo:hi])
+        assert np.all(d <= 2e-2 * rms + 2.0 ** -8 * np.abs(ref["out_f32"][lo:hi]))   # bf16 output: one rounding allowed
+
+
+def test_peer_exchange_reports_overflow(pkg):
+    dev = torch.device("cuda", 0)
+    all_counts = torch.tensor([[5, 0], [4, 1]], dtype=torch.int32, device=dev)
+    pkg.ops.ep_layout(all_counts, 1, 8)          # rank 0 would receive 9 rows, its buffers hold 8
+    with pytest.raises(pkg.B200Error, match="more rows"):
+        pkg.default_context().check()
+    pkg.default_context().check()                # the status word is cleared by the failed check
