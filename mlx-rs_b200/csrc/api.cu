@@ -82,7 +82,7 @@ static size_t block_scratch_bytes(const b200_moe_config& cfg, int64_t T) {
   b += al(sizeof(float) * n * cfg.hidden);           // per-assignment outputs (float32)
   b += al(sizeof(uint16_t) * n * cfg.hidden);        // rows gathered into expert order, fp16 (tensor-core path)
   b += al(sizeof(uint16_t) * n * cfg.inter) + 2 * al(sizeof(float) * n);  // fp16 copy of h, row scales
-  b += al(sizeof(uint32_t) * prefill_tile_words(n, (int)E)) * 3 + al(16);
+  b += (al(sizeof(uint32_t) * prefill_tile_words(n, (int)E)) * 3 + al(16)) * 2;
   return b + 4096;
 }
 
@@ -112,6 +112,7 @@ static int check_cfg(const b200_moe_config* cfg) {
   } while (0)
 
 static inline int permute_launches(int64_t n) { return n <= 1024 ? 1 : 3; }
+constexpr int kTicketWord = 8;  // word of the status block that the fused small-batch router uses as its ticket counter
 
 extern "C" {
 
@@ -171,8 +172,9 @@ int b200_ctx_check(b200_ctx* c, void* stream) {
   if (h != 0) {
     B200_CUDA(cudaMemset(c->err, 0, sizeof(int)));
     B200_FAIL(h == 2   ? "an expert index was out of range"
-              : h == 3 ? "a rank would receive more rows than its exchange buffers hold"
-              : h == 4 ? "an expert-parallel routing table was inconsistent"
+              : h == 3 ? "a kernel gave up waiting on its own pipeline (2 s limit)"
+              : h == 5 ? "a rank would receive more rows than its exchange buffers hold"
+              : h == 6 ? "an expert-parallel routing table was inconsistent"
                        : "a gather index was out of range");
   }
   return 0;
@@ -492,6 +494,29 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
                           const uint32_t* active, const uint32_t* n_active, int64_t n, const void* scores, void* yk,
                           cudaStream_t st, bool* yk_is_bf16);
 
+// Outputs of the token -> expert sort (scratch, or the caller's aux buffers where given).
+struct SortBufs {
+  uint32_t *perm, *inv, *counts, *offsets, *active, *n_active, *chunk;
+};
+static int take_sort_bufs(b200_ctx* c, int64_t n, int E, const b200_moe_aux* aux, SortBufs& sb) {
+  sb.perm = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
+  sb.inv = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
+  sb.counts = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  sb.offsets = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  sb.active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  sb.n_active = static_cast<uint32_t*>(c->take(16));
+  sb.chunk = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * permute_scratch_words(n, E)));
+  B200_REQUIRE(sb.perm && sb.inv && sb.counts && sb.offsets && sb.active && sb.n_active && sb.chunk,
+               "scratch arena too small");
+  if (aux) {
+    if (aux->perm) sb.perm = aux->perm;
+    if (aux->inv_perm) sb.inv = aux->inv_perm;
+    if (aux->counts) sb.counts = aux->counts;
+    if (aux->offsets) sb.offsets = aux->offsets;
+  }
+  return 0;
+}
+
 // Shared tail of switch_glu_forward and moe_block_forward: permute, gate/up, down.
 // `scores` null: unweighted per-assignment outputs go to `yk` ([T*k, H]).
 static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_moe_params& p, const void* x,
@@ -499,23 +524,12 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
                            cudaStream_t st, bool* yk_is_bf16 = nullptr) {
   const int64_t n = T * cfg.top_k;
   const int E = cfg.n_experts;
-  uint32_t* perm = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
-  uint32_t* inv = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
-  uint32_t* counts = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
-  uint32_t* offsets = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
-  uint32_t* active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
-  uint32_t* n_active = static_cast<uint32_t*>(c->take(16));
-  uint32_t* chunk = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * permute_scratch_words(n, E)));
-  B200_REQUIRE(perm && inv && counts && offsets && active && n_active && chunk, "scratch arena too small");
-  if (aux) {
-    if (aux->perm) perm = aux->perm;
-    if (aux->inv_perm) inv = aux->inv_perm;
-    if (aux->counts) counts = aux->counts;
-    if (aux->offsets) offsets = aux->offsets;
-  }
-  launch_permute(idx, n, E, perm, inv, counts, offsets, active, n_active, chunk, c->err, st);
+  SortBufs sb;
+  if (take_sort_bufs(c, n, E, aux, sb)) return 1;
+  launch_permute(idx, n, E, sb.perm, sb.inv, sb.counts, sb.offsets, sb.active, sb.n_active, sb.chunk, c->err, st);
   LAUNCHED(c, permute_launches(n));
-  return experts_sorted(c, cfg, p, x, perm, cfg.top_k, counts, offsets, active, n_active, n, scores, yk, st, yk_is_bf16);
+  return experts_sorted(c, cfg, p, x, sb.perm, cfg.top_k, sb.counts, sb.offsets, sb.active, sb.n_active, n, scores, yk, st,
+                        yk_is_bf16);
 }
 
 static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_moe_params& p, const void* x,
@@ -529,23 +543,34 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
 
   // Regime: the tensor-core path once experts own enough rows to fill 128-row tiles.
   const bool tc = use_tensor_core_path(c, cfg, n, max_active);
+  // two row-tile lists: 256-row tiles for gate/up (both accumulators share each dequantised weight
+  // stage), 128-row tiles for down (short K: the accumulators alternate so that the drain of one
+  // tile runs under the products of the next)
   uint32_t *tile_expert = nullptr, *tile_row0 = nullptr, *tile_rows = nullptr, *n_row_tiles = nullptr;
+  uint32_t *tile_expert1 = nullptr, *tile_row01 = nullptr, *tile_rows1 = nullptr, *n_row_tiles1 = nullptr;
   void *xs = nullptr, *h16 = nullptr;
   float *rs_x = nullptr, *rs_h = nullptr;
+  static const bool alt_down = [] { const char* v = getenv("B200_TC_DEBUG"); return !(v && (atoi(v) & 64)); }();
   if (tc) {
     const size_t tw = prefill_tile_words(n, E);
     tile_expert = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
     tile_row0 = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
     tile_rows = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
     n_row_tiles = static_cast<uint32_t*>(c->take(16));
+    tile_expert1 = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
+    tile_row01 = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
+    tile_rows1 = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
+    n_row_tiles1 = static_cast<uint32_t*>(c->take(16));
+    B200_REQUIRE(tile_expert1 && tile_row01 && tile_rows1 && n_row_tiles1, "scratch arena too small");
     xs = c->take(sizeof(uint16_t) * n * cfg.hidden);
     h16 = c->take(sizeof(uint16_t) * n * cfg.inter);
     rs_x = static_cast<float*>(c->take(sizeof(float) * n));
     rs_h = static_cast<float*>(c->take(sizeof(float) * n));
     B200_REQUIRE(tile_expert && tile_row0 && tile_rows && n_row_tiles && xs && h16 && rs_x && rs_h,
                  "scratch arena too small");
-    launch_build_row_tiles(counts, offsets, E, tile_expert, tile_row0, tile_rows, n_row_tiles, st);
-    LAUNCHED(c, 1);
+    launch_build_row_tiles(counts, offsets, E, tile_expert, tile_row0, tile_rows, n_row_tiles, 256, st);
+    if (alt_down) launch_build_row_tiles(counts, offsets, E, tile_expert1, tile_row01, tile_rows1, n_row_tiles1, 128, st);
+    LAUNCHED(c, alt_down ? 2 : 1);
   }
   c->mark(3, st);
 
@@ -571,8 +596,8 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   if (tc) {
     // rows gathered into expert order, converted to row-normalised fp16, in the k order the 4-bit unpack produces
     launch_prepare_rows(x, perm, perm ? src_div : 1, n, cfg.hidden, cfg.bits == 4, xs, rs_x, st);
-    if (launch_grouped_qmm_tc(xs, rs_x, n, gu, 2, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, c->err,
-                              st))
+    if (launch_grouped_qmm_tc(xs, rs_x, n, gu, 2, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, false,
+                              c->err, st))
       return 1;
     LAUNCHED(c, 2);
   } else if (run_grouped(c, gu, 2, cfg.bits, max_active, n, st)) {
@@ -604,8 +629,10 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   if (tc) {
     // h was written (bf16-rounded) already in unpack order; only the fp16 conversion remains
     launch_prepare_rows(h, nullptr, 1, n, cfg.inter, 0, h16, rs_h, st);
-    if (launch_grouped_qmm_tc(h16, rs_h, n, dn, 1, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, c->err,
-                              st))
+    if (alt_down ? launch_grouped_qmm_tc(h16, rs_h, n, dn, 1, cfg.bits, tile_expert1, tile_row01, tile_rows1, n_row_tiles1,
+                                         E, true, c->err, st)
+                 : launch_grouped_qmm_tc(h16, rs_h, n, dn, 1, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E,
+                                         false, c->err, st))
       return 1;
     LAUNCHED(c, 2);
   } else if (run_grouped(c, dn, 1, cfg.bits, max_active, n, st)) {
@@ -656,14 +683,32 @@ int b200_moe_block_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_m
     if (aux->scores) scores = aux->scores;
   }
   c->mark(0, st);
-  launch_router_logits(x, params->router_weight, params->router_logit_bias, logits, (int)T, cfg->hidden, cfg->n_experts, st);
-  c->mark(1, st);
-  launch_route_topk(logits, (int)T, cfg->n_experts, cfg->top_k, cfg->router_mode, cfg->norm_topk_prob, idx, scores,
-                    nullptr, st);
-  c->mark(2, st);
-  LAUNCHED(c, 2);
   bool yk_bf16 = false;
-  if (experts_forward(c, *cfg, *params, x, idx, scores, T, yk, aux, st, &yk_bf16)) return 1;
+  if (router_fused_small_ok((int)T, cfg->hidden, cfg->n_experts, cfg->top_k)) {
+    // small batch: logits, routing and the sort in one launch (stages 1 and 2 read as zero)
+    SortBufs sb;
+    if (take_sort_bufs(c, n, cfg->n_experts, aux, sb)) return 1;
+    if (launch_router_fused_small(x, params->router_weight, params->router_logit_bias, logits, (int)T, cfg->hidden,
+                                  cfg->n_experts, cfg->top_k, cfg->router_mode, cfg->norm_topk_prob, idx, scores, sb.perm,
+                                  sb.inv, sb.counts, sb.offsets, sb.active, sb.n_active,
+                                  reinterpret_cast<unsigned int*>(c->err + kTicketWord), c->err, st))
+      return 1;
+    LAUNCHED(c, 1);
+    c->mark(1, st);
+    c->mark(2, st);
+    if (experts_sorted(c, *cfg, *params, x, sb.perm, cfg->top_k, sb.counts, sb.offsets, sb.active, sb.n_active, n, scores,
+                       yk, st, &yk_bf16))
+      return 1;
+  } else {
+    launch_router_logits(x, params->router_weight, params->router_logit_bias, logits, (int)T, cfg->hidden, cfg->n_experts,
+                         st);
+    c->mark(1, st);
+    launch_route_topk(logits, (int)T, cfg->n_experts, cfg->top_k, cfg->router_mode, cfg->norm_topk_prob, idx, scores,
+                      nullptr, st);
+    c->mark(2, st);
+    LAUNCHED(c, 2);
+    if (experts_forward(c, *cfg, *params, x, idx, scores, T, yk, aux, st, &yk_bf16)) return 1;
+  }
   if (launch_combine(yk, yk_bf16, T, cfg->top_k, cfg->hidden, out, aux ? aux->out_f32 : nullptr, st)) return 1;
   c->mark(6, st);
   c->ev_valid = c->profiling;

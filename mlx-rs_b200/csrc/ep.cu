@@ -60,7 +60,7 @@ __global__ void ep_layout_kernel(const uint32_t* __restrict__ all_counts, int G,
       for (int s = 0; s < G; ++s) row += all_counts[s * E + f];
     for (int s = 0; s < rank; ++s) row += all_counts[s * E + e];
     dst_row0[e] = row;
-    if (row + all_counts[rank * E + e] > capacity) *err = 3;
+    if (row + all_counts[rank * E + e] > capacity) *err = 5;
     if (d == rank) {
       uint32_t c = 0;
       for (int s = 0; s < G; ++s) c += all_counts[s * E + e];
@@ -86,17 +86,17 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const uint4* __restric
   for (int64_t j = blockIdx.x; j < n; j += gridDim.x) {
     const uint32_t a = perm[j];
     if (a >= n) {
-      if (threadIdx.x == 0) *err = 4;
+      if (threadIdx.x == 0) *err = 6;
       continue;
     }
     const uint32_t e = idx[a];
     if (e >= (uint32_t)E) {
-      if (threadIdx.x == 0) *err = 4;
+      if (threadIdx.x == 0) *err = 6;
       continue;
     }
     const uint32_t row = dst_row0[e] + (uint32_t)j - offsets[e];
     if (row >= capacity) {
-      if (threadIdx.x == 0) *err = 3;
+      if (threadIdx.x == 0) *err = 5;
       continue;
     }
     const uint4* src = x + (size_t)(a / k) * vec_per_row;
@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(EpPeers peers, const ui
         const uint32_t row = dst_row0[e] + inv[a] - offsets[e];
         if (row < capacity) ptr = static_cast<const uint4*>(peers.p[e / Eg]) + (size_t)row * vec_per_row;
       }
-      if (!ptr) *err = 4;
+      if (!ptr) *err = 6;
       s_row[threadIdx.x] = ptr;
       s_w[threadIdx.x] = bf16_bits_to_f32(scores[a]);
     }

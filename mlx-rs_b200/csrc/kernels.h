@@ -33,6 +33,12 @@ int launch_router_logits(const void* x, const void* w, const float* logit_bias, 
                          cudaStream_t st);
 int launch_route_topk(const void* logits, int T, int E, int k, int mode, int renorm, uint32_t* idx, void* scores,
                       void* probs, cudaStream_t st);
+// logits + top-k + token -> expert sort in one launch (T*k <= 1024); `ticket` is a zero-initialised device word
+bool router_fused_small_ok(int T, int H, int E, int k);
+int launch_router_fused_small(const void* x, const void* w, const float* logit_bias, void* logits, int T, int H, int E,
+                              int k, int mode, int renorm, uint32_t* idx, void* scores, uint32_t* perm, uint32_t* inv,
+                              uint32_t* counts, uint32_t* offsets, uint32_t* active, uint32_t* n_active,
+                              unsigned int* ticket, int* err, cudaStream_t st);
 int launch_argpartition(const void* a, int rows, int cols, int kth, uint32_t* out, cudaStream_t st);
 int launch_softmax(const void* a, int rows, int cols, void* out, cudaStream_t st);
 int launch_take_along(const void* a, int rows, int cols, const uint32_t* idx, int icol, void* out, int* err,
@@ -56,12 +62,13 @@ int launch_grouped_qmm_stream(const GroupedArgs& g, int nmat, int bits, int n_ex
 size_t prefill_tile_words(int64_t rows, int E);
 bool prefill_shape_ok(int K, int N, int nmat);
 int launch_build_row_tiles(const uint32_t* counts, const uint32_t* offsets, int E, uint32_t* tile_expert,
-                           uint32_t* tile_row0, uint32_t* tile_rows, uint32_t* n_row_tiles, cudaStream_t st);
+                           uint32_t* tile_row0, uint32_t* tile_rows, uint32_t* n_row_tiles, int rows_per_tile,
+                           cudaStream_t st);
 int launch_prepare_rows(const void* x, const uint32_t* perm, int src_div, int64_t n_rows, int K, int permute8, void* xs,
                         float* row_scale, cudaStream_t st);
 int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows, const GroupedArgs& g, int nmat, int bits, const uint32_t* tile_expert,
                           const uint32_t* tile_row0, const uint32_t* tile_rows, const uint32_t* n_row_tiles, int E,
-                          int* err, cudaStream_t st);
+                          bool alternate, int* err, cudaStream_t st);
 
 // misc.cu
 int launch_quantize(const void* w, int is_bf16, int64_t rows, int64_t K, int gs, int bits, uint32_t* wq, void* scales,

@@ -15,19 +15,9 @@
 // over chunk histograms gives each chunk its base.
 #include "common.cuh"
 #include "kernels.h"
+#include "permute_small.cuh"
 
 namespace b200 {
-
-constexpr int kChunk = 1024;
-
-// warp_cnt[w*E + e] := number of assignments of expert e in warp w (shared memory, zeroed by caller)
-__device__ __forceinline__ int warp_rank_and_count(uint32_t e, bool valid, int lane, int warp, int E, int* warp_cnt) {
-  uint32_t key = valid ? e : 0xffffffffu;
-  uint32_t m = __match_any_sync(0xffffffffu, key);
-  int rank = __popc(m & ((1u << lane) - 1u));
-  if (valid && rank == 0) warp_cnt[warp * E + e] = __popc(m);
-  return rank;
-}
 
 // Phase 1 (multi-chunk path): chunk histograms.  chunk_cnt [nchunks, E]
 __global__ void __launch_bounds__(kChunk) permute_hist_kernel(const uint32_t* __restrict__ idx, int n, int E,
@@ -118,48 +108,7 @@ __global__ void __launch_bounds__(kChunk) permute_small_kernel(const uint32_t* _
                                                                uint32_t* __restrict__ active, uint32_t* __restrict__ n_active,
                                                                int* __restrict__ err) {
   extern __shared__ int sh[];  // warp_cnt [32, E] then base [E]
-  int* base = sh + 32 * E;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < 32 * E; i += kChunk) sh[i] = 0;
-  __syncthreads();
-  int i = threadIdx.x;
-  bool valid = i < n;
-  uint32_t e = valid ? idx[i] : 0u;
-  if (valid && e >= (uint32_t)E) {
-    *err = 2;
-    valid = false;
-  }
-  int rank = warp_rank_and_count(e, valid, lane, warp, E, sh);
-  __syncthreads();
-  for (int ee = threadIdx.x; ee < E; ee += kChunk) {
-    int run = 0;
-    for (int w = 0; w < 32; ++w) {
-      int v = sh[w * E + ee];
-      sh[w * E + ee] = run;
-      run += v;
-    }
-    base[ee] = run;  // total of expert ee
-    counts[ee] = run;
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    uint32_t run = 0, na = 0;
-    for (int ee = 0; ee < E; ++ee) {
-      uint32_t c = base[ee];
-      offsets[ee] = run;
-      base[ee] = run;
-      if (c) active[na++] = ee;
-      run += c;
-    }
-    offsets[E] = run;
-    *n_active = na;
-  }
-  __syncthreads();
-  if (valid) {
-    uint32_t p = base[e] + sh[warp * E + e] + rank;
-    perm[p] = (uint32_t)i;
-    inv[i] = p;
-  }
+  permute_small_block<kChunk>(idx, n, E, perm, inv, counts, offsets, active, n_active, err, sh);
 }
 
 int launch_permute(const uint32_t* idx, int64_t n, int E, uint32_t* perm, uint32_t* inv, uint32_t* counts,

@@ -5,10 +5,12 @@
 // mlx-rs/src/ops/quantization.rs:160-230, with the SiLU-gate and routing-weight epilogues
 // fused), chosen when experts own many rows.  Per CTA (persistent over a tile list):
 //
-//   tile    = 128 rows of one expert's segment  x  256 accumulator columns
-//             (NMAT = 2: 128 gate features + the same 128 up features; NMAT = 1: 256 features)
-//   K loop  = blocks of 64 (= one quantisation group), 4 UMMA instructions m128 n256 k16 each
-//   A       = activations [rows, K] fp16, one TMA tile load (128 x 64, 128-byte swizzle) per block
+//   tile    = 256 rows of one expert's segment (two 128-row accumulators)  x  256 accumulator columns
+//             (NMAT = 2: 128 gate features + the same 128 up features; NMAT = 1: 256 features);
+//             both accumulators consume every dequantised B stage, which halves the
+//             dequantisation work per product
+//   K loop  = blocks of 64 (= one quantisation group), 2 x 4 UMMA instructions m128 n256 k16 each
+//   A       = activations [rows, K] fp16, two TMA tile loads (128 x 64, 128-byte swizzle) per block
 //   W       = the packed weights of the tile's 256 accumulator columns, 128 bytes per row (four
 //             4-bit or two 8-bit K blocks) per TMA stage: per-lane loads of 32 bytes from 256
 //             different rows cost the L1 a cycle per row, bulk tensor copies do not
@@ -22,11 +24,13 @@
 //             column in the epilogue.  kind::f16 wants both operands in one format, so A is
 //             converted to fp16 too, each row scaled by its own power of two (undone per
 //             accumulator row in the epilogue).
-//   D       = float32 in tensor memory, two accumulator stages (2 x 256 columns) so that the
-//             epilogue of tile i overlaps the main loop of tile i+1
+//   D       = float32 in tensor memory: the two accumulators fill all 512 columns, so the
+//             epilogue of a tile and the main loop of the next one do not overlap (the short K
+//             of the down projection pays for that)
 //
-// Warp roles (15 warps): 0-3 epilogue (one TMEM lane quarter each), 4-11 dequantisation,
-// 12 TMA producer for A, 13 MMA issuer (also owns the TMEM allocation), 14 TMA producer for W.  Stages hand over through
+// Warp roles (19 warps): 0-7 epilogue (0-3 drain the first accumulator, 4-7 the second; one TMEM lane
+// quarter each, through shared memory to row-contiguous stores), 8-15 dequantisation,
+// 16 TMA producer for A, 17 MMA issuer (also owns the TMEM allocation), 18 TMA producer for W.  Stages hand over through
 // mbarriers; every wait is bounded by a 2 s timer after which the CTA sets a status word, drops
 // out of its loops, releases its tensor memory and returns.
 //
@@ -193,6 +197,7 @@ struct PrefillArgs {
   int K, N;                     // reduction length, output features per matrix
   int* err;
   int debug;                    // development: 1 = skip the dequantisation work, 2 = skip the MMAs
+  int alt;                      // 1: row tiles hold <= 128 rows and alternate between the two accumulators
 };
 
 // dequantise 8 codes of one 4-bit word -> 16 bytes of fp16 (k order [0,4,1,5,2,6,3,7]).
@@ -255,7 +260,10 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (4 + s); };
-  const uint32_t tfull_bar = bar0 + 8u * 8, tempty_bar = bar0 + 8u * 9;
+  // accumulator barriers: [0] is the pair's (or accumulator 0's), [1] accumulator 1's in alternating mode
+  auto tfull_bar = [&](int a) { return bar0 + 8u * (a ? 10 : 8); };
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (a ? 11 : 9); };
+  const bool alt = p.alt != 0;
   auto wfull_bar = [&](int s) { return bar0 + 8u * (12 + s); };
   auto wempty_bar = [&](int s) { return bar0 + 8u * (14 + s); };
   auto afull_bar = [&](int s) { return bar0 + 8u * (16 + s); };
@@ -275,8 +283,10 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       mbar_init(afull_bar(s), 1);
       mbar_init(aempty_bar(s), 1);
     }
-    mbar_init(tfull_bar, 1);
-    mbar_init(tempty_bar, N_EPI / 32);
+    mbar_init(tfull_bar(0), 1);
+    mbar_init(tempty_bar(0), alt ? N_EPI / 64 : N_EPI / 32);
+    mbar_init(tfull_bar(1), 1);
+    mbar_init(tempty_bar(1), N_EPI / 64);
     for (int w = 0; w < W_STAGES; ++w) {
       mbar_init(wfull_bar(w), 1);
       mbar_init(wempty_bar(w), N_DEQ / 32);
@@ -304,24 +314,28 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     int tphase = 0, tcount = 0;
     RoleTimer tm((p.debug & 32) && blockIdx.x == 0 && tid == 0);
     float* stg = stage_buf + warp * (32 * STG_LD);
+    const int tb = alt ? sub : 0;  // which accumulator barrier pair this warp uses
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
+      // alternating mode: tile i of this CTA lives in accumulator i & 1 and is drained by that
+      // accumulator's four warps while the other accumulator is being filled
+      if (alt && (tcount & 1) != sub) continue;
       const int rt = tile / n_col_tiles, ct = tile % n_col_tiles;
       const float* cs = colscale + (tcount % CS_BUFS) * NCOL;
       tm.start();
       const uint32_t row0 = p.tile_row0[rt];
       const int rows = (int)p.tile_rows[rt];
-      const int r = sub * 128 + q4 * 32 + lane;  // row of the tile
+      const int r = (alt ? 0 : sub * 128) + q4 * 32 + lane;  // row of the tile
       const bool row_ok = r < rows;
       const uint32_t sp = row0 + r;
       const uint32_t dst = row_ok ? (p.dst_perm ? p.perm[sp] : sp) : 0xffffffffu;  // 0xffffffff: row not stored
       const float ar = row_ok ? p.a_row_scale[sp] : 1.0f;
-      if (!mbar_wait(tfull_bar, tphase, abort_flag)) break;
+      if (!mbar_wait(tfull_bar(tb), tphase, abort_flag)) break;
       tphase ^= 1;
       tm.stop(0);
       tm.start();
       tc_fence_after();
       const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(sub * NCOL);
-      if (sub * 128 < rows) {  // (warp-uniform) this accumulator holds rows of the tile
+      if (alt || sub * 128 < rows) {  // (warp-uniform) this accumulator holds rows of the tile
         if constexpr (NMAT == 2) {
           uint32_t g[16], u[16];
           tmem_ld16(lane_addr, g);
@@ -427,7 +441,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
       }
       tc_fence_before();
-      mbar_arrive_warp(tempty_bar, lane);
+      mbar_arrive_warp(tempty_bar(tb), lane);
       tm.stop(1);
     }
     tm.flush(p.err + 16 + (NMAT == 1 ? 24 : 0));
@@ -598,7 +612,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
         const int rt = tile / n_col_tiles;
         const int row0 = (int)p.tile_row0[rt];
-        const int n_sub = ((int)p.tile_rows[rt] > BM) ? 2 : 1;
+        const int n_sub = (!alt && (int)p.tile_rows[rt] > BM) ? 2 : 1;
         for (int kb = 0; kb < KB; ++kb) {
           tm.start();
           if (!mbar_wait(aempty_bar(s), phase ^ 1, abort_flag)) {
@@ -623,16 +637,19 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   } else if (warp == WARP_MMA) {
     // ------------------------------- MMA issuer ----------------------------------------------
     if (lane == 0) {
-      int s = 0, phase = 0, sa = 0, aphase = 0, tphase = 0;
+      int s = 0, phase = 0, sa = 0, aphase = 0, tcount = 0;
+      int tph[2] = {0, 0};
       bool dead = false;
       RoleTimer tm((p.debug & 32) && blockIdx.x == 0);
       const long long t_begin = clock64();
-      for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x, ++tcount) {
         const int rt = tile / n_col_tiles;
-        const int n_sub = ((int)p.tile_rows[rt] > BM) ? 2 : 1;
+        const int n_sub = (!alt && (int)p.tile_rows[rt] > BM) ? 2 : 1;
+        const int acc = alt ? (tcount & 1) : 0;
+        const uint32_t d_addr = tmem_base + (uint32_t)(acc * NCOL);
         tm.start();
-        if (!mbar_wait(tempty_bar, tphase ^ 1, abort_flag)) break;
-        tphase ^= 1;
+        if (!mbar_wait(tempty_bar(acc), tph[acc] ^ 1, abort_flag)) break;
+        tph[acc] ^= 1;
         tm.stop(2);
         tc_fence_after();
         for (int kb = 0; kb < KB; ++kb) {
@@ -654,7 +671,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {
               const uint64_t bd = umma_desc(b_addr + k * 32);
-              umma_bf16(tmem_base, umma_desc(a_addr + k * 32), bd, (kb | k) ? 1u : 0u);
+              umma_bf16(d_addr, umma_desc(a_addr + k * 32), bd, (kb | k) ? 1u : 0u);
               if (n_sub == 2) umma_bf16(tmem_base + NCOL, umma_desc(a_addr + A_BYTES + k * 32), bd, (kb | k) ? 1u : 0u);
             }
           }
@@ -670,7 +687,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
         }
         if (dead) break;
-        umma_commit(tfull_bar);  // accumulators complete
+        umma_commit(tfull_bar(acc));  // accumulators complete
       }
       tm.acc[3] = clock64() - t_begin;
       tm.flush(p.err + 28 + (NMAT == 1 ? 24 : 0));
@@ -734,11 +751,11 @@ __global__ void __launch_bounds__(256) build_row_tiles_kernel(const uint32_t* __
                                                               uint32_t* __restrict__ tile_expert,
                                                               uint32_t* __restrict__ tile_row0,
                                                               uint32_t* __restrict__ tile_rows,
-                                                              uint32_t* __restrict__ n_row_tiles) {
+                                                              uint32_t* __restrict__ n_row_tiles, uint32_t bmt) {
   __shared__ uint32_t pre[257];
   const int e = threadIdx.x;
   const uint32_t c = (e < E) ? counts[e] : 0u;
-  const uint32_t nt = (c + BMT - 1) / BMT;
+  const uint32_t nt = (c + bmt - 1) / bmt;
   pre[e + 1] = nt;
   if (e == 0) pre[0] = 0;
   __syncthreads();
@@ -751,8 +768,8 @@ __global__ void __launch_bounds__(256) build_row_tiles_kernel(const uint32_t* __
     const uint32_t base = pre[e], o = offsets[e];
     for (uint32_t i = 0; i < nt; ++i) {
       tile_expert[base + i] = (uint32_t)e;
-      tile_row0[base + i] = o + i * BMT;
-      tile_rows[base + i] = min((uint32_t)BMT, c - i * BMT);
+      tile_row0[base + i] = o + i * bmt;
+      tile_rows[base + i] = min(bmt, c - i * bmt);
     }
   }
 }
@@ -822,13 +839,15 @@ static EncodeTiledFn encode_fn() {
 
 }  // namespace
 
-size_t prefill_tile_words(int64_t rows, int E) { return (size_t)(rows / BMT + E + 1); }
+size_t prefill_tile_words(int64_t rows, int E) { return (size_t)(rows / BM + E + 1); }  // enough for 128-row tiles
 
 bool prefill_shape_ok(int K, int N, int nmat) { return K % 64 == 0 && N % (nmat == 2 ? 128 : 256) == 0; }
 
 int launch_build_row_tiles(const uint32_t* counts, const uint32_t* offsets, int E, uint32_t* tile_expert,
-                           uint32_t* tile_row0, uint32_t* tile_rows, uint32_t* n_row_tiles, cudaStream_t st) {
-  build_row_tiles_kernel<<<1, 256, 0, st>>>(counts, offsets, E, tile_expert, tile_row0, tile_rows, n_row_tiles);
+                           uint32_t* tile_row0, uint32_t* tile_rows, uint32_t* n_row_tiles, int rows_per_tile,
+                           cudaStream_t st) {
+  build_row_tiles_kernel<<<1, 256, 0, st>>>(counts, offsets, E, tile_expert, tile_row0, tile_rows, n_row_tiles,
+                                            (uint32_t)rows_per_tile);
   return 0;
 }
 
@@ -843,8 +862,9 @@ int launch_prepare_rows(const void* x, const uint32_t* perm, int src_div, int64_
 // a: activations [rows, K] fp16 (rows scaled by 1/a_row_scale) in the k order the weights are unpacked in.
 int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows, const GroupedArgs& g, int nmat, int bits, const uint32_t* tile_expert,
                           const uint32_t* tile_row0, const uint32_t* tile_rows, const uint32_t* n_row_tiles, int E,
-                          int* err, cudaStream_t st) {
+                          bool alternate, int* err, cudaStream_t st) {
   if (rows == 0) return 0;
+  B200_REQUIRE(!alternate || nmat == 1, "alternating accumulators are for single-matrix products");
   B200_REQUIRE(prefill_shape_ok(g.K, g.N, nmat), "shape not supported by the tensor-core path");
   EncodeTiledFn enc = encode_fn();
   B200_REQUIRE(enc != nullptr, "cuTensorMapEncodeTiled is not available from the driver");
@@ -889,6 +909,7 @@ int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows,
   p.K = g.K;
   p.N = g.N;
   p.err = err;
+  p.alt = alternate ? 1 : 0;
   {
     static const int dbg = [] { const char* v = getenv("B200_TC_DEBUG"); return v ? atoi(v) : 0; }();
     p.debug = dbg;

@@ -16,6 +16,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "permute_small.cuh"
 
 namespace b200 {
 
@@ -193,10 +194,13 @@ __global__ void __launch_bounds__(256) router_logits_warp_kernel(const __nv_bflo
 }
 
 // ---------------------------------------------------------------------------------------
-// Large token counts: float64 tensor-core variant.  CTA = 8 warps over TT tokens x 128 experts;
-// a warp owns 32 tokens x TT/2 experts as 8x8 accumulator tiles of mma.sync m8n8k4 (f64), the
-// operands being converted to float64 once per 32-wide K chunk while they are staged in shared
-// memory (row-major, rows padded by 32 bytes so that fragment loads spread over all banks).
+// Large token counts: float64 tensor-core variant.  CTA = 8 warps over MT*8 tokens x 128 experts;
+// a warp owns all the tokens x 16 experts as 8x8 accumulator tiles of mma.sync m8n8k4 (f64).  The
+// operands are converted to float64 once per 32-wide K chunk while they are staged in shared
+// memory (row-major, rows padded by 32 bytes so that fragment loads spread over all banks);
+// two buffers, and the next chunk's global loads are issued before the current chunk's products.
+// The token tile (32..64 rows) is chosen per launch so that the last wave over 148 SMs is full
+// (T = 8192: 56 rows -> 147 CTAs).
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void dmma_884(double (&c)[2], double a, double b) {
   asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
@@ -204,71 +208,91 @@ __device__ __forceinline__ void dmma_884(double (&c)[2], double a, double b) {
                : "d"(a), "d"(b));
 }
 
-template <int TT>
+template <int MT>
 __global__ void __launch_bounds__(256) router_logits_dmma_kernel(const __nv_bfloat16* __restrict__ x,
                                                                  const __nv_bfloat16* __restrict__ w,
                                                                  const float* __restrict__ logit_bias,
                                                                  __nv_bfloat16* __restrict__ logits, int T, int H, int E) {
-  constexpr int KC = 32, LD = KC + 4, TE = 128;
-  constexpr int WE = TT / 2;       // experts per warp
-  constexpr int NE = WE / 8;       // expert tiles per warp
-  constexpr int TW = TT / 32;      // warps along tokens
+  constexpr int KC = 32, LD = KC + 4, TE = 128, TT = MT * 8;
+  constexpr int ROWS = TT + TE;
+  constexpr int NLD = (ROWS * (KC / 8) + 255) / 256;  // 128-bit loads per thread and chunk
   extern __shared__ __align__(16) unsigned char dsm[];
-  double* xs = reinterpret_cast<double*>(dsm);  // [TT][LD]
-  double* ws = xs + TT * LD;                     // [TE][LD]
+  double* buf0 = reinterpret_cast<double*>(dsm);       // two buffers of [TT + TE][LD]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int wt = warp % TW, we = warp / TW;
   const int t0 = blockIdx.x * TT, e0 = blockIdx.y * TE;
   const int r = lane >> 2, kq = lane & 3;
 
-  double acc[4][NE][2];
+  double acc[MT][2][2];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < MT; ++i)
 #pragma unroll
-    for (int j = 0; j < NE; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+    for (int j = 0; j < 2; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
 
-  for (int k0 = 0; k0 < H; k0 += KC) {
-    // stage + convert: one 128-bit load = 8 consecutive k of one row
-    for (int i = tid; i < (TT + TE) * (KC / 8); i += 256) {
+  uint4 pre[NLD];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int u = 0; u < NLD; ++u) {
+      const int i = tid + u * 256;
       const int row = i / (KC / 8), c = i % (KC / 8);
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (k0 + c * 8 < H) {
+      if (i < ROWS * (KC / 8) && k0 + c * 8 < H) {
         if (row < TT) {
           if (t0 + row < T) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + row) * H + k0) + c);
         } else if (e0 + row - TT < E) {
           v = __ldg(reinterpret_cast<const uint4*>(w + (size_t)(e0 + row - TT) * H + k0) + c);
         }
       }
-      double* d = (row < TT ? xs + row * LD : ws + (row - TT) * LD) + c * 8;
-      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+      pre[u] = v;
+    }
+  };
+  auto stash = [&](double* buf) {  // convert the prefetched chunk and store it
+#pragma unroll
+    for (int u = 0; u < NLD; ++u) {
+      const int i = tid + u * 256;
+      if (i >= ROWS * (KC / 8)) break;
+      const int row = i / (KC / 8), c = i % (KC / 8);
+      double* d = buf + row * LD + c * 8;
+      const uint32_t q4[4] = {pre[u].x, pre[u].y, pre[u].z, pre[u].w};
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        d[2 * q] = bf16_bits_to_f64(u[q] & 0xffffu);
-        d[2 * q + 1] = bf16_bits_to_f64(u[q] >> 16);
+        d[2 * q] = bf16_bits_to_f64(q4[q] & 0xffffu);
+        d[2 * q + 1] = bf16_bits_to_f64(q4[q] >> 16);
       }
     }
-    __syncthreads();
+  };
+
+  fetch(0);
+  stash(buf0);
+  __syncthreads();
+  int cur = 0;
+  for (int k0 = 0; k0 < H; k0 += KC) {
+    const bool more = k0 + KC < H;
+    if (more) fetch(k0 + KC);                       // global loads in flight under the products below
+    const double* xs = buf0 + cur * ROWS * LD;
+    const double* ws = xs + TT * LD;
 #pragma unroll
     for (int kk = 0; kk < KC; kk += 4) {
-      double a[4], b[NE];
+      double a[MT], b[2];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = xs[(wt * 32 + i * 8 + r) * LD + kk + kq];
+      for (int i = 0; i < MT; ++i) a[i] = xs[(i * 8 + r) * LD + kk + kq];
 #pragma unroll
-      for (int j = 0; j < NE; ++j) b[j] = ws[(we * WE + j * 8 + r) * LD + kk + kq];
+      for (int j = 0; j < 2; ++j) b[j] = ws[(warp * 16 + j * 8 + r) * LD + kk + kq];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < MT; ++i)
 #pragma unroll
-        for (int j = 0; j < NE; ++j) dmma_884(acc[i][j], a[i], b[j]);
+        for (int j = 0; j < 2; ++j) dmma_884(acc[i][j], a[i], b[j]);
     }
+    if (more) stash(buf0 + (cur ^ 1) * ROWS * LD);    // the other buffer: last read before the previous barrier
     __syncthreads();
+    cur ^= 1;
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < MT; ++i)
 #pragma unroll
-    for (int j = 0; j < NE; ++j)
+    for (int j = 0; j < 2; ++j)
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
-        const int t = t0 + wt * 32 + i * 8 + r, e = e0 + we * WE + j * 8 + kq * 2 + q;
+        const int t = t0 + i * 8 + r, e = e0 + warp * 16 + j * 8 + kq * 2 + q;
         if (t < T && e < E) {
           uint32_t bits = f64_to_bf16_bits(acc[i][j][q]);
           if (logit_bias) bits = f32_to_bf16_bits(bf16_bits_to_f32(bits) + logit_bias[e]);
@@ -277,19 +301,35 @@ __global__ void __launch_bounds__(256) router_logits_dmma_kernel(const __nv_bflo
       }
 }
 
-template <int TT>
+template <int MT>
 static int launch_router_dmma(const __nv_bfloat16* xp, const __nv_bfloat16* wp, const float* logit_bias,
                               __nv_bfloat16* lp, int T, int H, int E, cudaStream_t st) {
-  constexpr size_t smem = sizeof(double) * (TT + 128) * 36;
-  auto kern = router_logits_dmma_kernel<TT>;
+  constexpr size_t smem = sizeof(double) * 2 * (MT * 8 + 128) * 36;
+  auto kern = router_logits_dmma_kernel<MT>;
   static bool attr = false;
   if (!attr) {
     B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr = true;
   }
-  dim3 grid(cdiv(T, TT), cdiv(E, 128));
+  dim3 grid(cdiv(T, MT * 8), cdiv(E, 128));
   kern<<<grid, 256, smem, st>>>(xp, wp, logit_bias, lp, T, H, E);
   return 0;
+}
+
+// Token rows per CTA (a multiple of 8, 32..64) that wastes the least of the last wave on 148 SMs.
+static int dmma_token_tiles(int T, int e_blocks) {
+  int best = 8;
+  double best_eff = 0.0;
+  for (int mt = 8; mt >= 4; --mt) {
+    const long tiles = (long)cdiv(T, mt * 8) * e_blocks;
+    const long waves = (tiles + 147) / 148;
+    const double eff = (double)T * e_blocks / (double)(waves * 148 * mt * 8);
+    if (eff > best_eff + 1e-9) {
+      best_eff = eff;
+      best = mt;
+    }
+  }
+  return best;
 }
 
 template <int TT>
@@ -319,8 +359,13 @@ int launch_router_logits(const void* x, const void* w, const float* logit_bias, 
   const bool warp_ok = (H % 8 == 0) && ((size_t)8 * H * 2 <= 200 * 1024);
   const bool dmma_ok = (H % 8 == 0);
   if (dmma_ok && (force == 3 || (!force && T >= 1024))) {
-    if (T >= 6144) return launch_router_dmma<64>(xp, wp, logit_bias, lp, T, H, E, st);
-    return launch_router_dmma<32>(xp, wp, logit_bias, lp, T, H, E, st);
+    switch (dmma_token_tiles(T, cdiv(E, 128))) {
+      case 4: return launch_router_dmma<4>(xp, wp, logit_bias, lp, T, H, E, st);
+      case 5: return launch_router_dmma<5>(xp, wp, logit_bias, lp, T, H, E, st);
+      case 6: return launch_router_dmma<6>(xp, wp, logit_bias, lp, T, H, E, st);
+      case 7: return launch_router_dmma<7>(xp, wp, logit_bias, lp, T, H, E, st);
+      default: return launch_router_dmma<8>(xp, wp, logit_bias, lp, T, H, E, st);
+    }
   }
   const bool use_warp = force ? (force == 1 && warp_ok) : warp_ok;
   if (use_warp) {
@@ -356,13 +401,13 @@ __device__ __forceinline__ uint32_t key_to_bits(uint32_t key16) {
 constexpr int kMaxPerLane = 8;   // experts per lane -> E <= 256
 constexpr int kMaxTopK = 32;
 
-__global__ void __launch_bounds__(128) route_topk_kernel(const __nv_bfloat16* __restrict__ logits, int T, int E, int k,
-                                                         int mode, int renorm, uint32_t* __restrict__ idx,
-                                                         __nv_bfloat16* __restrict__ scores,
-                                                         __nv_bfloat16* __restrict__ probs /*nullable [T,E]*/) {
-  const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (t >= T) return;
+// One warp routes token t.  L2: read the logits with ld.global.cg (they were written by other
+// CTAs of the same launch).
+template <bool L2>
+__device__ __forceinline__ void route_topk_token(const __nv_bfloat16* logits, int t, int lane, int E, int k, int mode,
+                                                 int renorm, uint32_t* __restrict__ idx,
+                                                 __nv_bfloat16* __restrict__ scores,
+                                                 __nv_bfloat16* __restrict__ probs /*nullable [T,E]*/) {
   const unsigned short* row = reinterpret_cast<const unsigned short*>(logits) + (size_t)t * E;
 
   uint32_t bits[kMaxPerLane];
@@ -370,7 +415,7 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const __nv_bfloat16* __
 #pragma unroll
   for (int i = 0; i < kMaxPerLane; ++i) {
     int e = lane + 32 * i;
-    bits[i] = (e < E) ? row[e] : 0xff80u;  // -inf padding
+    bits[i] = (e < E) ? (L2 ? __ldcg(row + e) : row[e]) : 0xff80u;  // -inf padding
     lf[i] = bf16_bits_to_f32(bits[i]);
   }
 
@@ -442,6 +487,144 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const __nv_bfloat16* __
     idx[(size_t)t * k + lane] = e_sel;
     scores[(size_t)t * k + lane] = __ushort_as_bfloat16((unsigned short)out_bits);
   }
+}
+
+__global__ void __launch_bounds__(128) route_topk_kernel(const __nv_bfloat16* __restrict__ logits, int T, int E, int k,
+                                                         int mode, int renorm, uint32_t* __restrict__ idx,
+                                                         __nv_bfloat16* __restrict__ scores,
+                                                         __nv_bfloat16* __restrict__ probs /*nullable [T,E]*/) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  route_topk_token<false>(logits, t, lane, E, k, mode, renorm, idx, scores, probs);
+}
+
+// ---------------------------------------------------------------------------------------
+// Small batches (T*k <= 1024): logits, routing and the token -> expert sort in ONE launch.
+// Every CTA computes its logits like router_logits_warp_kernel, publishes them (fence) and takes a
+// ticket; the CTA that draws the last ticket knows that all logits are in memory and finishes the
+// job alone: a warp per token for the top-k, then the single-chunk permutation.  Nobody waits:
+// the other CTAs simply exit.  The ticket word is reset by the last CTA for the next launch.
+// ---------------------------------------------------------------------------------------
+template <int TT>
+__global__ void __launch_bounds__(256) router_fused_small_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, const float* __restrict__ logit_bias,
+    __nv_bfloat16* logits, int T, int H, int E, int k, int mode, int renorm, uint32_t* idx, __nv_bfloat16* scores,
+    uint32_t* __restrict__ perm, uint32_t* __restrict__ inv, uint32_t* __restrict__ counts,
+    uint32_t* __restrict__ offsets, uint32_t* __restrict__ active, uint32_t* __restrict__ n_active,
+    unsigned int* ticket, int* __restrict__ err) {
+  extern __shared__ __align__(16) unsigned char rsm[];  // [TT][H] bf16, later the permutation's tables
+  __shared__ unsigned int s_ticket;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int t0 = blockIdx.y * TT;
+  const int e = blockIdx.x * 8 + warp;
+  const int nvec = H / 8;
+  for (int i = tid; i < TT * nvec; i += 256) {
+    int r = i / nvec, c = i % nvec;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t0 + r < T) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + r) * H) + c);
+    reinterpret_cast<uint4*>(rsm)[i] = v;
+  }
+  __syncthreads();
+  if (e < E) {
+    double acc[TT];
+#pragma unroll
+    for (int j = 0; j < TT; ++j) acc[j] = 0.0;
+    const uint4* wrow = reinterpret_cast<const uint4*>(w + (size_t)e * H);
+    constexpr int UN = 4;
+    for (int c0 = lane; c0 < nvec; c0 += 32 * UN) {
+      uint4 wv[UN];
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        int c = c0 + 32 * u;
+        wv[u] = (c < nvec) ? __ldg(wrow + c) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        int c = c0 + 32 * u;
+        if (c >= nvec) break;
+        const uint32_t wu[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+        double wd[8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          wd[2 * q] = bf16_bits_to_f64(wu[q] & 0xffffu);
+          wd[2 * q + 1] = bf16_bits_to_f64(wu[q] >> 16);
+        }
+#pragma unroll
+        for (int j = 0; j < TT; ++j) {
+          const uint4 xv = reinterpret_cast<const uint4*>(rsm)[j * nvec + c];
+          const uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            acc[j] = fma(bf16_bits_to_f64(xu[q] & 0xffffu), wd[2 * q], acc[j]);
+            acc[j] = fma(bf16_bits_to_f64(xu[q] >> 16), wd[2 * q + 1], acc[j]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < TT; ++j) {
+      double s = acc[j];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (lane == 0 && t0 + j < T) {
+        uint32_t bits = f64_to_bf16_bits(s);
+        if (logit_bias) bits = f32_to_bf16_bits(bf16_bits_to_f32(bits) + logit_bias[e]);
+        logits[(size_t)(t0 + j) * E + e] = __ushort_as_bfloat16((unsigned short)bits);
+      }
+    }
+  }
+  // publish, then take a ticket
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_ticket = atomicAdd(ticket, 1u);
+  __syncthreads();
+  if (s_ticket != gridDim.x * gridDim.y - 1) return;
+  __threadfence();
+  if (tid == 0) *ticket = 0u;
+  for (int t = warp; t < T; t += 8) route_topk_token<true>(logits, t, lane, E, k, mode, renorm, idx, scores, nullptr);
+  __syncthreads();  // idx written by this block is read back below
+  permute_small_block<256>(idx, T * k, E, perm, inv, counts, offsets, active, n_active, err,
+                           reinterpret_cast<int*>(rsm));
+}
+
+bool router_fused_small_ok(int T, int H, int E, int k) {
+  return (int64_t)T * k <= kChunk && H % 8 == 0 && (size_t)8 * H * 2 <= 200 * 1024 && E <= kMaxPerLane * 32;
+}
+
+template <int TT>
+static int launch_fused_small(const __nv_bfloat16* xp, const __nv_bfloat16* wp, const float* logit_bias,
+                              __nv_bfloat16* lp, int T, int H, int E, int k, int mode, int renorm, uint32_t* idx,
+                              __nv_bfloat16* scores, uint32_t* perm, uint32_t* inv, uint32_t* counts, uint32_t* offsets,
+                              uint32_t* active, uint32_t* n_active, unsigned int* ticket, int* err, cudaStream_t st) {
+  size_t smem = (size_t)TT * H * 2;
+  const size_t need = sizeof(int) * 33 * E;
+  if (smem < need) smem = need;
+  auto kern = router_fused_small_kernel<TT>;
+  static size_t attr_bytes = 0;
+  if (smem > 48 * 1024 && smem > attr_bytes) {
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_bytes = smem;
+  }
+  dim3 grid(cdiv(E, 8), cdiv(T, TT));
+  kern<<<grid, 256, smem, st>>>(xp, wp, logit_bias, lp, T, H, E, k, mode, renorm, idx, scores, perm, inv, counts, offsets,
+                                active, n_active, ticket, err);
+  return 0;
+}
+
+int launch_router_fused_small(const void* x, const void* w, const float* logit_bias, void* logits, int T, int H, int E,
+                              int k, int mode, int renorm, uint32_t* idx, void* scores, uint32_t* perm, uint32_t* inv,
+                              uint32_t* counts, uint32_t* offsets, uint32_t* active, uint32_t* n_active,
+                              unsigned int* ticket, int* err, cudaStream_t st) {
+  auto xp = static_cast<const __nv_bfloat16*>(x);
+  auto wp = static_cast<const __nv_bfloat16*>(w);
+  auto lp = static_cast<__nv_bfloat16*>(logits);
+  auto sp = static_cast<__nv_bfloat16*>(scores);
+  if (T <= 4)
+    return launch_fused_small<1>(xp, wp, logit_bias, lp, T, H, E, k, mode, renorm, idx, sp, perm, inv, counts, offsets,
+                                 active, n_active, ticket, err, st);
+  return launch_fused_small<8>(xp, wp, logit_bias, lp, T, H, E, k, mode, renorm, idx, sp, perm, inv, counts, offsets,
+                               active, n_active, ticket, err, st);
 }
 
 int launch_route_topk(const void* logits, int T, int E, int k, int mode, int renorm, uint32_t* idx, void* scores,

@@ -166,48 +166,100 @@ class PeerExpertParallelMoe:
     barrier -> SwitchGLU on the arrived rows in place -> barrier -> combine kernel (peer loads).
     The barriers are one-word all-reduces: stream-ordered, so no kernel of this library ever waits
     on another GPU.  The next forward's all-gather is what keeps a fast rank from overwriting
-    buffers that a slow rank still reads."""
+    buffers that a slow rank still reads.
+
+    With `chunks` = 2 the rank's tokens are cut in two halves that use separate exchange buffers:
+    the second half's dispatch and the first half's combine run on a side stream, under the expert
+    products of the other half, so most of the NVLink time hides behind the tensor-core time.
+    `buffers` is then a list of two PeerBuffers."""
 
     def __init__(self, pkg, gate_weight, local_switch_mlp, n_experts, top_k, buffers, norm_topk_prob=True,
                  router_mode=0, router_logit_bias=None, ctx=None):
-        self.pkg, self.ctx, self.buf = pkg, ctx, buffers
+        self.pkg, self.ctx = pkg, ctx
+        self.bufs = list(buffers) if isinstance(buffers, (list, tuple)) else [buffers]
+        self.chunks = len(self.bufs)
         self.gate_weight, self.mlp = gate_weight, local_switch_mlp
         self.E, self.k = n_experts, top_k
         self.norm, self.mode, self.bias = norm_topk_prob, router_mode, router_logit_bias
-        self.group, self.G, self.rank = buffers.group, buffers.G, buffers.rank
+        b0 = self.bufs[0]
+        self.group, self.G, self.rank = b0.group, b0.G, b0.rank
         if n_experts % self.G:
             raise ValueError("the number of experts must be divisible by the number of ranks")
         dev = gate_weight.device
         self._flag = torch.zeros(1, dtype=torch.int32, device=dev)
-        self._all_counts = torch.empty((self.G, n_experts), dtype=torch.int32, device=dev)
-        self._rows_view = _device_view(buffers.own[0], buffers.capacity, buffers.hidden, dev)
-        self._y_view = _device_view(buffers.own[1], buffers.capacity, buffers.hidden, dev)
+        self._all_counts = torch.empty((self.G, self.chunks, n_experts), dtype=torch.int32, device=dev)
+        self._views = [(_device_view(b.own[0], b.capacity, b.hidden, dev), _device_view(b.own[1], b.capacity, b.hidden, dev))
+                       for b in self.bufs]
+        self._side = torch.cuda.Stream(device=dev) if self.chunks > 1 else None
         self.last = {}
 
     def _barrier(self):
         dist.all_reduce(self._flag, group=self.group)
 
     def forward(self, x):
-        ops, E, k, G, cap = self.pkg.ops, self.E, self.k, self.G, self.buf.capacity
+        ops, E, k, G, C = self.pkg.ops, self.E, self.k, self.G, self.chunks
         Eg = E // G
+        T, H = x.shape
         idx, scores = self.pkg.nn.router_topk(x, self.gate_weight, k, self.mode, self.norm, self.bias, ctx=self.ctx)
-        perm, inv, counts, offsets = ops.moe_permute(idx.reshape(-1), E, ctx=self.ctx)
-        dist.all_gather_into_tensor(self._all_counts.view(-1), counts, group=self.group)
-        dst_row0, local_counts = ops.ep_layout(self._all_counts, self.rank, cap, ctx=self.ctx)
+        bounds = [(c * T // C, (c + 1) * T // C) for c in range(C)]
+        sort = [ops.moe_permute(idx[lo:hi].reshape(-1), E, ctx=self.ctx) for lo, hi in bounds]   # perm, inv, counts, offsets
+        mine = torch.stack([s_[2] for s_ in sort])                                                # [C, E]
+        dist.all_gather_into_tensor(self._all_counts.view(-1), mine.view(-1), group=self.group)
+        tables = []
+        for c in range(C):
+            per_chunk = self._all_counts[:, c, :].contiguous()
+            tables.append(ops.ep_layout(per_chunk, self.rank, self.bufs[c].capacity, ctx=self.ctx))
         table = self._all_counts.cpu().to(torch.int64)                 # the one host synchronisation of the step
-        arriving = table.view(G, G, Eg).sum(dim=(0, 2))
-        if int(arriving.max()) > cap:
-            raise self.pkg.B200Error(f"a rank would receive {int(arriving.max())} rows; the exchange buffers hold {cap}")
-        n_recv = int(arriving[self.rank])
-        ops.ep_dispatch(x, idx, perm, offsets, dst_row0, self.buf.rows_ptrs, cap, E, ctx=self.ctx)
-        self._barrier()
-        if n_recv:
-            self.mlp.forward_sorted(self._rows_view, local_counts, n_recv, out=self._y_view)
-        self._barrier()
-        out = ops.ep_combine(self.buf.y_ptrs, idx, inv, offsets, dst_row0, scores, x.shape[-1], cap, E, ctx=self.ctx)
-        mine = table[self.rank].view(G, Eg)
-        self.last = dict(idx=idx, scores=scores, perm=perm, counts=counts, recv_rows=n_recv,
-                         sent_rows=int(mine.sum() - mine[self.rank].sum()))
+        arriving = table.view(G, C, G, Eg).sum(dim=(0, 3))             # [C, destination rank]
+        n_recv = []
+        for c in range(C):
+            if int(arriving[c].max()) > self.bufs[c].capacity:
+                raise self.pkg.B200Error(f"a rank would receive {int(arriving[c].max())} rows; the exchange buffers hold "
+                                         f"{self.bufs[c].capacity}")
+            n_recv.append(int(arriving[c, self.rank]))
+        out = torch.empty_like(x)
+        main = torch.cuda.current_stream()
+        side = self._side or main
+
+        def dispatch(c):
+            lo, hi = bounds[c]
+            perm, inv, counts, offsets = sort[c]
+            ops.ep_dispatch(x[lo:hi], idx[lo:hi], perm, offsets, tables[c][0], self.bufs[c].rows_ptrs, self.bufs[c].capacity,
+                            E, ctx=self.ctx)
+
+        def combine(c):
+            lo, hi = bounds[c]
+            perm, inv, counts, offsets = sort[c]
+            ops.ep_combine(self.bufs[c].y_ptrs, idx[lo:hi], inv, offsets, tables[c][0], scores[lo:hi], H,
+                           self.bufs[c].capacity, E, out=out[lo:hi], ctx=self.ctx)
+
+        sent = [torch.cuda.Event() for _ in range(C)]
+        if C > 1:
+            side.wait_stream(main)
+        with torch.cuda.stream(side):
+            for c in range(C):
+                dispatch(c)
+                sent[c].record(side)
+        for c in range(C):
+            main.wait_event(sent[c])
+            self._barrier()                       # every rank's rows of chunk c have landed
+            if n_recv[c]:
+                rows_view, y_view = self._views[c]
+                self.mlp.forward_sorted(rows_view, tables[c][1], n_recv[c], out=y_view)
+            self._barrier()                       # every rank's outputs of chunk c are complete
+            if C > 1 and c + 1 < C:
+                done = torch.cuda.Event()
+                done.record(main)
+                with torch.cuda.stream(side):
+                    side.wait_event(done)
+                    combine(c)                    # under the next chunk's expert products
+            else:
+                combine(c)
+        if C > 1:
+            main.wait_stream(side)
+        own = table[self.rank].view(C, G, Eg)
+        self.last = dict(idx=idx, scores=scores, counts=mine.sum(dim=0).to(torch.int32), recv_rows=sum(n_recv),
+                         sent_rows=int(own.sum() - own[:, self.rank].sum()))
         return out
 
 
@@ -257,7 +309,8 @@ def bench_main(args, pkg, shape, peaks, metric, unit, workload_name, clock_sampl
     if args.ep_transport == "peer":
         # every rank can at worst receive every assignment of every rank; 2x the balanced load is
         # what this benchmark's random routing needs, and what a deployment would size by policy
-        bufs = PeerBuffers(pkg, H, min(T * k * world, 2 * T * k + 4096))
+        C_ = args.ep_chunks
+        bufs = [PeerBuffers(pkg, H, min(T * k * world, 2 * T * k + 4096) // C_ + 64) for _ in range(C_)]
         ep = PeerExpertParallelMoe(pkg, wr, mlp, E, k, bufs)
     else:
         ep = ExpertParallelMoe(B200Backend(pkg, wr, mlp, k), E, k)
@@ -308,6 +361,7 @@ def bench_main(args, pkg, shape, peaks, metric, unit, workload_name, clock_sampl
                                 l2="flushed between iterations (512 MB overwrite)",
                                 parallelism=f"ep{world} (" + ("dispatch/combine kernels over mapped peer memory"
                                                               if bufs else "NCCL all-to-all-v dispatch + combine") + ")",
+                                ep_chunks=(args.ep_chunks if bufs else 1),
                                 **shape),
                     roofline=dict(bound="tensor", achieved=flops / (ms * 1e-3) / 1e12 / world, peak=peaks["tensor"],
                                   unit="TFLOP/s", frac=flops / (ms * 1e-3) / 1e12 / world / peaks["tensor"],
@@ -320,7 +374,7 @@ def bench_main(args, pkg, shape, peaks, metric, unit, workload_name, clock_sampl
                     exchange=dict(rows_sent_off_rank_per_step=sent.item(), bytes_each_way=sent.item() * H * 2))
         print(json.dumps(line))
     ctx.check()
-    if bufs is not None:
-        bufs.close()
+    for b in bufs or []:
+        b.close()
     dist.barrier()
     dist.destroy_process_group()

@@ -102,11 +102,13 @@ class MoeBlock:
     def config(self):
         return self._cfg
 
-    def forward(self, x, return_aux=False):
-        ops._cuda(x)
+    def forward(self, x, return_aux=False, out=None):
+        ops._cuda(x, out)
         ops._req(x.dtype == torch.bfloat16 and x.shape[-1] == self.switch_mlp.hidden, "MoeBlock: bf16 x [.., hidden]")
         T = x.numel() // x.shape[-1]
-        out = torch.empty_like(x)
+        if out is None:
+            out = torch.empty_like(x)
+        ops._req(out.dtype == x.dtype and out.shape == x.shape, "MoeBlock: out must match x")
         aux_c, aux = None, None
         if return_aux:
             n, E, dev = T * self.top_k, self.switch_mlp.n_experts, x.device
@@ -139,6 +141,62 @@ def router_topk(x, gate_weight, top_k, router_mode=ROUTER_SOFTMAX_TOPK, norm_top
     L.check(L.lib().b200_router_topk(ops._ctx(ctx), C.byref(cfg), L.ptr(x), L.ptr(gate_weight), L.ptr(logit_bias), T,
                                      L.ptr(idx), L.ptr(sc), L.ptr(lg), L.stream_ptr()))
     return (idx, sc, lg) if return_logits else (idx, sc)
+
+
+class HostPipeline:
+    """Serves a block (anything with forward(x, out=...)) from HOST memory.  Each `submit(x_host,
+    out_host)` (pinned bf16 buffers [T, H]) uploads its input, runs the block and downloads the result;
+    successive submits are software-pipelined on three streams - the upload of call i+1 overlaps the
+    compute of call i and the download of call i-1 - with `depth` pairs of device buffers.  `submit`
+    returns a ticket; `wait(ticket)` blocks until that call's output is in its host buffer, `drain()`
+    until all are.  Results are those of block.forward on the same rows (same kernels, same order)."""
+
+    def __init__(self, block, max_tokens, hidden, device, depth=2):
+        self.block, self.depth = block, depth
+        self.up, self.run, self.down = (torch.cuda.Stream(device=device) for _ in range(3))
+        self.xd = [torch.empty((max_tokens, hidden), dtype=torch.bfloat16, device=device) for _ in range(depth)]
+        self.od = [torch.empty((max_tokens, hidden), dtype=torch.bfloat16, device=device) for _ in range(depth)]
+        self.ev_up = [torch.cuda.Event() for _ in range(depth)]
+        self.ev_run = [torch.cuda.Event() for _ in range(depth)]
+        self.ev_down = [torch.cuda.Event() for _ in range(depth)]
+        self.n = 0
+
+    def submit(self, x_host, out_host):
+        ops._req(x_host.is_pinned() and out_host.is_pinned(), "HostPipeline: pinned host buffers")
+        T = x_host.shape[0]
+        ops._req(T <= self.xd[0].shape[0], "HostPipeline: more tokens than max_tokens")
+        s = self.n % self.depth
+        first = self.n < self.depth
+        xd, od = self.xd[s][:T], self.od[s][:T]
+        if self.n == 0:
+            for st in (self.up, self.run, self.down):
+                st.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.up):
+            if not first:
+                self.up.wait_event(self.ev_run[s])     # the call that last read this input slot has run
+            xd.copy_(x_host, non_blocking=True)
+            self.ev_up[s].record(self.up)
+        with torch.cuda.stream(self.run):
+            self.run.wait_event(self.ev_up[s])
+            if not first:
+                self.run.wait_event(self.ev_down[s])   # this output slot has been downloaded
+            self.block.forward(xd, out=od)
+            self.ev_run[s].record(self.run)
+        with torch.cuda.stream(self.down):
+            self.down.wait_event(self.ev_run[s])
+            out_host.copy_(od, non_blocking=True)
+            self.ev_down[s].record(self.down)
+        self.n += 1
+        return s
+
+    def wait(self, ticket):
+        self.ev_down[ticket].synchronize()
+
+    def drain(self, stream=None):
+        """Make `stream` (default: the current one) wait for everything submitted so far."""
+        stream = stream or torch.cuda.current_stream()
+        for st in (self.up, self.run, self.down):
+            stream.wait_stream(st)
 
 
 class MoeStack:

@@ -207,11 +207,12 @@ def ep_dispatch(x, indices, perm, offsets, dst_row0, peer_rows, capacity_rows, n
                                      capacity_rows, L.stream_ptr()))
 
 
-def ep_combine(peer_y, indices, inv_perm, offsets, dst_row0, scores, hidden, capacity_rows, n_experts, ctx=None):
+def ep_combine(peer_y, indices, inv_perm, offsets, dst_row0, scores, hidden, capacity_rows, n_experts, out=None, ctx=None):
     """out[t] = bf16(sum_j scores[t, j] * y row of assignment (t, j) read from its owner's buffer)."""
-    _cuda(indices, inv_perm, offsets, dst_row0, scores)
+    _cuda(indices, inv_perm, offsets, dst_row0, scores, out)
     T, k = scores.shape
-    out = torch.empty((T, hidden), dtype=torch.bfloat16, device=scores.device)
+    if out is None:
+        out = torch.empty((T, hidden), dtype=torch.bfloat16, device=scores.device)
     L.check(L.lib().b200_ep_combine(_ctx(ctx), _ptr_array(peer_y), L.ptr(indices), L.ptr(inv_perm), L.ptr(offsets),
                                     L.ptr(dst_row0), L.ptr(scores), T, k, hidden, n_experts, len(peer_y), capacity_rows,
                                     L.ptr(out), L.stream_ptr()))

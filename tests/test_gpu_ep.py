@@ -28,8 +28,8 @@ def _worker(rank, world, port, cfg, transport, ret):
         mlp = ep.shard_switch_mlp(pkg, full.switch_mlp, rank, world)
         T = blk["T"]
         bufs = None
-        if transport == "peer":
-            bufs = ep.PeerBuffers(pkg, blk["H"], T * blk["k"])
+        if transport.startswith("peer"):
+            bufs = [ep.PeerBuffers(pkg, blk["H"], T * blk["k"]) for _ in range(2 if transport == "peer2" else 1)]
             moe = ep.PeerExpertParallelMoe(pkg, full.gate_weight, mlp, blk["E"], blk["k"], bufs)
         else:
             moe = ep.ExpertParallelMoe(ep.B200Backend(pkg, full.gate_weight, mlp, blk["k"]), blk["E"], blk["k"])
@@ -40,8 +40,8 @@ def _worker(rank, world, port, cfg, transport, ret):
         pkg.default_context().check()
         ret[rank] = dict(out=out.float().cpu().numpy(), idx=moe.last["idx"].cpu().numpy().view(np.uint32),
                          counts=moe.last["counts"].cpu().numpy().view(np.uint32), lo=lo, hi=hi)
-        if bufs is not None:
-            bufs.close()
+        for b in bufs or []:
+            b.close()
     finally:
         dist.destroy_process_group()
 
@@ -54,7 +54,7 @@ def _free_port():
 
 @pytest.mark.parametrize("cfg", [dict(T=96, H=256, E=8, I=128, k=2, seed=3),
                                  dict(T=700, H=512, E=16, I=256, k=4, seed=5)])
-@pytest.mark.parametrize("transport", ["nccl", "peer"])
+@pytest.mark.parametrize("transport", ["nccl", "peer", "peer2"])
 def test_expert_parallel_two_gpus(O, cfg, transport):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

@@ -210,3 +210,23 @@ def test_stack_of_blocks_with_norm_and_residual(pkg, O):
     rms = np.sqrt((h.astype(np.float64) ** 2).mean())
     ok = np.all(np.abs(got - h) <= TOL * rms + 2.0 ** -7 * np.abs(h), axis=1)
     assert ok.mean() >= 0.9, f"only {ok.mean():.2f} of the tokens agree"
+
+
+def test_host_pipeline_matches_direct_calls(pkg):
+    """Five pipelined submits from pinned host buffers (depth 2: slots are reused) return exactly what
+    block.forward returns for the same rows."""
+    blk = make_block(T=300, H=256, E=8, I=128, k=2, seed=21)
+    block = to_device(pkg, blk)
+    dev = torch.device("cuda", 0)
+    pipe = pkg.nn.HostPipeline(block, 300, 256, dev, depth=2)
+    g = torch.Generator().manual_seed(5)
+    xs = [torch.randn(300 - 17 * i, 256, generator=g).bfloat16().pin_memory() for i in range(5)]
+    outs = [torch.empty_like(x).pin_memory() for x in xs]
+    for x, o in zip(xs, outs):
+        pipe.submit(x, o)
+    pipe.drain()
+    torch.cuda.synchronize()
+    pkg.default_context().check()
+    for x, o in zip(xs, outs):
+        want = block.forward(x.to(dev)).cpu()
+        assert torch.equal(o.view(torch.int16), want.view(torch.int16))
