@@ -271,9 +271,10 @@ def main():
     ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
                     help="N > 1: peer = the library's dispatch/combine kernels over mapped peer memory; "
                          "nccl = torch.distributed all-to-all-v (the baseline it is measured against)")
-    ap.add_argument("--ep-chunks", type=int, default=2, choices=[1, 2],
-                    help="N > 1, peer transport: halves of a rank's tokens whose exchange overlaps the other half's products")
-    ap.add_argument("--qmm-path", default="auto", choices=["auto", "small", "stream", "tensor_core"],
+    ap.add_argument("--ep-chunks", type=int, default=0, choices=[0, 1, 2],
+                    help="N > 1, peer transport: halves of a rank's tokens whose exchange overlaps the other half's products "
+                         "(0 = two when every local expert still gets >= 1024 rows per half)")
+    ap.add_argument("--qmm-path", default="auto", choices=["auto", "small", "stream", "tensor_core", "tmem"],
                     help="pin the grouped-product kernel (default: the library chooses)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -303,7 +304,7 @@ def main():
     if args.workload == "stack":
         return run_stack(args, pkg, torch, dev, peaks)
     ctx = pkg.default_context()
-    ctx.set_qmm_path(dict(auto=ctx.QMM_AUTO, small=ctx.QMM_SMALL, stream=ctx.QMM_STREAM, tensor_core=ctx.QMM_TENSOR_CORE)[args.qmm_path])
+    ctx.set_qmm_path(dict(auto=ctx.QMM_AUTO, small=ctx.QMM_SMALL, stream=ctx.QMM_STREAM, tensor_core=ctx.QMM_TENSOR_CORE, tmem=ctx.QMM_TMEM)[args.qmm_path])
     block = build_block(pkg, torch, args.seed, SHAPE, dev)
     ctx.reserve(block.config, max(T, max(SWEEP)))
     flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)

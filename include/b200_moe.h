@@ -107,8 +107,10 @@ int64_t b200_ctx_launch_count(const b200_ctx* ctx);
 /* Which grouped-product kernel the routed block uses.  AUTO: the register-load mma.sync kernel
  * while experts own few rows, the tcgen05 tensor-core kernel beyond that (when inter % 128 == 0
  * and hidden % 256 == 0).  STREAM pins the TMA-streamed variant of the memory-bound kernel
- * (K % 256 == 0, N % 64 or 128 == 0).  A pinned kernel falls back when the shape does not allow it. */
-enum { B200_QMM_AUTO = 0, B200_QMM_SMALL = 1, B200_QMM_TENSOR_CORE = 2, B200_QMM_STREAM = 3 };
+ * (K % 256 == 0, N % 64 or 128 == 0).  TMEM pins the tensor-memory kernel of the memory-bound regime
+ * (packed codes go to the tensor core unscaled, one accumulator per quantisation group;
+ * hidden, inter % 256 == 0 and <= 2048).  A pinned kernel falls back when the shape does not allow it. */
+enum { B200_QMM_AUTO = 0, B200_QMM_SMALL = 1, B200_QMM_TENSOR_CORE = 2, B200_QMM_STREAM = 3, B200_QMM_TMEM = 4 };
 int b200_ctx_set_qmm_path(b200_ctx* ctx, int path);
 /* Diagnostic: synchronises the device and copies the first n (<= 64) 32-bit words of the
  * context's status buffer to HOST memory.  Word 0 is the status b200_ctx_check reports; words

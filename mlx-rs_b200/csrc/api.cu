@@ -83,6 +83,9 @@ static size_t block_scratch_bytes(const b200_moe_config& cfg, int64_t T) {
   b += al(sizeof(uint16_t) * n * cfg.hidden);        // rows gathered into expert order, fp16 (tensor-core path)
   b += al(sizeof(uint16_t) * n * cfg.inter) + 2 * al(sizeof(float) * n);  // fp16 copy of h, row scales
   b += (al(sizeof(uint32_t) * prefill_tile_words(n, (int)E)) * 3 + al(16)) * 2;
+  // tensor-memory small-batch path: 16 rows of padding on the prepared rows, per-group tables, 16-row tile list
+  b += al(sizeof(uint16_t) * 16 * (cfg.hidden + cfg.inter)) + al(8 * (n + 16) * (cfg.hidden / 64)) +
+       al(8 * (n + 16) * (cfg.inter / 64)) + al(sizeof(uint32_t) * (n / 16 + E + 1)) * 3;
   return b + 4096;
 }
 
@@ -192,7 +195,8 @@ int b200_ctx_debug_words(b200_ctx* c, int32_t* host_out, int n) {
 
 int b200_ctx_set_qmm_path(b200_ctx* c, int path) {
   CTX_ENTER(c);
-  B200_REQUIRE(path == B200_QMM_AUTO || path == B200_QMM_SMALL || path == B200_QMM_TENSOR_CORE || path == B200_QMM_STREAM,
+  B200_REQUIRE(path == B200_QMM_AUTO || path == B200_QMM_SMALL || path == B200_QMM_TENSOR_CORE || path == B200_QMM_STREAM ||
+                   path == B200_QMM_TMEM,
                "unknown path");
   c->qmm_path = path;
   return 0;
@@ -481,7 +485,7 @@ static bool use_tensor_core_path(const b200_ctx* c, const b200_moe_config& cfg, 
   // kernel, which streams activations by TMA, applies
   const int kmax = cfg.hidden > cfg.inter ? cfg.hidden : cfg.inter;
   if ((size_t)8 * (2 * kmax + 16) + sizeof(float) * (kmax / 64) * 8 > 220 * 1024) return true;
-  if (c->qmm_path == B200_QMM_SMALL || c->qmm_path == B200_QMM_STREAM) return false;
+  if (c->qmm_path == B200_QMM_SMALL || c->qmm_path == B200_QMM_STREAM || c->qmm_path == B200_QMM_TMEM) return false;
   if (c->qmm_path == B200_QMM_TENSOR_CORE) return true;
   return n / (max_active > 0 ? max_active : 1) >= 24;
 }
@@ -543,6 +547,9 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
 
   // Regime: the tensor-core path once experts own enough rows to fill 128-row tiles.
   const bool tc = use_tensor_core_path(c, cfg, n, max_active);
+  // memory-bound regime on tensor memory (codes go to the tensor core unscaled; per-group accumulators)
+  const bool mb = !tc && c->qmm_path == B200_QMM_TMEM && mb_shape_ok(cfg.hidden, cfg.inter) &&
+                  mb_shape_ok(cfg.inter, cfg.hidden);
   // two row-tile lists: 256-row tiles for gate/up (both accumulators share each dequantised weight
   // stage), 128-row tiles for down (short K: the accumulators alternate so that the drain of one
   // tile runs under the products of the next)
@@ -551,6 +558,24 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   void *xs = nullptr, *h16 = nullptr;
   float *rs_x = nullptr, *rs_h = nullptr;
   static const bool alt_down = [] { const char* v = getenv("B200_TC_DEBUG"); return !(v && (atoi(v) & 64)); }();
+  void *tab_x = nullptr, *tab_h = nullptr;
+  if (mb) {
+    const size_t tw = (size_t)(n / 16 + E + 1);
+    tile_expert = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
+    tile_row0 = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
+    tile_rows = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
+    n_row_tiles = static_cast<uint32_t*>(c->take(16));
+    xs = c->take(sizeof(uint16_t) * (n + 16) * cfg.hidden);
+    h16 = c->take(sizeof(uint16_t) * (n + 16) * cfg.inter);
+    rs_x = static_cast<float*>(c->take(sizeof(float) * n));
+    rs_h = static_cast<float*>(c->take(sizeof(float) * n));
+    tab_x = c->take(8 * (size_t)(n + 16) * (cfg.hidden / 64));
+    tab_h = c->take(8 * (size_t)(n + 16) * (cfg.inter / 64));
+    B200_REQUIRE(tile_expert && tile_row0 && tile_rows && n_row_tiles && xs && h16 && rs_x && rs_h && tab_x && tab_h,
+                 "scratch arena too small");
+    launch_build_row_tiles(counts, offsets, E, tile_expert, tile_row0, tile_rows, n_row_tiles, 16, st);
+    LAUNCHED(c, 1);
+  }
   if (tc) {
     const size_t tw = prefill_tile_words(n, E);
     tile_expert = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
@@ -600,6 +625,12 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
                               c->err, st))
       return 1;
     LAUNCHED(c, 2);
+  } else if (mb) {
+    launch_prepare_rows_mb(x, perm, perm ? src_div : 1, n, cfg.hidden, cfg.bits, xs, rs_x, tab_x, st);
+    if (launch_grouped_qmm_mb(xs, rs_x, tab_x, n, gu, 2, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, c->err,
+                              st))
+      return 1;
+    LAUNCHED(c, 2);
   } else if (run_grouped(c, gu, 2, cfg.bits, max_active, n, st)) {
     return 1;
   }
@@ -633,6 +664,12 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
                                          E, true, c->err, st)
                  : launch_grouped_qmm_tc(h16, rs_h, n, dn, 1, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E,
                                          false, c->err, st))
+      return 1;
+    LAUNCHED(c, 2);
+  } else if (mb) {
+    launch_prepare_rows_mb(h, nullptr, 1, n, cfg.inter, cfg.bits, h16, rs_h, tab_h, st);
+    if (launch_grouped_qmm_mb(h16, rs_h, tab_h, n, dn, 1, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, c->err,
+                              st))
       return 1;
     LAUNCHED(c, 2);
   } else if (run_grouped(c, dn, 1, cfg.bits, max_active, n, st)) {

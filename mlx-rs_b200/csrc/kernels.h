@@ -70,6 +70,14 @@ int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows,
                           const uint32_t* tile_row0, const uint32_t* tile_rows, const uint32_t* n_row_tiles, int E,
                           bool alternate, int* err, cudaStream_t st);
 
+// qmm_decode_tc.cu (tensor-memory path for the memory-bound regime)
+bool mb_shape_ok(int K, int N);
+int launch_prepare_rows_mb(const void* x, const uint32_t* perm, int src_div, int64_t n_rows, int K, int bits, void* xs,
+                           float* row_scale, void* tab, cudaStream_t st);
+int launch_grouped_qmm_mb(const void* xs, const float* a_row_scale, const void* tab, int64_t rows, const GroupedArgs& g,
+                          int nmat, int bits, const uint32_t* tile_expert, const uint32_t* tile_row0,
+                          const uint32_t* tile_rows, const uint32_t* n_row_tiles, int E, int* err, cudaStream_t st);
+
 // misc.cu
 int launch_quantize(const void* w, int is_bf16, int64_t rows, int64_t K, int gs, int bits, uint32_t* wq, void* scales,
                     void* biases, cudaStream_t st);

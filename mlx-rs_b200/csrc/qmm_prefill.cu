@@ -45,10 +45,13 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "tc_common.cuh"
 
 namespace b200 {
 
 namespace {
+
+using namespace tc;
 
 constexpr int BM = 128, BMT = 256, BK = 64, NCOL = 256;  // BMT: rows per tile = two 128-row accumulators sharing B
 constexpr int A_STAGES = 3, STAGES = 2, W_STAGES = 2;    // STAGES = dequantised-B stages
@@ -63,122 +66,12 @@ constexpr int CS_BUFS = 4;                // column-scale buffers (tiles in flig
 constexpr int RING_BYTES = A_STAGES * A_STAGE_BYTES + STAGES * B_BYTES + W_STAGES * W_BYTES;
 constexpr int STG_LD = 20;                // floats per staged row (16 + 4): 16-byte aligned, quarter-warps hit distinct banks
 constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512 + CS_BUFS * NCOL * 4 + (N_EPI / 32) * 32 * STG_LD * 4;
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// One arrival per warp: every lane has finished its part (and, where the async proxy will read
-// the data, executed its own proxy fence) before lane 0 signals.  256 individual arrivals on one
-// barrier serialise in shared memory and dominate a K block.
-__device__ __forceinline__ void mbar_arrive_warp(uint32_t bar, int lane) {
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar);
-}
-// Self-timing (diagnostic, enabled by bit 5 of PrefillArgs::debug): CTA 0 accumulates the
-// cycles each role spends in each of its waits and writes them to the status buffer.
-struct RoleTimer {
-  long long acc[4] = {0, 0, 0, 0};
-  long long t0 = 0;
-  bool on;
-  __device__ explicit RoleTimer(bool enable) : on(enable) {}
-  __device__ __forceinline__ void start() {
-    if (on) t0 = clock64();
-  }
-  __device__ __forceinline__ void stop(int i) {
-    if (on) acc[i] += clock64() - t0;
-  }
-  __device__ void flush(int* dst) {
-    if (on)
-      for (int i = 0; i < 4; ++i) dst[i] = (int)(acc[i] >> 10);
-  }
-};
-// Bounded wait: false when the abort flag is up or the time limit has passed.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  uint64_t t0 = 0;
-  for (uint32_t it = 0;; ++it) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    if ((it & 31u) == 31u) {
-      if (*abort_flag) return false;
-      uint64_t now = globaltimer_ns();
-      if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitNs) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-               : "memory");
-}
-// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr >> 4) & 0x3fffu);        // start address
-  d |= (uint64_t)1 << 16;                         // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                         // descriptor version of this architecture
-  d |= (uint64_t)2 << 61;                         // SWIZZLE_128B
-  return d;
-}
-// kind::f16, A = B = fp16 (format 0), D = f32 (format 1), both operands K-major, M = 128, N = 256
-constexpr uint32_t kIdesc = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(NCOL >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-
+// kind::f16, A = B = fp16, D = f32, both operands K-major, M = 128, N = 256
+constexpr uint32_t kIdesc = umma_idesc_f16(BM, NCOL);
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate)
-      : "memory");
+  umma_f16(d_tmem, adesc, bdesc, kIdesc, accumulate);
 }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 struct PrefillArgs {
   const uint32_t* w[2];
@@ -819,22 +712,6 @@ __global__ void __launch_bounds__(256) prepare_rows_kernel(const uint4* __restri
     }
     xs[(size_t)r * vec_per_row + c] = o;
   }
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = [] {
-    void* f = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      f = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(f);
-  }();
-  return fn;
 }
 
 }  // namespace

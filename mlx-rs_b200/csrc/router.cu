@@ -589,7 +589,7 @@ __global__ void __launch_bounds__(256) router_fused_small_kernel(
 }
 
 bool router_fused_small_ok(int T, int H, int E, int k) {
-  return (int64_t)T * k <= kChunk && H % 8 == 0 && (size_t)8 * H * 2 <= 200 * 1024 && E <= kMaxPerLane * 32;
+  return T <= 8 && (int64_t)T * k <= kChunk && H % 8 == 0 && (size_t)8 * H * 2 <= 200 * 1024 && E <= kMaxPerLane * 32;
 }
 
 template <int TT>

@@ -79,7 +79,7 @@ class ExpertParallelMoe:
             raise ValueError("the number of experts must be divisible by the number of ranks")
         self.last = {}
 
-    def forward(self, x):
+    def forward(self, x, out=None):
         """x: this rank's tokens [T, H] bf16 -> [T, H] bf16."""
         G, E, k = self.G, self.E, self.k
         Eg = E // G
@@ -99,10 +99,13 @@ class ExpertParallelMoe:
         y = self.be.experts(recv_rows, ids)
         back = torch.empty_like(rows)
         dist.all_to_all_single(back.view(torch.uint8), y.contiguous().view(torch.uint8), sc, rc, group=self.group)
-        out = self.be.combine(back, inv, scores)
+        res = self.be.combine(back, inv, scores)
+        if out is not None:
+            out.copy_(res)
+            res = out
         self.last = dict(idx=idx, scores=scores, perm=perm, counts=counts, sent_rows=sum(sc) - sc[self.rank],
                          recv_rows=n_recv)
-        return out
+        return res
 
 
 def layout_tables(all_counts, rank):
@@ -196,7 +199,7 @@ class PeerExpertParallelMoe:
     def _barrier(self):
         dist.all_reduce(self._flag, group=self.group)
 
-    def forward(self, x):
+    def forward(self, x, out=None):
         ops, E, k, G, C = self.pkg.ops, self.E, self.k, self.G, self.chunks
         Eg = E // G
         T, H = x.shape
@@ -217,7 +220,8 @@ class PeerExpertParallelMoe:
                 raise self.pkg.B200Error(f"a rank would receive {int(arriving[c].max())} rows; the exchange buffers hold "
                                          f"{self.bufs[c].capacity}")
             n_recv.append(int(arriving[c, self.rank]))
-        out = torch.empty_like(x)
+        if out is None:
+            out = torch.empty_like(x)
         main = torch.cuda.current_stream()
         side = self._side or main
 
@@ -309,7 +313,8 @@ def bench_main(args, pkg, shape, peaks, metric, unit, workload_name, clock_sampl
     if args.ep_transport == "peer":
         # every rank can at worst receive every assignment of every rank; 2x the balanced load is
         # what this benchmark's random routing needs, and what a deployment would size by policy
-        C_ = args.ep_chunks
+        # two chunks pay once every local expert still fills whole 256-row tiles per chunk
+        C_ = args.ep_chunks or (2 if T * k * world // E // 2 >= 1024 else 1)
         bufs = [PeerBuffers(pkg, H, min(T * k * world, 2 * T * k + 4096) // C_ + 64) for _ in range(C_)]
         ep = PeerExpertParallelMoe(pkg, wr, mlp, E, k, bufs)
     else:
@@ -341,14 +346,29 @@ def bench_main(args, pkg, shape, peaks, metric, unit, workload_name, clock_sampl
     with clock_sampler(local) as clk:
         ms = timed(lambda: ep.forward(x), args.steps, args.warmup)
     launches = (ctx.launch_count() - l0) // (args.steps + args.warmup) * args.steps
-    xh = x.cpu().pin_memory()
-    oh = torch.empty_like(xh).pin_memory()
-    xd = torch.empty_like(x)
-
-    def e2e_step():
-        xd.copy_(xh, non_blocking=True)
-        oh.copy_(ep.forward(xd), non_blocking=True)
-    e2e_ms = timed(e2e_step, args.steps, args.warmup)
+    # end to end from pinned host buffers through HostPipeline (upload of step i+1 and download of
+    # step i-1 under step i's kernels and exchanges); every step's copies are inside the timed region
+    xhs = [x.cpu().pin_memory(), x.cpu().pin_memory()]
+    ohs = [torch.empty_like(xhs[0]).pin_memory(), torch.empty_like(xhs[0]).pin_memory()]
+    xh, oh = xhs[0], ohs[0]
+    pipe = pkg.nn.HostPipeline(ep, T, H, dev, depth=2)
+    for i in range(max(3, args.warmup)):
+        pipe.submit(xhs[i % 2], ohs[i % 2])
+    pipe.drain()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        pipe.submit(xhs[i % 2], ohs[i % 2])
+    pipe.drain()
+    ev1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e2e_t = torch.tensor([ev0.elapsed_time(ev1) / args.steps], device=dev)
+    dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    e2e_ms = e2e_t.item()
     sent = torch.tensor([float(ep.last["sent_rows"])], device=dev)
     dist.all_reduce(sent, op=dist.ReduceOp.SUM)
     if rank == 0:
@@ -361,7 +381,7 @@ def bench_main(args, pkg, shape, peaks, metric, unit, workload_name, clock_sampl
                                 l2="flushed between iterations (512 MB overwrite)",
                                 parallelism=f"ep{world} (" + ("dispatch/combine kernels over mapped peer memory"
                                                               if bufs else "NCCL all-to-all-v dispatch + combine") + ")",
-                                ep_chunks=(args.ep_chunks if bufs else 1),
+                                ep_chunks=(len(bufs) if bufs else 1),
                                 **shape),
                     roofline=dict(bound="tensor", achieved=flops / (ms * 1e-3) / 1e12 / world, peak=peaks["tensor"],
                                   unit="TFLOP/s", frac=flops / (ms * 1e-3) / 1e12 / world / peaks["tensor"],

@@ -78,6 +78,20 @@ def test_decode_sweep_first_generation_kernel(pkg, O, config0, T):
         ctx.set_qmm_path(ctx.QMM_AUTO)
 
 
+@pytest.mark.parametrize("T", [1, 4, 16, 64])
+def test_decode_sweep_tensor_memory_kernel(pkg, O, config0, T):
+    # the tcgen05 kernel of the memory-bound regime: per-group accumulators in tensor memory
+    ctx = pkg.default_context()
+    ctx.set_qmm_path(ctx.QMM_TMEM)
+    try:
+        blk = dict(config0)
+        blk["x"] = config0["x"][:T].copy()
+        blk["T"] = T
+        check_block(pkg, O, blk)
+    finally:
+        ctx.set_qmm_path(ctx.QMM_AUTO)
+
+
 @pytest.mark.parametrize("T", [1, 4, 16])
 def test_decode_sweep(pkg, O, config0, T):
     # BASELINE.json configs[1], decode points (64 is test_config0_block): same weights, fewer tokens
@@ -87,12 +101,12 @@ def test_decode_sweep(pkg, O, config0, T):
     check_block(pkg, O, blk)
 
 
-@pytest.fixture(params=["small", "stream", "tensor_core"])
+@pytest.fixture(params=["small", "stream", "tensor_core", "tmem"])
 def qmm_path(request, pkg):
     """Runs a test once per grouped-product kernel (register-load mma.sync / TMA-streamed mma.sync / tcgen05)
     and restores AUTO."""
     ctx = pkg.default_context()
-    ctx.set_qmm_path(dict(small=ctx.QMM_SMALL, stream=ctx.QMM_STREAM, tensor_core=ctx.QMM_TENSOR_CORE)[request.param])
+    ctx.set_qmm_path(dict(small=ctx.QMM_SMALL, stream=ctx.QMM_STREAM, tensor_core=ctx.QMM_TENSOR_CORE, tmem=ctx.QMM_TMEM)[request.param])
     yield request.param
     ctx.set_qmm_path(ctx.QMM_AUTO)
 
