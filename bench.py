@@ -273,7 +273,7 @@ def main():
                          "nccl = torch.distributed all-to-all-v (the baseline it is measured against)")
     ap.add_argument("--ep-chunks", type=int, default=0, choices=[0, 1, 2],
                     help="N > 1, peer transport: halves of a rank's tokens whose exchange overlaps the other half's products "
-                         "(0 = two when every local expert still gets >= 1024 rows per half)")
+                         "(0 = default: one)")
     ap.add_argument("--qmm-path", default="auto", choices=["auto", "small", "stream", "tensor_core", "tmem"],
                     help="pin the grouped-product kernel (default: the library chooses)")
     args = ap.parse_args()

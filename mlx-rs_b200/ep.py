@@ -313,8 +313,7 @@ def bench_main(args, pkg, shape, peaks, metric, unit, workload_name, clock_sampl
     if args.ep_transport == "peer":
         # every rank can at worst receive every assignment of every rank; 2x the balanced load is
         # what this benchmark's random routing needs, and what a deployment would size by policy
-        # two chunks pay once every local expert still fills whole 256-row tiles per chunk
-        C_ = args.ep_chunks or (2 if T * k * world // E // 2 >= 1024 else 1)
+        C_ = args.ep_chunks or 1
         bufs = [PeerBuffers(pkg, H, min(T * k * world, 2 * T * k + 4096) // C_ + 64) for _ in range(C_)]
         ep = PeerExpertParallelMoe(pkg, wr, mlp, E, k, bufs)
     else:
