@@ -131,6 +131,7 @@ def cpu_baseline(T_sample, shape, seed, reps_budget_s=15.0):
     import numpy as np
     import torch
     from oracle import oracle as O
+    O.set_num_threads(0)   # all host cores, also when a launcher exported OMP_NUM_THREADS=1
     H, I, E, k = shape["hidden"], shape["inter"], shape["n_experts"], shape["top_k"]
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(T_sample, H, generator=g).bfloat16().float().numpy()

@@ -22,8 +22,6 @@
 //
 // CTA = 8 warps = RT row tiles (16 output features each) x KS slices of the K groups;
 // partial sums of the KS slices meet in shared memory in a fixed order.
-#include <cstdlib>
-
 #include "common.cuh"
 #include "kernels.h"
 
@@ -83,9 +81,10 @@ __device__ __forceinline__ void a_frag(const typename WVec<BITS>::T& ra, const t
   }
 }
 
-template <int BITS, int NMAT, int RT, int NT, int UG = 4, int MINB = 1>
-__global__ void __launch_bounds__(256, MINB) grouped_qmm_small_kernel(GroupedArgs p) {
-  constexpr int KS = 8 / RT;      // UG = groups in flight per warp
+template <int BITS, int NMAT, int RT, int NT>
+__global__ void __launch_bounds__(256) grouped_qmm_small_kernel(GroupedArgs p) {
+  constexpr int KS = 8 / RT;
+  constexpr int UG = 4;           // groups in flight per warp
   constexpr int ROWS = 8 * NT;    // x rows per pass
   constexpr int WPG = (BITS == 4) ? 8 : 16;    // packed words per group per row
   constexpr int WPT = (BITS == 4) ? 2 : 4;     // packed words per thread per group per row
@@ -181,8 +180,6 @@ __global__ void __launch_bounds__(256, MINB) grouped_qmm_small_kernel(GroupedArg
 #pragma unroll
         for (int q = 0; q < 4; ++q) tot[mt][nt][q] = 0.f;
 
-    // consecutive groups per warp and whole 8-byte pieces of the scale rows: vector loads of scales / biases
-    const bool vec_sb = (KS == 1) && (UG == 4) && ((G & 3) == 0);
     for (int g0 = ks; g0 < G; g0 += KS * UG) {
       typename WV::T wa[UG][NMAT], wb[UG][NMAT];
       unsigned short sa[UG][NMAT], sb[UG][NMAT], ba[UG][NMAT], bb[UG][NMAT];
@@ -195,32 +192,10 @@ __global__ void __launch_bounds__(256, MINB) grouped_qmm_small_kernel(GroupedArg
           const uint32_t* pa = wbase[mt] + (size_t)gq * wrow + g * WPG + t * WPT;
           wa[u][mt] = (ok && row_ok_a) ? WV::load(pa) : WV::zero();
           wb[u][mt] = (ok && row_ok_b) ? WV::load(pa + (size_t)8 * wrow) : WV::zero();
-          if (!vec_sb) {
-            sa[u][mt] = (ok && row_ok_a) ? __ldg(sbase[mt] + (size_t)gq * G + g) : (unsigned short)0;
-            ba[u][mt] = (ok && row_ok_a) ? __ldg(bbase[mt] + (size_t)gq * G + g) : (unsigned short)0;
-            sb[u][mt] = (ok && row_ok_b) ? __ldg(sbase[mt] + (size_t)(gq + 8) * G + g) : (unsigned short)0;
-            bb[u][mt] = (ok && row_ok_b) ? __ldg(bbase[mt] + (size_t)(gq + 8) * G + g) : (unsigned short)0;
-          }
-        }
-      }
-      if (vec_sb) {
-        // the four groups in flight are consecutive: one 8-byte load per row brings all four scales (biases)
-#pragma unroll
-        for (int mt = 0; mt < NMAT; ++mt) {
-          const uint2 z = make_uint2(0, 0);
-          const uint2 va = row_ok_a ? __ldg(reinterpret_cast<const uint2*>(sbase[mt] + (size_t)gq * G + g0)) : z;
-          const uint2 vb = row_ok_b ? __ldg(reinterpret_cast<const uint2*>(sbase[mt] + (size_t)(gq + 8) * G + g0)) : z;
-          const uint2 wa2 = row_ok_a ? __ldg(reinterpret_cast<const uint2*>(bbase[mt] + (size_t)gq * G + g0)) : z;
-          const uint2 wb2 = row_ok_b ? __ldg(reinterpret_cast<const uint2*>(bbase[mt] + (size_t)(gq + 8) * G + g0)) : z;
-          const uint32_t q[4][2] = {{va.x, va.y}, {vb.x, vb.y}, {wa2.x, wa2.y}, {wb2.x, wb2.y}};
-#pragma unroll
-          for (int u = 0; u < UG; ++u) {
-            const int sh = (u & 1) * 16;
-            sa[u][mt] = (unsigned short)(q[0][u >> 1] >> sh);
-            sb[u][mt] = (unsigned short)(q[1][u >> 1] >> sh);
-            ba[u][mt] = (unsigned short)(q[2][u >> 1] >> sh);
-            bb[u][mt] = (unsigned short)(q[3][u >> 1] >> sh);
-          }
+          sa[u][mt] = (ok && row_ok_a) ? __ldg(sbase[mt] + (size_t)gq * G + g) : (unsigned short)0;
+          ba[u][mt] = (ok && row_ok_a) ? __ldg(bbase[mt] + (size_t)gq * G + g) : (unsigned short)0;
+          sb[u][mt] = (ok && row_ok_b) ? __ldg(sbase[mt] + (size_t)(gq + 8) * G + g) : (unsigned short)0;
+          bb[u][mt] = (ok && row_ok_b) ? __ldg(bbase[mt] + (size_t)(gq + 8) * G + g) : (unsigned short)0;
         }
       }
 #pragma unroll
@@ -318,13 +293,13 @@ __global__ void __launch_bounds__(256, MINB) grouped_qmm_small_kernel(GroupedArg
   }
 }
 
-template <int BITS, int NMAT, int RT, int NT, int UG = 4, int MINB = 1>
+template <int BITS, int NMAT, int RT, int NT>
 static int launch_cfg(const GroupedArgs& a, int max_active, cudaStream_t st) {
   const int K = a.K;
   size_t smem = (size_t)8 * NT * (2 * K + 16) + sizeof(float) * (K / 64) * 8 * NT;
   size_t red = sizeof(float) * 8 * NMAT * NT * 128;
   if (red > smem) smem = red;
-  auto kern = grouped_qmm_small_kernel<BITS, NMAT, RT, NT, UG, MINB>;
+  auto kern = grouped_qmm_small_kernel<BITS, NMAT, RT, NT>;
   static size_t attr_bytes = 0;  // one process drives one GPU, so a per-instantiation cache is enough
   if (smem > attr_bytes) {
     B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -350,16 +325,10 @@ static int launch_bits_nmat(const GroupedArgs& a, int max_active, int64_t rows, 
   }
   // shared memory for the wide variant: 32 rows of x must fit
   const bool wide_fits = ((size_t)32 * (2 * a.K + 16) + sizeof(float) * (a.K / 64) * 32) <= 200 * 1024;
-  static const int variant = [] { const char* v = getenv("B200_SMALL_VARIANT"); return v ? atoi(v) : 0; }();
-  if (variant && !(wide && wide_fits) && rt == 8) {
-    if (variant == 1) return launch_cfg<BITS, NMAT, 8, 1, 2, 3>(a, max_active, st);
-    if (variant == 2) return launch_cfg<BITS, NMAT, 8, 1, 2, 2>(a, max_active, st);
-    if (variant == 3) return launch_cfg<BITS, NMAT, 8, 1, 4, 3>(a, max_active, st);
-  }
 #define B200_DISPATCH_RT(RTV)                                                          \
   case RTV:                                                                            \
     return (wide && wide_fits) ? launch_cfg<BITS, NMAT, RTV, 4>(a, max_active, st)     \
-                               : launch_cfg<BITS, NMAT, RTV, 1, 4, 2>(a, max_active, st);
+                               : launch_cfg<BITS, NMAT, RTV, 1>(a, max_active, st);
   switch (rt) {
     B200_DISPATCH_RT(1)
     B200_DISPATCH_RT(2)

@@ -90,6 +90,18 @@ int orc_num_threads() {
 #endif
 }
 
+// The launcher of multi-process runs exports OMP_NUM_THREADS=1; a caller that owns the host (the
+// timed CPU baseline) can ask for all cores again.  n <= 0: one thread per available processor.
+int orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  omp_set_num_threads(n > 0 ? n : omp_get_num_procs());
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
+
 void orc_f32_to_bf16(const float* in, int64_t n, uint16_t* out) {
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < n; ++i) out[i] = f32_to_bf16_bits(in[i]);

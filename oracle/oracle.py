@@ -41,6 +41,11 @@ def num_threads():
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n=0):
+    """n <= 0: one OpenMP thread per available processor (undoes an inherited OMP_NUM_THREADS=1)."""
+    return int(lib().orc_set_num_threads(int(n)))
+
+
 def to_bf16_bits(a):
     a = _f32(a)
     out = np.empty(a.shape, dtype=np.uint16)
