@@ -249,6 +249,17 @@ int b200_ep_buffer_alloc(b200_ctx* ctx, size_t bytes, void** ptr, unsigned char*
 int b200_ep_buffer_open(b200_ctx* ctx, const unsigned char* handle, void** ptr);
 int b200_ep_buffer_close(b200_ctx* ctx, void* ptr);
 int b200_ep_buffer_free(b200_ctx* ctx, void* ptr);
+/* Return path fused into the down projection.  b200_ep_return_table fills row_addr[i], for every
+ * row i this rank received, with the address of that row's output in the SOURCE rank's return buffer
+ * (peer_y[s], bf16 [T_s * top_k, hidden] in the source's own sorted order); b200_switch_glu_sorted_scatter
+ * is b200_switch_glu_sorted whose epilogue stores each finished row to row_addr[i] (peer stores), so
+ * the transfer back overlaps the products tile by tile and the source finishes with a local
+ * b200_moe_combine after one barrier. */
+int b200_ep_return_table(b200_ctx* ctx, const uint32_t* all_counts, int n_ranks, int n_experts, int rank,
+                         void* const* peer_y, int64_t hidden, unsigned long long* row_addr, void* stream);
+int b200_switch_glu_sorted_scatter(b200_ctx* ctx, const b200_moe_config* cfg, const b200_moe_params* params,
+                                   const void* rows, const uint32_t* counts, int64_t n,
+                                   const unsigned long long* out_row_addr, void* stream);
 /* all_counts [n_ranks, n_experts] (rows rank s routes to expert e, on the device) ->
  * dst_row0 [n_experts]: row on the owner of e where this rank's rows of e start;
  * local_counts [n_experts / n_ranks]: rows arriving here per local expert. */

@@ -496,7 +496,7 @@ static bool use_tensor_core_path(const b200_ctx* c, const b200_moe_config& cfg, 
 static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_moe_params& p, const void* x,
                           const uint32_t* perm, int src_div, const uint32_t* counts, const uint32_t* offsets,
                           const uint32_t* active, const uint32_t* n_active, int64_t n, const void* scores, void* yk,
-                          cudaStream_t st, bool* yk_is_bf16);
+                          cudaStream_t st, bool* yk_is_bf16, const unsigned long long* out_row_addr = nullptr);
 
 // Outputs of the token -> expert sort (scratch, or the caller's aux buffers where given).
 struct SortBufs {
@@ -539,7 +539,7 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
 static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_moe_params& p, const void* x,
                           const uint32_t* perm, int src_div, const uint32_t* counts, const uint32_t* offsets,
                           const uint32_t* active, const uint32_t* n_active, int64_t n, const void* scores, void* yk,
-                          cudaStream_t st, bool* yk_is_bf16) {
+                          cudaStream_t st, bool* yk_is_bf16, const unsigned long long* out_row_addr) {
   const int E = cfg.n_experts;
   void* h = c->take(sizeof(uint16_t) * n * cfg.inter);
   B200_REQUIRE(h, "scratch arena too small");
@@ -548,7 +548,7 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   // Regime: the tensor-core path once experts own enough rows to fill 128-row tiles.
   const bool tc = use_tensor_core_path(c, cfg, n, max_active);
   // memory-bound regime on tensor memory (codes go to the tensor core unscaled; per-group accumulators)
-  const bool mb = !tc && c->qmm_path == B200_QMM_TMEM && mb_shape_ok(cfg.hidden, cfg.inter) &&
+  const bool mb = !tc && !out_row_addr && c->qmm_path == B200_QMM_TMEM && mb_shape_ok(cfg.hidden, cfg.inter) &&
                   mb_shape_ok(cfg.inter, cfg.hidden);
   // two row-tile lists: 256-row tiles for gate/up (both accumulators share each dequantised weight
   // stage), 128-row tiles for down (short K: the accumulators alternate so that the drain of one
@@ -653,6 +653,7 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   // tensor-core path's epilogue but triples its error against the 2e-2 bar: measured 0.017 at
   // T=512); SwitchGlu's own output is bf16
   dn.out_f32 = scores != nullptr;
+  dn.out_row_addr = out_row_addr;   // rows go to per-row addresses (bf16): the expert-parallel return path
   if (yk_is_bf16) *yk_is_bf16 = !dn.out_f32;
   dn.K = cfg.inter;
   dn.N = cfg.hidden;
@@ -672,6 +673,9 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
                               st))
       return 1;
     LAUNCHED(c, 2);
+  } else if (out_row_addr) {  // per-row addresses: the register kernel (the streamed variant does not take them)
+    if (launch_grouped_qmm_small(dn, 1, cfg.bits, max_active, n, st)) return 1;
+    LAUNCHED(c, 1);
   } else if (run_grouped(c, dn, 1, cfg.bits, max_active, n, st)) {
     return 1;
   }
@@ -774,6 +778,44 @@ int b200_switch_glu_sorted(b200_ctx* c, const b200_moe_config* cfg, const b200_m
   launch_segments_from_counts(counts, E, offsets, active, n_active, st);
   LAUNCHED(c, 1);
   return experts_sorted(c, one, *params, rows, nullptr, 1, counts, offsets, active, n_active, n, nullptr, out, st, nullptr);
+}
+
+static int fill_peers(EpPeers& pe, void* const* peers, int G);
+
+int b200_switch_glu_sorted_scatter(b200_ctx* c, const b200_moe_config* cfg, const b200_moe_params* params, const void* rows,
+                                   const uint32_t* counts, int64_t n, const unsigned long long* out_row_addr, void* stream) {
+  CTX_ENTER(c);
+  if (check_cfg(cfg) || check_params(params, false)) return 1;
+  B200_REQUIRE(n >= 0 && n < (int64_t(1) << 31), "bad row count");
+  if (n == 0) return 0;
+  B200_REQUIRE(rows && counts && out_row_addr, "null tensor");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  b200_moe_config one = *cfg;
+  one.top_k = 1;
+  if (ctx_grow(c, block_scratch_bytes(one, n))) return 1;
+  const int E = cfg->n_experts;
+  uint32_t* offsets = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  uint32_t* active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  uint32_t* n_active = static_cast<uint32_t*>(c->take(16));
+  B200_REQUIRE(offsets && active && n_active, "scratch arena too small");
+  launch_segments_from_counts(counts, E, offsets, active, n_active, st);
+  LAUNCHED(c, 1);
+  return experts_sorted(c, one, *params, rows, nullptr, 1, counts, offsets, active, n_active, n, nullptr, nullptr, st,
+                        nullptr, out_row_addr);
+}
+
+int b200_ep_return_table(b200_ctx* c, const uint32_t* all_counts, int n_ranks, int n_experts, int rank, void* const* peer_y,
+                         int64_t hidden, unsigned long long* row_addr, void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(all_counts && row_addr, "null tensor");
+  B200_REQUIRE(n_ranks >= 1 && n_ranks <= kEpMaxRanks && rank >= 0 && rank < n_ranks, "bad rank");
+  B200_REQUIRE(n_experts > 0 && n_experts % n_ranks == 0, "experts must divide evenly over the ranks");
+  B200_REQUIRE(hidden > 0 && hidden % 8 == 0, "hidden must be a multiple of 8");
+  EpPeers pe;
+  if (fill_peers(pe, peer_y, n_ranks)) return 1;
+  launch_ep_return_table(all_counts, n_ranks, n_experts, rank, pe, hidden, row_addr, static_cast<cudaStream_t>(stream));
+  LAUNCHED(c, 1);
+  return 0;
 }
 
 int b200_ep_buffer_alloc(b200_ctx* c, size_t bytes, void** ptr, unsigned char* handle) {

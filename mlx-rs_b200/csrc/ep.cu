@@ -115,6 +115,43 @@ int launch_ep_dispatch(const void* x, const uint32_t* idx, const uint32_t* perm,
   return 0;
 }
 
+// ---- return path fused into the down projection ------------------------------------------------
+// For every row this rank received (numbered by local expert, source rank, source order) the address
+// of its output row in the SOURCE rank's return buffer, which is laid out in the source's own sorted
+// order: row (offsets_s[e] + j) for the j-th row rank s routed to expert e.  The grouped product's
+// epilogue stores each finished row straight to that address (peer stores), so the transfer back
+// overlaps the products tile by tile and the source's combine reads local memory only.
+// One CTA per (local expert, source rank) segment.
+__global__ void __launch_bounds__(256) ep_return_table_kernel(const uint32_t* __restrict__ all_counts, int G, int E,
+                                                              int rank, EpPeers peers_y, int64_t row_bytes,
+                                                              unsigned long long* __restrict__ row_addr) {
+  const int Eg = E / G;
+  const int el = blockIdx.x / G, s = blockIdx.x % G;
+  const int e = rank * Eg + el;
+  __shared__ uint32_t s_start, s_src0;
+  if (threadIdx.x == 0) {
+    uint32_t start = 0;
+    for (int f = rank * Eg; f < e; ++f)
+      for (int q = 0; q < G; ++q) start += all_counts[q * E + f];
+    for (int q = 0; q < s; ++q) start += all_counts[q * E + e];
+    uint32_t src0 = 0;
+    for (int f = 0; f < e; ++f) src0 += all_counts[s * E + f];
+    s_start = start;
+    s_src0 = src0;
+  }
+  __syncthreads();
+  const uint32_t len = all_counts[s * E + e];
+  const unsigned long long base = reinterpret_cast<unsigned long long>(peers_y.p[s]);
+  for (uint32_t j = threadIdx.x; j < len; j += blockDim.x)
+    row_addr[s_start + j] = base + (unsigned long long)(s_src0 + j) * (unsigned long long)row_bytes;
+}
+
+int launch_ep_return_table(const uint32_t* all_counts, int G, int E, int rank, const EpPeers& peers_y, int64_t H,
+                           unsigned long long* row_addr, cudaStream_t st) {
+  ep_return_table_kernel<<<(E / G) * G, 256, 0, st>>>(all_counts, G, E, rank, peers_y, H * 2, row_addr);
+  return 0;
+}
+
 // ---- combine: read the k expert outputs from their owners + weighted sum ------------------------
 // out[t, :] = bf16( sum_j score[t, j] * y_owner(idx[t,j])[row(t, j), :] ), float32 accumulation, j ascending.
 __device__ __forceinline__ uint4 ld_cg_v4(const uint4* p) {

@@ -23,6 +23,8 @@ struct GroupedArgs {
   int dst_perm;               // 0: out row = sorted position, 1: out row = perm[p]
   const void* row_scale;      // bf16, indexed by out row; may be null
   void* out;                  // [rows, N], bf16 or float32
+  const unsigned long long* out_row_addr;  // optional, by sorted position: address of the row's bf16 output
+                                           // (overrides out/dst_perm; rows may live on peer GPUs)
   int out_f32;                // 1: float32 output (no rounding before the k-way combine)
   int K, N;
   int n_experts;              // number of stacked weight matrices
@@ -111,6 +113,8 @@ int launch_ep_layout(const uint32_t* all_counts, int G, int E, int rank, uint32_
 int launch_ep_dispatch(const void* x, const uint32_t* idx, const uint32_t* perm, const uint32_t* offsets,
                        const uint32_t* dst_row0, int64_t n, int k, int64_t H, int E, int G, const EpPeers& peers,
                        uint32_t capacity, int* err, cudaStream_t st);
+int launch_ep_return_table(const uint32_t* all_counts, int G, int E, int rank, const EpPeers& peers_y, int64_t H,
+                           unsigned long long* row_addr, cudaStream_t st);
 int launch_ep_combine(const EpPeers& peers, const uint32_t* idx, const uint32_t* inv, const uint32_t* offsets,
                       const uint32_t* dst_row0, const void* scores, int64_t T, int k, int64_t H, int E, int G,
                       uint32_t capacity, void* out, int* err, cudaStream_t st);

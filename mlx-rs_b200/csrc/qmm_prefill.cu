@@ -88,6 +88,7 @@ struct PrefillArgs {
   const float* a_row_scale;     // by sorted position: the power of two each A row was divided by
   const void* row_scale;        // bf16 by out row, or null
   void* out;
+  const unsigned long long* out_row_addr;  // optional, by sorted position: where the row's bf16 output goes
   int out_f32;
   int K, N;                     // reduction length, output features per matrix
   int* err;
@@ -224,6 +225,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       const uint32_t sp = row0 + r;
       const uint32_t dst = row_ok ? (p.dst_perm ? p.perm[sp] : sp) : 0xffffffffu;  // 0xffffffff: row not stored
       const float ar = row_ok ? p.a_row_scale[sp] : 1.0f;
+      const unsigned long long daddr = (row_ok && p.out_row_addr) ? p.out_row_addr[sp] : 0ull;
       if (!mbar_wait(tfull_bar(tb), tphase, abort_flag)) break;
       tphase ^= 1;
       tm.stop(0);
@@ -328,8 +330,12 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 o.y = f32_to_bf16_bits(v0.z * c0.z) | (f32_to_bf16_bits(v0.w * c0.w) << 16);
                 o.z = f32_to_bf16_bits(v1.x * c1.x) | (f32_to_bf16_bits(v1.y * c1.y) << 16);
                 o.w = f32_to_bf16_bits(v1.z * c1.z) | (f32_to_bf16_bits(v1.w * c1.w) << 16);
-                if (d != 0xffffffffu)
-                  *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)d * p.N + ct * FEAT + c + cg8) = o;
+                const unsigned long long da = __shfl_sync(0xffffffffu, daddr, rr);
+                if (d != 0xffffffffu) {
+                  __nv_bfloat16* orow = p.out_row_addr ? reinterpret_cast<__nv_bfloat16*>(da)
+                                                       : static_cast<__nv_bfloat16*>(p.out) + (size_t)d * p.N;
+                  *reinterpret_cast<uint4*>(orow + ct * FEAT + c + cg8) = o;
+                }
               }
             }
           }
@@ -784,6 +790,7 @@ int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows,
   p.a_row_scale = a_row_scale;
   p.row_scale = g.row_scale;
   p.out = g.out;
+  p.out_row_addr = g.out_row_addr;
   p.out_f32 = g.out_f32;
   p.K = g.K;
   p.N = g.N;

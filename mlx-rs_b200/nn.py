@@ -86,6 +86,17 @@ class SwitchGlu:
         return out
 
 
+    def forward_sorted_scatter(self, rows, counts, n, out_row_addr):
+        """forward_sorted whose output rows go to the per-row addresses `out_row_addr` (int64 [n], bf16 rows of
+        `hidden` elements each; the addresses may be in peer GPUs' memory)."""
+        ops._cuda(rows, counts, out_row_addr)
+        ops._req(rows.dtype == torch.bfloat16 and counts.dtype == torch.int32 and out_row_addr.dtype == torch.int64,
+                 "forward_sorted_scatter: bf16 rows, int32 counts, int64 addresses")
+        cfg, params = self._cfg(1), self._params()
+        L.check(L.lib().b200_switch_glu_sorted_scatter(ops._ctx(self.ctx), C.byref(cfg), C.byref(params), L.ptr(rows),
+                                                       L.ptr(counts), n, L.ptr(out_row_addr), L.stream_ptr()))
+
+
 class MoeBlock:
     """gate (router Linear, weight [E,H] bf16) + switch_mlp (SwitchGlu)."""
 

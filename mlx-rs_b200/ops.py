@@ -167,12 +167,13 @@ def take_rows(x, indices, div=1, ctx=None):
     return out
 
 
-def moe_combine(y_sorted, inv_perm, scores, return_f32=False, ctx=None):
+def moe_combine(y_sorted, inv_perm, scores, return_f32=False, out=None, ctx=None):
     """out[t] = sum_j scores[t, j] * y_sorted[inv_perm[t*k + j]] (float32 accumulation) -> bf16 [T, H]."""
-    _cuda(y_sorted, inv_perm, scores)
+    _cuda(y_sorted, inv_perm, scores, out)
     T, k = scores.shape
     H = y_sorted.shape[-1]
-    out = torch.empty((T, H), dtype=torch.bfloat16, device=y_sorted.device)
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=y_sorted.device)
     o32 = torch.empty((T, H), dtype=torch.float32, device=y_sorted.device) if return_f32 else None
     L.check(L.lib().b200_moe_combine(_ctx(ctx), L.ptr(y_sorted), L.ptr(inv_perm), L.ptr(scores), T, k, H, L.ptr(out),
                                      L.ptr(o32), L.stream_ptr()))
@@ -195,6 +196,17 @@ def ep_layout(all_counts, rank, capacity_rows, ctx=None):
     L.check(L.lib().b200_ep_layout(_ctx(ctx), L.ptr(all_counts), G, E, rank, capacity_rows, L.ptr(dst_row0),
                                    L.ptr(local_counts), L.stream_ptr()))
     return dst_row0, local_counts
+
+
+def ep_return_table(all_counts, rank, peer_y, hidden, n_rows, ctx=None):
+    """-> int64 [n_rows]: for every row this rank receives, the address of its output row in the source
+    rank's return buffer (peer_y: device addresses of all ranks' return buffers)."""
+    _cuda(all_counts)
+    G, E = all_counts.shape
+    addr = torch.empty(max(n_rows, 1), dtype=torch.int64, device=all_counts.device)
+    L.check(L.lib().b200_ep_return_table(_ctx(ctx), L.ptr(all_counts), G, E, rank, _ptr_array(peer_y), hidden, L.ptr(addr),
+                                         L.stream_ptr()))
+    return addr
 
 
 def ep_dispatch(x, indices, perm, offsets, dst_row0, peer_rows, capacity_rows, n_experts, ctx=None):

@@ -30,7 +30,8 @@ def _worker(rank, world, port, cfg, transport, ret):
         bufs = None
         if transport.startswith("peer"):
             bufs = [ep.PeerBuffers(pkg, blk["H"], T * blk["k"]) for _ in range(2 if transport == "peer2" else 1)]
-            moe = ep.PeerExpertParallelMoe(pkg, full.gate_weight, mlp, blk["E"], blk["k"], bufs)
+            moe = ep.PeerExpertParallelMoe(pkg, full.gate_weight, mlp, blk["E"], blk["k"], bufs,
+                                           fused_return=(transport == "peer_push"))
         else:
             moe = ep.ExpertParallelMoe(ep.B200Backend(pkg, full.gate_weight, mlp, blk["k"]), blk["E"], blk["k"])
         lo, hi = rank * T // world, (rank + 1) * T // world
@@ -54,7 +55,7 @@ def _free_port():
 
 @pytest.mark.parametrize("cfg", [dict(T=96, H=256, E=8, I=128, k=2, seed=3),
                                  dict(T=700, H=512, E=16, I=256, k=4, seed=5)])
-@pytest.mark.parametrize("transport", ["nccl", "peer", "peer2"])
+@pytest.mark.parametrize("transport", ["nccl", "peer", "peer2", "peer_push"])
 def test_expert_parallel_two_gpus(O, cfg, transport):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

@@ -50,6 +50,23 @@ def test_peer_exchange_emulated_ranks(pkg, O, cfg, G):
             mlps[r].forward_sorted(rows_buf[r], tables[r][1], n_recv, out=y_buf[r])
     ref = O.moe_block(blk["x"], blk["wr"], blk["gate"], blk["up"], blk["down"], k)
     rms = np.sqrt((ref["out_f32"] ** 2).mean())
+    # the same again with the return fused into the down projection: every owner's epilogue stores the
+    # rows into the SOURCE rank's return buffer (sorted order of the source), the combine is local
+    ret_buf = [torch.zeros((cap, H), dtype=torch.bfloat16, device=dev) for _ in range(G)]
+    ret_ptrs = [b.data_ptr() for b in ret_buf]
+    for r in range(G):
+        n_recv = int(tables[r][1].sum())
+        if n_recv:
+            addr = ops.ep_return_table(all_counts, r, ret_ptrs, H, n_recv)
+            mlps[r].forward_sorted_scatter(rows_buf[r], tables[r][1], n_recv, addr)
+    for r in range(G):
+        idx, scores, perm, inv, counts, offsets = routed[r]
+        n_own = idx.numel()
+        out = ops.moe_combine(ret_buf[r][:n_own], inv, scores)
+        pkg.default_context().check()
+        lo, hi = r * T // G, (r + 1) * T // G
+        d = np.abs(out.float().cpu().numpy() - ref["out_f32"][lo:hi])
+        assert np.all(d <= 2e-2 * rms + 2.0 ** -8 * np.abs(ref["out_f32"][lo:hi]))
     for r in range(G):      # phase 3
         idx, scores, perm, inv, counts, offsets = routed[r]
         out = ops.ep_combine(y_ptrs, idx, inv, offsets, tables[r][0], scores, H, cap, E)
