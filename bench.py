@@ -431,7 +431,10 @@ def main():
     else:
         roof = dict(bound="tensor", achieved=gu["tflops"], peak=peaks["tensor"], unit="TFLOP/s",
                     frac=gu["tflops"] / peaks["tensor"])
-    roof.update(kernel="gate+up grouped quantized GEMM (dominant)", peak_source=peaks["source"], traffic=None,
+    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size, from the ncu
+    # captures summarised under profiles/ (a profiler cannot run inside the timed bench)
+    ncu_traffic = {8192: 584.3e6, 64: 228.7e6}
+    roof.update(kernel="gate+up grouped quantized GEMM (dominant)", peak_source=peaks["source"], traffic=ncu_traffic.get(T),
                 kernel_ms=gu["ms"], algorithmic_bytes=gu["bytes"], algorithmic_flops=gu["flops"])
 
     base = None if args.no_cpu_baseline else cpu_baseline(min(T, 256), SHAPE, args.seed)

@@ -117,7 +117,10 @@ int b200_ctx_set_qmm_path(b200_ctx* ctx, int path);
  * 16.. hold the tensor-core kernel's self-timing (kilo-cycles per role and wait) when the
  * environment variable B200_TC_DEBUG has bit 5 set. */
 int b200_ctx_debug_words(b200_ctx* ctx, int32_t* host_out, int n);
-#define B200_N_STAGES 6
+/* Per-stage CUDA-event times of the last b200_moe_block_forward (profiling on): router logits, top-k,
+ * sort (+ tile lists), activation preparation for gate/up, gate/up product, activation preparation
+ * for down, down product, combine. */
+#define B200_N_STAGES 8
 int b200_ctx_set_profiling(b200_ctx* ctx, int enable);
 int b200_ctx_stage_ms(b200_ctx* ctx, float* ms, int n);
 

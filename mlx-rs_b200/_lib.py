@@ -151,7 +151,7 @@ class Context:
     def check(self):
         check(lib().b200_ctx_check(self._h, stream_ptr()))
 
-    STAGES = ("router_logits", "route_topk", "permute", "gate_up", "down", "combine")
+    STAGES = ("router_logits", "route_topk", "permute", "prepare_x", "gate_up", "prepare_h", "down", "combine")
 
     def debug_words(self, n=64):
         buf = (C.c_int32 * n)()

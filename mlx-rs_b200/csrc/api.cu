@@ -74,6 +74,7 @@ static size_t block_scratch_bytes(const b200_moe_config& cfg, int64_t T) {
   const int64_t n = T * cfg.top_k, E = cfg.n_experts;
   size_t b = 0;
   b += al(sizeof(uint16_t) * T * E);                 // logits
+  b += al(sizeof(double) * E * cfg.hidden);          // float64 image of the router weight
   b += al(sizeof(uint32_t) * n) * 3;                 // idx, perm, inv
   b += al(sizeof(uint16_t) * n);                     // scores
   b += al(sizeof(uint32_t) * (E + 1)) * 3 + al(16);  // counts, offsets, active, n_active
@@ -448,11 +449,12 @@ int b200_router_topk(b200_ctx* c, const b200_moe_config* cfg, const void* x, con
   B200_REQUIRE(T >= 0 && T < (1 << 24), "bad token count");
   if (T == 0) return 0;
   B200_REQUIRE(x && wr && indices && scores, "null tensor");
-  if (!logits) {
-    if (ctx_grow(c, al(sizeof(uint16_t) * T * cfg->n_experts) + 4096)) return 1;
-    logits = c->take(sizeof(uint16_t) * T * cfg->n_experts);
-  }
-  launch_router_logits(x, wr, logit_bias, logits, (int)T, cfg->hidden, cfg->n_experts, st);
+  const size_t w64_bytes = sizeof(double) * (size_t)cfg->n_experts * cfg->hidden;
+  if (ctx_grow(c, al(sizeof(uint16_t) * T * cfg->n_experts) + al(w64_bytes) + 4096)) return 1;
+  if (!logits) logits = c->take(sizeof(uint16_t) * T * cfg->n_experts);
+  double* w64 = static_cast<double*>(c->take(w64_bytes));
+  B200_REQUIRE(logits && w64, "scratch arena too small");
+  launch_router_logits(x, wr, logit_bias, logits, (int)T, cfg->hidden, cfg->n_experts, w64, st);
   launch_route_topk(logits, (int)T, cfg->n_experts, cfg->top_k, cfg->router_mode, cfg->norm_topk_prob, indices, scores,
                     nullptr, st);
   LAUNCHED(c, 2);
@@ -487,7 +489,9 @@ static bool use_tensor_core_path(const b200_ctx* c, const b200_moe_config& cfg, 
   if ((size_t)8 * (2 * kmax + 16) + sizeof(float) * (kmax / 64) * 8 > 220 * 1024) return true;
   if (c->qmm_path == B200_QMM_SMALL || c->qmm_path == B200_QMM_STREAM || c->qmm_path == B200_QMM_TMEM) return false;
   if (c->qmm_path == B200_QMM_TENSOR_CORE) return true;
-  return n / (max_active > 0 ? max_active : 1) >= 24;
+  // measured crossover on the Qwen3-30B-A3B shape: 8 rows per expert 257 us (register kernel) against 336 us,
+  // 12 rows per expert 377 us against 351 us
+  return n / (max_active > 0 ? max_active : 1) >= 10;
 }
 
 // Gate/up and down products over rows that are grouped by expert (offsets/active/n_active describe
@@ -621,20 +625,23 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   if (tc) {
     // rows gathered into expert order, converted to row-normalised fp16, in the k order the 4-bit unpack produces
     launch_prepare_rows(x, perm, perm ? src_div : 1, n, cfg.hidden, cfg.bits == 4, xs, rs_x, st);
+    c->mark(4, st);
     if (launch_grouped_qmm_tc(xs, rs_x, n, gu, 2, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, false,
                               c->err, st))
       return 1;
     LAUNCHED(c, 2);
   } else if (mb) {
     launch_prepare_rows_mb(x, perm, perm ? src_div : 1, n, cfg.hidden, cfg.bits, xs, rs_x, tab_x, st);
+    c->mark(4, st);
     if (launch_grouped_qmm_mb(xs, rs_x, tab_x, n, gu, 2, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, c->err,
                               st))
       return 1;
     LAUNCHED(c, 2);
-  } else if (run_grouped(c, gu, 2, cfg.bits, max_active, n, st)) {
-    return 1;
+  } else {
+    c->mark(4, st);
+    if (run_grouped(c, gu, 2, cfg.bits, max_active, n, st)) return 1;
   }
-  c->mark(4, st);
+  c->mark(5, st);
 
   GroupedArgs dn{};
   dn.x = h;
@@ -661,6 +668,7 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   if (tc) {
     // h was written (bf16-rounded) already in unpack order; only the fp16 conversion remains
     launch_prepare_rows(h, nullptr, 1, n, cfg.inter, 0, h16, rs_h, st);
+    c->mark(6, st);
     if (alt_down ? launch_grouped_qmm_tc(h16, rs_h, n, dn, 1, cfg.bits, tile_expert1, tile_row01, tile_rows1, n_row_tiles1,
                                          E, true, c->err, st)
                  : launch_grouped_qmm_tc(h16, rs_h, n, dn, 1, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E,
@@ -669,17 +677,20 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
     LAUNCHED(c, 2);
   } else if (mb) {
     launch_prepare_rows_mb(h, nullptr, 1, n, cfg.inter, cfg.bits, h16, rs_h, tab_h, st);
+    c->mark(6, st);
     if (launch_grouped_qmm_mb(h16, rs_h, tab_h, n, dn, 1, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, c->err,
                               st))
       return 1;
     LAUNCHED(c, 2);
   } else if (out_row_addr) {  // per-row addresses: the register kernel (the streamed variant does not take them)
+    c->mark(6, st);
     if (launch_grouped_qmm_small(dn, 1, cfg.bits, max_active, n, st)) return 1;
     LAUNCHED(c, 1);
-  } else if (run_grouped(c, dn, 1, cfg.bits, max_active, n, st)) {
-    return 1;
+  } else {
+    c->mark(6, st);
+    if (run_grouped(c, dn, 1, cfg.bits, max_active, n, st)) return 1;
   }
-  c->mark(5, st);
+  c->mark(7, st);
   return 0;
 }
 
@@ -741,8 +752,10 @@ int b200_moe_block_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_m
                        yk, st, &yk_bf16))
       return 1;
   } else {
+    double* w64 = static_cast<double*>(c->take(sizeof(double) * (size_t)cfg->n_experts * cfg->hidden));
+    B200_REQUIRE(w64, "scratch arena too small");
     launch_router_logits(x, params->router_weight, params->router_logit_bias, logits, (int)T, cfg->hidden, cfg->n_experts,
-                         st);
+                         w64, st);
     c->mark(1, st);
     launch_route_topk(logits, (int)T, cfg->n_experts, cfg->top_k, cfg->router_mode, cfg->norm_topk_prob, idx, scores,
                       nullptr, st);
@@ -751,7 +764,7 @@ int b200_moe_block_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_m
     if (experts_forward(c, *cfg, *params, x, idx, scores, T, yk, aux, st, &yk_bf16)) return 1;
   }
   if (launch_combine(yk, yk_bf16, T, cfg->top_k, cfg->hidden, out, aux ? aux->out_f32 : nullptr, st)) return 1;
-  c->mark(6, st);
+  c->mark(8, st);
   c->ev_valid = c->profiling;
   LAUNCHED(c, 1);
   return 0;

@@ -31,8 +31,9 @@ struct GroupedArgs {
 };
 
 // router.cu
+// w64: optional scratch of E*H doubles (the float64 image of the router weight, rewritten by the call)
 int launch_router_logits(const void* x, const void* w, const float* logit_bias, void* logits, int T, int H, int E,
-                         cudaStream_t st);
+                         double* w64, cudaStream_t st);
 int launch_route_topk(const void* logits, int T, int E, int k, int mode, int renorm, uint32_t* idx, void* scores,
                       void* probs, cudaStream_t st);
 // logits + top-k + token -> expert sort in one launch (T*k <= 1024); `ticket` is a zero-initialised device word

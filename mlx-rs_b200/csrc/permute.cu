@@ -37,38 +37,60 @@ __global__ void __launch_bounds__(kChunk) permute_hist_kernel(const uint32_t* __
   for (int e = threadIdx.x; e < E; e += kChunk) chunk_cnt[(size_t)blockIdx.x * E + e] = sh[e];
 }
 
-// Phase 2: per-expert running sum over chunks, expert prefix sum, active list.  One CTA.
+// Phase 2: per-expert running sum over chunks, expert prefix sum, active list.  One CTA of 1024
+// threads = floor(1024 / E) groups x E experts; a group owns a contiguous range of chunks, so the
+// running sums are short chains (a single chain over 64 chunks cost 22 us of load latency).
 // On exit chunk_cnt[c,e] holds the absolute base position of expert e's assignments of chunk c.
 __global__ void __launch_bounds__(1024) permute_scan_kernel(uint32_t* __restrict__ chunk_cnt, int nchunks, int E,
                                                             uint32_t* __restrict__ counts, uint32_t* __restrict__ offsets,
                                                             uint32_t* __restrict__ active, uint32_t* __restrict__ n_active) {
-  extern __shared__ int sh[];  // [E] totals -> exclusive offsets
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    uint32_t run = 0;
-    for (int c = 0; c < nchunks; ++c) {
-      uint32_t v = chunk_cnt[(size_t)c * E + e];
-      chunk_cnt[(size_t)c * E + e] = run;
-      run += v;
+  extern __shared__ int sh[];  // [ngrp][E] partial sums, then [E] exclusive offsets
+  const int ngrp = max(1, (int)blockDim.x / E);
+  int* off = sh + ngrp * E;
+  const int grp = threadIdx.x / E, e = threadIdx.x % E;
+  const bool live = grp < ngrp;
+  const int cpg = (nchunks + ngrp - 1) / ngrp;
+  const int c0 = min(nchunks, grp * cpg), c1 = min(nchunks, c0 + cpg);
+  if (live) {
+    uint32_t sum = 0;
+    for (int c = c0; c < c1; ++c) sum += chunk_cnt[(size_t)c * E + e];
+    sh[grp * E + e] = (int)sum;
+  }
+  __syncthreads();
+  uint32_t before = 0;  // assignments of expert e in the chunks of earlier groups
+  if (live) {
+    uint32_t total = 0;
+    for (int g = 0; g < ngrp; ++g) {
+      if (g == grp) before = total;
+      total += (uint32_t)sh[g * E + e];
     }
-    sh[e] = run;
-    counts[e] = run;
+    if (grp == 0) {
+      off[e] = (int)total;
+      counts[e] = total;
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {  // E is at most a few hundred: a serial scan costs well under a microsecond
     uint32_t run = 0, na = 0;
-    for (int e = 0; e < E; ++e) {
-      uint32_t c = sh[e];
-      offsets[e] = run;
-      sh[e] = run;
-      if (c) active[na++] = e;
+    for (int ee = 0; ee < E; ++ee) {
+      uint32_t c = (uint32_t)off[ee];
+      offsets[ee] = run;
+      off[ee] = (int)run;
+      if (c) active[na++] = ee;
       run += c;
     }
     offsets[E] = run;
     *n_active = na;
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < E; e += blockDim.x)
-    for (int c = 0; c < nchunks; ++c) chunk_cnt[(size_t)c * E + e] += sh[e];
+  if (live) {
+    uint32_t run = (uint32_t)off[e] + before;
+    for (int c = c0; c < c1; ++c) {
+      const uint32_t v = chunk_cnt[(size_t)c * E + e];
+      chunk_cnt[(size_t)c * E + e] = run;
+      run += v;
+    }
+  }
 }
 
 // Phase 3: stable scatter of one chunk.
@@ -122,7 +144,8 @@ int launch_permute(const uint32_t* idx, int64_t n, int E, uint32_t* perm, uint32
   }
   const int nchunks = cdiv(n, kChunk);
   permute_hist_kernel<<<nchunks, kChunk, sizeof(int) * E, st>>>(idx, (int)n, E, chunk_scratch, err);
-  permute_scan_kernel<<<1, 1024, sizeof(int) * E, st>>>(chunk_scratch, nchunks, E, counts, offsets, active, n_active);
+  permute_scan_kernel<<<1, 1024, sizeof(int) * (1024 / E + 1) * E, st>>>(chunk_scratch, nchunks, E, counts, offsets, active,
+                                                                          n_active);
   permute_scatter_kernel<<<nchunks, kChunk, sh_scatter, st>>>(idx, (int)n, E, chunk_scratch, perm, inv);
   return 0;
 }

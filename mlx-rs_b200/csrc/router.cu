@@ -194,13 +194,13 @@ __global__ void __launch_bounds__(256) router_logits_warp_kernel(const __nv_bflo
 }
 
 // ---------------------------------------------------------------------------------------
-// Large token counts: float64 tensor-core variant.  CTA = 8 warps over MT*8 tokens x 128 experts;
-// a warp owns all the tokens x 16 experts as 8x8 accumulator tiles of mma.sync m8n8k4 (f64).  The
+// Mid and large token counts: float64 tensor-core variant.  CTA = 8 warps over MT*8 tokens x NE*64
+// experts; a warp owns all the tokens x NE*8 experts as 8x8 accumulator tiles of mma.sync m8n8k4 (f64).  The
 // operands are converted to float64 once per 32-wide K chunk while they are staged in shared
 // memory (row-major, rows padded by 32 bytes so that fragment loads spread over all banks);
 // two buffers, and the next chunk's global loads are issued before the current chunk's products.
-// The token tile (32..64 rows) is chosen per launch so that the last wave over 148 SMs is full
-// (T = 8192: 56 rows -> 147 CTAs).
+// The tile shape is chosen per launch so that the waves over 148 SMs are full
+// (T = 8192: 56 tokens x 128 experts -> 147 CTAs; T = 2048: 32 x 64 -> 128 CTAs).
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void dmma_884(double (&c)[2], double a, double b) {
   asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
@@ -208,25 +208,46 @@ __device__ __forceinline__ void dmma_884(double (&c)[2], double a, double b) {
                : "d"(a), "d"(b));
 }
 
-template <int MT>
+// Router weight -> float64, once per call (E*H elements): the tiles then stage weight rows with plain
+// 16-byte asynchronous copies instead of converting the same rows again in every token tile.
+__global__ void router_weight_f64_kernel(const __nv_bfloat16* __restrict__ w, double* __restrict__ w64, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) w64[i] = bf16_bits_to_f64((uint32_t)__bfloat16_as_ushort(w[i]));
+}
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// W64: the weight arrives as float64 (w64) and is copied, only the token rows are converted.
+template <int MT, int NE, int KC, bool W64>
 __global__ void __launch_bounds__(256) router_logits_dmma_kernel(const __nv_bfloat16* __restrict__ x,
                                                                  const __nv_bfloat16* __restrict__ w,
+                                                                 const double* __restrict__ w64,
                                                                  const float* __restrict__ logit_bias,
                                                                  __nv_bfloat16* __restrict__ logits, int T, int H, int E) {
-  constexpr int KC = 32, LD = KC + 4, TE = 128, TT = MT * 8;
-  constexpr int ROWS = TT + TE;
+  constexpr int LD = KC + 4, TE = 64 * NE, TT = MT * 8;  // a warp owns NE 8-expert tiles; KC = k per staged chunk
+  constexpr int ROWS = W64 ? TT : TT + TE;             // rows that pass through registers (converted)
   constexpr int NLD = (ROWS * (KC / 8) + 255) / 256;  // 128-bit loads per thread and chunk
   extern __shared__ __align__(16) unsigned char dsm[];
   double* buf0 = reinterpret_cast<double*>(dsm);       // two buffers of [TT + TE][LD]
+  constexpr int BUF = (TT + TE) * LD;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int t0 = blockIdx.x * TT, e0 = blockIdx.y * TE;
   const int r = lane >> 2, kq = lane & 3;
 
-  double acc[MT][2][2];
+  // small tiles give a warp one or two accumulator tiles: consecutive k steps then alternate between KI
+  // independent partial sums so that the tensor-pipe latency of one step does not serialise the next
+  constexpr int KI = (MT * NE <= 2) ? 4 : (MT * NE <= 4) ? 2 : 1;
+  double acc[KI][MT][NE][2];
 #pragma unroll
-  for (int i = 0; i < MT; ++i)
+  for (int q = 0; q < KI; ++q)
 #pragma unroll
-    for (int j = 0; j < 2; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+      for (int j = 0; j < NE; ++j) acc[q][i][j][0] = acc[q][i][j][1] = 0.0;
 
   uint4 pre[NLD];
   auto fetch = [&](int k0) {
@@ -261,75 +282,114 @@ __global__ void __launch_bounds__(256) router_logits_dmma_kernel(const __nv_bflo
     }
   };
 
+  auto copy_w = [&](int k0, double* buf) {  // float64 weight rows: 16-byte asynchronous copies (2 elements each)
+    if constexpr (W64) {
+      for (int i = tid; i < TE * (KC / 2); i += 256) {
+        const int row = i / (KC / 2), c = i % (KC / 2);
+        double* d = buf + (TT + row) * LD + c * 2;
+        if (e0 + row < E && k0 + c * 2 < H)
+          cp_async16(d, w64 + (size_t)(e0 + row) * H + k0 + c * 2);
+        else
+          d[0] = d[1] = 0.0;
+      }
+    }
+  };
+
   fetch(0);
+  copy_w(0, buf0);
   stash(buf0);
+  cp_async_wait_all();
   __syncthreads();
   int cur = 0;
   for (int k0 = 0; k0 < H; k0 += KC) {
     const bool more = k0 + KC < H;
-    if (more) fetch(k0 + KC);                       // global loads in flight under the products below
-    const double* xs = buf0 + cur * ROWS * LD;
+    if (more) {
+      fetch(k0 + KC);                               // global loads in flight under the products below
+      copy_w(k0 + KC, buf0 + (cur ^ 1) * BUF);      // the other buffer was last read before the previous barrier
+    }
+    const double* xs = buf0 + cur * BUF;
     const double* ws = xs + TT * LD;
 #pragma unroll
     for (int kk = 0; kk < KC; kk += 4) {
-      double a[MT], b[2];
+      double a[MT], b[NE];
 #pragma unroll
       for (int i = 0; i < MT; ++i) a[i] = xs[(i * 8 + r) * LD + kk + kq];
 #pragma unroll
-      for (int j = 0; j < 2; ++j) b[j] = ws[(warp * 16 + j * 8 + r) * LD + kk + kq];
+      for (int j = 0; j < NE; ++j) b[j] = ws[(warp * (8 * NE) + j * 8 + r) * LD + kk + kq];
 #pragma unroll
       for (int i = 0; i < MT; ++i)
 #pragma unroll
-        for (int j = 0; j < 2; ++j) dmma_884(acc[i][j], a[i], b[j]);
+        for (int j = 0; j < NE; ++j) dmma_884(acc[(kk / 4) % KI][i][j], a[i], b[j]);
     }
-    if (more) stash(buf0 + (cur ^ 1) * ROWS * LD);    // the other buffer: last read before the previous barrier
+    if (more) stash(buf0 + (cur ^ 1) * BUF);
+    cp_async_wait_all();
     __syncthreads();
     cur ^= 1;
   }
 #pragma unroll
   for (int i = 0; i < MT; ++i)
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
+    for (int j = 0; j < NE; ++j)
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
-        const int t = t0 + i * 8 + r, e = e0 + warp * 16 + j * 8 + kq * 2 + q;
+        const int t = t0 + i * 8 + r, e = e0 + warp * (8 * NE) + j * 8 + kq * 2 + q;
         if (t < T && e < E) {
-          uint32_t bits = f64_to_bf16_bits(acc[i][j][q]);
+          double sum = acc[0][i][j][q];
+#pragma unroll
+          for (int u = 1; u < KI; ++u) sum += acc[u][i][j][q];
+          uint32_t bits = f64_to_bf16_bits(sum);
           if (logit_bias) bits = f32_to_bf16_bits(bf16_bits_to_f32(bits) + logit_bias[e]);
           logits[(size_t)t * E + e] = __ushort_as_bfloat16((unsigned short)bits);
         }
       }
 }
 
-template <int MT>
-static int launch_router_dmma(const __nv_bfloat16* xp, const __nv_bfloat16* wp, const float* logit_bias,
+template <int MT, int NE>
+static int launch_router_dmma(const __nv_bfloat16* xp, const __nv_bfloat16* wp, const double* w64, const float* logit_bias,
                               __nv_bfloat16* lp, int T, int H, int E, cudaStream_t st) {
-  constexpr size_t smem = sizeof(double) * 2 * (MT * 8 + 128) * 36;
-  auto kern = router_logits_dmma_kernel<MT>;
-  static bool attr = false;
-  if (!attr) {
-    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr = true;
+  // small tiles are bound by the barrier + load round trip per chunk, not by the products: longer chunks
+  constexpr int KC = (MT * NE <= 2) ? 128 : (MT * NE <= 4) ? 64 : 32;
+  constexpr size_t smem = sizeof(double) * 2 * (MT * 8 + 64 * NE) * (KC + 4);
+  dim3 grid(cdiv(T, MT * 8), cdiv(E, 64 * NE));
+  if (w64 && H % 2 == 0) {
+    auto kern = router_logits_dmma_kernel<MT, NE, KC, true>;
+    static bool attr = false;
+    if (!attr) {
+      B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      attr = true;
+    }
+    const int64_t n = (int64_t)E * H;
+    router_weight_f64_kernel<<<cdiv(n, 256), 256, 0, st>>>(wp, const_cast<double*>(w64), n);
+    kern<<<grid, 256, smem, st>>>(xp, wp, w64, logit_bias, lp, T, H, E);
+  } else {
+    auto kern = router_logits_dmma_kernel<MT, NE, KC, false>;
+    static bool attr = false;
+    if (!attr) {
+      B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      attr = true;
+    }
+    kern<<<grid, 256, smem, st>>>(xp, wp, nullptr, logit_bias, lp, T, H, E);
   }
-  dim3 grid(cdiv(T, MT * 8), cdiv(E, 128));
-  kern<<<grid, 256, smem, st>>>(xp, wp, logit_bias, lp, T, H, E);
   return 0;
 }
 
-// Token rows per CTA (a multiple of 8, 32..64) that wastes the least of the last wave on 148 SMs.
-static int dmma_token_tiles(int T, int e_blocks) {
-  int best = 8;
-  double best_eff = 0.0;
-  for (int mt = 8; mt >= 4; --mt) {
-    const long tiles = (long)cdiv(T, mt * 8) * e_blocks;
-    const long waves = (tiles + 147) / 148;
-    const double eff = (double)T * e_blocks / (double)(waves * 148 * mt * 8);
-    if (eff > best_eff + 1e-9) {
-      best_eff = eff;
-      best = mt;
+// Tile shape (MT*8 tokens x NE*64 experts per CTA) with the least estimated time on 148 SMs:
+// waves x (products of a tile + the staging/conversion work of its rows, weighted).
+static void dmma_tile_shape(int T, int E, int& mt_best, int& ne_best) {
+  double best = 1e300;
+  mt_best = 8;
+  ne_best = 2;
+  for (int ne = 2; ne >= 1; --ne)
+    for (int mt = 8; mt >= 1; --mt) {
+      const long tiles = (long)cdiv(T, mt * 8) * cdiv(E, 64 * ne);
+      const long waves = (tiles + 147) / 148;
+      const double cost = (double)waves * ((double)(mt * 8) * (64 * ne) + 8.0 * (mt * 8 + 64 * ne));
+      if (cost < best - 1e-9) {
+        best = cost;
+        mt_best = mt;
+        ne_best = ne;
+      }
     }
-  }
-  return best;
 }
 
 template <int TT>
@@ -348,7 +408,7 @@ static int launch_router_warp(const __nv_bfloat16* xp, const __nv_bfloat16* wp, 
 }
 
 int launch_router_logits(const void* x, const void* w, const float* logit_bias, void* logits, int T, int H, int E,
-                         cudaStream_t st) {
+                         double* w64, cudaStream_t st) {
   auto xp = static_cast<const __nv_bfloat16*>(x);
   auto wp = static_cast<const __nv_bfloat16*>(w);
   auto lp = static_cast<__nv_bfloat16*>(logits);
@@ -358,14 +418,26 @@ int launch_router_logits(const void* x, const void* w, const float* logit_bias, 
   }();
   const bool warp_ok = (H % 8 == 0) && ((size_t)8 * H * 2 <= 200 * 1024);
   const bool dmma_ok = (H % 8 == 0);
-  if (dmma_ok && (force == 3 || (!force && T >= 1024))) {
-    switch (dmma_token_tiles(T, cdiv(E, 128))) {
-      case 4: return launch_router_dmma<4>(xp, wp, logit_bias, lp, T, H, E, st);
-      case 5: return launch_router_dmma<5>(xp, wp, logit_bias, lp, T, H, E, st);
-      case 6: return launch_router_dmma<6>(xp, wp, logit_bias, lp, T, H, E, st);
-      case 7: return launch_router_dmma<7>(xp, wp, logit_bias, lp, T, H, E, st);
-      default: return launch_router_dmma<8>(xp, wp, logit_bias, lp, T, H, E, st);
+  if (dmma_ok && (force == 3 || (!force && T >= 256))) {
+    int mt, ne;
+    dmma_tile_shape(T, E, mt, ne);
+#define B200_DMMA_CASE(MTV)                                                                  \
+  case MTV:                                                                                  \
+    return ne == 2 ? launch_router_dmma<MTV, 2>(xp, wp, w64, logit_bias, lp, T, H, E, st)         \
+                   : launch_router_dmma<MTV, 1>(xp, wp, w64, logit_bias, lp, T, H, E, st);
+    switch (mt) {
+      B200_DMMA_CASE(1)
+      B200_DMMA_CASE(2)
+      B200_DMMA_CASE(3)
+      B200_DMMA_CASE(4)
+      B200_DMMA_CASE(5)
+      B200_DMMA_CASE(6)
+      B200_DMMA_CASE(7)
+      default:
+        return ne == 2 ? launch_router_dmma<8, 2>(xp, wp, w64, logit_bias, lp, T, H, E, st)
+                       : launch_router_dmma<8, 1>(xp, wp, w64, logit_bias, lp, T, H, E, st);
     }
+#undef B200_DMMA_CASE
   }
   const bool use_warp = force ? (force == 1 && warp_ok) : warp_ok;
   if (use_warp) {
