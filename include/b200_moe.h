@@ -93,6 +93,8 @@ int b200_ctx_destroy(b200_ctx* ctx);
 /* Pre-sizes the scratch memory for blocks of up to `max_tokens` tokens so that later calls
  * do not allocate (allocation synchronises the device). */
 int b200_ctx_reserve(b200_ctx* ctx, const b200_moe_config* cfg, int64_t max_tokens);
+/* Scratch bytes one b200_moe_block_forward over max_tokens tokens needs (what b200_ctx_reserve allocates). */
+int b200_workspace_bytes(const b200_moe_config* cfg, int64_t max_tokens, size_t* bytes);
 /* Synchronises `stream` and reports device-side findings (an expert or gather index out of
  * range) of the calls issued since the last check; they surface here because argument values
  * living on the device cannot be validated before launch. */
@@ -144,6 +146,12 @@ int b200_dequantize(b200_ctx* ctx, const uint32_t* w_q, const void* scales, cons
 int b200_quantized_matmul(b200_ctx* ctx, const void* x, const uint32_t* w, const void* scales, const void* biases,
                           int transpose, int group_size, int bits, int64_t M, int64_t K, int64_t N, void* out,
                           void* stream);
+
+/* gather_mm(a, b, lhs_indices, rhs_indices); mlx-rs/src/ops/arithmetic.rs:1568-1632 (un-quantised).
+ * out[i] = a[lhs[i]] @ b[rhs[i]] with a bf16 [Ba, M, K], b bf16 [Bb, K, N], out bf16 [n_idx, M, N], float32
+ * accumulation.  Either index array may be NULL (identity).  n_idx < 65536 per call. */
+int b200_gather_mm(b200_ctx* ctx, const void* a, const void* b, const uint32_t* lhs_indices, const uint32_t* rhs_indices,
+                   int64_t Ba, int64_t Bb, int64_t M, int64_t K, int64_t N, int64_t n_idx, void* out, void* stream);
 
 /* gather_qmm(x, w, scales, biases, lhs_indices, rhs_indices, transpose, group_size, bits,
  * sorted_indices); mlx-rs/src/ops/quantization.rs:160-230.

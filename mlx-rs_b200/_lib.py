@@ -36,6 +36,7 @@ EXPORTS = {
     "b200_set_error_handler": (None, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200_ctx_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int]),
     "b200_ctx_destroy": (C.c_int, [C.c_void_p]),
+    "b200_workspace_bytes": (C.c_int, [C.POINTER(MoeConfig), C.c_int64, C.POINTER(C.c_size_t)]),
     "b200_ctx_reserve": (C.c_int, [C.c_void_p, C.POINTER(MoeConfig), C.c_int64]),
     "b200_ctx_check": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200_ctx_launch_count": (C.c_int64, [C.c_void_p]),
@@ -49,6 +50,8 @@ EXPORTS = {
                                   C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "b200_quantized_matmul": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                                         C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
+    "b200_gather_mm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                 C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
     "b200_gather_qmm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                   C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                   C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
@@ -147,6 +150,12 @@ class Context:
 
     def reserve(self, cfg, max_tokens):
         check(lib().b200_ctx_reserve(self._h, C.byref(cfg), int(max_tokens)))
+
+    @staticmethod
+    def workspace_bytes(cfg, max_tokens):
+        n = C.c_size_t(0)
+        check(lib().b200_workspace_bytes(C.byref(cfg), int(max_tokens), C.byref(n)))
+        return int(n.value)
 
     def check(self):
         check(lib().b200_ctx_check(self._h, stream_ptr()))

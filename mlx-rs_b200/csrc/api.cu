@@ -168,6 +168,13 @@ int b200_ctx_reserve(b200_ctx* c, const b200_moe_config* cfg, int64_t max_tokens
   return ctx_grow(c, block_scratch_bytes(*cfg, max_tokens));
 }
 
+int b200_workspace_bytes(const b200_moe_config* cfg, int64_t max_tokens, size_t* bytes) {
+  if (check_cfg(cfg)) return 1;
+  B200_REQUIRE(bytes != nullptr && max_tokens >= 0, "bad arguments");
+  *bytes = block_scratch_bytes(*cfg, max_tokens);
+  return 0;
+}
+
 int b200_ctx_check(b200_ctx* c, void* stream) {
   CTX_ENTER(c);
   B200_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
@@ -360,6 +367,21 @@ int b200_gather_qmm(b200_ctx* c, const void* x, const uint32_t* w, const void* s
   a.N = (int)N;
   a.n_experts = (int)E;
   return run_grouped(c, a, 1, bits, (int)(E < n ? E : n), n, st);
+}
+
+int b200_gather_mm(b200_ctx* c, const void* a, const void* b, const uint32_t* lhs_indices, const uint32_t* rhs_indices,
+                   int64_t Ba, int64_t Bb, int64_t M, int64_t K, int64_t N, int64_t n_idx, void* out, void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(Ba > 0 && Bb > 0 && M >= 0 && K > 0 && N >= 0 && n_idx >= 0, "bad shape");
+  B200_REQUIRE(M < (1 << 20) && K < (1 << 24) && N < (1 << 24), "dimension too large");
+  B200_REQUIRE(lhs_indices || n_idx <= Ba, "without lhs_indices a needs one batch entry per index");
+  B200_REQUIRE(rhs_indices || n_idx <= Bb, "without rhs_indices b needs one batch entry per index");
+  if (n_idx == 0 || M == 0 || N == 0) return 0;
+  B200_REQUIRE(a && b && out, "null tensor");
+  if (launch_gather_mm(a, b, lhs_indices, rhs_indices, Ba, Bb, M, K, N, n_idx, out, c->err, static_cast<cudaStream_t>(stream)))
+    return 1;
+  LAUNCHED(c, 1);
+  return 0;
 }
 
 int b200_softmax_axis(b200_ctx* c, const void* a, int64_t rows, int64_t cols, int precise, void* out, void* stream) {

@@ -96,6 +96,8 @@ int launch_rms_norm(const void* x, const void* residual, const void* weight, flo
 int launch_add(const void* a, const void* b, int64_t n, void* out, cudaStream_t st);
 int launch_qmm_rowmajor(const void* x, const uint32_t* wq, const void* scales, const void* biases, int64_t M, int64_t K,
                         int64_t N, int gs, int bits, void* out, cudaStream_t st);
+int launch_gather_mm(const void* a, const void* b, const uint32_t* lhs, const uint32_t* rhs, int64_t Ba, int64_t Bb,
+                     int64_t M, int64_t K, int64_t N, int64_t n_idx, void* out, int* err, cudaStream_t st);
 int launch_dense_segments(uint32_t* counts, uint32_t* offsets, uint32_t* active, uint32_t* n_active, uint32_t rows,
                           cudaStream_t st);
 int launch_expand_indices(const uint32_t* lhs, const uint32_t* rhs, int64_t n_idx, int M, uint32_t* flat_expert,

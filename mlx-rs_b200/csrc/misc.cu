@@ -333,6 +333,65 @@ int launch_dense_segments(uint32_t* counts, uint32_t* offsets, uint32_t* active,
   return 0;
 }
 
+// gather_mm(a, b, lhs_indices, rhs_indices) (mlx-rs/src/ops/arithmetic.rs:1568-1632), un-quantised:
+// out[i] = a[lhs[i]] @ b[rhs[i]] with a bf16 [Ba, M, K], b bf16 [Bb, K, N] (row-major, not transposed),
+// float32 accumulation, bf16 output.  The routed block never takes this path (its experts are
+// quantised); it completes the op surface for callers that keep some SwitchLinear layers in bf16.
+// One CTA = one batch entry x 128 output columns x up to 8 rows of a (staged in shared memory);
+// a thread owns one output column, so every load of b is a coalesced row segment read once.
+constexpr int kGmmRows = 8, kGmmKc = 512;
+__global__ void __launch_bounds__(128) gather_mm_kernel(const __nv_bfloat16* __restrict__ a,
+                                                        const __nv_bfloat16* __restrict__ b,
+                                                        const uint32_t* __restrict__ lhs, const uint32_t* __restrict__ rhs,
+                                                        int64_t Ba, int64_t Bb, int M, int K, int N,
+                                                        __nv_bfloat16* __restrict__ out, int* __restrict__ err) {
+  __shared__ float as[kGmmRows][kGmmKc];
+  const int64_t i = blockIdx.y;
+  const uint32_t la = lhs ? lhs[i] : (uint32_t)i, rb = rhs ? rhs[i] : (uint32_t)i;
+  if (la >= Ba || rb >= Bb) {
+    if (threadIdx.x == 0) *err = 1;
+    return;
+  }
+  const int n = blockIdx.x * 128 + threadIdx.x;
+  const __nv_bfloat16* arow = a + (size_t)la * M * K;
+  const __nv_bfloat16* bmat = b + (size_t)rb * K * N;
+  for (int m0 = 0; m0 < M; m0 += kGmmRows) {
+    const int mr = min(kGmmRows, M - m0);
+    float acc[kGmmRows];
+#pragma unroll
+    for (int r = 0; r < kGmmRows; ++r) acc[r] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += kGmmKc) {
+      const int kc = min(kGmmKc, K - k0);
+      __syncthreads();
+      for (int t = threadIdx.x; t < mr * kc; t += 128) {
+        const int r = t / kc, kk = t % kc;
+        as[r][kk] = __bfloat162float(arow[(size_t)(m0 + r) * K + k0 + kk]);
+      }
+      __syncthreads();
+      if (n < N) {
+        for (int kk = 0; kk < kc; ++kk) {
+          const float bv = __bfloat162float(bmat[(size_t)(k0 + kk) * N + n]);
+#pragma unroll
+          for (int r = 0; r < kGmmRows; ++r)
+            if (r < mr) acc[r] = fmaf(as[r][kk], bv, acc[r]);
+        }
+      }
+    }
+    if (n < N)
+      for (int r = 0; r < mr; ++r) out[((size_t)i * M + m0 + r) * N + n] = __float2bfloat16_rn(acc[r]);
+  }
+}
+
+int launch_gather_mm(const void* a, const void* b, const uint32_t* lhs, const uint32_t* rhs, int64_t Ba, int64_t Bb,
+                     int64_t M, int64_t K, int64_t N, int64_t n_idx, void* out, int* err, cudaStream_t st) {
+  if (n_idx == 0 || M == 0 || N == 0) return 0;
+  B200_REQUIRE(n_idx < 65536, "at most 65535 index entries per call");
+  dim3 grid(cdiv(N, 128), (unsigned)n_idx);
+  gather_mm_kernel<<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), lhs, rhs,
+                                         Ba, Bb, (int)M, (int)K, (int)N, static_cast<__nv_bfloat16*>(out), err);
+  return 0;
+}
+
 // gather_qmm with M rows per batch entry: assignment i*M + m uses expert rhs[i] and source
 // row lhs[i]*M + m (lhs == null: i*M + m).
 __global__ void expand_indices_kernel(const uint32_t* __restrict__ lhs, const uint32_t* __restrict__ rhs, int64_t n_idx,

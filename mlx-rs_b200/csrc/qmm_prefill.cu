@@ -54,8 +54,10 @@ namespace {
 using namespace tc;
 
 constexpr int BM = 128, BMT = 256, BK = 64, NCOL = 256;  // BMT: rows per tile = two 128-row accumulators sharing B
-// STAGES = dequantised-B stages.  (Two activation stages + four packed-weight stages in the same
-// shared memory measured 3-7 % slower at every batch size than three + two.)
+// STAGES = dequantised-B stages.  (Measured alternatives in the same shared memory: two activation + four
+// packed-weight stages 3-7 % slower at every batch size; two activation + three dequantised-B stages no
+// different.  With few rows per expert a K block costs ~1.7 k cycles whatever the number of MMAs: the
+// hand-over latency between the unpack warps and the MMA issuer, not the stage count, sets that floor.)
 constexpr int A_STAGES = 3, STAGES = 2, W_STAGES = 2;
 constexpr int A_BYTES = BM * BK * 2;                     // 16 KB per 128-row sub-tile
 constexpr int A_STAGE_BYTES = 2 * A_BYTES;               // both sub-tiles of a K block

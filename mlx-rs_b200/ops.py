@@ -73,6 +73,24 @@ def quantized_matmul(x, w, scales, biases, transpose=False, group_size=DEFAULT_G
     return out
 
 
+def gather_mm(a, b, lhs_indices=None, rhs_indices=None, ctx=None):
+    """a [..., M, K], b [..., K, N] (batch dims flattened) -> [*idx.shape, M, N]; bf16, float32 accumulation."""
+    _cuda(a, b, lhs_indices, rhs_indices)
+    _req(a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "gather_mm: bf16 operands")
+    M, K = a.shape[-2], a.shape[-1]
+    N = b.shape[-1]
+    _req(b.shape[-2] == K, "gather_mm: inner dimensions differ")
+    Ba, Bb = a.numel() // (M * K), b.numel() // (K * N)
+    idx = lhs_indices if lhs_indices is not None else rhs_indices
+    _req(idx is not None, "gather_mm: at least one index array")
+    _req(lhs_indices is None or rhs_indices is None or lhs_indices.shape == rhs_indices.shape,
+         "gather_mm: index shapes differ")
+    out = torch.empty(tuple(idx.shape) + (M, N), dtype=a.dtype, device=a.device)
+    L.check(L.lib().b200_gather_mm(_ctx(ctx), L.ptr(a), L.ptr(b), L.ptr(lhs_indices), L.ptr(rhs_indices), Ba, Bb, M, K, N,
+                                   idx.numel(), L.ptr(out), L.stream_ptr()))
+    return out
+
+
 def gather_qmm(x, w, scales, biases, lhs_indices=None, rhs_indices=None, transpose=True, group_size=DEFAULT_GROUP_SIZE,
                bits=DEFAULT_BITS, sorted_indices=False, ctx=None):
     """x [..., M, K] (batch dims flattened), w [E, N, K*bits/32] -> [*idx.shape, M, N]."""

@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from tests.helpers import bf16_cuda, rel_err, u32
+from tests.helpers import bf16_cuda, close_up_to_bf16_rounding, rel_err, u32
 
 pytestmark = pytest.mark.gpu
 
@@ -163,3 +163,30 @@ def test_rms_norm_and_residual(pkg, O):
     sref = O.round_bf16(x + r)
     assert np.array_equal(s.float().cpu().numpy(), sref)
     assert close(n.float().cpu().numpy(), O.rms_norm(sref, None, 1e-6))
+
+
+def test_gather_mm_reference_cases(pkg, O):
+    # mlx-rs/src/ops/arithmetic.rs:3140-3238: gather = take on the flattened batch + matmul; sorted rhs case
+    rng = np.random.default_rng(5)
+    a = O.round_bf16((rng.standard_normal((100, 1, 100)) / 10).astype(np.float32))
+    b = O.round_bf16((rng.standard_normal((8, 100, 100)) / 10).astype(np.float32))
+    rhs = np.sort(rng.integers(0, 8, size=100)).astype(np.uint32)
+    ref = O.gather_mm(a, b, None, rhs)
+    got = pkg.ops.gather_mm(bf16_cuda(a), bf16_cuda(b), None, torch.from_numpy(rhs.view(np.int32)).cuda())
+    pkg.default_context().check()
+    assert tuple(got.shape) == (100, 1, 100)
+    assert close_up_to_bf16_rounding(got.float().cpu().numpy(), ref, 1e-3)
+    # both index arrays, several rows per entry, ragged N
+    a = O.round_bf16((rng.standard_normal((5, 11, 300)) / 10).astype(np.float32))
+    b = O.round_bf16((rng.standard_normal((3, 300, 200)) / 10).astype(np.float32))
+    lhs = rng.integers(0, 5, size=(4, 2)).astype(np.uint32)
+    rhs = rng.integers(0, 3, size=(4, 2)).astype(np.uint32)
+    ref = O.gather_mm(a, b, lhs, rhs)
+    got = pkg.ops.gather_mm(bf16_cuda(a), bf16_cuda(b), torch.from_numpy(lhs.view(np.int32)).cuda(),
+                            torch.from_numpy(rhs.view(np.int32)).cuda())
+    pkg.default_context().check()
+    assert tuple(got.shape) == (4, 2, 11, 200)
+    assert close_up_to_bf16_rounding(got.float().cpu().numpy(), ref, 1e-3)
+    with pytest.raises(pkg.B200Error):      # an index past the batch is reported, not read
+        pkg.ops.gather_mm(bf16_cuda(a), bf16_cuda(b), None, torch.tensor([7, 0, 1, 2, 0], dtype=torch.int32).cuda())
+        pkg.default_context().check()
