@@ -83,25 +83,39 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const uint4* __restric
                                                           const uint32_t* __restrict__ dst_row0, int64_t n, uint32_t k,
                                                           int vec_per_row, int E, int Eg, EpPeers peers,
                                                           uint32_t capacity, int* __restrict__ err) {
-  for (int64_t j = blockIdx.x; j < n; j += gridDim.x) {
+  // one warp per row; a lane keeps eight 16-byte pieces in flight before it stores them
+  const int lane = threadIdx.x & 31, wpc = blockDim.x >> 5;
+  for (int64_t j = (int64_t)blockIdx.x * wpc + (threadIdx.x >> 5); j < n; j += (int64_t)gridDim.x * wpc) {
     const uint32_t a = perm[j];
     if (a >= n) {
-      if (threadIdx.x == 0) *err = 6;
+      if (lane == 0) *err = 6;
       continue;
     }
     const uint32_t e = idx[a];
     if (e >= (uint32_t)E) {
-      if (threadIdx.x == 0) *err = 6;
+      if (lane == 0) *err = 6;
       continue;
     }
     const uint32_t row = dst_row0[e] + (uint32_t)j - offsets[e];
     if (row >= capacity) {
-      if (threadIdx.x == 0) *err = 5;
+      if (lane == 0) *err = 5;
       continue;
     }
     const uint4* src = x + (size_t)(a / k) * vec_per_row;
     uint4* dst = static_cast<uint4*>(peers.p[e / Eg]) + (size_t)row * vec_per_row;
-    for (int c = threadIdx.x; c < vec_per_row; c += blockDim.x) dst[c] = __ldg(src + c);
+    for (int c0 = 0; c0 < vec_per_row; c0 += 256) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int c = c0 + u * 32 + lane;
+        if (c < vec_per_row) v[u] = __ldg(src + c);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int c = c0 + u * 32 + lane;
+        if (c < vec_per_row) dst[c] = v[u];
+      }
+    }
   }
 }
 
@@ -109,8 +123,10 @@ int launch_ep_dispatch(const void* x, const uint32_t* idx, const uint32_t* perm,
                        const uint32_t* dst_row0, int64_t n, int k, int64_t H, int E, int G, const EpPeers& peers,
                        uint32_t capacity, int* err, cudaStream_t st) {
   if (n == 0) return 0;
+  // 128 threads x 32 registers: small enough to share an SM with a resident 608-thread tensor-core CTA
+  // (7168 registers are left beside it), so that a dispatch on a side stream overlaps the products
   const int grid = (int)(n < 148 * 16 ? n : 148 * 16);
-  ep_dispatch_kernel<<<grid, 256, 0, st>>>(static_cast<const uint4*>(x), idx, perm, offsets, dst_row0, n, (uint32_t)k,
+  ep_dispatch_kernel<<<grid, 128, 0, st>>>(static_cast<const uint4*>(x), idx, perm, offsets, dst_row0, n, (uint32_t)k,
                                            (int)(H / 8), E, E / G, peers, capacity, err);
   return 0;
 }
@@ -230,7 +246,7 @@ int launch_ep_combine(const EpPeers& peers, const uint32_t* idx, const uint32_t*
   if (T == 0) return 0;
   B200_REQUIRE(k <= kEpMaxTopK, "top_k above 32");
   const int grid = (int)(T < 148 * 16 ? T : 148 * 16);
-  ep_combine_kernel<<<grid, 256, 0, st>>>(peers, idx, inv, offsets, dst_row0, static_cast<const unsigned short*>(scores), T,
+  ep_combine_kernel<<<grid, 128, 0, st>>>(peers, idx, inv, offsets, dst_row0, static_cast<const unsigned short*>(scores), T,
                                           k, (int)(H / 8), E, E / G, capacity, static_cast<uint4*>(out), err);
   return 0;
 }

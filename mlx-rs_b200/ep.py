@@ -201,6 +201,7 @@ class PeerExpertParallelMoe:
                        for b in self.bufs]
         self._side = torch.cuda.Stream(device=dev) if self.chunks > 1 else None
         self.last = {}
+        self.profile = False      # one-chunk forwards record an event after every phase into self.phase_ms
 
     def _barrier(self):
         dist.all_reduce(self._flag, group=self.group)
@@ -209,7 +210,16 @@ class PeerExpertParallelMoe:
         ops, E, k, G, C = self.pkg.ops, self.E, self.k, self.G, self.chunks
         Eg = E // G
         T, H = x.shape
+        marks = []
+
+        def mark(name):
+            if self.profile and C == 1:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+        mark("start")
         idx, scores = self.pkg.nn.router_topk(x, self.gate_weight, k, self.mode, self.norm, self.bias, ctx=self.ctx)
+        mark("router")
         bounds = [(c * T // C, (c + 1) * T // C) for c in range(C)]
         sort = [ops.moe_permute(idx[lo:hi].reshape(-1), E, ctx=self.ctx) for lo, hi in bounds]   # perm, inv, counts, offsets
         mine = torch.stack([s_[2] for s_ in sort])                                                # [C, E]
@@ -219,7 +229,9 @@ class PeerExpertParallelMoe:
             per_chunk = self._all_counts[:, c, :].contiguous()
             chunk_counts.append(per_chunk)
             tables.append(ops.ep_layout(per_chunk, self.rank, self.bufs[c].capacity, ctx=self.ctx))
+        mark("sort+allgather+layout")
         table = self._all_counts.cpu().to(torch.int64)                 # the one host synchronisation of the step
+        mark("host_sync")
         arriving = table.view(G, C, G, Eg).sum(dim=(0, 3))             # [C, destination rank]
         n_recv = []
         for c in range(C):
@@ -258,7 +270,9 @@ class PeerExpertParallelMoe:
                 sent[c].record(side)
         for c in range(C):
             main.wait_event(sent[c])
+            mark("dispatch")
             self._barrier()                       # every rank's rows of chunk c have landed
+            mark("barrier1")
             if n_recv[c]:
                 rows_view, y_view = self._views[c]
                 if self.fused_return:
@@ -266,7 +280,9 @@ class PeerExpertParallelMoe:
                     self.mlp.forward_sorted_scatter(rows_view, tables[c][1], n_recv[c], addr)
                 else:
                     self.mlp.forward_sorted(rows_view, tables[c][1], n_recv[c], out=y_view)
+            mark("experts")
             self._barrier()                       # every rank's outputs of chunk c are complete
+            mark("barrier2")
             if C > 1 and c + 1 < C:
                 done = torch.cuda.Event()
                 done.record(main)
@@ -277,6 +293,10 @@ class PeerExpertParallelMoe:
                 combine(c)
         if C > 1:
             main.wait_stream(side)
+        mark("combine")
+        if marks:
+            torch.cuda.synchronize()
+            self.phase_ms = {b[0]: a[1].elapsed_time(b[1]) for a, b in zip(marks, marks[1:])}
         own = table[self.rank].view(C, G, Eg)
         self.last = dict(idx=idx, scores=scores, counts=mine.sum(dim=0).to(torch.int32), recv_rows=sum(n_recv),
                          sent_rows=int(own.sum() - own[:, self.rank].sum()))
@@ -386,6 +406,17 @@ def bench_main(args, pkg, shape, peaks, metric, unit, workload_name, clock_sampl
     e2e_ms = e2e_t.item()
     sent = torch.tensor([float(ep.last["sent_rows"])], device=dev)
     dist.all_reduce(sent, op=dist.ReduceOp.SUM)
+    phases = None
+    if bufs and len(bufs) == 1 and os.environ.get("B200_EP_PHASES"):
+        ep.profile = True
+        acc = {}
+        for _ in range(5):
+            flush_buf.fill_(1)
+            ep.forward(x)
+            for kk, vv in ep.phase_ms.items():
+                acc[kk] = acc.get(kk, 0.0) + vv / 5
+        ep.profile = False
+        phases = acc
     if rank == 0:
         total = T * world
         flops = total * (k * 3 * 2 * H * I + 2 * H * E)
@@ -407,7 +438,7 @@ def bench_main(args, pkg, shape, peaks, metric, unit, workload_name, clock_sampl
                     cpu_baseline=None,
                     e2e=dict(value=total / (e2e_ms * 1e-3), unit=unit, h2d_bytes_per_step=xh.numel() * 2 * world,
                              d2h_bytes_per_step=oh.numel() * 2 * world),
-                    gpu_launches=launches, clocks=clk.summary(),
+                    gpu_launches=launches, clocks=clk.summary(), phase_ms=phases,
                     exchange=dict(rows_sent_off_rank_per_step=sent.item(), bytes_each_way=sent.item() * H * 2))
         print(json.dumps(line))
     ctx.check()

@@ -244,3 +244,41 @@ def test_host_pipeline_matches_direct_calls(pkg):
     for x, o in zip(xs, outs):
         want = block.forward(x.to(dev)).cpu()
         assert torch.equal(o.view(torch.int16), want.view(torch.int16))
+
+
+def test_full_size_block_properties(pkg, O, config0):
+    """BASELINE.json configs[1] at its largest point (8192 tokens, 128 experts): the oracle cannot run the
+    whole block in seconds, so parity is checked through properties that do not depend on size.
+    (1) routing of ALL tokens bit-exact against the oracle's router; (2) perm is the stable sort of the
+    flat expert list, inv its inverse, counts/offsets its histogram; (3) the bf16 output is exactly the
+    rounding of the float32 output; (4) a token's output does not depend on the other tokens in the
+    batch, so 96 sampled tokens must match the oracle's block on those tokens alone - this compares
+    the tensor-core path at full size with the CPU restatement directly."""
+    T, k, E = 8192, 8, 128
+    g = torch.Generator().manual_seed(81)
+    x = torch.randn(T, 2048, generator=g).bfloat16()
+    blk = dict(config0)
+    block = to_device(pkg, blk)
+    out, aux = block.forward(x.cuda(), return_aux=True)
+    pkg.default_context().check()
+    xn = x.float().numpy()
+    ridx, rsc = O.router(xn, blk["wr"], k)
+    idx = u32(aux["indices"])
+    assert np.array_equal(idx, ridx) and np.array_equal(aux["scores"].float().cpu().numpy(), rsc)
+    flat = idx.reshape(-1)
+    perm = u32(aux["perm"])
+    assert np.array_equal(perm, np.argsort(flat, kind="stable").astype(np.uint32))
+    inv = u32(aux["inv_perm"])
+    assert np.array_equal(inv[perm], np.arange(T * k, dtype=np.uint32))
+    counts = np.bincount(flat, minlength=E).astype(np.uint32)
+    assert np.array_equal(u32(aux["counts"]), counts)
+    assert np.array_equal(u32(aux["offsets"]), np.concatenate([[0], np.cumsum(counts)]).astype(np.uint32))
+    got32 = aux["out_f32"].cpu().numpy()
+    assert np.array_equal(out.float().cpu().numpy(), O.round_bf16(got32))
+    sample = np.sort(np.random.default_rng(3).choice(T, size=96, replace=False))
+    ref = O.moe_block(xn[sample], blk["wr"], blk["gate"], blk["up"], blk["down"], k)
+    assert np.array_equal(ref["idx"], idx[sample])
+    rms = np.sqrt((ref["out_f32"].astype(np.float64) ** 2).mean())
+    err = float(np.abs(got32[sample] - ref["out_f32"]).max() / rms)
+    print(f"[parity] full size T={T}: max|d|/rms over 96 sampled tokens = {err:.4f}")
+    assert err <= TOL
