@@ -12,6 +12,11 @@
 
 namespace b200 {
 
+bool pdl_enabled() {
+  static const bool on = getenv("B200_NO_PDL") == nullptr;
+  return on;
+}
+
 // ---- error slot: thread-local message + optional process-wide handler ----------------------
 static thread_local std::string g_last_error;
 static std::mutex g_handler_mu;

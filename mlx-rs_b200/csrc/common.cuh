@@ -55,6 +55,35 @@ __device__ __forceinline__ double bf16_bits_to_f64(uint32_t b) {
   return static_cast<double>(bf16_bits_to_f32(b));
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+// The kernels of the small-batch path are a chain of short launches.  Each of them begins with
+// pdl_prologue(): it lets the NEXT kernel of the stream start launching at once (its blocks become
+// resident and then sit in their own pdl_prologue) and waits until the PREVIOUS kernel has
+// completed and its writes are visible.  Because every kernel of the chain waits before it touches
+// memory, the order of all reads and writes is the stream order; only launch latency overlaps.
+// launch_pdl() is the matching launch; a kernel launched with it MUST start with pdl_prologue().
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+bool pdl_enabled();  // false when the environment variable B200_NO_PDL is set (development switch)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"

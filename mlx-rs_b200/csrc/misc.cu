@@ -115,6 +115,7 @@ int launch_dequantize(const uint32_t* wq, const void* scales, const void* biases
 // float32 results are summed here without an intermediate rounding).
 __global__ void combine_kernel(const float4* __restrict__ yk, int64_t T, int k, int64_t H4, uint2* __restrict__ out,
                                float4* __restrict__ out_f32) {
+  pdl_prologue();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= T * H4) return;
   const int64_t t = i / H4, c = i % H4;
@@ -137,6 +138,7 @@ __global__ void combine_kernel(const float4* __restrict__ yk, int64_t T, int k, 
 // traffic of its write-bound epilogue).
 __global__ void combine_bf16_kernel(const uint2* __restrict__ yk, int64_t T, int k, int64_t H4, uint2* __restrict__ out,
                                     float4* __restrict__ out_f32) {
+  pdl_prologue();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= T * H4) return;
   const int64_t t = i / H4, c = i % H4;
@@ -160,14 +162,14 @@ int launch_combine(const void* yk, int yk_bf16, int64_t T, int k, int64_t H, voi
   if (yk_bf16) {
     B200_REQUIRE(H % 4 == 0, "hidden size must be a multiple of 4");
     int64_t n4 = T * (H / 4);
-    combine_bf16_kernel<<<cdiv(n4, 256), 256, 0, st>>>(static_cast<const uint2*>(yk), T, k, H / 4,
-                                                       static_cast<uint2*>(out), static_cast<float4*>(out_f32));
+    B200_CUDA(launch_pdl(combine_bf16_kernel, dim3(cdiv(n4, 256)), dim3(256), 0, st, static_cast<const uint2*>(yk), T, k, H / 4,
+                         static_cast<uint2*>(out), static_cast<float4*>(out_f32)));
     return 0;
   }
   B200_REQUIRE(H % 4 == 0, "hidden size must be a multiple of 4");
   int64_t n = T * (H / 4);
-  combine_kernel<<<cdiv(n, 256), 256, 0, st>>>(static_cast<const float4*>(yk), T, k, H / 4, static_cast<uint2*>(out),
-                                               static_cast<float4*>(out_f32));
+  B200_CUDA(launch_pdl(combine_kernel, dim3(cdiv(n, 256)), dim3(256), 0, st, static_cast<const float4*>(yk), T, k, H / 4,
+                       static_cast<uint2*>(out), static_cast<float4*>(out_f32)));
   return 0;
 }
 
@@ -240,6 +242,7 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const __nv_bfloat16* __re
                                                        const __nv_bfloat16* __restrict__ residual,
                                                        const __nv_bfloat16* __restrict__ weight, float eps, int64_t cols,
                                                        __nv_bfloat16* __restrict__ out, __nv_bfloat16* __restrict__ sum_out) {
+  pdl_prologue();
   const int64_t r = blockIdx.x;
   const __nv_bfloat16* xr = x + r * cols;
   __shared__ float part[8];
@@ -272,21 +275,21 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const __nv_bfloat16* __re
 int launch_rms_norm(const void* x, const void* residual, const void* weight, float eps, int64_t rows, int64_t cols,
                     void* out, void* sum_out, cudaStream_t st) {
   if (rows == 0) return 0;
-  rms_norm_kernel<<<(unsigned)rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x),
-                                                  static_cast<const __nv_bfloat16*>(residual),
-                                                  static_cast<const __nv_bfloat16*>(weight), eps, cols,
-                                                  static_cast<__nv_bfloat16*>(out), static_cast<__nv_bfloat16*>(sum_out));
+  B200_CUDA(launch_pdl(rms_norm_kernel, dim3((unsigned)rows), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(x),
+                       static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(weight), eps, cols,
+                       static_cast<__nv_bfloat16*>(out), static_cast<__nv_bfloat16*>(sum_out)));
   return 0;
 }
 
 __global__ void add_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, int64_t n, __nv_bfloat16* out) {
+  pdl_prologue();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) out[i] = __float2bfloat16_rn(__bfloat162float(a[i]) + __bfloat162float(b[i]));
 }
 int launch_add(const void* a, const void* b, int64_t n, void* out, cudaStream_t st) {
   if (n == 0) return 0;
-  add_kernel<<<cdiv(n, 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b),
-                                          n, static_cast<__nv_bfloat16*>(out));
+  B200_CUDA(launch_pdl(add_kernel, dim3(cdiv(n, 256)), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(a),
+                       static_cast<const __nv_bfloat16*>(b), n, static_cast<__nv_bfloat16*>(out)));
   return 0;
 }
 

@@ -130,6 +130,7 @@ __global__ void __launch_bounds__(kChunk) permute_small_kernel(const uint32_t* _
                                                                uint32_t* __restrict__ active, uint32_t* __restrict__ n_active,
                                                                int* __restrict__ err) {
   extern __shared__ int sh[];  // warp_cnt [32, E] then base [E]
+  pdl_prologue();
   permute_small_block<kChunk>(idx, n, E, perm, inv, counts, offsets, active, n_active, err, sh);
 }
 
@@ -138,8 +139,8 @@ int launch_permute(const uint32_t* idx, int64_t n, int E, uint32_t* perm, uint32
                    cudaStream_t st) {
   const size_t sh_scatter = sizeof(int) * 32 * E;
   if (n <= kChunk) {
-    permute_small_kernel<<<1, kChunk, sh_scatter + sizeof(int) * E, st>>>(idx, (int)n, E, perm, inv, counts, offsets,
-                                                                        active, n_active, err);
+    B200_CUDA(launch_pdl(permute_small_kernel, dim3(1), dim3(kChunk), sh_scatter + sizeof(int) * E, st, idx, (int)n, E, perm, inv,
+                         counts, offsets, active, n_active, err));
     return 0;
   }
   const int nchunks = cdiv(n, kChunk);

@@ -91,6 +91,7 @@ __global__ void __launch_bounds__(256) grouped_qmm_small_kernel(GroupedArgs p) {
   constexpr float kOff = (BITS == 4) ? 128.0f : 0.0f;
   using WV = WVec<BITS>;
 
+  pdl_prologue();
   const int ea = blockIdx.y;
   if (ea >= (int)*p.n_active) return;
   const int e = p.active[ea];
@@ -308,7 +309,7 @@ static int launch_cfg(const GroupedArgs& a, int max_active, cudaStream_t st) {
     attr_bytes = smem;
   }
   dim3 grid(cdiv(a.N, 16 * RT), max_active);
-  kern<<<grid, 256, smem, st>>>(a);
+  B200_CUDA(launch_pdl(kern, grid, dim3(256), smem, st, a));
   return 0;
 }
 

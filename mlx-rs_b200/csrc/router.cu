@@ -132,6 +132,7 @@ __global__ void __launch_bounds__(256) router_logits_warp_kernel(const __nv_bflo
                                                                  const float* __restrict__ logit_bias,
                                                                  __nv_bfloat16* __restrict__ logits, int T, int H, int E) {
   extern __shared__ __align__(16) unsigned char rsm[];  // [TT][H] bf16
+  pdl_prologue();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int t0 = blockIdx.y * TT;
   const int e = blockIdx.x * 8 + warp;
@@ -403,7 +404,7 @@ static int launch_router_warp(const __nv_bfloat16* xp, const __nv_bfloat16* wp, 
     attr_bytes = smem;
   }
   dim3 grid(cdiv(E, 8), cdiv(T, TT));
-  kern<<<grid, 256, smem, st>>>(xp, wp, logit_bias, lp, T, H, E);
+  B200_CUDA(launch_pdl(kern, grid, dim3(256), smem, st, xp, wp, logit_bias, lp, T, H, E));
   return 0;
 }
 
@@ -565,6 +566,7 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const __nv_bfloat16* __
                                                          int mode, int renorm, uint32_t* __restrict__ idx,
                                                          __nv_bfloat16* __restrict__ scores,
                                                          __nv_bfloat16* __restrict__ probs /*nullable [T,E]*/) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
@@ -587,6 +589,7 @@ __global__ void __launch_bounds__(256) router_fused_small_kernel(
     unsigned int* ticket, int* __restrict__ err) {
   extern __shared__ __align__(16) unsigned char rsm[];  // [TT][H] bf16, later the permutation's tables
   __shared__ unsigned int s_ticket;
+  pdl_prologue();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int t0 = blockIdx.y * TT;
   const int e = blockIdx.x * 8 + warp;
@@ -679,8 +682,8 @@ static int launch_fused_small(const __nv_bfloat16* xp, const __nv_bfloat16* wp, 
     attr_bytes = smem;
   }
   dim3 grid(cdiv(E, 8), cdiv(T, TT));
-  kern<<<grid, 256, smem, st>>>(xp, wp, logit_bias, lp, T, H, E, k, mode, renorm, idx, scores, perm, inv, counts, offsets,
-                                active, n_active, ticket, err);
+  B200_CUDA(launch_pdl(kern, grid, dim3(256), smem, st, xp, wp, logit_bias, lp, T, H, E, k, mode, renorm, idx, scores, perm, inv,
+                       counts, offsets, active, n_active, ticket, err));
   return 0;
 }
 
@@ -702,9 +705,8 @@ int launch_router_fused_small(const void* x, const void* w, const float* logit_b
 int launch_route_topk(const void* logits, int T, int E, int k, int mode, int renorm, uint32_t* idx, void* scores,
                       void* probs, cudaStream_t st) {
   if (T == 0) return 0;
-  route_topk_kernel<<<cdiv(T, 4), 128, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), T, E, k, mode, renorm, idx,
-                                                static_cast<__nv_bfloat16*>(scores),
-                                                static_cast<__nv_bfloat16*>(probs));
+  B200_CUDA(launch_pdl(route_topk_kernel, dim3(cdiv(T, 4)), dim3(128), 0, st, static_cast<const __nv_bfloat16*>(logits), T, E, k,
+                       mode, renorm, idx, static_cast<__nv_bfloat16*>(scores), static_cast<__nv_bfloat16*>(probs)));
   return 0;
 }
 

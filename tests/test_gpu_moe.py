@@ -220,7 +220,7 @@ def test_stack_of_blocks_with_norm_and_residual(pkg, O):
     got = stack.forward(bf16_cuda(blks[0]["x"])).float().cpu().numpy()
     pkg.default_context().check()
     # a last-bit difference in one layer's output can flip a near-tie in the next layer's routing,
-    # which changes that token's output discontinuously: judge token by token
+    # which changes that token's output discontinuously: compare token by token
     rms = np.sqrt((h.astype(np.float64) ** 2).mean())
     ok = np.all(np.abs(got - h) <= TOL * rms + 2.0 ** -7 * np.abs(h), axis=1)
     assert ok.mean() >= 0.9, f"only {ok.mean():.2f} of the tokens agree"
