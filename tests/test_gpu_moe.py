@@ -282,3 +282,16 @@ def test_full_size_block_properties(pkg, O, config0):
     err = float(np.abs(got32[sample] - ref["out_f32"]).max() / rms)
     print(f"[parity] full size T={T}: max|d|/rms over 96 sampled tokens = {err:.4f}")
     assert err <= TOL
+
+
+@pytest.mark.parametrize("T", [5, 700])
+def test_all_tokens_to_the_same_experts(pkg, O, T):
+    """Maximum skew: a logit bias sends every token to experts 2 and 5, so six of the eight experts are
+    empty and two own T rows each (one long segment per kernel, empty segments around it)."""
+    blk = make_block(T, 256, 8, 128, 2, seed=77)
+    bias = np.full(8, -40.0, dtype=np.float32)
+    bias[[2, 5]] = 40.0
+    blk["bias"] = bias
+    err, dev, ref = check_block(pkg, O, blk, mode=1, renorm=False)
+    assert sorted(np.unique(ref["idx"]).tolist()) == [2, 5]
+    assert ref["counts"][2] == T and ref["counts"][5] == T and ref["counts"].sum() == 2 * T
