@@ -278,9 +278,11 @@ int b200_ep_layout(b200_ctx* ctx, const uint32_t* all_counts, int n_ranks, int n
                    uint32_t* dst_row0, uint32_t* local_counts, void* stream);
 /* Gather into expert order fused with the send: sorted position j (assignment perm[j], token
  * perm[j] / top_k, expert indices[perm[j]]) is stored into the owner's rows buffer
- * peer_rows[owner] (host array of n_ranks device pointers, own entry local). */
+ * peer_rows[owner] (host array of n_ranks device pointers, own entry local).  Rows are sent destination by
+ * destination starting after `rank` and wrapping around, so that the ranks do not all write to the same
+ * GPU at the same time. */
 int b200_ep_dispatch(b200_ctx* ctx, const void* x, const uint32_t* indices, const uint32_t* perm, const uint32_t* offsets,
-                     const uint32_t* dst_row0, int64_t n, int top_k, int64_t hidden, int n_experts, int n_ranks,
+                     const uint32_t* dst_row0, int64_t n, int top_k, int64_t hidden, int n_experts, int n_ranks, int rank,
                      void* const* peer_rows, uint32_t capacity_rows, void* stream);
 /* Return fused with the weighted combine: out[t, :] = bf16( sum_j scores[t, j] * y_owner[row(t, j), :] ),
  * float32 accumulation, j ascending, read from the owners' output buffers peer_y. */

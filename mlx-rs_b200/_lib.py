@@ -76,7 +76,8 @@ EXPORTS = {
     "b200_ep_layout": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_void_p, C.c_void_p,
                                  C.c_void_p]),
     "b200_ep_dispatch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
-                                   C.c_int, C.c_int64, C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_uint32, C.c_void_p]),
+                                   C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_uint32,
+                                   C.c_void_p]),
     "b200_ep_combine": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                   C.c_void_p, C.c_int64, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_uint32, C.c_void_p,
                                   C.c_void_p]),

@@ -919,17 +919,18 @@ int b200_ep_layout(b200_ctx* c, const uint32_t* all_counts, int n_ranks, int n_e
 }
 
 int b200_ep_dispatch(b200_ctx* c, const void* x, const uint32_t* indices, const uint32_t* perm, const uint32_t* offsets,
-                     const uint32_t* dst_row0, int64_t n, int top_k, int64_t hidden, int n_experts, int n_ranks,
+                     const uint32_t* dst_row0, int64_t n, int top_k, int64_t hidden, int n_experts, int n_ranks, int rank,
                      void* const* peer_rows, uint32_t capacity_rows, void* stream) {
   CTX_ENTER(c);
   B200_REQUIRE(n >= 0 && n < (int64_t(1) << 31) && top_k > 0, "bad row count");
   B200_REQUIRE(hidden > 0 && hidden % 8 == 0, "hidden must be a multiple of 8");
   B200_REQUIRE(n_experts > 0 && n_ranks > 0 && n_experts % n_ranks == 0, "experts must divide evenly over the ranks");
+  B200_REQUIRE(rank >= 0 && rank < n_ranks, "bad rank");
   EpPeers pe;
   if (fill_peers(pe, peer_rows, n_ranks)) return 1;
   if (n == 0) return 0;
   B200_REQUIRE(x && indices && perm && offsets && dst_row0, "null tensor");
-  launch_ep_dispatch(x, indices, perm, offsets, dst_row0, n, top_k, hidden, n_experts, n_ranks, pe, capacity_rows, c->err,
+  launch_ep_dispatch(x, indices, perm, offsets, dst_row0, n, top_k, hidden, n_experts, n_ranks, rank, pe, capacity_rows, c->err,
                      static_cast<cudaStream_t>(stream));
   LAUNCHED(c, 1);
   return 0;

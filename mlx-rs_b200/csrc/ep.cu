@@ -81,11 +81,37 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const uint4* __restric
                                                           const uint32_t* __restrict__ perm,
                                                           const uint32_t* __restrict__ offsets,
                                                           const uint32_t* __restrict__ dst_row0, int64_t n, uint32_t k,
-                                                          int vec_per_row, int E, int Eg, EpPeers peers,
+                                                          int vec_per_row, int E, int Eg, int rank, EpPeers peers,
                                                           uint32_t capacity, int* __restrict__ err) {
+  // Sorted rows are grouped by destination rank (contiguous experts).  Walking them front to back
+  // would make every source write to destination 0 first, then 1, ...: all GPUs on one ingress
+  // link at a time (measured at 8 GPUs: 0.44 ms + 0.23 ms of waiting for the slowest rank).  Each
+  // source therefore starts with the destination after itself and wraps around, the classic
+  // all-to-all schedule; its own rows come last.
+  __shared__ uint32_t s_cum[kEpMaxRanks + 1], s_base[kEpMaxRanks];
+  const int G = E / Eg;
+  if (threadIdx.x == 0) {
+    uint32_t run = 0;
+    for (int i = 0; i < G; ++i) {
+      const int d = (rank + 1 + i) % G;
+      const uint32_t b = offsets[d * Eg], e_ = offsets[(d + 1) * Eg];
+      s_base[i] = b;
+      s_cum[i] = run;
+      run += e_ - b;
+    }
+    s_cum[G] = run;
+  }
+  __syncthreads();
   // one warp per row; a lane keeps eight 16-byte pieces in flight before it stores them
   const int lane = threadIdx.x & 31, wpc = blockDim.x >> 5;
-  for (int64_t j = (int64_t)blockIdx.x * wpc + (threadIdx.x >> 5); j < n; j += (int64_t)gridDim.x * wpc) {
+  for (int64_t v = (int64_t)blockIdx.x * wpc + (threadIdx.x >> 5); v < n; v += (int64_t)gridDim.x * wpc) {
+    int i = 0;
+    while (i + 1 < G && (uint32_t)v >= s_cum[i + 1]) ++i;
+    const int64_t j = (int64_t)s_base[i] + (v - (int64_t)s_cum[i]);
+    if (j >= n) {   // counts that do not add up to n: a routing table that does not belong to these rows
+      if (lane == 0) *err = 6;
+      continue;
+    }
     const uint32_t a = perm[j];
     if (a >= n) {
       if (lane == 0) *err = 6;
@@ -120,14 +146,14 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const uint4* __restric
 }
 
 int launch_ep_dispatch(const void* x, const uint32_t* idx, const uint32_t* perm, const uint32_t* offsets,
-                       const uint32_t* dst_row0, int64_t n, int k, int64_t H, int E, int G, const EpPeers& peers,
+                       const uint32_t* dst_row0, int64_t n, int k, int64_t H, int E, int G, int rank, const EpPeers& peers,
                        uint32_t capacity, int* err, cudaStream_t st) {
   if (n == 0) return 0;
   // 128 threads x 32 registers: small enough to share an SM with a resident 608-thread tensor-core CTA
   // (7168 registers are left beside it), so that a dispatch on a side stream overlaps the products
   const int grid = (int)(n < 148 * 16 ? n : 148 * 16);
   ep_dispatch_kernel<<<grid, 128, 0, st>>>(static_cast<const uint4*>(x), idx, perm, offsets, dst_row0, n, (uint32_t)k,
-                                           (int)(H / 8), E, E / G, peers, capacity, err);
+                                           (int)(H / 8), E, E / G, rank, peers, capacity, err);
   return 0;
 }
 

@@ -114,7 +114,7 @@ int launch_segments_from_counts(const uint32_t* counts, int E, uint32_t* offsets
 int launch_ep_layout(const uint32_t* all_counts, int G, int E, int rank, uint32_t capacity, uint32_t* dst_row0,
                      uint32_t* local_counts, int* err, cudaStream_t st);
 int launch_ep_dispatch(const void* x, const uint32_t* idx, const uint32_t* perm, const uint32_t* offsets,
-                       const uint32_t* dst_row0, int64_t n, int k, int64_t H, int E, int G, const EpPeers& peers,
+                       const uint32_t* dst_row0, int64_t n, int k, int64_t H, int E, int G, int rank, const EpPeers& peers,
                        uint32_t capacity, int* err, cudaStream_t st);
 int launch_ep_return_table(const uint32_t* all_counts, int G, int E, int rank, const EpPeers& peers_y, int64_t H,
                            unsigned long long* row_addr, cudaStream_t st);

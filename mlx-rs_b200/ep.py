@@ -250,7 +250,7 @@ class PeerExpertParallelMoe:
             lo, hi = bounds[c]
             perm, inv, counts, offsets = sort[c]
             ops.ep_dispatch(x[lo:hi], idx[lo:hi], perm, offsets, tables[c][0], self.bufs[c].rows_ptrs, self.bufs[c].capacity,
-                            E, ctx=self.ctx)
+                            E, rank=self.rank, ctx=self.ctx)
 
         def combine(c):
             lo, hi = bounds[c]

@@ -227,13 +227,13 @@ def ep_return_table(all_counts, rank, peer_y, hidden, n_rows, ctx=None):
     return addr
 
 
-def ep_dispatch(x, indices, perm, offsets, dst_row0, peer_rows, capacity_rows, n_experts, ctx=None):
+def ep_dispatch(x, indices, perm, offsets, dst_row0, peer_rows, capacity_rows, n_experts, rank=0, ctx=None):
     """Store every sorted row of this rank into the rows buffer of the rank that owns its expert
     (peer_rows: device addresses of all ranks' buffers, own entry included)."""
     _cuda(x, indices, perm, offsets, dst_row0)
     k = indices.shape[-1]
     L.check(L.lib().b200_ep_dispatch(_ctx(ctx), L.ptr(x), L.ptr(indices), L.ptr(perm), L.ptr(offsets), L.ptr(dst_row0),
-                                     perm.numel(), k, x.shape[-1], n_experts, len(peer_rows), _ptr_array(peer_rows),
+                                     perm.numel(), k, x.shape[-1], n_experts, len(peer_rows), rank, _ptr_array(peer_rows),
                                      capacity_rows, L.stream_ptr()))
 
 

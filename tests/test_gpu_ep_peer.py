@@ -43,7 +43,7 @@ def test_peer_exchange_emulated_ranks(pkg, O, cfg, G):
         tables.append((dst_row0, local_counts))
     for r in range(G):      # phase 1 on every rank, then the barrier
         idx, scores, perm, inv, counts, offsets = routed[r]
-        ops.ep_dispatch(xs[r], idx, perm, offsets, tables[r][0], rows_ptrs, cap, E)
+        ops.ep_dispatch(xs[r], idx, perm, offsets, tables[r][0], rows_ptrs, cap, E, rank=r)
     for r in range(G):      # phase 2
         n_recv = int(tables[r][1].sum())
         if n_recv:
