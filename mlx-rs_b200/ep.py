@@ -200,6 +200,9 @@ class PeerExpertParallelMoe:
         self._views = [(_device_view(b.own[0], b.capacity, b.hidden, dev), _device_view(b.own[1], b.capacity, b.hidden, dev))
                        for b in self.bufs]
         self._side = torch.cuda.Stream(device=dev) if self.chunks > 1 else None
+        # the count table goes to the host on its own stream, so that waiting for it overlaps the dispatch
+        self._copy = torch.cuda.Stream(device=dev)
+        self._table_host = torch.empty((self.G, self.chunks, n_experts), dtype=torch.int32).pin_memory()
         self.last = {}
         self.profile = False      # one-chunk forwards record an event after every phase into self.phase_ms
 
@@ -230,17 +233,13 @@ class PeerExpertParallelMoe:
             chunk_counts.append(per_chunk)
             tables.append(ops.ep_layout(per_chunk, self.rank, self.bufs[c].capacity, ctx=self.ctx))
         mark("sort+allgather+layout")
-        table = self._all_counts.cpu().to(torch.int64)                 # the one host synchronisation of the step
-        mark("host_sync")
-        arriving = table.view(G, C, G, Eg).sum(dim=(0, 3))             # [C, destination rank]
-        n_recv = []
-        for c in range(C):
-            if int(arriving[c].max()) > self.bufs[c].capacity:
-                raise self.pkg.B200Error(f"a rank would receive {int(arriving[c].max())} rows; the exchange buffers hold "
-                                         f"{self.bufs[c].capacity}")
-            n_recv.append(int(arriving[c, self.rank]))
-            if self.fused_return and (bounds[c][1] - bounds[c][0]) * k > self.bufs[c].capacity:
-                raise self.pkg.B200Error("the return buffer is smaller than this rank's own assignments")
+        gathered = torch.cuda.Event()
+        gathered.record()
+        with torch.cuda.stream(self._copy):
+            self._copy.wait_event(gathered)
+            self._table_host.copy_(self._all_counts, non_blocking=True)
+            on_host = torch.cuda.Event()
+            on_host.record(self._copy)
         if out is None:
             out = torch.empty_like(x)
         main = torch.cuda.current_stream()
@@ -268,6 +267,19 @@ class PeerExpertParallelMoe:
             for c in range(C):
                 dispatch(c)
                 sent[c].record(side)
+        # The dispatch needs nothing from the host (the kernels check the capacity themselves and skip rows
+        # that would not fit), so the one host synchronisation of the step happens while it runs.
+        on_host.synchronize()
+        table = self._table_host.to(torch.int64)
+        arriving = table.view(G, C, G, Eg).sum(dim=(0, 3))             # [C, destination rank]
+        n_recv = []
+        for c in range(C):
+            if int(arriving[c].max()) > self.bufs[c].capacity:
+                raise self.pkg.B200Error(f"a rank would receive {int(arriving[c].max())} rows; the exchange buffers hold "
+                                         f"{self.bufs[c].capacity}")
+            n_recv.append(int(arriving[c, self.rank]))
+            if self.fused_return and (bounds[c][1] - bounds[c][0]) * k > self.bufs[c].capacity:
+                raise self.pkg.B200Error("the return buffer is smaller than this rank's own assignments")
         for c in range(C):
             main.wait_event(sent[c])
             mark("dispatch")
