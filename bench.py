@@ -22,10 +22,46 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-SHAPE = dict(hidden=2048, inter=768, n_experts=128, top_k=8, bits=4, group_size=64)  # Qwen3-30B-A3B MoE layer
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 SWEEP = (1, 4, 16, 64, 512, 2048, 8192)  # BASELINE.json configs[1]
+
+# BASELINE.json configs: 1 = Qwen3-30B-A3B layer (the metric's configuration; its sweep is attached to the
+# default run), 2 = 48-layer stack of config 1 (--workload stack), 3 = Qwen3-235B-A22B layer, 4 = Mixtral
+# layer (top-k on the logits then softmax over the selected; Zipf(1.2)-skewed routing; 4- or 8-bit).
+CONFIGS = {
+    1: dict(shape=dict(hidden=2048, inter=768, n_experts=128, top_k=8, bits=4, group_size=64), tokens=8192,
+            router_mode=0, norm_topk_prob=True, zipf=False,
+            name="configs[1] point T={T}: Qwen3-30B-A3B MoE layer (H2048 E128 top-8 I768, {bits}-bit g64), bf16 N(0,1) tokens"),
+    3: dict(shape=dict(hidden=4096, inter=1536, n_experts=128, top_k=8, bits=4, group_size=64), tokens=8192,
+            router_mode=0, norm_topk_prob=True, zipf=False,
+            name="configs[3] T={T}: Qwen3-235B-A22B MoE layer (H4096 E128 top-8 I1536, {bits}-bit g64), bf16 N(0,1) tokens"),
+    4: dict(shape=dict(hidden=4096, inter=14336, n_experts=8, top_k=2, bits=4, group_size=64), tokens=16384,
+            router_mode=1, norm_topk_prob=False, zipf=True,
+            name="configs[4] T={T}: Mixtral MoE layer (H4096 E8 top-2 I14336, {bits}-bit g64, softmax over the selected, "
+                 "Zipf(1.2) logit bias), bf16 N(0,1) tokens"),
+}
+CONFIGS[2] = dict(CONFIGS[1])
+SHAPE = dict(CONFIGS[1]["shape"])   # replaced by main() according to --config / --bits
+CFG = CONFIGS[1]
+
+
+def zipf_bias(E):
+    """Per-expert router logit bias 2*ln(p_e), p_e ~ rank^-1.2 (constant offset dropped)."""
+    import math
+    return [-2.4 * math.log(r) for r in range(1, E + 1)]
+
+
+def traffic_table():
+    """profiles/traffic.json: DRAM bytes per launch of the dominant kernel from the committed ncu
+    summaries, keyed by (config, tokens, bits); written next to each summary, never typed in here."""
+    p = os.path.join(ROOT, "profiles", "traffic.json")
+    if not os.path.exists(p):
+        return {}
+    out = {}
+    for e in json.load(open(p)).get("entries", []):
+        out[(int(e["config"]), int(e["tokens"]), int(e["bits"]), e["kernel"])] = e
+    return out
 
 
 def measured_peaks():
@@ -96,17 +132,23 @@ class ClockSampler:
                     samples=len(self.sm))
 
 
-def build_block(pkg, torch, seed, shape, device):
+def build_block(pkg, torch, seed, shape, device, cfg=None):
     """Seeded random-init weights of the named architecture, quantized on the GPU by the library."""
+    cfg = cfg or CFG
     H, I, E = shape["hidden"], shape["inter"], shape["n_experts"]
     g = torch.Generator(device=device).manual_seed(seed)
     lin = []
     for r, c in ((I, H), (I, H), (H, I)):
-        w = (torch.randn(E, r, c, generator=g, device=device, dtype=torch.float32) * 0.02).bfloat16()
-        lin.append(pkg.nn.QuantizedSwitchLinear.from_weight(w, shape["group_size"], shape["bits"]))
-        del w
+        parts = []
+        for e0 in range(0, E, 16):       # sixteen experts at a time bounds the float32 staging memory
+            w = (torch.randn(min(16, E - e0), r, c, generator=g, device=device, dtype=torch.float32) * 0.02).bfloat16()
+            parts.append(pkg.ops.quantize(w, shape["group_size"], shape["bits"]))
+            del w
+        wq, sc, bi = (torch.cat([p_[i] for p_ in parts]) for i in range(3))
+        lin.append(pkg.nn.QuantizedSwitchLinear(wq, sc, bi, shape["group_size"], shape["bits"]))
     wr = (torch.randn(E, H, generator=g, device=device, dtype=torch.float32) * 0.02).bfloat16()
-    return pkg.nn.MoeBlock(wr, pkg.nn.SwitchGlu(*lin), shape["top_k"], True, 0)
+    bias = torch.tensor(zipf_bias(E), dtype=torch.float32, device=device) if cfg["zipf"] else None
+    return pkg.nn.MoeBlock(wr, pkg.nn.SwitchGlu(*lin), shape["top_k"], cfg["norm_topk_prob"], cfg["router_mode"], bias)
 
 
 def time_steps(torch, fn, steps, warmup, flush):
@@ -125,63 +167,105 @@ def time_steps(torch, fn, steps, warmup, flush):
     return [a.elapsed_time(b) for a, b in evs]
 
 
-def cpu_baseline(T_sample, shape, seed, reps_budget_s=15.0):
-    """Times the CPU oracle (a port: the reference's MLX CPU path cannot be built here) on the
-    host cores: a block of `T_sample` tokens over a bounded number of experts' worth of work."""
+def cpu_block_inputs(T_sample, shape, cfg, seed):
+    """Seeded CPU-side inputs of the oracle block: every expert distinct, drawn and quantized one expert
+    at a time so that only the packed weights stay in memory."""
     import numpy as np
     import torch
     from oracle import oracle as O
-    O.set_num_threads(0)   # all host cores, also when a launcher exported OMP_NUM_THREADS=1
-    H, I, E, k = shape["hidden"], shape["inter"], shape["n_experts"], shape["top_k"]
+    H, I, E = shape["hidden"], shape["inter"], shape["n_experts"]
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(T_sample, H, generator=g).bfloat16().float().numpy()
     wr = (torch.randn(E, H, generator=g) * 0.02).bfloat16().float().numpy()
     q = []
     for r, c in ((I, H), (I, H), (H, I)):
-        # one expert's random weights tiled over all experts: the arithmetic per token is identical
-        # and the host spends its time on the timed work, not on drawing 600 M normals
-        w1 = (torch.randn(8, r, c, generator=g) * 0.02).bfloat16().float().numpy()
-        w = np.tile(w1, (E // 8, 1, 1))
-        q.append(O.quantize(w, shape["group_size"], shape["bits"]))
-    O.moe_block(x, wr, q[0], q[1], q[2], k)  # warm-up
-    t0, n = time.perf_counter(), 0
-    while True:
-        O.moe_block(x, wr, q[0], q[1], q[2], k)
+        parts = [O.quantize((torch.randn(1, r, c, generator=g) * 0.02).bfloat16().float().numpy(), shape["group_size"],
+                            shape["bits"]) for _ in range(E)]
+        q.append(tuple(np.concatenate([p_[i] for p_ in parts]) for i in range(3)))
+    bias = np.asarray(zipf_bias(E), dtype=np.float32) if cfg["zipf"] else None
+    return x, wr, q, bias
+
+
+def cpu_sample_tokens(T, shape):
+    """Tokens of the bounded CPU sample: about 4e10 flop per forward (a fraction of a second to a few
+    seconds on the host cores), at most 512 tokens (a T = 512 slice for the large points)."""
+    per_token = shape["top_k"] * 3 * 2 * shape["hidden"] * shape["inter"]
+    return int(max(8, min(T, 512, 4e10 // per_token)))
+
+
+def cpu_forward_timer(T_sample, shape, cfg, seed):
+    """-> (callable running one oracle forward of the sample and returning its seconds, thread count)."""
+    from oracle import oracle as O
+    O.set_num_threads(0)   # all host cores, also when a launcher exported OMP_NUM_THREADS=1
+    x, wr, q, bias = cpu_block_inputs(T_sample, shape, cfg, seed)
+    k = shape["top_k"]
+
+    def once():
+        t0 = time.perf_counter()
+        O.moe_block(x, wr, q[0], q[1], q[2], k, cfg["router_mode"], cfg["norm_topk_prob"], bias, shape["group_size"],
+                    shape["bits"])
+        return time.perf_counter() - t0
+    return once, O.num_threads()
+
+
+def cpu_baseline(T, shape, cfg, seed, reps_budget_s=15.0):
+    """Times the CPU oracle (a port: the reference's MLX CPU path cannot be built here) on the host
+    cores on a bounded sample of the workload: forwards of a `cpu_sample_tokens`-token block."""
+    Ts = cpu_sample_tokens(T, shape)
+    once, cores = cpu_forward_timer(Ts, shape, cfg, seed)
+    once()  # warm-up
+    t, n = 0.0, 0
+    while t < reps_budget_s and n < 50:
+        t += once()
         n += 1
-        dt = time.perf_counter() - t0
-        if dt > reps_budget_s or n >= 50:
-            break
-    return dict(value=T_sample * n / dt, unit=UNIT, cores=O.num_threads(), kind="port",
-                sample=f"{n} forwards of a {T_sample}-token block, {dt:.1f} s, OpenMP on all host threads; "
-                       "weights are 8 distinct random experts tiled to 128")
+    return dict(value=Ts * n / t, unit=UNIT, cores=cores, kind="port",
+                sample=f"{n} forwards of a {Ts}-token block of the same layer (all {shape['n_experts']} experts distinct), "
+                       f"{t:.1f} s, OpenMP on all host threads")
+
+
+def layer_config(T, shape, **extra):
+    """The `config` object of the JSON line: the same keys for both arms."""
+    d = dict(workload=workload_name(T), tokens=T)
+    d.update(extra)
+    d.update(shape)
+    d.update(router_mode=CFG["router_mode"], norm_topk_prob=CFG["norm_topk_prob"], zipf_skew=CFG["zipf"])
+    return d
 
 
 def run_reference(args):
     """Reference arm: the CPU oracle (port of the reference semantics; the reference itself is a
-    Rust binding over an absent MLX and cannot be built) on all host threads, same config."""
+    Rust binding over an absent MLX and cannot be built) on all host threads, same config.  One
+    step = one forward of a bounded sample of the workload (`sample_tokens` tokens of the same
+    layer); `ms_per_step` is what that sample forward took, `value` the tokens/s it achieved, and
+    `extrapolated` says what a full step would take at that rate (linear in the token count)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     T = args.tokens
-    T_sample = min(T, 256)
-    per_step = []
-    base = None
-    for i in range(args.warmup + args.steps):
-        base = cpu_baseline(T_sample, SHAPE, args.seed, reps_budget_s=max(2.0, 40.0 / (args.warmup + args.steps)))
-        if i >= args.warmup:
-            per_step.append(base["value"])
-    v = statistics.mean(per_step)
+    Ts = cpu_sample_tokens(T, SHAPE)
+    once, cores = cpu_forward_timer(Ts, SHAPE, CFG, args.seed)
+    for _ in range(args.warmup):
+        once()
+    secs = [once() for _ in range(args.steps)]
+    ms = 1e3 * statistics.mean(secs)
+    v = Ts / (ms * 1e-3)
+    sample = (f"{args.steps} forwards of a {Ts}-token block of the same layer (all {SHAPE['n_experts']} experts distinct), "
+              f"{sum(secs):.1f} s, OpenMP on all host threads")
     line = dict(metric=METRIC, value=v, unit=UNIT, n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
-                ms_per_step=1e3 * T / v, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32",
+                ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32",
                 data="synthetic", impl="reference",
-                config=dict(workload=workload_name(T), tokens=T, **SHAPE),
-                cpu_baseline=dict(value=v, unit=UNIT, cores=base["cores"], kind="port", sample=base["sample"]),
+                config=layer_config(T, SHAPE, l2="not applicable (host cores)", parallelism=f"{cores} host threads",
+                                    cuda_graph=False),
+                sample_tokens=Ts, sample_ms=ms,
+                extrapolated=dict(is_extrapolated=Ts != T, full_step_tokens=T, full_step_ms=ms * T / Ts,
+                                  rule="linear in the token count"),
+                cpu_baseline=dict(value=v, unit=UNIT, cores=cores, kind="port", sample=sample),
                 e2e=dict(value=v, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line))
 
 
 def workload_name(T):
-    return f"configs[1] point T={T}: Qwen3-30B-A3B MoE layer (H2048 E128 top-8 I768, 4-bit g64), bf16 N(0,1) tokens"
+    return CFG["name"].format(T=T, bits=SHAPE["bits"])
 
 
 def run_stack(args, pkg, torch, dev, peaks):
@@ -255,14 +339,19 @@ def run_stack(args, pkg, torch, dev, peaks):
 
 
 def main():
+    global SHAPE, CFG
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="layer", choices=["layer", "stack"],
-                    help="layer: one MoE layer (configs[1], the metric's config); stack: configs[2]")
+    ap.add_argument("--config", type=int, default=1, choices=[1, 2, 3, 4],
+                    help="BASELINE.json configs index: 1 = Qwen3-30B-A3B layer (default, the metric's configuration), "
+                         "2 = its 48-layer stack, 3 = Qwen3-235B-A22B layer, 4 = Mixtral layer with skewed routing")
+    ap.add_argument("--bits", type=int, default=None, choices=[4, 8], help="weight bits (configs[4] asks for both)")
+    ap.add_argument("--workload", default=None, choices=["layer", "stack"],
+                    help="layer: one MoE layer; stack: configs[2] (implied by --config 2)")
     ap.add_argument("--layers", type=int, default=48)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--tokens", type=int, default=8192, help="tokens per step per GPU (configs[1] sweep point)")
+    ap.add_argument("--tokens", type=int, default=None, help="tokens per step per GPU (default: the config's)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -276,9 +365,18 @@ def main():
     ap.add_argument("--ep-chunks", type=int, default=0, choices=[0, 1, 2],
                     help="N > 1, peer transport: halves of a rank's tokens whose exchange overlaps the other half's products "
                          "(0 = default: one)")
-    ap.add_argument("--qmm-path", default="auto", choices=["auto", "small", "stream", "tensor_core", "tmem"],
+    ap.add_argument("--qmm-path", default="auto", choices=["auto", "small", "tensor_core"],
                     help="pin the grouped-product kernel (default: the library chooses)")
     args = ap.parse_args()
+    CFG = CONFIGS[args.config]
+    SHAPE = dict(CFG["shape"])
+    if args.bits:
+        SHAPE["bits"] = args.bits
+    if args.tokens is None:
+        args.tokens = CFG["tokens"]
+    if args.workload is None:
+        args.workload = "stack" if args.config == 2 else "layer"
+    args.config_id = args.config
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
@@ -286,7 +384,6 @@ def main():
     import torch
     import __graft_entry__ as ge
     pkg = ge.load_package()
-    rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -301,20 +398,22 @@ def main():
     if world > 1:
         from importlib import import_module
         ep = import_module("mlx_rs_b200.ep")
-        return ep.bench_main(args, pkg, SHAPE, peaks, METRIC, UNIT, workload_name, ClockSampler)
+        return ep.bench_main(args, pkg, SHAPE, CFG, peaks, METRIC, UNIT, workload_name, ClockSampler, zipf_bias)
 
     if args.workload == "stack":
         return run_stack(args, pkg, torch, dev, peaks)
     ctx = pkg.default_context()
-    ctx.set_qmm_path(dict(auto=ctx.QMM_AUTO, small=ctx.QMM_SMALL, stream=ctx.QMM_STREAM, tensor_core=ctx.QMM_TENSOR_CORE, tmem=ctx.QMM_TMEM)[args.qmm_path])
+    ctx.set_qmm_path(dict(auto=ctx.QMM_AUTO, small=ctx.QMM_SMALL, tensor_core=ctx.QMM_TENSOR_CORE)[args.qmm_path])
     block = build_block(pkg, torch, args.seed, SHAPE, dev)
-    ctx.reserve(block.config, max(T, max(SWEEP)))
+    do_sweep = args.config == 1 and bits == 4 and not args.no_sweep
+    ctx.reserve(block.config, max(T, max(SWEEP)) if do_sweep else T)
     flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
 
     def flush():
         flush_buf.fill_(1)
 
     g = torch.Generator(device=dev).manual_seed(args.seed + 1)
+    decode_below = 1024      # steps below this many tokens are reported against the HBM roofline
 
     def point(Tp, steps, warmup, profile):
         x = torch.randn(Tp, H, generator=g, device=dev, dtype=torch.float32).bfloat16()
@@ -350,6 +449,7 @@ def main():
         counts = aux["counts"].cpu()
         n_act = int((counts > 0).sum())
         res["active_experts"] = n_act
+        res["max_expert_share"] = float(counts.max()) / max(1, int(counts.sum()))
         we = expert_bytes(H, I, bits)
         res["block_bytes"] = n_act * we + E * H * 2 + 2 * Tp * H * 2
         res["block_flops"] = Tp * (k * 3 * 2 * H * I + 2 * H * E)
@@ -370,6 +470,9 @@ def main():
             gu_flops = Tp * k * 2 * 2 * H * I
             res["gate_up"] = dict(ms=gu_ms, bytes=gu_bytes, flops=gu_flops, gbs=gu_bytes / (gu_ms * 1e-3) / 1e9,
                                   tflops=gu_flops / (gu_ms * 1e-3) / 1e12)
+            dn_ms = res["stage_ms"]["down"]
+            dn_flops = Tp * k * 2 * H * I
+            res["down"] = dict(ms=dn_ms, flops=dn_flops, tflops=dn_flops / (dn_ms * 1e-3) / 1e12)
         return res, x
 
     with ClockSampler(local) as clk:
@@ -387,9 +490,9 @@ def main():
         oh.copy_(o, non_blocking=True)
     serial_ms = time_steps(torch, e2e_step, max(3, args.steps // 4), 3, flush)
     # The serving form of the same call: HostPipeline overlaps step i+1's upload and step i-1's
-    # download with step i's kernels.  Every step's 33.5 MB upload and download is inside the timed
+    # download with step i's kernels.  Every step's upload and download is inside the timed
     # region; all K steps are timed as one region (they overlap, so per-step events mean nothing).
-    # L2: each step streams 340 MB of weights and > 1 GB of intermediates, far more than the 126 MB L2.
+    # L2: each step streams the layer's weights and its intermediates, far more than the 126 MB L2.
     pipe = pkg.nn.HostPipeline(block, T, H, dev, depth=2)
     xhs = [xh, xh.clone().pin_memory()]
     ohs = [oh, torch.empty_like(oh).pin_memory()]
@@ -411,14 +514,14 @@ def main():
                unpipelined_value=T / (statistics.mean(serial_ms) * 1e-3))
 
     sweep = []
-    if not args.no_sweep:
+    if do_sweep:
         for Tp in SWEEP:
             if Tp == T:
                 r = main_res
             else:
                 r, _ = point(Tp, max(5, min(args.steps, 10)), 3, True)
             gu = r["gate_up"]
-            decode = Tp < 1024
+            decode = Tp < decode_below
             sweep.append(dict(tokens=Tp, tokens_per_s=r["tokens_per_s"], ms=r["ms_per_step"], cuda_graph=r["cuda_graph"],
                               active_experts=r["active_experts"], launches=r["launches_per_step"],
                               block_frac_hbm=r["block_gbs"] / peaks["hbm"], block_frac_tensor=r["block_tflops"] / peaks["tensor"],
@@ -426,25 +529,29 @@ def main():
                               bound="hbm" if decode else "tensor", stage_ms=r["stage_ms"]))
 
     gu = main_res["gate_up"]
-    if T < 1024:
-        roof = dict(bound="hbm", achieved=gu["gbs"], peak=peaks["hbm"], unit="GB/s", frac=gu["gbs"] / peaks["hbm"])
+    if T < decode_below:
+        roof = dict(bound="hbm", achieved=gu["gbs"], peak=peaks["hbm"], unit="GB/s", frac=gu["gbs"] / peaks["hbm"],
+                    block_frac=main_res["block_gbs"] / peaks["hbm"])
     else:
         roof = dict(bound="tensor", achieved=gu["tflops"], peak=peaks["tensor"], unit="TFLOP/s",
-                    frac=gu["tflops"] / peaks["tensor"])
+                    frac=gu["tflops"] / peaks["tensor"], block_frac=main_res["block_tflops"] / peaks["tensor"],
+                    down_frac=main_res["down"]["tflops"] / peaks["tensor"])
     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size, from the ncu
-    # captures summarised under profiles/ (a profiler cannot run inside the timed bench)
-    ncu_traffic = {8192: 584.3e6, 64: 228.7e6}
-    roof.update(kernel="gate+up grouped quantized GEMM (dominant)", peak_source=peaks["source"], traffic=ncu_traffic.get(T),
+    # capture summarised under profiles/ (a profiler cannot run inside the timed bench)
+    tr = traffic_table().get((args.config_id, T, bits, "gate_up"))
+    roof.update(kernel="gate+up grouped quantized GEMM (dominant)", peak_source=peaks["source"],
+                traffic=(tr["dram_bytes_per_launch"] if tr else None), traffic_source=(tr["profile"] if tr else None),
                 kernel_ms=gu["ms"], algorithmic_bytes=gu["bytes"], algorithmic_flops=gu["flops"])
 
-    base = None if args.no_cpu_baseline else cpu_baseline(min(T, 256), SHAPE, args.seed)
+    base = None if args.no_cpu_baseline else cpu_baseline(T, SHAPE, CFG, args.seed)
     line = dict(metric=METRIC, value=main_res["tokens_per_s"], unit=UNIT, n_gpus=1, steps=args.steps, warmup=args.warmup,
                 ms_per_step=main_res["ms_per_step"], higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
                 data="synthetic",
-                config=dict(workload=workload_name(T), tokens=T, l2="flushed between iterations (512 MB overwrite)",
-                            parallelism="single GPU", cuda_graph=main_res["cuda_graph"], **SHAPE),
+                config=layer_config(T, SHAPE, l2="flushed between iterations (512 MB overwrite)", parallelism="single GPU",
+                                    cuda_graph=main_res["cuda_graph"]),
                 roofline=roof, cpu_baseline=base, e2e=e2e, gpu_launches=main_res["launches_per_step"] * args.steps,
-                clocks=clocks, block=dict(active_experts=main_res["active_experts"], gbs=main_res["block_gbs"],
+                clocks=clocks, block=dict(active_experts=main_res["active_experts"],
+                                          max_expert_share=main_res["max_expert_share"], gbs=main_res["block_gbs"],
                                           tflops=main_res["block_tflops"], stage_ms=main_res["stage_ms"]),
                 sweep=sweep)
     print(json.dumps(line))

@@ -101,18 +101,10 @@ int b200_workspace_bytes(const b200_moe_config* cfg, int64_t max_tokens, size_t*
 int b200_ctx_check(b200_ctx* ctx, void* stream);
 /* Number of kernels launched through this context so far. */
 int64_t b200_ctx_launch_count(const b200_ctx* ctx);
-/* Stage timing of b200_moe_block_forward (the library's stand-in for a profiler hook; the
- * reference has none).  While enabled, an event is recorded on the call's stream between the
- * stages; b200_ctx_stage_ms waits for the last profiled call and returns the milliseconds of
- * its stages in this order: router logits, softmax/top-k, permutation, gate+up product,
- * down product, combine. */
 /* Which grouped-product kernel the routed block uses.  AUTO: the register-load mma.sync kernel
  * while experts own few rows, the tcgen05 tensor-core kernel beyond that (when inter % 128 == 0
- * and hidden % 256 == 0).  STREAM pins the TMA-streamed variant of the memory-bound kernel
- * (K % 256 == 0, N % 64 or 128 == 0).  TMEM pins the tensor-memory kernel of the memory-bound regime
- * (packed codes go to the tensor core unscaled, one accumulator per quantisation group;
- * hidden, inter % 256 == 0 and <= 2048).  A pinned kernel falls back when the shape does not allow it. */
-enum { B200_QMM_AUTO = 0, B200_QMM_SMALL = 1, B200_QMM_TENSOR_CORE = 2, B200_QMM_STREAM = 3, B200_QMM_TMEM = 4 };
+ * and hidden % 256 == 0).  A pinned kernel falls back when the shape does not allow it. */
+enum { B200_QMM_AUTO = 0, B200_QMM_SMALL = 1, B200_QMM_TENSOR_CORE = 2 };
 int b200_ctx_set_qmm_path(b200_ctx* ctx, int path);
 /* Diagnostic: synchronises the device and copies the first n (<= 64) 32-bit words of the
  * context's status buffer to HOST memory.  Word 0 is the status b200_ctx_check reports; words
@@ -219,9 +211,11 @@ int b200_moe_permute(b200_ctx* ctx, const uint32_t* indices, int64_t n, int n_ex
  * are rejected with an error.  The call performs no cudaMalloc/cudaFree and uses no allocating
  * library routine.  Its first call on a device resolves the array's device address
  * (cudaGetSymbolAddress) and should therefore happen before any stream capture begins.  All
- * calls share the one array and it keeps the previous call's contents (the call clears what
- * has to start at zero): calls whose kernels overlap on the GPU - two streams, two threads -
- * race on it, so serialise them.  Expert indices >= n_experts are skipped, not reported. */
+ * calls share the one array and it keeps the previous call's contents (nothing in it has to start
+ * at zero: every word is rewritten by the call before it is read): calls whose kernels overlap on
+ * the GPU - two streams, two threads - race on it, so serialise them.  Expert indices >= n_experts
+ * are skipped, not reported: counts then sums to less than n and the skipped positions of perm /
+ * inv_perm keep what the caller's buffers held (compare offsets[n_experts] with n to detect it). */
 int b200_moe_permute_static(const uint32_t* indices, int64_t n, int n_experts, uint32_t* perm, uint32_t* inv_perm,
                             uint32_t* counts, uint32_t* offsets, void* stream);
 

@@ -168,7 +168,7 @@ class Context:
         check(lib().b200_ctx_debug_words(self._h, buf, n))
         return list(buf)
 
-    QMM_AUTO, QMM_SMALL, QMM_TENSOR_CORE, QMM_STREAM, QMM_TMEM = 0, 1, 2, 3, 4
+    QMM_AUTO, QMM_SMALL, QMM_TENSOR_CORE = 0, 1, 2
 
     def set_qmm_path(self, path):
         """Pin the grouped-product kernel (QMM_SMALL / QMM_TENSOR_CORE) or let the library choose (QMM_AUTO)."""

@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libb200moe.so")
-SOURCES = ["api.cu", "router.cu", "permute.cu", "qmm_decode.cu", "qmm_stream.cu", "qmm_prefill.cu", "qmm_decode_tc.cu", "misc.cu", "ep.cu"]
+SOURCES = ["api.cu", "router.cu", "permute.cu", "qmm_decode.cu", "qmm_prefill.cu", "misc.cu", "ep.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

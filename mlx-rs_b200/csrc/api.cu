@@ -12,10 +12,12 @@
 
 namespace b200 {
 
+#ifdef B200_DEV
 bool pdl_enabled() {
   static const bool on = getenv("B200_NO_PDL") == nullptr;
   return on;
 }
+#endif
 
 // ---- error slot: thread-local message + optional process-wide handler ----------------------
 static thread_local std::string g_last_error;
@@ -84,14 +86,11 @@ static size_t block_scratch_bytes(const b200_moe_config& cfg, int64_t T) {
   b += al(sizeof(uint16_t) * n);                     // scores
   b += al(sizeof(uint32_t) * (E + 1)) * 3 + al(16);  // counts, offsets, active, n_active
   b += al(sizeof(uint32_t) * permute_scratch_words(n, (int)E));
-  b += al(sizeof(uint16_t) * n * cfg.inter);         // h
-  b += al(sizeof(float) * n * cfg.hidden);           // per-assignment outputs (float32)
+  b += al(sizeof(uint16_t) * n * cfg.inter);         // h (bf16, or fp16 on the tensor-core path)
+  b += al(sizeof(float) * n * cfg.hidden);           // per-assignment outputs (float32, or fp16 on the tensor-core path)
   b += al(sizeof(uint16_t) * n * cfg.hidden);        // rows gathered into expert order, fp16 (tensor-core path)
-  b += al(sizeof(uint16_t) * n * cfg.inter) + 2 * al(sizeof(float) * n);  // fp16 copy of h, row scales
+  b += al(sizeof(float) * n);                        // their row scales
   b += (al(sizeof(uint32_t) * prefill_tile_words(n, (int)E)) * 3 + al(16)) * 2;
-  // tensor-memory small-batch path: 16 rows of padding on the prepared rows, per-group tables, 16-row tile list
-  b += al(sizeof(uint16_t) * 16 * (cfg.hidden + cfg.inter)) + al(8 * (n + 16) * (cfg.hidden / 64)) +
-       al(8 * (n + 16) * (cfg.inter / 64)) + al(sizeof(uint32_t) * (n / 16 + E + 1)) * 3;
   return b + 4096;
 }
 
@@ -208,9 +207,7 @@ int b200_ctx_debug_words(b200_ctx* c, int32_t* host_out, int n) {
 
 int b200_ctx_set_qmm_path(b200_ctx* c, int path) {
   CTX_ENTER(c);
-  B200_REQUIRE(path == B200_QMM_AUTO || path == B200_QMM_SMALL || path == B200_QMM_TENSOR_CORE || path == B200_QMM_STREAM ||
-                   path == B200_QMM_TMEM,
-               "unknown path");
+  B200_REQUIRE(path == B200_QMM_AUTO || path == B200_QMM_SMALL || path == B200_QMM_TENSOR_CORE, "unknown path");
   c->qmm_path = path;
   return 0;
 }
@@ -271,13 +268,6 @@ int b200_dequantize(b200_ctx* c, const uint32_t* wq, const void* scales, const v
 // Shared by quantized_matmul, gather_qmm and the block: run one grouped product.
 static int run_grouped(b200_ctx* c, GroupedArgs& a, int nmat, int bits, int max_active, int64_t rows, cudaStream_t st) {
   if (rows == 0) return 0;
-  // memory-bound regime: the register-load kernel by default; the TMA-streamed variant when pinned
-  // (it measures the same within a few percent, see qmm_stream.cu)
-  if (c->qmm_path == B200_QMM_STREAM && a.n_experts > 0 && stream_shape_ok(a.K, a.N, nmat, bits)) {
-    if (launch_grouped_qmm_stream(a, nmat, bits, a.n_experts, max_active, rows, c->err, st)) return 1;
-    LAUNCHED(c, 1);
-    return 0;
-  }
   if (launch_grouped_qmm_small(a, nmat, bits, max_active, rows, st)) return 1;
   LAUNCHED(c, 1);
   return 0;
@@ -325,13 +315,13 @@ int b200_gather_qmm(b200_ctx* c, const void* x, const uint32_t* w, const void* s
                     const uint32_t* lhs, const uint32_t* rhs, int transpose, int gs, int bits, int sorted_indices,
                     int64_t Bx, int64_t M, int64_t K, int64_t E, int64_t N, int64_t n_idx, void* out, void* stream) {
   (void)sorted_indices;
-  (void)Bx;
   CTX_ENTER(c);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   B200_REQUIRE(transpose != 0, "only transpose = true is supported (the form every layer uses)");
   B200_REQUIRE(bits == 4 || bits == 8, "bits must be 4 or 8");
   B200_REQUIRE(gs == 64, "group_size must be 64");
-  B200_REQUIRE(M > 0 && K > 0 && N > 0 && n_idx >= 0, "bad shape");
+  B200_REQUIRE(Bx > 0 && M > 0 && K > 0 && N > 0 && n_idx >= 0, "bad shape");
+  B200_REQUIRE(lhs != nullptr || n_idx <= Bx, "without lhs_indices x needs one batch entry per index");
   B200_REQUIRE(K % gs == 0, "K must be a multiple of group_size");
   B200_REQUIRE(E > 0 && E <= 256, "the number of weight matrices must be in 1..256");
   B200_REQUIRE(biases != nullptr, "biases are required in affine mode");
@@ -352,7 +342,7 @@ int b200_gather_qmm(b200_ctx* c, const void* x, const uint32_t* w, const void* s
   uint32_t* active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
   uint32_t* n_active = static_cast<uint32_t*>(c->take(16));
   uint32_t* chunk = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * permute_scratch_words(n, (int)E)));
-  launch_expand_indices(lhs, rhs, n_idx, (int)M, flat_e, flat_s, st);
+  launch_expand_indices(lhs, rhs, n_idx, (int)M, Bx, flat_e, flat_s, c->err, st);
   launch_permute(flat_e, n, (int)E, perm, inv, counts, offsets, active, n_active, chunk, c->err, st);
   LAUNCHED(c, 1 + permute_launches(n));
   GroupedArgs a{};
@@ -514,7 +504,7 @@ static bool use_tensor_core_path(const b200_ctx* c, const b200_moe_config& cfg, 
   // kernel, which streams activations by TMA, applies
   const int kmax = cfg.hidden > cfg.inter ? cfg.hidden : cfg.inter;
   if ((size_t)8 * (2 * kmax + 16) + sizeof(float) * (kmax / 64) * 8 > 220 * 1024) return true;
-  if (c->qmm_path == B200_QMM_SMALL || c->qmm_path == B200_QMM_STREAM || c->qmm_path == B200_QMM_TMEM) return false;
+  if (c->qmm_path == B200_QMM_SMALL) return false;
   if (c->qmm_path == B200_QMM_TENSOR_CORE) return true;
   // measured crossover on the Qwen3-30B-A3B shape: 8 rows per expert 257 us (register kernel) against 336 us,
   // 12 rows per expert 377 us against 351 us
@@ -527,7 +517,7 @@ static bool use_tensor_core_path(const b200_ctx* c, const b200_moe_config& cfg, 
 static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_moe_params& p, const void* x,
                           const uint32_t* perm, int src_div, const uint32_t* counts, const uint32_t* offsets,
                           const uint32_t* active, const uint32_t* n_active, int64_t n, const void* scores, void* yk,
-                          cudaStream_t st, bool* yk_is_bf16, const unsigned long long* out_row_addr = nullptr);
+                          cudaStream_t st, int* yk_fmt, const unsigned long long* out_row_addr = nullptr);
 
 // Outputs of the token -> expert sort (scratch, or the caller's aux buffers where given).
 struct SortBufs {
@@ -556,7 +546,7 @@ static int take_sort_bufs(b200_ctx* c, int64_t n, int E, const b200_moe_aux* aux
 // `scores` null: unweighted per-assignment outputs go to `yk` ([T*k, H]).
 static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_moe_params& p, const void* x,
                            const uint32_t* idx, const void* scores, int64_t T, void* yk, const b200_moe_aux* aux,
-                           cudaStream_t st, bool* yk_is_bf16 = nullptr) {
+                           cudaStream_t st, int* yk_fmt = nullptr) {
   const int64_t n = T * cfg.top_k;
   const int E = cfg.n_experts;
   SortBufs sb;
@@ -564,13 +554,13 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
   launch_permute(idx, n, E, sb.perm, sb.inv, sb.counts, sb.offsets, sb.active, sb.n_active, sb.chunk, c->err, st);
   LAUNCHED(c, permute_launches(n));
   return experts_sorted(c, cfg, p, x, sb.perm, cfg.top_k, sb.counts, sb.offsets, sb.active, sb.n_active, n, scores, yk, st,
-                        yk_is_bf16);
+                        yk_fmt);
 }
 
 static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_moe_params& p, const void* x,
                           const uint32_t* perm, int src_div, const uint32_t* counts, const uint32_t* offsets,
                           const uint32_t* active, const uint32_t* n_active, int64_t n, const void* scores, void* yk,
-                          cudaStream_t st, bool* yk_is_bf16, const unsigned long long* out_row_addr) {
+                          cudaStream_t st, int* yk_fmt, const unsigned long long* out_row_addr) {
   const int E = cfg.n_experts;
   void* h = c->take(sizeof(uint16_t) * n * cfg.inter);
   B200_REQUIRE(h, "scratch arena too small");
@@ -578,35 +568,18 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
 
   // Regime: the tensor-core path once experts own enough rows to fill 128-row tiles.
   const bool tc = use_tensor_core_path(c, cfg, n, max_active);
-  // memory-bound regime on tensor memory (codes go to the tensor core unscaled; per-group accumulators)
-  const bool mb = !tc && !out_row_addr && c->qmm_path == B200_QMM_TMEM && mb_shape_ok(cfg.hidden, cfg.inter) &&
-                  mb_shape_ok(cfg.inter, cfg.hidden);
   // two row-tile lists: 256-row tiles for gate/up (both accumulators share each dequantised weight
   // stage), 128-row tiles for down (short K: the accumulators alternate so that the drain of one
   // tile runs under the products of the next)
   uint32_t *tile_expert = nullptr, *tile_row0 = nullptr, *tile_rows = nullptr, *n_row_tiles = nullptr;
   uint32_t *tile_expert1 = nullptr, *tile_row01 = nullptr, *tile_rows1 = nullptr, *n_row_tiles1 = nullptr;
-  void *xs = nullptr, *h16 = nullptr;
-  float *rs_x = nullptr, *rs_h = nullptr;
+  void* xs = nullptr;
+  float* rs_x = nullptr;
+#ifdef B200_DEV
   static const bool alt_down = [] { const char* v = getenv("B200_TC_DEBUG"); return !(v && (atoi(v) & 64)); }();
-  void *tab_x = nullptr, *tab_h = nullptr;
-  if (mb) {
-    const size_t tw = (size_t)(n / 16 + E + 1);
-    tile_expert = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
-    tile_row0 = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
-    tile_rows = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
-    n_row_tiles = static_cast<uint32_t*>(c->take(16));
-    xs = c->take(sizeof(uint16_t) * (n + 16) * cfg.hidden);
-    h16 = c->take(sizeof(uint16_t) * (n + 16) * cfg.inter);
-    rs_x = static_cast<float*>(c->take(sizeof(float) * n));
-    rs_h = static_cast<float*>(c->take(sizeof(float) * n));
-    tab_x = c->take(8 * (size_t)(n + 16) * (cfg.hidden / 64));
-    tab_h = c->take(8 * (size_t)(n + 16) * (cfg.inter / 64));
-    B200_REQUIRE(tile_expert && tile_row0 && tile_rows && n_row_tiles && xs && h16 && rs_x && rs_h && tab_x && tab_h,
-                 "scratch arena too small");
-    launch_build_row_tiles(counts, offsets, E, tile_expert, tile_row0, tile_rows, n_row_tiles, 16, st);
-    LAUNCHED(c, 1);
-  }
+#else
+  constexpr bool alt_down = true;
+#endif
   if (tc) {
     const size_t tw = prefill_tile_words(n, E);
     tile_expert = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
@@ -619,11 +592,8 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
     n_row_tiles1 = static_cast<uint32_t*>(c->take(16));
     B200_REQUIRE(tile_expert1 && tile_row01 && tile_rows1 && n_row_tiles1, "scratch arena too small");
     xs = c->take(sizeof(uint16_t) * n * cfg.hidden);
-    h16 = c->take(sizeof(uint16_t) * n * cfg.inter);
     rs_x = static_cast<float*>(c->take(sizeof(float) * n));
-    rs_h = static_cast<float*>(c->take(sizeof(float) * n));
-    B200_REQUIRE(tile_expert && tile_row0 && tile_rows && n_row_tiles && xs && h16 && rs_x && rs_h,
-                 "scratch arena too small");
+    B200_REQUIRE(tile_expert && tile_row0 && tile_rows && n_row_tiles && xs && rs_x, "scratch arena too small");
     launch_build_row_tiles(counts, offsets, E, tile_expert, tile_row0, tile_rows, n_row_tiles, 256, st);
     if (alt_down) launch_build_row_tiles(counts, offsets, E, tile_expert1, tile_row01, tile_rows1, n_row_tiles1, 128, st);
     LAUNCHED(c, alt_down ? 2 : 1);
@@ -646,6 +616,7 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   gu.src_div = src_div;
   gu.dst_perm = 0;
   gu.out = h;
+  gu.out_f16 = tc ? 1 : 0;  // the tensor-core down projection takes fp16 rows: its producer writes them directly
   gu.K = cfg.hidden;
   gu.N = cfg.inter;
   gu.n_experts = E;
@@ -655,13 +626,6 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
     c->mark(4, st);
     if (launch_grouped_qmm_tc(xs, rs_x, n, gu, 2, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, false,
                               c->err, st))
-      return 1;
-    LAUNCHED(c, 2);
-  } else if (mb) {
-    launch_prepare_rows_mb(x, perm, perm ? src_div : 1, n, cfg.hidden, cfg.bits, xs, rs_x, tab_x, st);
-    c->mark(4, st);
-    if (launch_grouped_qmm_mb(xs, rs_x, tab_x, n, gu, 2, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, c->err,
-                              st))
       return 1;
     LAUNCHED(c, 2);
   } else {
@@ -683,32 +647,25 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   dn.dst_perm = perm ? 1 : 0;
   dn.row_scale = scores;
   dn.out = yk;
-  // weighted rows stay float32 until the combine (storing them as bf16 halves the traffic of the
-  // tensor-core path's epilogue but triples its error against the 2e-2 bar: measured 0.017 at
-  // T=512); SwitchGlu's own output is bf16
-  dn.out_f32 = scores != nullptr;
+  // weighted rows keep more than bf16's 8 significant bits until the combine (bf16 rows measured 0.017 of
+  // the 2e-2 bar at T=512): float32 from the register kernel, fp16 (11 bits, half the traffic of the
+  // store-bound epilogue and of the combine's reads) from the tensor-core kernel; SwitchGlu's own output is bf16
+  dn.out_f32 = scores != nullptr && !tc;
+  dn.out_f16 = scores != nullptr && tc && !out_row_addr;
   dn.out_row_addr = out_row_addr;   // rows go to per-row addresses (bf16): the expert-parallel return path
-  if (yk_is_bf16) *yk_is_bf16 = !dn.out_f32;
+  if (yk_fmt) *yk_fmt = dn.out_f32 ? kOutF32 : (dn.out_f16 ? kOutF16 : kOutBf16);
   dn.K = cfg.inter;
   dn.N = cfg.hidden;
   dn.n_experts = E;
   if (tc) {
-    // h was written (bf16-rounded) already in unpack order; only the fp16 conversion remains
-    launch_prepare_rows(h, nullptr, 1, n, cfg.inter, 0, h16, rs_h, st);
+    // h is already fp16 in unpack order, unscaled (stage 6, the former conversion pass, is empty)
     c->mark(6, st);
-    if (alt_down ? launch_grouped_qmm_tc(h16, rs_h, n, dn, 1, cfg.bits, tile_expert1, tile_row01, tile_rows1, n_row_tiles1,
+    if (alt_down ? launch_grouped_qmm_tc(h, nullptr, n, dn, 1, cfg.bits, tile_expert1, tile_row01, tile_rows1, n_row_tiles1,
                                          E, true, c->err, st)
-                 : launch_grouped_qmm_tc(h16, rs_h, n, dn, 1, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E,
+                 : launch_grouped_qmm_tc(h, nullptr, n, dn, 1, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E,
                                          false, c->err, st))
       return 1;
-    LAUNCHED(c, 2);
-  } else if (mb) {
-    launch_prepare_rows_mb(h, nullptr, 1, n, cfg.inter, cfg.bits, h16, rs_h, tab_h, st);
-    c->mark(6, st);
-    if (launch_grouped_qmm_mb(h16, rs_h, tab_h, n, dn, 1, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, c->err,
-                              st))
-      return 1;
-    LAUNCHED(c, 2);
+    LAUNCHED(c, 1);
   } else if (out_row_addr) {  // per-row addresses: the register kernel (the streamed variant does not take them)
     c->mark(6, st);
     if (launch_grouped_qmm_small(dn, 1, cfg.bits, max_active, n, st)) return 1;
@@ -762,7 +719,7 @@ int b200_moe_block_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_m
     if (aux->scores) scores = aux->scores;
   }
   c->mark(0, st);
-  bool yk_bf16 = false;
+  int yk_fmt = kOutF32;
   if (router_fused_small_ok((int)T, cfg->hidden, cfg->n_experts, cfg->top_k)) {
     // small batch: logits, routing and the sort in one launch (stages 1 and 2 read as zero)
     SortBufs sb;
@@ -776,7 +733,7 @@ int b200_moe_block_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_m
     c->mark(1, st);
     c->mark(2, st);
     if (experts_sorted(c, *cfg, *params, x, sb.perm, cfg->top_k, sb.counts, sb.offsets, sb.active, sb.n_active, n, scores,
-                       yk, st, &yk_bf16))
+                       yk, st, &yk_fmt))
       return 1;
   } else {
     double* w64 = static_cast<double*>(c->take(sizeof(double) * (size_t)cfg->n_experts * cfg->hidden));
@@ -788,9 +745,9 @@ int b200_moe_block_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_m
                       nullptr, st);
     c->mark(2, st);
     LAUNCHED(c, 2);
-    if (experts_forward(c, *cfg, *params, x, idx, scores, T, yk, aux, st, &yk_bf16)) return 1;
+    if (experts_forward(c, *cfg, *params, x, idx, scores, T, yk, aux, st, &yk_fmt)) return 1;
   }
-  if (launch_combine(yk, yk_bf16, T, cfg->top_k, cfg->hidden, out, aux ? aux->out_f32 : nullptr, st)) return 1;
+  if (launch_combine(yk, yk_fmt, T, cfg->top_k, cfg->hidden, out, aux ? aux->out_f32 : nullptr, st)) return 1;
   c->mark(8, st);
   c->ev_valid = c->profiling;
   LAUNCHED(c, 1);

@@ -67,7 +67,11 @@ __device__ __forceinline__ void pdl_prologue() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
-bool pdl_enabled();  // false when the environment variable B200_NO_PDL is set (development switch)
+#ifdef B200_DEV
+bool pdl_enabled();  // development build: false when the environment variable B200_NO_PDL is set
+#else
+inline bool pdl_enabled() { return true; }
+#endif
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
@@ -82,6 +86,39 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the CURRENT device only, and one process
+// may hold contexts on several devices: remember, per kernel instantiation and device, the largest size
+// that has been set.  One cache object per kernel (a function-local static at the launch site).
+constexpr int kMaxDevices = 64;
+struct DynSmemCache {
+  size_t bytes[kMaxDevices] = {};
+};
+template <typename Kern>
+inline cudaError_t ensure_dyn_smem(Kern kern, size_t bytes, DynSmemCache& cache) {
+  if (bytes <= 48 * 1024) return cudaSuccess;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const bool cached = dev >= 0 && dev < kMaxDevices;
+  if (cached && bytes <= cache.bytes[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess && cached) cache.bytes[dev] = bytes;
+  return e;
+}
+// Number of SMs of the current device (cached per device).
+inline int current_sm_count() {
+  static int n_sm[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev < 0 || dev >= kMaxDevices) {
+    int n = 148;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n;
+  }
+  if (!n_sm[dev]) cudaDeviceGetAttribute(&n_sm[dev], cudaDevAttrMultiProcessorCount, dev);
+  return n_sm[dev] > 0 ? n_sm[dev] : 148;
 }
 
 __device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {

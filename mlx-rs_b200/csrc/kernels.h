@@ -6,6 +6,7 @@
 namespace b200 {
 
 enum { kSrcIdent = 0, kSrcPermDiv = 1, kSrcMap = 2 };
+enum { kOutBf16 = 0, kOutF32 = 1, kOutF16 = 2 };  // element format of a grouped product's output / of the combine's input
 
 // One grouped product over rows that are sorted by expert.
 struct GroupedArgs {
@@ -26,6 +27,7 @@ struct GroupedArgs {
   const unsigned long long* out_row_addr;  // optional, by sorted position: address of the row's bf16 output
                                            // (overrides out/dst_perm; rows may live on peer GPUs)
   int out_f32;                // 1: float32 output (no rounding before the k-way combine)
+  int out_f16;                // 1: fp16 output with saturation (tensor-core kernel only; out_f32 wins when both are set)
   int K, N;
   int n_experts;              // number of stacked weight matrices
 };
@@ -56,11 +58,6 @@ size_t permute_scratch_words(int64_t n, int E);
 // qmm_decode.cu
 int launch_grouped_qmm_small(const GroupedArgs& a, int nmat, int bits, int max_active, int64_t rows, cudaStream_t st);
 
-// qmm_stream.cu (memory-bound regime, TMA-streamed weights)
-bool stream_shape_ok(int K, int N, int nmat, int bits);
-int launch_grouped_qmm_stream(const GroupedArgs& g, int nmat, int bits, int n_experts, int max_active, int64_t rows,
-                              int* err, cudaStream_t st);
-
 // qmm_prefill.cu (tcgen05 path)
 size_t prefill_tile_words(int64_t rows, int E);
 bool prefill_shape_ok(int K, int N, int nmat);
@@ -73,20 +70,12 @@ int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows,
                           const uint32_t* tile_row0, const uint32_t* tile_rows, const uint32_t* n_row_tiles, int E,
                           bool alternate, int* err, cudaStream_t st);
 
-// qmm_decode_tc.cu (tensor-memory path for the memory-bound regime)
-bool mb_shape_ok(int K, int N);
-int launch_prepare_rows_mb(const void* x, const uint32_t* perm, int src_div, int64_t n_rows, int K, int bits, void* xs,
-                           float* row_scale, void* tab, cudaStream_t st);
-int launch_grouped_qmm_mb(const void* xs, const float* a_row_scale, const void* tab, int64_t rows, const GroupedArgs& g,
-                          int nmat, int bits, const uint32_t* tile_expert, const uint32_t* tile_row0,
-                          const uint32_t* tile_rows, const uint32_t* n_row_tiles, int E, int* err, cudaStream_t st);
-
 // misc.cu
 int launch_quantize(const void* w, int is_bf16, int64_t rows, int64_t K, int gs, int bits, uint32_t* wq, void* scales,
                     void* biases, cudaStream_t st);
 int launch_dequantize(const uint32_t* wq, const void* scales, const void* biases, int is_bf16, int64_t rows, int64_t K,
                       int gs, int bits, void* out, cudaStream_t st);
-int launch_combine(const void* yk, int yk_bf16, int64_t T, int k, int64_t H, void* out, void* out_f32, cudaStream_t st);
+int launch_combine(const void* yk, int yk_fmt, int64_t T, int k, int64_t H, void* out, void* out_f32, cudaStream_t st);
 int launch_take_rows(const void* x, const uint32_t* indices, uint32_t div, int64_t n_rows, int64_t x_rows, int64_t cols,
                      void* out, int* err, cudaStream_t st);
 int launch_gather_combine(const void* y, const uint32_t* inv, const void* scores, int64_t T, int k, int64_t H, void* out,
@@ -100,8 +89,8 @@ int launch_gather_mm(const void* a, const void* b, const uint32_t* lhs, const ui
                      int64_t M, int64_t K, int64_t N, int64_t n_idx, void* out, int* err, cudaStream_t st);
 int launch_dense_segments(uint32_t* counts, uint32_t* offsets, uint32_t* active, uint32_t* n_active, uint32_t rows,
                           cudaStream_t st);
-int launch_expand_indices(const uint32_t* lhs, const uint32_t* rhs, int64_t n_idx, int M, uint32_t* flat_expert,
-                          uint32_t* flat_src, cudaStream_t st);
+int launch_expand_indices(const uint32_t* lhs, const uint32_t* rhs, int64_t n_idx, int M, int64_t Bx, uint32_t* flat_expert,
+                          uint32_t* flat_src, int* err, cudaStream_t st);
 
 
 // ep.cu (expert-parallel exchange over peer memory)

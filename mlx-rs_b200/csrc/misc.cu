@@ -1,5 +1,7 @@
 // Memory-bound helpers of the quantized path: affine quantize / dequantize, the k-way
 // combine, residual-add + RMSNorm, and small index utilities.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -134,10 +136,12 @@ __global__ void combine_kernel(const float4* __restrict__ yk, int64_t T, int k, 
   if (out_f32) out_f32[i] = acc;  // the sum before its rounding to bf16
 }
 
-// Same sum over bf16 inputs (the tensor-core path stores its weighted rows as bf16 to halve the
-// traffic of its write-bound epilogue).
-__global__ void combine_bf16_kernel(const uint2* __restrict__ yk, int64_t T, int k, int64_t H4, uint2* __restrict__ out,
-                                    float4* __restrict__ out_f32) {
+// Same sum over 16-bit inputs: bf16 rows, or the fp16 rows the tensor-core down projection stores
+// (half the traffic of float32 rows; fp16's 11 significant bits keep the k-way sum an order of
+// magnitude inside the output tolerance, bf16's 8 would not).
+template <bool F16>
+__global__ void combine_16_kernel(const uint2* __restrict__ yk, int64_t T, int k, int64_t H4, uint2* __restrict__ out,
+                                  float4* __restrict__ out_f32) {
   pdl_prologue();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= T * H4) return;
@@ -145,10 +149,19 @@ __global__ void combine_bf16_kernel(const uint2* __restrict__ yk, int64_t T, int
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int j = 0; j < k; ++j) {
     const uint2 v = __ldg(&yk[(t * k + j) * H4 + c]);
-    acc.x += __uint_as_float(v.x << 16);
-    acc.y += __uint_as_float(v.x & 0xffff0000u);
-    acc.z += __uint_as_float(v.y << 16);
-    acc.w += __uint_as_float(v.y & 0xffff0000u);
+    if constexpr (F16) {
+      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+      acc.x += a.x;
+      acc.y += a.y;
+      acc.z += b.x;
+      acc.w += b.y;
+    } else {
+      acc.x += __uint_as_float(v.x << 16);
+      acc.y += __uint_as_float(v.x & 0xffff0000u);
+      acc.z += __uint_as_float(v.y << 16);
+      acc.w += __uint_as_float(v.y & 0xffff0000u);
+    }
   }
   uint2 o;
   o.x = f32_to_bf16_bits(acc.x) | (f32_to_bf16_bits(acc.y) << 16);
@@ -157,19 +170,19 @@ __global__ void combine_bf16_kernel(const uint2* __restrict__ yk, int64_t T, int
   if (out_f32) out_f32[i] = acc;
 }
 
-int launch_combine(const void* yk, int yk_bf16, int64_t T, int k, int64_t H, void* out, void* out_f32, cudaStream_t st) {
+int launch_combine(const void* yk, int yk_fmt, int64_t T, int k, int64_t H, void* out, void* out_f32, cudaStream_t st) {
   if (T == 0) return 0;
-  if (yk_bf16) {
-    B200_REQUIRE(H % 4 == 0, "hidden size must be a multiple of 4");
-    int64_t n4 = T * (H / 4);
-    B200_CUDA(launch_pdl(combine_bf16_kernel, dim3(cdiv(n4, 256)), dim3(256), 0, st, static_cast<const uint2*>(yk), T, k, H / 4,
-                         static_cast<uint2*>(out), static_cast<float4*>(out_f32)));
-    return 0;
-  }
   B200_REQUIRE(H % 4 == 0, "hidden size must be a multiple of 4");
-  int64_t n = T * (H / 4);
-  B200_CUDA(launch_pdl(combine_kernel, dim3(cdiv(n, 256)), dim3(256), 0, st, static_cast<const float4*>(yk), T, k, H / 4,
-                       static_cast<uint2*>(out), static_cast<float4*>(out_f32)));
+  const int64_t n4 = T * (H / 4);
+  if (yk_fmt == kOutF16)
+    B200_CUDA(launch_pdl(combine_16_kernel<true>, dim3(cdiv(n4, 256)), dim3(256), 0, st, static_cast<const uint2*>(yk), T, k,
+                         H / 4, static_cast<uint2*>(out), static_cast<float4*>(out_f32)));
+  else if (yk_fmt == kOutBf16)
+    B200_CUDA(launch_pdl(combine_16_kernel<false>, dim3(cdiv(n4, 256)), dim3(256), 0, st, static_cast<const uint2*>(yk), T, k,
+                         H / 4, static_cast<uint2*>(out), static_cast<float4*>(out_f32)));
+  else
+    B200_CUDA(launch_pdl(combine_kernel, dim3(cdiv(n4, 256)), dim3(256), 0, st, static_cast<const float4*>(yk), T, k, H / 4,
+                         static_cast<uint2*>(out), static_cast<float4*>(out_f32)));
   return 0;
 }
 
@@ -396,19 +409,26 @@ int launch_gather_mm(const void* a, const void* b, const uint32_t* lhs, const ui
 }
 
 // gather_qmm with M rows per batch entry: assignment i*M + m uses expert rhs[i] and source
-// row lhs[i]*M + m (lhs == null: i*M + m).
+// row lhs[i]*M + m (lhs == null: i*M + m).  A batch index >= Bx sets *err = 1 and reads batch entry 0
+// instead (the access is skipped, never out of bounds); expert indices are checked by the sort.
 __global__ void expand_indices_kernel(const uint32_t* __restrict__ lhs, const uint32_t* __restrict__ rhs, int64_t n_idx,
-                                      int M, uint32_t* __restrict__ flat_expert, uint32_t* __restrict__ flat_src) {
+                                      int M, int64_t Bx, uint32_t* __restrict__ flat_expert,
+                                      uint32_t* __restrict__ flat_src, int* __restrict__ err) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_idx * M) return;
   int64_t b = i / M, m = i % M;
   flat_expert[i] = rhs[b];
-  flat_src[i] = (lhs ? lhs[b] : (uint32_t)b) * (uint32_t)M + (uint32_t)m;
+  uint32_t src = lhs ? lhs[b] : (uint32_t)b;
+  if ((int64_t)src >= Bx) {
+    *err = 1;
+    src = 0;
+  }
+  flat_src[i] = src * (uint32_t)M + (uint32_t)m;
 }
-int launch_expand_indices(const uint32_t* lhs, const uint32_t* rhs, int64_t n_idx, int M, uint32_t* flat_expert,
-                          uint32_t* flat_src, cudaStream_t st) {
+int launch_expand_indices(const uint32_t* lhs, const uint32_t* rhs, int64_t n_idx, int M, int64_t Bx, uint32_t* flat_expert,
+                          uint32_t* flat_src, int* err, cudaStream_t st) {
   if (n_idx * M == 0) return 0;
-  expand_indices_kernel<<<cdiv(n_idx * M, 256), 256, 0, st>>>(lhs, rhs, n_idx, M, flat_expert, flat_src);
+  expand_indices_kernel<<<cdiv(n_idx * M, 256), 256, 0, st>>>(lhs, rhs, n_idx, M, Bx, flat_expert, flat_src, err);
   return 0;
 }
 

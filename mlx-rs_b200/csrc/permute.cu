@@ -174,7 +174,6 @@ constexpr int kStaticTableWords = 1 << 16;  // chunk table capacity: ceil(n/1024
 constexpr int kStaticTailWords = 512;       // active list (<= 257), n_active, status word
 static __device__ __align__(256) uint32_t g_permute_static_scratch[kStaticTableWords + kStaticTailWords];
 
-constexpr int kMaxDevices = 64;
 static uint32_t* g_static_scratch_addr[kMaxDevices] = {};
 
 }  // namespace b200
@@ -203,10 +202,10 @@ extern "C" int b200_moe_permute_static(const uint32_t* indices, int64_t n, int n
   uint32_t* n_active = active + 260;
   int* status = reinterpret_cast<int*>(active + 264);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // The array keeps whatever the previous call left.  The chunk table, the active list and
-  // n_active are fully rewritten by the kernels before they are read; only the status word is
-  // written conditionally, so it is the one thing that has to be cleared.
-  B200_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
+  // The array keeps whatever the previous call left.  Nothing in it has to start at zero: the chunk
+  // table, the active list and n_active are fully rewritten by the kernels before they are read, and
+  // the status word is write-only (the kernels set it when they skip an out-of-range expert index;
+  // nothing reads it back - this entry point has no context to report through).
   launch_permute(indices, n, n_experts, perm, inv_perm, counts, offsets, active, n_active, base, status, st);
   cudaError_t le = cudaGetLastError();
   if (le != cudaSuccess) B200_FAIL(std::string("kernel launch failed: ") + cudaGetErrorString(le));

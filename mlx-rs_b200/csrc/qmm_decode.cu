@@ -303,11 +303,8 @@ static int launch_cfg(const GroupedArgs& a, int max_active, cudaStream_t st) {
   size_t red = sizeof(float) * 8 * NMAT * NT * 128;
   if (red > smem) smem = red;
   auto kern = grouped_qmm_small_kernel<BITS, NMAT, RT, NT>;
-  static size_t attr_bytes = 0;  // one process drives one GPU, so a per-instantiation cache is enough
-  if (smem > attr_bytes) {
-    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_bytes = smem;
-  }
+  static DynSmemCache attr;
+  B200_CUDA(ensure_dyn_smem(kern, smem, attr));
   dim3 grid(cdiv(a.N, 16 * RT), max_active);
   B200_CUDA(launch_pdl(kern, grid, dim3(256), smem, st, a));
   return 0;

@@ -77,6 +77,15 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
   umma_f16(d_tmem, adesc, bdesc, kIdesc, accumulate);
 }
 
+// two float32 -> packed fp16 pair (lo in the low half), round to nearest, finite overflow saturates
+__device__ __forceinline__ uint32_t f16x2_sat(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float round_to_bf16(float f) { return __uint_as_float(f32_to_bf16_bits(f) << 16); }
+__device__ __forceinline__ uint32_t bf16x2(float lo, float hi) { return f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16); }
+
 struct PrefillArgs {
   const uint32_t* w[2];
   const void* scales[2];
@@ -87,14 +96,15 @@ struct PrefillArgs {
   const uint32_t* n_row_tiles;  // device scalar
   const uint32_t* perm;         // sorted position -> flat assignment index
   int dst_perm;                 // out row = perm[p] instead of p
-  const float* a_row_scale;     // by sorted position: the power of two each A row was divided by
+  const float* a_row_scale;     // by sorted position: the power of two each A row was divided by (null: rows are unscaled)
   const void* row_scale;        // bf16 by out row, or null
   void* out;
   const unsigned long long* out_row_addr;  // optional, by sorted position: where the row's bf16 output goes
-  int out_f32;
+  int out_fmt;                  // kOutBf16 / kOutF32 / kOutF16 (fp16 with saturation instead of infinities)
   int K, N;                     // reduction length, output features per matrix
   int* err;
-  int debug;                    // development: 1 = skip the dequantisation work, 2 = skip the MMAs
+  int debug;                    // development builds (-DB200_DEV) only: 1 = skip the dequantisation work, 2 = skip the MMAs,
+                                // 32 = per-role self-timing; always 0 otherwise
   int alt;                      // 1: row tiles hold <= 128 rows and alternate between the two accumulators
 };
 
@@ -226,7 +236,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       const bool row_ok = r < rows;
       const uint32_t sp = row0 + r;
       const uint32_t dst = row_ok ? (p.dst_perm ? p.perm[sp] : sp) : 0xffffffffu;  // 0xffffffff: row not stored
-      const float ar = row_ok ? p.a_row_scale[sp] : 1.0f;
+      const float ar = (row_ok && p.a_row_scale) ? p.a_row_scale[sp] : 1.0f;
       const unsigned long long daddr = (row_ok && p.out_row_addr) ? p.out_row_addr[sp] : 0ull;
       if (!mbar_wait(tfull_bar(tb), tphase, abort_flag)) break;
       tphase ^= 1;
@@ -268,17 +278,26 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
               const uint32_t d = __shfl_sync(0xffffffffu, dst, rr);
               const float4 v0 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8);
               const float4 v1 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8 + 4);
-              uint4 o;
+              // h = bf16(silu(g) * u) is the value the down projection consumes; kOutF16 stores that same
+              // value as fp16 (exact for 2^-14 <= |h| <= 65504, saturating beyond), the A-operand format of
+              // the tensor-core down projection, so no conversion pass is needed between the two products
+              float e0, e1, e2, e3, e4, e5, e6, e7;
               if constexpr (BITS == 4) {  // the consumer (down projection) reads k in [0,4,1,5,2,6,3,7] order
-                o.x = f32_to_bf16_bits(v0.x) | (f32_to_bf16_bits(v1.x) << 16);
-                o.y = f32_to_bf16_bits(v0.y) | (f32_to_bf16_bits(v1.y) << 16);
-                o.z = f32_to_bf16_bits(v0.z) | (f32_to_bf16_bits(v1.z) << 16);
-                o.w = f32_to_bf16_bits(v0.w) | (f32_to_bf16_bits(v1.w) << 16);
+                e0 = v0.x, e1 = v1.x, e2 = v0.y, e3 = v1.y, e4 = v0.z, e5 = v1.z, e6 = v0.w, e7 = v1.w;
               } else {
-                o.x = f32_to_bf16_bits(v0.x) | (f32_to_bf16_bits(v0.y) << 16);
-                o.y = f32_to_bf16_bits(v0.z) | (f32_to_bf16_bits(v0.w) << 16);
-                o.z = f32_to_bf16_bits(v1.x) | (f32_to_bf16_bits(v1.y) << 16);
-                o.w = f32_to_bf16_bits(v1.z) | (f32_to_bf16_bits(v1.w) << 16);
+                e0 = v0.x, e1 = v0.y, e2 = v0.z, e3 = v0.w, e4 = v1.x, e5 = v1.y, e6 = v1.z, e7 = v1.w;
+              }
+              uint4 o;
+              if (p.out_fmt == kOutF16) {
+                o.x = f16x2_sat(round_to_bf16(e0), round_to_bf16(e1));
+                o.y = f16x2_sat(round_to_bf16(e2), round_to_bf16(e3));
+                o.z = f16x2_sat(round_to_bf16(e4), round_to_bf16(e5));
+                o.w = f16x2_sat(round_to_bf16(e6), round_to_bf16(e7));
+              } else {
+                o.x = bf16x2(e0, e1);
+                o.y = bf16x2(e2, e3);
+                o.z = bf16x2(e4, e5);
+                o.w = bf16x2(e6, e7);
               }
               if (d != 0xffffffffu)
                 *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)d * p.N + ct * FEAT + c + cg8) = o;
@@ -301,7 +320,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                               __uint_as_float(v[i + 3]) * sc);
             if (c + 16 < 256) tmem_ld16(lane_addr + c + 16, v);
             __syncwarp();
-            if (p.out_f32) {
+            if (p.out_fmt == kOutF32) {
               // 4 lanes per row (4 columns = 16 bytes each): 64 bytes per row, 8 rows per instruction
               const int c4 = (lane & 3) * 4;
               const float4 cc = *reinterpret_cast<const float4*>(cs + c + c4);
@@ -328,10 +347,17 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 const float4 v0 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8);
                 const float4 v1 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8 + 4);
                 uint4 o;
-                o.x = f32_to_bf16_bits(v0.x * c0.x) | (f32_to_bf16_bits(v0.y * c0.y) << 16);
-                o.y = f32_to_bf16_bits(v0.z * c0.z) | (f32_to_bf16_bits(v0.w * c0.w) << 16);
-                o.z = f32_to_bf16_bits(v1.x * c1.x) | (f32_to_bf16_bits(v1.y * c1.y) << 16);
-                o.w = f32_to_bf16_bits(v1.z * c1.z) | (f32_to_bf16_bits(v1.w * c1.w) << 16);
+                if (p.out_fmt == kOutF16) {
+                  o.x = f16x2_sat(v0.x * c0.x, v0.y * c0.y);
+                  o.y = f16x2_sat(v0.z * c0.z, v0.w * c0.w);
+                  o.z = f16x2_sat(v1.x * c1.x, v1.y * c1.y);
+                  o.w = f16x2_sat(v1.z * c1.z, v1.w * c1.w);
+                } else {
+                  o.x = bf16x2(v0.x * c0.x, v0.y * c0.y);
+                  o.y = bf16x2(v0.z * c0.z, v0.w * c0.w);
+                  o.z = bf16x2(v1.x * c1.x, v1.y * c1.y);
+                  o.w = bf16x2(v1.z * c1.z, v1.w * c1.w);
+                }
                 const unsigned long long da = __shfl_sync(0xffffffffu, daddr, rr);
                 if (d != 0xffffffffu) {
                   __nv_bfloat16* orow = p.out_row_addr ? reinterpret_cast<__nv_bfloat16*>(da)
@@ -362,7 +388,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     int s = 0, phase = 0, tcount = 0, ws = 0, wphase = 0;
     constexpr float kQmax = (BITS == 4) ? 15.f : 255.f;
     RoleTimer tm((p.debug & 32) && blockIdx.x == 0 && tid == N_EPI);
-    const long long t_begin = clock64();
+    const long long t_begin = B200_DEV_CLOCK();
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
       const int rt = tile / n_col_tiles, ct = tile % n_col_tiles;
       const int e = (int)p.tile_expert[rt];
@@ -451,6 +477,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
         tm.stop(0);
         tm.start();
+#ifdef B200_DEV
         if (p.debug & 1) {
           mbar_arrive_warp(full_bar(s), lane);
           if (++s == STAGES) {
@@ -466,6 +493,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
           continue;
         }
+#endif
         const __half2 s2 = __float2half2_rn(bf16_bits_to_f32(cs) * down_f);
         const __half2 b2 = __float2half2_rn(bf16_bits_to_f32(cb) * down_f);
         const unsigned char* wsrc = w_st + (size_t)ws * W_BYTES + w_row_off;
@@ -503,7 +531,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       }
       if (dead) break;
     }
-    tm.acc[3] = clock64() - t_begin;
+    tm.total(t_begin);
     tm.flush(p.err + 20 + (NMAT == 1 ? 24 : 0));
   } else if (warp == WARP_TMA_A) {
     // ------------------------------- TMA producer (A) ---------------------------------------
@@ -511,7 +539,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       int s = 0, phase = 0;
       bool dead = false;
       RoleTimer tm((p.debug & 32) && blockIdx.x == 0);
-      const long long t_begin = clock64();
+      const long long t_begin = B200_DEV_CLOCK();
       for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
         const int rt = tile / n_col_tiles;
         const int row0 = (int)p.tile_row0[rt];
@@ -533,7 +561,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
         }
       }
-      tm.acc[3] = clock64() - t_begin;
+      tm.total(t_begin);
       tm.flush(p.err + 24 + (NMAT == 1 ? 24 : 0));
     }
     __syncwarp();
@@ -544,7 +572,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       int tph[2] = {0, 0};
       bool dead = false;
       RoleTimer tm((p.debug & 32) && blockIdx.x == 0);
-      const long long t_begin = clock64();
+      const long long t_begin = B200_DEV_CLOCK();
       for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x, ++tcount) {
         const int rt = tile / n_col_tiles;
         const int n_sub = (!alt && (int)p.tile_rows[rt] > BM) ? 2 : 1;
@@ -570,7 +598,10 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           tm.stop(1);
           tc_fence_after();
           const uint32_t a_addr = smem_u32(a_st + (size_t)sa * A_STAGE_BYTES), b_addr = smem_u32(b_st + (size_t)s * B_BYTES);
-          if (!(p.debug & 2)) {
+#ifdef B200_DEV
+          if (!(p.debug & 2))
+#endif
+          {
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {
               const uint64_t bd = umma_desc(b_addr + k * 32);
@@ -592,7 +623,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         if (dead) break;
         umma_commit(tfull_bar(acc));  // accumulators complete
       }
-      tm.acc[3] = clock64() - t_begin;
+      tm.total(t_begin);
       tm.flush(p.err + 28 + (NMAT == 1 ? 24 : 0));
     }
     __syncwarp();
@@ -603,7 +634,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       bool dead = false;
       const int n_wst = (KB + KPS - 1) / KPS;
       RoleTimer tm((p.debug & 32) && blockIdx.x == 0);
-      const long long t_begin = clock64();
+      const long long t_begin = B200_DEV_CLOCK();
       for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
         const int rt = tile / n_col_tiles, ct = tile % n_col_tiles;
         const int row_base = (int)p.tile_expert[rt] * p.N + ct * FEAT;
@@ -629,7 +660,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
         }
       }
-      tm.acc[3] = clock64() - t_begin;
+      tm.total(t_begin);
       tm.flush(p.err + 32 + (NMAT == 1 ? 24 : 0));
     }
     __syncwarp();
@@ -793,22 +824,18 @@ int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows,
   p.row_scale = g.row_scale;
   p.out = g.out;
   p.out_row_addr = g.out_row_addr;
-  p.out_f32 = g.out_f32;
+  p.out_fmt = g.out_f32 ? kOutF32 : (g.out_f16 ? kOutF16 : kOutBf16);
   p.K = g.K;
   p.N = g.N;
   p.err = err;
   p.alt = alternate ? 1 : 0;
+#ifdef B200_DEV
   {
     static const int dbg = [] { const char* v = getenv("B200_TC_DEBUG"); return v ? atoi(v) : 0; }();
     p.debug = dbg;
   }
-
-  static int n_sm = 0;
-  if (!n_sm) {
-    int dev = 0;
-    B200_CUDA(cudaGetDevice(&dev));
-    B200_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-  }
+#endif
+  const int n_sm = current_sm_count();
   const int feat = nmat == 2 ? 128 : 256;
   const int64_t max_tiles = (int64_t)prefill_tile_words(rows, E) * (g.N / feat);
   const int grid = (int)(max_tiles < n_sm ? max_tiles : n_sm);
@@ -816,11 +843,8 @@ int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows,
 #define B200_TC_LAUNCH(BITSV, NMATV)                                                                          \
   do {                                                                                                        \
     auto kern = grouped_qmm_tc_kernel<BITSV, NMATV>;                                                          \
-    static bool attr = false;                                                                                 \
-    if (!attr) {                                                                                              \
-      B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));         \
-      attr = true;                                                                                            \
-    }                                                                                                         \
+    static DynSmemCache attr;                                                                                 \
+    B200_CUDA(ensure_dyn_smem(kern, SMEM_BYTES, attr));                                                       \
     kern<<<grid, N_THREADS, SMEM_BYTES, st>>>(tmap, tmap_w[0], tmap_w[1], p);                                                       \
   } while (0)
   if (bits == 4 && nmat == 2)

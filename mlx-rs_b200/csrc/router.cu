@@ -354,21 +354,15 @@ static int launch_router_dmma(const __nv_bfloat16* xp, const __nv_bfloat16* wp, 
   dim3 grid(cdiv(T, MT * 8), cdiv(E, 64 * NE));
   if (w64 && H % 2 == 0) {
     auto kern = router_logits_dmma_kernel<MT, NE, KC, true>;
-    static bool attr = false;
-    if (!attr) {
-      B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      attr = true;
-    }
+    static DynSmemCache attr;
+    B200_CUDA(ensure_dyn_smem(kern, smem, attr));
     const int64_t n = (int64_t)E * H;
     router_weight_f64_kernel<<<cdiv(n, 256), 256, 0, st>>>(wp, const_cast<double*>(w64), n);
     kern<<<grid, 256, smem, st>>>(xp, wp, w64, logit_bias, lp, T, H, E);
   } else {
     auto kern = router_logits_dmma_kernel<MT, NE, KC, false>;
-    static bool attr = false;
-    if (!attr) {
-      B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      attr = true;
-    }
+    static DynSmemCache attr;
+    B200_CUDA(ensure_dyn_smem(kern, smem, attr));
     kern<<<grid, 256, smem, st>>>(xp, wp, nullptr, logit_bias, lp, T, H, E);
   }
   return 0;
@@ -398,11 +392,8 @@ static int launch_router_warp(const __nv_bfloat16* xp, const __nv_bfloat16* wp, 
                               __nv_bfloat16* lp, int T, int H, int E, cudaStream_t st) {
   size_t smem = (size_t)TT * H * 2;
   auto kern = router_logits_warp_kernel<TT>;
-  static size_t attr_bytes = 0;
-  if (smem > 48 * 1024 && smem > attr_bytes) {
-    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_bytes = smem;
-  }
+  static DynSmemCache attr;
+  B200_CUDA(ensure_dyn_smem(kern, smem, attr));
   dim3 grid(cdiv(E, 8), cdiv(T, TT));
   B200_CUDA(launch_pdl(kern, grid, dim3(256), smem, st, xp, wp, logit_bias, lp, T, H, E));
   return 0;
@@ -413,10 +404,14 @@ int launch_router_logits(const void* x, const void* w, const float* logit_bias, 
   auto xp = static_cast<const __nv_bfloat16*>(x);
   auto wp = static_cast<const __nv_bfloat16*>(w);
   auto lp = static_cast<__nv_bfloat16*>(logits);
+#ifdef B200_DEV
   static const int force = [] {
     const char* v = getenv("B200_ROUTER_KERNEL");  // "warp" / "tile" / "dmma": development override
     return !v ? 0 : (v[0] == 'w' ? 1 : (v[0] == 't' ? 2 : 3));
   }();
+#else
+  constexpr int force = 0;
+#endif
   const bool warp_ok = (H % 8 == 0) && ((size_t)8 * H * 2 <= 200 * 1024);
   const bool dmma_ok = (H % 8 == 0);
   if (dmma_ok && (force == 3 || (!force && T >= 256))) {
@@ -676,11 +671,8 @@ static int launch_fused_small(const __nv_bfloat16* xp, const __nv_bfloat16* wp, 
   const size_t need = sizeof(int) * 33 * E;
   if (smem < need) smem = need;
   auto kern = router_fused_small_kernel<TT>;
-  static size_t attr_bytes = 0;
-  if (smem > 48 * 1024 && smem > attr_bytes) {
-    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_bytes = smem;
-  }
+  static DynSmemCache attr;
+  B200_CUDA(ensure_dyn_smem(kern, smem, attr));
   dim3 grid(cdiv(E, 8), cdiv(T, TT));
   B200_CUDA(launch_pdl(kern, grid, dim3(256), smem, st, xp, wp, logit_bias, lp, T, H, E, k, mode, renorm, idx, scores, perm, inv,
                        counts, offsets, active, n_active, ticket, err));

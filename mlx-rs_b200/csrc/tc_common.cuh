@@ -33,8 +33,9 @@ __device__ __forceinline__ void mbar_arrive_warp(uint32_t bar, int lane) {
   __syncwarp();
   if (lane == 0) mbar_arrive(bar);
 }
-// Self-timing (diagnostic, enabled by bit 5 of PrefillArgs::debug): CTA 0 accumulates the
-// cycles each role spends in each of its waits and writes them to the status buffer.
+// Self-timing (development builds only, -DB200_DEV): CTA 0 accumulates the cycles each role spends in
+// each of its waits and writes them to the status buffer.  In a normal build every member is a no-op.
+#ifdef B200_DEV
 struct RoleTimer {
   long long acc[4] = {0, 0, 0, 0};
   long long t0 = 0;
@@ -46,11 +47,23 @@ struct RoleTimer {
   __device__ __forceinline__ void stop(int i) {
     if (on) acc[i] += clock64() - t0;
   }
+  __device__ __forceinline__ void total(long long t_begin) { acc[3] = clock64() - t_begin; }
   __device__ void flush(int* dst) {
     if (on)
       for (int i = 0; i < 4; ++i) dst[i] = (int)(acc[i] >> 10);
   }
 };
+#define B200_DEV_CLOCK() clock64()
+#else
+struct RoleTimer {
+  __device__ explicit RoleTimer(bool) {}
+  __device__ __forceinline__ void start() {}
+  __device__ __forceinline__ void stop(int) {}
+  __device__ __forceinline__ void total(long long) {}
+  __device__ __forceinline__ void flush(int*) {}
+};
+#define B200_DEV_CLOCK() 0ll
+#endif
 // Bounded wait: false when the abort flag is up or the time limit has passed.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   uint64_t t0 = 0;

@@ -336,39 +336,93 @@ def shard_switch_mlp(pkg, switch_mlp, rank, world):
     return pkg.nn.SwitchGlu(cut(switch_mlp.gate_proj), cut(switch_mlp.up_proj), cut(switch_mlp.down_proj))
 
 
-def bench_main(args, pkg, shape, peaks, metric, unit, workload_name, clock_sampler):
+def _draw_shard(pkg, shape, seed, rank, n_local, dev):
+    """The quantized experts rank `rank` owns (seeded by rank, so any process can rebuild any shard)."""
+    H, I = shape["hidden"], shape["inter"]
+    gl = torch.Generator(device=dev).manual_seed(seed + 1000 + rank)
+    lin = []
+    for r_, c_ in ((I, H), (I, H), (H, I)):
+        parts = []
+        for e0 in range(0, n_local, 16):
+            w = (torch.randn(min(16, n_local - e0), r_, c_, generator=gl, device=dev, dtype=torch.float32) * 0.02).bfloat16()
+            parts.append(pkg.ops.quantize(w, shape["group_size"], shape["bits"]))
+            del w
+        lin.append(tuple(torch.cat([p_[i] for p_ in parts]) for i in range(3)))
+    return lin
+
+
+def ep_parity(pkg, shape, cfg, seed, world, wr, bias, x, y_ep, idx_ep, n_sample=32):
+    """Checks this rank's expert-parallel output against a single-process computation of the same
+    tokens: every rank rebuilds ALL experts (the shards are seeded by rank), runs the one-GPU block on
+    `n_sample` of its tokens and compares routing (exactly) and outputs (|d| <= 2e-2 rms + two bf16
+    roundings: expert outputs cross NVLink as bf16).  -> (max|d| / rms, ok)."""
+    dev = x.device
+    E, k = shape["n_experts"], shape["top_k"]
+    shards = [_draw_shard(pkg, shape, seed, r, E // world, dev) for r in range(world)]
+    lin = [pkg.nn.QuantizedSwitchLinear(*(torch.cat([sh[m][i] for sh in shards]) for i in range(3)), shape["group_size"],
+                                        shape["bits"]) for m in range(3)]
+    del shards
+    block = pkg.nn.MoeBlock(wr, pkg.nn.SwitchGlu(*lin), k, cfg["norm_topk_prob"], cfg["router_mode"], bias)
+    T = x.shape[0]
+    g = torch.Generator().manual_seed(seed + 77)
+    rows = torch.randperm(T, generator=g)[:min(n_sample, T)].sort().values.to(dev)
+    ref, aux = block.forward(x[rows].contiguous(), return_aux=True)
+    torch.cuda.synchronize()
+    same_routing = bool(torch.equal(aux["indices"], idx_ep[rows]))
+    ref32, got = aux["out_f32"], y_ep[rows].float()
+    rms = float(ref32.double().pow(2).mean().sqrt())
+    d = (got - ref32).abs()
+    ok = same_routing and bool((d <= 2e-2 * rms + 2.0 ** -7 * ref32.abs()).all())
+    del block, lin
+    torch.cuda.empty_cache()
+    return float(d.max()) / max(rms, 1e-30), ok
+
+
+def bench_main(args, pkg, shape, cfg, peaks, metric, unit, workload_name, clock_sampler, zipf_bias):
     """bench.py for N > 1: weak scaling, `--tokens` tokens per GPU, experts sharded E/N per GPU.
-    Timing: barrier + synchronize, per-step CUDA events, max over ranks."""
+    Timing: barrier + synchronize, per-step CUDA events, max over ranks.  Before anything is timed one
+    step's output is checked against the single-GPU block on sampled tokens of every rank (`ep_parity`);
+    the run fails when that check does."""
     import json
     import os
     rank, world = dist.get_rank(), dist.get_world_size()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     dev = torch.device("cuda", local)
     H, I, E, k = shape["hidden"], shape["inter"], shape["n_experts"], shape["top_k"]
+    if E % world:
+        raise SystemExit(f"{E} experts do not divide over {world} GPUs")
     Eg = E // world
     T = args.tokens
     ctx = pkg.default_context()
     # identical router on every rank; each rank draws only its own experts (seeded by expert range)
     g = torch.Generator(device=dev).manual_seed(args.seed)
     wr = (torch.randn(E, H, generator=g, device=dev, dtype=torch.float32) * 0.02).bfloat16()
-    gl = torch.Generator(device=dev).manual_seed(args.seed + 1000 + rank)
-    lin = []
-    for r_, c_ in ((I, H), (I, H), (H, I)):
-        w = (torch.randn(Eg, r_, c_, generator=gl, device=dev, dtype=torch.float32) * 0.02).bfloat16()
-        lin.append(pkg.nn.QuantizedSwitchLinear.from_weight(w, shape["group_size"], shape["bits"]))
-        del w
+    bias = torch.tensor(zipf_bias(E), dtype=torch.float32, device=dev) if cfg["zipf"] else None
+    lin = [pkg.nn.QuantizedSwitchLinear(*t_, shape["group_size"], shape["bits"])
+           for t_ in _draw_shard(pkg, shape, args.seed, rank, Eg, dev)]
     mlp = pkg.nn.SwitchGlu(*lin)
     bufs = None
     if args.ep_transport in ("peer", "peer_push"):
-        # every rank can at worst receive every assignment of every rank; 2x the balanced load is
-        # what this benchmark's random routing needs, and what a deployment would size by policy
+        # every rank can at worst receive every assignment of every rank; 2x the balanced load is what uniform
+        # random routing needs; skewed routing (one expert per GPU owning 43 % of all rows) needs the worst case
         C_ = args.ep_chunks or 1
-        bufs = [PeerBuffers(pkg, H, min(T * k * world, 2 * T * k + 4096) // C_ + 64) for _ in range(C_)]
-        ep = PeerExpertParallelMoe(pkg, wr, mlp, E, k, bufs, fused_return=(args.ep_transport == "peer_push"))
+        cap = T * k * world if cfg["zipf"] else min(T * k * world, 2 * T * k + 4096)
+        bufs = [PeerBuffers(pkg, H, cap // C_ + 64) for _ in range(C_)]
+        ep = PeerExpertParallelMoe(pkg, wr, mlp, E, k, bufs, norm_topk_prob=cfg["norm_topk_prob"],
+                                   router_mode=cfg["router_mode"], router_logit_bias=bias,
+                                   fused_return=(args.ep_transport == "peer_push"))
     else:
-        ep = ExpertParallelMoe(B200Backend(pkg, wr, mlp, k), E, k)
+        ep = ExpertParallelMoe(B200Backend(pkg, wr, mlp, k, cfg["norm_topk_prob"], cfg["router_mode"], bias), E, k)
     gx = torch.Generator(device=dev).manual_seed(args.seed + 2000 + rank)
     x = torch.randn(T, H, generator=gx, device=dev, dtype=torch.float32).bfloat16()
+    y0 = ep.forward(x).clone()
+    ctx.check()
+    par_rel, par_ok = ep_parity(pkg, shape, cfg, args.seed, world, wr, bias, x, y0, ep.last["idx"])
+    par = torch.tensor([par_rel, 0.0 if par_ok else 1.0], device=dev)
+    dist.all_reduce(par, op=dist.ReduceOp.MAX)
+    parity = dict(max_rel=par[0].item(), ok=par[1].item() == 0.0, sampled_tokens_per_rank=min(32, T),
+                  against="the single-GPU block on the same tokens with all experts rebuilt on every rank")
+    del y0
     flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
 
     def timed(fn, steps, warmup):
@@ -437,6 +491,7 @@ def bench_main(args, pkg, shape, peaks, metric, unit, workload_name, clock_sampl
                     warmup=args.warmup, ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None,
                     dtype="bf16", data="synthetic",
                     config=dict(workload=workload_name(T) + f" per GPU, {Eg} experts per GPU", tokens_per_gpu=T,
+                                router_mode=cfg["router_mode"], norm_topk_prob=cfg["norm_topk_prob"], zipf_skew=cfg["zipf"],
                                 l2="flushed between iterations (512 MB overwrite)",
                                 parallelism=f"ep{world} (" + (("dispatch kernel + return fused into the down projection"
                                                                if args.ep_transport == "peer_push" else
@@ -451,7 +506,7 @@ def bench_main(args, pkg, shape, peaks, metric, unit, workload_name, clock_sampl
                     cpu_baseline=None,
                     e2e=dict(value=total / (e2e_ms * 1e-3), unit=unit, h2d_bytes_per_step=xh.numel() * 2 * world,
                              d2h_bytes_per_step=oh.numel() * 2 * world),
-                    gpu_launches=launches, clocks=clk.summary(), phase_ms=phases,
+                    gpu_launches=launches, clocks=clk.summary(), phase_ms=phases, ep_parity=parity,
                     exchange=dict(rows_sent_off_rank_per_step=sent.item(), bytes_each_way=sent.item() * H * 2))
         print(json.dumps(line))
     ctx.check()
@@ -459,3 +514,5 @@ def bench_main(args, pkg, shape, peaks, metric, unit, workload_name, clock_sampl
         b.close()
     dist.barrier()
     dist.destroy_process_group()
+    if not parity["ok"]:
+        raise SystemExit("expert-parallel output differs from the single-GPU block: " + json.dumps(parity))

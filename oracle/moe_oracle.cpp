@@ -80,6 +80,31 @@ struct ValIdx {
 
 }  // namespace
 
+// dense row-major helper: out[M,N] = a[M,K] . b[N,K]^T with float32 accumulation.
+// Every dot product is summed the same way whatever the blocking: eight interleaved partial sums
+// over k (lane j takes k = j mod 8), combined pairwise at the end, then the tail of K.  A block
+// of MB rows of a against NB rows of b shares the loads (register blocking); results are
+// bit-identical to one dot product at a time.
+template <int MB, int NB>
+static inline void dot_block(const float* a, const float* b, int64_t K, int64_t lda, int64_t ldb, float* out, int64_t ldo) {
+  float acc[MB][NB][8];
+  for (int i = 0; i < MB; ++i)
+    for (int j = 0; j < NB; ++j)
+      for (int l = 0; l < 8; ++l) acc[i][j][l] = 0.f;
+  int64_t k = 0;
+  for (; k + 8 <= K; k += 8)
+    for (int i = 0; i < MB; ++i)
+      for (int j = 0; j < NB; ++j)
+        for (int l = 0; l < 8; ++l) acc[i][j][l] += a[i * lda + k + l] * b[j * ldb + k + l];
+  for (int i = 0; i < MB; ++i)
+    for (int j = 0; j < NB; ++j) {
+      const float* c = acc[i][j];
+      float s = ((c[0] + c[1]) + (c[2] + c[3])) + ((c[4] + c[5]) + (c[6] + c[7]));
+      for (int64_t kk = k; kk < K; ++kk) s += a[i * lda + kk] * b[j * ldb + kk];
+      out[i * ldo + j] = s;
+    }
+}
+
 extern "C" {
 
 int orc_num_threads() {
@@ -171,27 +196,38 @@ int orc_dequantize(const uint32_t* wq, const float* scales, const float* biases,
   const int64_t G = K / gs, Wp = K / epw;
 #pragma omp parallel for schedule(static)
   for (int64_t r = 0; r < rows; ++r)
-    for (int64_t k = 0; k < K; ++k) {
-      uint32_t q = (wq[r * Wp + k / epw] >> (bits * (k % epw))) & mask;
-      out[r * K + k] = scales[r * G + k / gs] * static_cast<float>(q) + biases[r * G + k / gs];
+    for (int64_t g = 0; g < G; ++g) {
+      const float s = scales[r * G + g], b = biases[r * G + g];
+      const uint32_t* pw = wq + r * Wp + g * (gs / epw);
+      float* po = out + r * K + g * gs;
+      for (int w = 0; w < gs / epw; ++w) {
+        const uint32_t word = pw[w];
+        for (int j = 0; j < epw; ++j) po[w * epw + j] = s * static_cast<float>((word >> (bits * j)) & mask) + b;
+      }
     }
   return 0;
 }
 
-// dense row-major helper: out[M,N] = a[M,K] . b[N,K]^T with float32 accumulation
 static void matmul_nt(const float* a, const float* b, int64_t M, int64_t N, int64_t K, float* out) {
+  const int64_t mb = (M + 3) / 4, nb = (N + 1) / 2;
 #pragma omp parallel for schedule(static) collapse(2)
-  for (int64_t m = 0; m < M; ++m)
-    for (int64_t n = 0; n < N; ++n) {
+  for (int64_t bm = 0; bm < mb; ++bm)
+    for (int64_t bn = 0; bn < nb; ++bn) {
+      const int64_t m = bm * 4, n = bn * 2;
+      const int mr = static_cast<int>(std::min<int64_t>(4, M - m)), nr = static_cast<int>(std::min<int64_t>(2, N - n));
       const float* pa = a + m * K;
       const float* pb = b + n * K;
-      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      int64_t k = 0;
-      for (; k + 8 <= K; k += 8)
-        for (int j = 0; j < 8; ++j) acc[j] += pa[k + j] * pb[k + j];
-      float s = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
-      for (; k < K; ++k) s += pa[k] * pb[k];
-      out[m * N + n] = s;
+      float* po = out + m * N + n;
+      switch (mr * 2 + (nr - 1)) {
+        case 2: dot_block<1, 1>(pa, pb, K, K, K, po, N); break;
+        case 3: dot_block<1, 2>(pa, pb, K, K, K, po, N); break;
+        case 4: dot_block<2, 1>(pa, pb, K, K, K, po, N); break;
+        case 5: dot_block<2, 2>(pa, pb, K, K, K, po, N); break;
+        case 6: dot_block<3, 1>(pa, pb, K, K, K, po, N); break;
+        case 7: dot_block<3, 2>(pa, pb, K, K, K, po, N); break;
+        case 8: dot_block<4, 1>(pa, pb, K, K, K, po, N); break;
+        default: dot_block<4, 2>(pa, pb, K, K, K, po, N); break;
+      }
     }
 }
 

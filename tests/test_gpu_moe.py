@@ -78,20 +78,6 @@ def test_decode_sweep_first_generation_kernel(pkg, O, config0, T):
         ctx.set_qmm_path(ctx.QMM_AUTO)
 
 
-@pytest.mark.parametrize("T", [1, 4, 16, 64])
-def test_decode_sweep_tensor_memory_kernel(pkg, O, config0, T):
-    # the tcgen05 kernel of the memory-bound regime: per-group accumulators in tensor memory
-    ctx = pkg.default_context()
-    ctx.set_qmm_path(ctx.QMM_TMEM)
-    try:
-        blk = dict(config0)
-        blk["x"] = config0["x"][:T].copy()
-        blk["T"] = T
-        check_block(pkg, O, blk)
-    finally:
-        ctx.set_qmm_path(ctx.QMM_AUTO)
-
-
 @pytest.mark.parametrize("T", [1, 4, 16])
 def test_decode_sweep(pkg, O, config0, T):
     # BASELINE.json configs[1], decode points (64 is test_config0_block): same weights, fewer tokens
@@ -101,12 +87,11 @@ def test_decode_sweep(pkg, O, config0, T):
     check_block(pkg, O, blk)
 
 
-@pytest.fixture(params=["small", "stream", "tensor_core", "tmem"])
+@pytest.fixture(params=["small", "tensor_core"])
 def qmm_path(request, pkg):
-    """Runs a test once per grouped-product kernel (register-load mma.sync / TMA-streamed mma.sync / tcgen05)
-    and restores AUTO."""
+    """Runs a test once per grouped-product kernel (register-load mma.sync / tcgen05) and restores AUTO."""
     ctx = pkg.default_context()
-    ctx.set_qmm_path(dict(small=ctx.QMM_SMALL, stream=ctx.QMM_STREAM, tensor_core=ctx.QMM_TENSOR_CORE, tmem=ctx.QMM_TMEM)[request.param])
+    ctx.set_qmm_path(dict(small=ctx.QMM_SMALL, tensor_core=ctx.QMM_TENSOR_CORE)[request.param])
     yield request.param
     ctx.set_qmm_path(ctx.QMM_AUTO)
 
@@ -282,6 +267,72 @@ def test_full_size_block_properties(pkg, O, config0):
     err = float(np.abs(got32[sample] - ref["out_f32"]).max() / rms)
     print(f"[parity] full size T={T}: max|d|/rms over 96 sampled tokens = {err:.4f}")
     assert err <= TOL
+
+
+def _gpu_block(pkg, H, E, I, k, bits, seed, mode, renorm, zipf):
+    """A full-size block whose weights are drawn and quantized on the GPU (the CUDA quantizer is bit-exact
+    with the oracle's, tests/test_gpu_ops.py), plus the same packed weights as numpy for the oracle."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    lin, host = [], []
+    for r, c in ((I, H), (I, H), (H, I)):
+        parts = []
+        for e0 in range(0, E, 16):
+            w = (torch.randn(min(16, E - e0), r, c, generator=g, device="cuda", dtype=torch.float32) * 0.02).bfloat16()
+            parts.append(pkg.ops.quantize(w, 64, bits))
+            del w
+        wq, sc, bi = (torch.cat([p_[i] for p_ in parts]) for i in range(3))
+        lin.append(pkg.nn.QuantizedSwitchLinear(wq, sc, bi, 64, bits))
+        host.append((wq.cpu().numpy().view(np.uint32), sc.float().cpu().numpy(), bi.float().cpu().numpy()))
+    wr = (torch.randn(E, H, generator=g, device="cuda", dtype=torch.float32) * 0.02).bfloat16()
+    bias = (-2.4 * np.log(np.arange(1, E + 1))).astype(np.float32) if zipf else None
+    block = pkg.nn.MoeBlock(wr, pkg.nn.SwitchGlu(*lin), k, renorm, mode, torch.from_numpy(bias).cuda() if zipf else None)
+    return block, wr.float().cpu().numpy(), host, bias
+
+
+def _full_size_properties(pkg, O, T, H, E, I, k, bits, mode, renorm, zipf, seed, n_sample=64):
+    """The size-independent properties of test_full_size_block_properties for any layer shape."""
+    block, wr, host, bias = _gpu_block(pkg, H, E, I, k, bits, seed, mode, renorm, zipf)
+    g = torch.Generator().manual_seed(seed + 1)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    out, aux = block.forward(x.cuda(), return_aux=True)
+    pkg.default_context().check()
+    xn = x.float().numpy()
+    ridx, rsc = O.router(xn, wr, k, mode, renorm, bias)
+    idx = u32(aux["indices"])
+    assert np.array_equal(idx, ridx), "top-k indices of all tokens"
+    assert np.array_equal(aux["scores"].float().cpu().numpy(), rsc), "scores of all tokens"
+    flat = idx.reshape(-1)
+    perm = u32(aux["perm"])
+    assert np.array_equal(perm, np.argsort(flat, kind="stable").astype(np.uint32))
+    assert np.array_equal(u32(aux["inv_perm"])[perm], np.arange(T * k, dtype=np.uint32))
+    counts = np.bincount(flat, minlength=E).astype(np.uint32)
+    assert np.array_equal(u32(aux["counts"]), counts)
+    assert np.array_equal(u32(aux["offsets"]), np.concatenate([[0], np.cumsum(counts)]).astype(np.uint32))
+    got32 = aux["out_f32"].cpu().numpy()
+    assert np.array_equal(out.float().cpu().numpy(), O.round_bf16(got32))
+    sample = np.sort(np.random.default_rng(3).choice(T, size=n_sample, replace=False))
+    ref = O.moe_block(xn[sample], wr, host[0], host[1], host[2], k, mode, renorm, bias, 64, bits)
+    assert np.array_equal(ref["idx"], idx[sample])
+    rms = np.sqrt((ref["out_f32"].astype(np.float64) ** 2).mean())
+    err = float(np.abs(got32[sample] - ref["out_f32"]).max() / rms)
+    print(f"[parity] full size T={T} H={H} E={E} I={I} k={k} bits={bits}: max|d|/rms over {n_sample} sampled tokens = "
+          f"{err:.4f}; largest expert share {counts.max() / counts.sum():.3f}")
+    assert err <= TOL
+    return counts
+
+
+def test_full_size_config3(pkg, O):
+    """BASELINE.json configs[3] at full size: Qwen3-235B-A22B layer (hidden 4096, 128 experts, top-8
+    renormalised, inter 1536, 4-bit), 8192 tokens."""
+    _full_size_properties(pkg, O, 8192, 4096, 128, 1536, 8, 4, 0, True, False, seed=303)
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_full_size_config4(pkg, O, bits):
+    """BASELINE.json configs[4] at full size: Mixtral layer (hidden 4096, 8 experts, top-2 with softmax over
+    the selected logits, inter 14336), 16384 tokens, Zipf(1.2)-skewed routing, 4- and 8-bit."""
+    counts = _full_size_properties(pkg, O, 16384, 4096, 8, 14336, 2, bits, 1, False, True, seed=404 + bits)
+    assert counts.max() > 3 * counts.min()     # the skew is real: the first expert owns several times the last one's rows
 
 
 @pytest.mark.parametrize("T", [5, 700])

@@ -121,6 +121,13 @@ def test_gather_qmm_switch_linear_shape(pkg, O):
     with pytest.raises(pkg.B200Error):
         pkg.default_context().check()
     pkg.default_context().check()       # the status word is cleared once reported
+    # out-of-range batch index of x: reported the same way (the read is redirected, never out of bounds)
+    xb = bf16_cuda(x[:4])
+    lhs = np.array([0, 3, 9, 1], np.uint32)     # x has 4 batch entries
+    pkg.ops.gather_qmm(xb, np_i32(wq), bf16_cuda(s), bf16_cuda(b), np_i32(lhs), np_i32(rhs[:4]))
+    with pytest.raises(pkg.B200Error):
+        pkg.default_context().check()
+    pkg.default_context().check()
 
 
 @pytest.mark.parametrize("cols", [8, 128, 200, 256])
