@@ -522,14 +522,20 @@ def main():
                 r, _ = point(Tp, max(5, min(args.steps, 10)), 3, True)
             gu = r["gate_up"]
             decode = Tp < decode_below
+            fused = r["launches_per_step"] == 1      # a whole block in one launch would have no per-stage split
             sweep.append(dict(tokens=Tp, tokens_per_s=r["tokens_per_s"], ms=r["ms_per_step"], cuda_graph=r["cuda_graph"],
-                              active_experts=r["active_experts"], launches=r["launches_per_step"],
+                              active_experts=r["active_experts"], launches=r["launches_per_step"], single_launch=fused,
                               block_frac_hbm=r["block_gbs"] / peaks["hbm"], block_frac_tensor=r["block_tflops"] / peaks["tensor"],
-                              gate_up_ms=gu["ms"], gate_up_frac=(gu["gbs"] / peaks["hbm"]) if decode else (gu["tflops"] / peaks["tensor"]),
-                              bound="hbm" if decode else "tensor", stage_ms=r["stage_ms"]))
+                              gate_up_ms=None if fused else gu["ms"],
+                              gate_up_frac=None if fused else ((gu["gbs"] / peaks["hbm"]) if decode else (gu["tflops"] / peaks["tensor"])),
+                              bound="hbm" if decode else "tensor", stage_ms=None if fused else r["stage_ms"]))
 
     gu = main_res["gate_up"]
-    if T < decode_below:
+    if main_res["launches_per_step"] == 1:     # single-launch block: the dominant kernel is the whole step
+        roof = dict(bound="hbm", achieved=main_res["block_gbs"], peak=peaks["hbm"], unit="GB/s",
+                    frac=main_res["block_gbs"] / peaks["hbm"], block_frac=main_res["block_gbs"] / peaks["hbm"])
+        gu = dict(ms=main_res["ms_per_step"], bytes=main_res["block_bytes"], flops=main_res["block_flops"])
+    elif T < decode_below:
         roof = dict(bound="hbm", achieved=gu["gbs"], peak=peaks["hbm"], unit="GB/s", frac=gu["gbs"] / peaks["hbm"],
                     block_frac=main_res["block_gbs"] / peaks["hbm"])
     else:
@@ -539,7 +545,8 @@ def main():
     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size, from the ncu
     # capture summarised under profiles/ (a profiler cannot run inside the timed bench)
     tr = traffic_table().get((args.config_id, T, bits, "gate_up"))
-    roof.update(kernel="gate+up grouped quantized GEMM (dominant)", peak_source=peaks["source"],
+    roof.update(kernel="whole block, one launch" if main_res["launches_per_step"] == 1 else "gate+up grouped quantized GEMM (dominant)",
+                peak_source=peaks["source"],
                 traffic=(tr["dram_bytes_per_launch"] if tr else None), traffic_source=(tr["profile"] if tr else None),
                 kernel_ms=gu["ms"], algorithmic_bytes=gu["bytes"], algorithmic_flops=gu["flops"])
 

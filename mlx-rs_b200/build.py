@@ -36,6 +36,8 @@ def build(force=False, verbose=False):
     flags = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-ccbin", "/usr/bin/g++"] + ARCH
     if verbose:
         flags += ["-Xptxas", "-v"]
+    if os.environ.get("B200_DEV"):      # development build: self-timing and debug switches compiled in
+        flags += ["-DB200_DEV"]
 
     def one(src):
         obj = os.path.join(OBJ, src.replace(".cu", ".o"))

@@ -121,6 +121,9 @@ static int check_cfg(const b200_moe_config* cfg) {
 
 static inline int permute_launches(int64_t n) { return n <= 1024 ? 1 : 3; }
 constexpr int kTicketWord = 8;  // word of the status block that the fused small-batch router uses as its ticket counter
+// Status block of a context: word 0 = device-side status, word 8 = ticket of the fused router, words 16..63 =
+// self-timing of development builds.
+constexpr size_t kStatusBytes = 1024;
 
 extern "C" {
 
@@ -145,7 +148,8 @@ int b200_ctx_create(b200_ctx** out, int device) {
   B200_REQUIRE(prop.major == 10, "this library contains sm_100a code only; a Blackwell B200 is required");
   b200_ctx* c = new b200_ctx();
   c->device = device;
-  if (cudaMalloc(reinterpret_cast<void**>(&c->err), 256) != cudaSuccess || cudaMemset(c->err, 0, 256) != cudaSuccess) {
+  if (cudaMalloc(reinterpret_cast<void**>(&c->err), kStatusBytes) != cudaSuccess ||
+      cudaMemset(c->err, 0, kStatusBytes) != cudaSuccess) {
     delete c;
     B200_FAIL("cannot allocate the status word");
   }
@@ -186,6 +190,8 @@ int b200_ctx_check(b200_ctx* c, void* stream) {
   B200_CUDA(cudaMemcpy(&h, c->err, sizeof(int), cudaMemcpyDeviceToHost));
   if (h != 0) {
     B200_CUDA(cudaMemset(c->err, 0, sizeof(int)));
+    // a kernel that gave up waiting may have left its ticket half-way
+    if (h == 3) B200_CUDA(cudaMemset(c->err + kTicketWord, 0, kStatusBytes - sizeof(int) * kTicketWord));
     B200_FAIL(h == 2   ? "an expert index was out of range"
               : h == 3 ? "a kernel gave up waiting on its own pipeline (2 s limit)"
               : h == 5 ? "a rank would receive more rows than its exchange buffers hold"
@@ -265,11 +271,19 @@ int b200_dequantize(b200_ctx* c, const uint32_t* wq, const void* scales, const v
   return 0;
 }
 
-// Shared by quantized_matmul, gather_qmm and the block: run one grouped product.
-static int run_grouped(b200_ctx* c, GroupedArgs& a, int nmat, int bits, int max_active, int64_t rows, cudaStream_t st) {
+// Shared by quantized_matmul and gather_qmm: one grouped product over bf16 source rows x [src_rows, K]
+// with the register kernel.  The rows are first prepared (fp16, row-scaled, unpack order) into scratch.
+static int run_grouped(b200_ctx* c, GroupedArgs& a, int nmat, int bits, int max_active, int64_t rows, const void* x,
+                       int64_t src_rows, cudaStream_t st) {
   if (rows == 0) return 0;
+  void* xs = c->take(sizeof(uint16_t) * src_rows * a.K);
+  float* rs = static_cast<float*>(c->take(sizeof(float) * src_rows));
+  B200_REQUIRE(xs && rs, "scratch arena too small");
+  if (launch_prepare_rows_small(x, 0, src_rows, a.K, bits, xs, rs, st)) return 1;
+  a.x = xs;
+  a.x_rowscale = rs;
   if (launch_grouped_qmm_small(a, nmat, bits, max_active, rows, st)) return 1;
-  LAUNCHED(c, 1);
+  LAUNCHED(c, 2);
   return 0;
 }
 
@@ -290,12 +304,12 @@ int b200_quantized_matmul(b200_ctx* c, const void* x, const uint32_t* w, const v
     return 0;
   }
   B200_REQUIRE(K % gs == 0, "K must be a multiple of group_size");
-  if (ctx_grow(c, 4096)) return 1;
+  B200_REQUIRE(small_shape_ok((int)K), "K too large");
+  if (ctx_grow(c, 4096 + al(sizeof(uint16_t) * M * K) + al(sizeof(float) * M))) return 1;
   uint32_t* seg = static_cast<uint32_t*>(c->take(64));
   launch_dense_segments(seg + 0, seg + 4, seg + 8, seg + 12, (uint32_t)M, st);
   LAUNCHED(c, 1);
   GroupedArgs a{};
-  a.x = x;
   a.w[0] = w;
   a.scales[0] = scales;
   a.biases[0] = biases;
@@ -308,7 +322,7 @@ int b200_quantized_matmul(b200_ctx* c, const void* x, const uint32_t* w, const v
   a.K = (int)K;
   a.N = (int)N;
   a.n_experts = 1;
-  return run_grouped(c, a, 1, bits, 1, M, st);
+  return run_grouped(c, a, 1, bits, 1, M, x, M, st);
 }
 
 int b200_gather_qmm(b200_ctx* c, const void* x, const uint32_t* w, const void* scales, const void* biases,
@@ -330,8 +344,10 @@ int b200_gather_qmm(b200_ctx* c, const void* x, const uint32_t* w, const void* s
   B200_REQUIRE(x && w && scales && out, "null tensor");
   const int64_t n = n_idx * M;
   B200_REQUIRE(n < (int64_t(1) << 31), "too many rows");
+  B200_REQUIRE(small_shape_ok((int)K), "K too large");
   size_t need = al(sizeof(uint32_t) * n) * 4 + al(sizeof(uint32_t) * (E + 1)) * 3 + al(16) +
-                al(sizeof(uint32_t) * permute_scratch_words(n, (int)E)) + 4096;
+                al(sizeof(uint32_t) * permute_scratch_words(n, (int)E)) + al(sizeof(uint16_t) * Bx * M * K) +
+                al(sizeof(float) * Bx * M) + 4096;
   if (ctx_grow(c, need)) return 1;
   uint32_t* flat_e = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
   uint32_t* flat_s = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
@@ -346,7 +362,6 @@ int b200_gather_qmm(b200_ctx* c, const void* x, const uint32_t* w, const void* s
   launch_permute(flat_e, n, (int)E, perm, inv, counts, offsets, active, n_active, chunk, c->err, st);
   LAUNCHED(c, 1 + permute_launches(n));
   GroupedArgs a{};
-  a.x = x;
   a.w[0] = w;
   a.scales[0] = scales;
   a.biases[0] = biases;
@@ -361,7 +376,7 @@ int b200_gather_qmm(b200_ctx* c, const void* x, const uint32_t* w, const void* s
   a.K = (int)K;
   a.N = (int)N;
   a.n_experts = (int)E;
-  return run_grouped(c, a, 1, bits, (int)(E < n ? E : n), n, st);
+  return run_grouped(c, a, 1, bits, (int)(E < n ? E : n), n, x, Bx * M, st);
 }
 
 int b200_gather_mm(b200_ctx* c, const void* a, const void* b, const uint32_t* lhs_indices, const uint32_t* rhs_indices,
@@ -502,13 +517,13 @@ static bool use_tensor_core_path(const b200_ctx* c, const b200_moe_config& cfg, 
   // the memory-bound kernels stage eight activation rows of length K in shared memory; beyond
   // that (e.g. the 14336-wide down projection of a Mixtral-shaped layer) only the tensor-core
   // kernel, which streams activations by TMA, applies
-  const int kmax = cfg.hidden > cfg.inter ? cfg.hidden : cfg.inter;
-  if ((size_t)8 * (2 * kmax + 16) + sizeof(float) * (kmax / 64) * 8 > 220 * 1024) return true;
+  if (!small_shape_ok(cfg.hidden) || !small_shape_ok(cfg.inter)) return true;
   if (c->qmm_path == B200_QMM_SMALL) return false;
   if (c->qmm_path == B200_QMM_TENSOR_CORE) return true;
-  // measured crossover on the Qwen3-30B-A3B shape: 8 rows per expert 257 us (register kernel) against 336 us,
-  // 12 rows per expert 377 us against 351 us
-  return n / (max_active > 0 ? max_active : 1) >= 10;
+  // measured crossover (whole block, register kernel against tensor-core kernel): Qwen3-30B-A3B layer 12 rows per
+  // expert 0.32 ms against 0.35 ms, 16 rows 0.37 against 0.34; Qwen3-235B-A22B layer 12 rows 1.01 against 1.10 ms,
+  // 16 rows 1.23 against 1.08
+  return n / (max_active > 0 ? max_active : 1) >= 14;
 }
 
 // Gate/up and down products over rows that are grouped by expert (offsets/active/n_active describe
@@ -629,8 +644,19 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
       return 1;
     LAUNCHED(c, 2);
   } else {
+    // register kernel: the source rows (the tokens when rows are gathered through perm, else the n rows
+    // themselves) are prepared once - fp16, row-scaled, unpack order - and every CTA copies what it needs
+    const int64_t src_rows = perm ? n / src_div : n;
+    void* xp = c->take(sizeof(uint16_t) * src_rows * cfg.hidden);
+    float* rp = static_cast<float*>(c->take(sizeof(float) * src_rows));
+    B200_REQUIRE(xp && rp, "scratch arena too small");
+    if (launch_prepare_rows_small(x, 0, src_rows, cfg.hidden, cfg.bits, xp, rp, st)) return 1;
     c->mark(4, st);
-    if (run_grouped(c, gu, 2, cfg.bits, max_active, n, st)) return 1;
+    gu.x = xp;
+    gu.x_rowscale = rp;
+    gu.out_f16 = 1;  // h in the prepared layout, ready for the down projection
+    if (launch_grouped_qmm_small(gu, 2, cfg.bits, max_active, n, st)) return 1;
+    LAUNCHED(c, 2);
   }
   c->mark(5, st);
 
@@ -666,13 +692,10 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
                                          false, c->err, st))
       return 1;
     LAUNCHED(c, 1);
-  } else if (out_row_addr) {  // per-row addresses: the register kernel (the streamed variant does not take them)
+  } else {
     c->mark(6, st);
     if (launch_grouped_qmm_small(dn, 1, cfg.bits, max_active, n, st)) return 1;
     LAUNCHED(c, 1);
-  } else {
-    c->mark(6, st);
-    if (run_grouped(c, dn, 1, cfg.bits, max_active, n, st)) return 1;
   }
   c->mark(7, st);
   return 0;

@@ -1,5 +1,7 @@
 // Internal launch interface between the C-ABI layer (api.cu) and the kernel files.
 #pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -10,7 +12,9 @@ enum { kOutBf16 = 0, kOutF32 = 1, kOutF16 = 2 };  // element format of a grouped
 
 // One grouped product over rows that are sorted by expert.
 struct GroupedArgs {
-  const void* x;              // bf16 source rows [*, K]
+  const void* x;              // source rows [*, K]: bf16 for the tensor-core path's own preparation; PREPARED fp16 rows
+                              // (launch_prepare_rows_small, or an out_f16 gate/up epilogue) for the register kernel
+  const float* x_rowscale;    // register kernel: power of two each prepared source row was divided by (null: 1)
   const uint32_t* w[2];       // packed weights [E, N, K*bits/32]   ([1] = second matrix when NMAT == 2)
   const void* scales[2];      // bf16 [E, N, K/64]
   const void* biases[2];      // bf16 [E, N, K/64]
@@ -27,7 +31,8 @@ struct GroupedArgs {
   const unsigned long long* out_row_addr;  // optional, by sorted position: address of the row's bf16 output
                                            // (overrides out/dst_perm; rows may live on peer GPUs)
   int out_f32;                // 1: float32 output (no rounding before the k-way combine)
-  int out_f16;                // 1: fp16 output with saturation (tensor-core kernel only; out_f32 wins when both are set)
+  int out_f16;                // 1: fp16 output with saturation, out_f32 wins when both are set.  Two-matrix products write h
+                              // in the A-operand layout of the same path's down projection (register kernel: prepared rows)
   int K, N;
   int n_experts;              // number of stacked weight matrices
 };
@@ -55,7 +60,11 @@ int launch_permute(const uint32_t* idx, int64_t n, int E, uint32_t* perm, uint32
                    cudaStream_t st);
 size_t permute_scratch_words(int64_t n, int E);
 
-// qmm_decode.cu
+// qmm_decode.cu (register kernel of the memory-bound regime)
+bool small_shape_ok(int K);
+// x [n_rows, K] bf16 (in_f16: fp16) -> prepared fp16 rows xs [n_rows, K] + row_scale [n_rows]
+int launch_prepare_rows_small(const void* x, int in_f16, int64_t n_rows, int K, int bits, void* xs, float* row_scale,
+                              cudaStream_t st);
 int launch_grouped_qmm_small(const GroupedArgs& a, int nmat, int bits, int max_active, int64_t rows, cudaStream_t st);
 
 // qmm_prefill.cu (tcgen05 path)
