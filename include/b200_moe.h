@@ -38,7 +38,7 @@ extern "C" {
 
 typedef struct b200_ctx b200_ctx;
 
-enum { B200_F32 = 0, B200_BF16 = 1 };
+enum { B200_F32 = 0, B200_BF16 = 1, B200_F16 = 2 };
 enum { B200_ROUTER_SOFTMAX_TOPK = 0, B200_ROUTER_TOPK_SOFTMAX = 1 };
 
 /* Stacked quantized projection of all experts: weight [E, out, in*bits/32] uint32,
@@ -132,11 +132,14 @@ int b200_dequantize(b200_ctx* ctx, const uint32_t* w_q, const void* scales, cons
                     int64_t K, int group_size, int bits, void* out, void* stream);
 
 /* quantized_matmul(x, w, scales, biases, transpose, group_size, bits);
- * mlx-rs/src/ops/quantization.rs:88-122.  x bf16 [M, K]; transpose != 0: w [N, K*bits/32]
- * and out = x . w_hat^T (the form every layer uses, mlx-rs/src/nn/quantized.rs:363-381);
- * transpose == 0: w [K, N*bits/32] and out = x . w_hat.  out bf16 [M, N]. */
+ * mlx-rs/src/ops/quantization.rs:88-122.  x [M, K]; transpose != 0: w [N, K*bits/32] and out = x . w_hat^T (the
+ * form every layer uses, mlx-rs/src/nn/quantized.rs:363-381); transpose == 0: w [K, N*bits/32] and out = x . w_hat.
+ * out [M, N].  `dtype` (B200_F32 / B200_BF16 / B200_F16) is the type of x, scales, biases and out alike (MLX keeps
+ * the scales in the type of the weights they came from).  bfloat16 with transpose != 0, group_size 64 and 4 or 8
+ * bits runs on the tensor cores; every other combination (float32 - the reference's own tests, `:319-342` -
+ * float16, transpose == 0, group sizes 32 / 128, 2 bits) takes an exact float32 CUDA-core kernel. */
 int b200_quantized_matmul(b200_ctx* ctx, const void* x, const uint32_t* w, const void* scales, const void* biases,
-                          int transpose, int group_size, int bits, int64_t M, int64_t K, int64_t N, void* out,
+                          int transpose, int group_size, int bits, int dtype, int64_t M, int64_t K, int64_t N, void* out,
                           void* stream);
 
 /* gather_mm(a, b, lhs_indices, rhs_indices); mlx-rs/src/ops/arithmetic.rs:1568-1632 (un-quantised).
@@ -147,13 +150,15 @@ int b200_gather_mm(b200_ctx* ctx, const void* a, const void* b, const uint32_t* 
 
 /* gather_qmm(x, w, scales, biases, lhs_indices, rhs_indices, transpose, group_size, bits,
  * sorted_indices); mlx-rs/src/ops/quantization.rs:160-230.
- * out[i] = x[lhs[i]] . dequantize(w[rhs[i]])^T with x bf16 [Bx, M, K], w [E, N, K*bits/32],
- * out bf16 [n_idx, M, N].  lhs_indices may be NULL (lhs[i] = i).  transpose must be non-zero.
- * `sorted_indices` is accepted for signature parity; rows are always grouped internally. */
+ * out[i] = x[lhs[i]] . dequantize(w[rhs[i]])^T (transpose != 0; w [E, N, K*bits/32]) or x[lhs[i]] . dequantize(w[rhs[i]])
+ * (transpose == 0; w [E, K, N*bits/32]) with x [Bx, M, K], out [n_idx, M, N].  lhs_indices may be NULL (lhs[i] = i).
+ * `dtype` and the fast / exact split as for b200_quantized_matmul (the fast form also needs E <= 256): few rows
+ * per matrix run the register kernel, many the tcgen05 kernel.  `sorted_indices` is accepted for signature parity;
+ * rows are always grouped internally.  Index values out of range are reported by b200_ctx_check. */
 int b200_gather_qmm(b200_ctx* ctx, const void* x, const uint32_t* w, const void* scales, const void* biases,
                     const uint32_t* lhs_indices, const uint32_t* rhs_indices, int transpose, int group_size, int bits,
-                    int sorted_indices, int64_t Bx, int64_t M, int64_t K, int64_t E, int64_t N, int64_t n_idx, void* out,
-                    void* stream);
+                    int sorted_indices, int dtype, int64_t Bx, int64_t M, int64_t K, int64_t E, int64_t N, int64_t n_idx,
+                    void* out, void* stream);
 
 /* softmax_axis(a, -1, precise); mlx-rs/src/ops/arithmetic.rs:1312-1327.  bf16 [rows, cols],
  * cols <= 256.  Always the precise form: exact softmax, correctly rounded to bf16. */
@@ -175,6 +180,19 @@ int b200_take_along_axis(b200_ctx* ctx, const void* a, int64_t rows, int64_t col
  * x [x_rows, cols], indices [n_rows], cols a multiple of 8. */
 int b200_take_rows(b200_ctx* ctx, const void* x, const uint32_t* indices, uint32_t div, int64_t n_rows, int64_t x_rows,
                    int64_t cols, void* out, void* stream);
+/* take_axis(x, indices, 0); mlx-rs/src/ops/indexing/mod.rs:374-401, 641-660: b200_take_rows without the division. */
+int b200_take_axis(b200_ctx* ctx, const void* x, const uint32_t* indices, int64_t n_rows, int64_t x_rows, int64_t cols,
+                   void* out, void* stream);
+
+/* argsort_axis(a, -1) for rows of small unsigned keys (expert indices); mlx-rs/src/ops/sort.rs:57-83.
+ * keys uint32 [rows, cols], every key < key_bound <= 256 -> out uint32 [rows, cols], the STABLE ascending order of
+ * each row (the order the token -> expert sort uses).  Keys >= key_bound are reported by b200_ctx_check. */
+int b200_argsort_axis(b200_ctx* ctx, const uint32_t* keys, int64_t rows, int64_t cols, int key_bound, uint32_t* out,
+                      void* stream);
+
+/* topk_axis(a, k, -1); mlx-rs/src/ops/indexing/mod.rs:674-700.  bf16 [rows, cols], cols <= 256 -> out bf16 [rows, k]:
+ * the k largest values of each row, ascending (MLX leaves their order unspecified). */
+int b200_topk_axis(b200_ctx* ctx, const void* a, int64_t rows, int64_t cols, int k, void* out, void* stream);
 
 /* fast::rms_norm(x, weight, eps); mlx-rs/src/fast.rs:178-205.  bf16 [rows, cols]; weight
  * bf16 [cols] or NULL for ones. */

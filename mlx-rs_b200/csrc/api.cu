@@ -120,6 +120,8 @@ static int check_cfg(const b200_moe_config* cfg) {
   } while (0)
 
 static inline int permute_launches(int64_t n) { return n <= 1024 ? 1 : 3; }
+// rows per expert (average over the experts that can be active) from which the tensor-core kernel is used
+constexpr int64_t kTensorCoreRowsPerExpert = 14;
 constexpr int kTicketWord = 8;  // word of the status block that the fused small-batch router uses as its ticket counter
 // Status block of a context: word 0 = device-side status, word 8 = ticket of the fused router, words 16..63 =
 // self-timing of development builds.
@@ -271,41 +273,83 @@ int b200_dequantize(b200_ctx* c, const uint32_t* wq, const void* scales, const v
   return 0;
 }
 
-// Shared by quantized_matmul and gather_qmm: one grouped product over bf16 source rows x [src_rows, K]
-// with the register kernel.  The rows are first prepared (fp16, row-scaled, unpack order) into scratch.
-static int run_grouped(b200_ctx* c, GroupedArgs& a, int nmat, int bits, int max_active, int64_t rows, const void* x,
-                       int64_t src_rows, cudaStream_t st) {
-  if (rows == 0) return 0;
+// Shared by quantized_matmul and gather_qmm (bf16, transpose = true, group 64, 4 or 8 bits): one grouped product
+// of n sorted rows over bf16 source rows x [src_rows, K].  Few rows per weight matrix: the register kernel on
+// prepared rows; many: the tcgen05 kernel on gathered fp16 rows (same rule as the routed block).
+static bool grouped_wants_tensor_cores(const b200_ctx* c, int K, int N, int64_t n, int max_active) {
+  if (!prefill_shape_ok(K, N, 1)) return false;
+  if (!small_shape_ok(K) || c->qmm_path == B200_QMM_TENSOR_CORE) return true;
+  if (c->qmm_path == B200_QMM_SMALL) return false;
+  return n / (max_active > 0 ? max_active : 1) >= kTensorCoreRowsPerExpert;
+}
+static size_t grouped_scratch_bytes(int64_t n, int64_t src_rows, int64_t K, int64_t E) {
+  const int64_t r = n > src_rows ? n : src_rows;
+  return al(sizeof(uint16_t) * r * K) + al(sizeof(float) * r) + (al(sizeof(uint32_t) * prefill_tile_words(n, (int)E)) * 3 + al(16));
+}
+static int run_grouped(b200_ctx* c, GroupedArgs& a, int bits, int max_active, int64_t n, const void* x, int64_t src_rows,
+                       const uint32_t* counts, cudaStream_t st) {
+  if (n == 0) return 0;
+  const int E = a.n_experts;
+  if (grouped_wants_tensor_cores(c, a.K, a.N, n, max_active)) {
+    const size_t tw = prefill_tile_words(n, E);
+    uint32_t* tile_expert = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
+    uint32_t* tile_row0 = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
+    uint32_t* tile_rows = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
+    uint32_t* n_row_tiles = static_cast<uint32_t*>(c->take(16));
+    void* xs = c->take(sizeof(uint16_t) * n * a.K);
+    float* rs = static_cast<float*>(c->take(sizeof(float) * n));
+    B200_REQUIRE(tile_expert && tile_row0 && tile_rows && n_row_tiles && xs && rs, "scratch arena too small");
+    launch_build_row_tiles(counts, a.offsets, E, tile_expert, tile_row0, tile_rows, n_row_tiles, 256, st);
+    launch_prepare_rows(x, a.perm, a.src_map, 1, n, a.K, bits == 4, xs, rs, st);
+    if (launch_grouped_qmm_tc(xs, rs, n, a, 1, bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, false, c->err, st))
+      return 1;
+    LAUNCHED(c, 3);
+    return 0;
+  }
+  B200_REQUIRE(small_shape_ok(a.K), "K too large");
   void* xs = c->take(sizeof(uint16_t) * src_rows * a.K);
   float* rs = static_cast<float*>(c->take(sizeof(float) * src_rows));
   B200_REQUIRE(xs && rs, "scratch arena too small");
   if (launch_prepare_rows_small(x, 0, src_rows, a.K, bits, xs, rs, st)) return 1;
   a.x = xs;
   a.x_rowscale = rs;
-  if (launch_grouped_qmm_small(a, nmat, bits, max_active, rows, st)) return 1;
+  if (launch_grouped_qmm_small(a, 1, bits, max_active, n, st)) return 1;
   LAUNCHED(c, 2);
   return 0;
 }
 
+static int check_qmm_common(int gs, int bits, int dtype, int transpose, int64_t K, int64_t N) {
+  B200_REQUIRE(dtype == B200_F32 || dtype == B200_BF16 || dtype == B200_F16, "dtype must be float32, bfloat16 or float16");
+  B200_REQUIRE(bits == 2 || bits == 4 || bits == 8, "bits must be 2, 4 or 8");
+  B200_REQUIRE(gs == 32 || gs == 64 || gs == 128, "group_size must be 32, 64 or 128");
+  if (transpose)
+    B200_REQUIRE(K % gs == 0, "K must be a multiple of group_size");
+  else
+    B200_REQUIRE(N % gs == 0, "N must be a multiple of group_size when transpose is false");
+  return 0;
+}
+static bool fast_qmm_form(int gs, int bits, int dtype, int transpose) {
+  return dtype == B200_BF16 && transpose && gs == 64 && (bits == 4 || bits == 8);
+}
+
 int b200_quantized_matmul(b200_ctx* c, const void* x, const uint32_t* w, const void* scales, const void* biases,
-                          int transpose, int gs, int bits, int64_t M, int64_t K, int64_t N, void* out, void* stream) {
+                          int transpose, int gs, int bits, int dtype, int64_t M, int64_t K, int64_t N, void* out,
+                          void* stream) {
   CTX_ENTER(c);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  B200_REQUIRE(bits == 4 || bits == 8, "bits must be 4 or 8");
-  B200_REQUIRE(gs == 64, "group_size must be 64");
-  B200_REQUIRE(M >= 0 && K > 0 && N > 0, "bad shape");
+  B200_REQUIRE(M >= 0 && K > 0 && N > 0 && M < (int64_t(1) << 31), "bad shape");
+  if (check_qmm_common(gs, bits, dtype, transpose, K, N)) return 1;
   B200_REQUIRE(biases != nullptr, "biases are required in affine mode");
   B200_REQUIRE(M == 0 || (x && w && scales && out), "null tensor");
   if (M == 0) return 0;
-  if (!transpose) {
-    B200_REQUIRE(N % gs == 0, "N must be a multiple of group_size when transpose is false");
-    if (launch_qmm_rowmajor(x, w, scales, biases, M, K, N, gs, bits, out, st)) return 1;
+  if (!fast_qmm_form(gs, bits, dtype, transpose) || (!small_shape_ok((int)K) && !prefill_shape_ok((int)K, (int)N, 1))) {
+    if (launch_gather_qmm_generic(x, w, scales, biases, nullptr, nullptr, dtype, 1, M, K, 1, N, 1, transpose, gs, bits, out, c->err,
+                                  st))
+      return 1;
     LAUNCHED(c, 1);
     return 0;
   }
-  B200_REQUIRE(K % gs == 0, "K must be a multiple of group_size");
-  B200_REQUIRE(small_shape_ok((int)K), "K too large");
-  if (ctx_grow(c, 4096 + al(sizeof(uint16_t) * M * K) + al(sizeof(float) * M))) return 1;
+  if (ctx_grow(c, 4096 + grouped_scratch_bytes(M, M, K, 1))) return 1;
   uint32_t* seg = static_cast<uint32_t*>(c->take(64));
   launch_dense_segments(seg + 0, seg + 4, seg + 8, seg + 12, (uint32_t)M, st);
   LAUNCHED(c, 1);
@@ -322,32 +366,35 @@ int b200_quantized_matmul(b200_ctx* c, const void* x, const uint32_t* w, const v
   a.K = (int)K;
   a.N = (int)N;
   a.n_experts = 1;
-  return run_grouped(c, a, 1, bits, 1, M, x, M, st);
+  return run_grouped(c, a, bits, 1, M, x, M, seg + 0, st);
 }
 
 int b200_gather_qmm(b200_ctx* c, const void* x, const uint32_t* w, const void* scales, const void* biases,
-                    const uint32_t* lhs, const uint32_t* rhs, int transpose, int gs, int bits, int sorted_indices,
+                    const uint32_t* lhs, const uint32_t* rhs, int transpose, int gs, int bits, int sorted_indices, int dtype,
                     int64_t Bx, int64_t M, int64_t K, int64_t E, int64_t N, int64_t n_idx, void* out, void* stream) {
   (void)sorted_indices;
   CTX_ENTER(c);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  B200_REQUIRE(transpose != 0, "only transpose = true is supported (the form every layer uses)");
-  B200_REQUIRE(bits == 4 || bits == 8, "bits must be 4 or 8");
-  B200_REQUIRE(gs == 64, "group_size must be 64");
   B200_REQUIRE(Bx > 0 && M > 0 && K > 0 && N > 0 && n_idx >= 0, "bad shape");
+  if (check_qmm_common(gs, bits, dtype, transpose, K, N)) return 1;
   B200_REQUIRE(lhs != nullptr || n_idx <= Bx, "without lhs_indices x needs one batch entry per index");
-  B200_REQUIRE(K % gs == 0, "K must be a multiple of group_size");
-  B200_REQUIRE(E > 0 && E <= 256, "the number of weight matrices must be in 1..256");
+  B200_REQUIRE(E > 0, "w needs at least one matrix");
   B200_REQUIRE(biases != nullptr, "biases are required in affine mode");
   B200_REQUIRE(rhs != nullptr, "rhs_indices is required");
   if (n_idx == 0) return 0;
   B200_REQUIRE(x && w && scales && out, "null tensor");
   const int64_t n = n_idx * M;
   B200_REQUIRE(n < (int64_t(1) << 31), "too many rows");
-  B200_REQUIRE(small_shape_ok((int)K), "K too large");
+  if (!fast_qmm_form(gs, bits, dtype, transpose) || E > 256 ||
+      (!small_shape_ok((int)K) && !prefill_shape_ok((int)K, (int)N, 1))) {
+    if (launch_gather_qmm_generic(x, w, scales, biases, lhs, rhs, dtype, Bx, M, K, E, N, n_idx, transpose, gs, bits, out, c->err,
+                                  st))
+      return 1;
+    LAUNCHED(c, 1);
+    return 0;
+  }
   size_t need = al(sizeof(uint32_t) * n) * 4 + al(sizeof(uint32_t) * (E + 1)) * 3 + al(16) +
-                al(sizeof(uint32_t) * permute_scratch_words(n, (int)E)) + al(sizeof(uint16_t) * Bx * M * K) +
-                al(sizeof(float) * Bx * M) + 4096;
+                al(sizeof(uint32_t) * permute_scratch_words(n, (int)E)) + grouped_scratch_bytes(n, Bx * M, K, E) + 4096;
   if (ctx_grow(c, need)) return 1;
   uint32_t* flat_e = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
   uint32_t* flat_s = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
@@ -376,7 +423,7 @@ int b200_gather_qmm(b200_ctx* c, const void* x, const uint32_t* w, const void* s
   a.K = (int)K;
   a.N = (int)N;
   a.n_experts = (int)E;
-  return run_grouped(c, a, 1, bits, (int)(E < n ? E : n), n, x, Bx * M, st);
+  return run_grouped(c, a, bits, (int)(E < n ? E : n), n, x, Bx * M, counts, st);
 }
 
 int b200_gather_mm(b200_ctx* c, const void* a, const void* b, const uint32_t* lhs_indices, const uint32_t* rhs_indices,
@@ -432,6 +479,47 @@ int b200_take_rows(b200_ctx* c, const void* x, const uint32_t* indices, uint32_t
   B200_REQUIRE(n_rows == 0 || (x && indices && out), "null tensor");
   launch_take_rows(x, indices, div, n_rows, x_rows, cols, out, c->err, static_cast<cudaStream_t>(stream));
   LAUNCHED(c, n_rows ? 1 : 0);
+  return 0;
+}
+
+int b200_take_axis(b200_ctx* c, const void* x, const uint32_t* indices, int64_t n_rows, int64_t x_rows, int64_t cols,
+                   void* out, void* stream) {
+  return b200_take_rows(c, x, indices, 1, n_rows, x_rows, cols, out, stream);
+}
+
+int b200_argsort_axis(b200_ctx* c, const uint32_t* keys, int64_t rows, int64_t cols, int key_bound, uint32_t* out,
+                      void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(key_bound > 0 && key_bound <= 256, "key_bound must be in 1..256");
+  B200_REQUIRE(rows >= 0 && cols >= 0 && cols < (int64_t(1) << 31), "bad shape");
+  if (rows * cols == 0) return 0;
+  B200_REQUIRE(keys && out, "null tensor");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int E = key_bound;
+  size_t need = al(sizeof(uint32_t) * cols) + al(sizeof(uint32_t) * (E + 1)) * 3 + al(16) +
+                al(sizeof(uint32_t) * permute_scratch_words(cols, E)) + 4096;
+  if (ctx_grow(c, need)) return 1;
+  uint32_t* inv = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * cols));
+  uint32_t* counts = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  uint32_t* offsets = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  uint32_t* active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  uint32_t* n_active = static_cast<uint32_t*>(c->take(16));
+  uint32_t* chunk = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * permute_scratch_words(cols, E)));
+  B200_REQUIRE(inv && counts && offsets && active && n_active && chunk, "scratch arena too small");
+  for (int64_t r = 0; r < rows; ++r) {  // stream order keeps the rows from sharing the scratch at the same time
+    launch_permute(keys + r * cols, cols, E, out + r * cols, inv, counts, offsets, active, n_active, chunk, c->err, st);
+    LAUNCHED(c, permute_launches(cols));
+  }
+  return 0;
+}
+
+int b200_topk_axis(b200_ctx* c, const void* a, int64_t rows, int64_t cols, int k, void* out, void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(cols > 0 && cols <= 256, "cols must be in 1..256");
+  B200_REQUIRE(k > 0 && k <= cols, "k is out of range for the axis");
+  B200_REQUIRE(rows >= 0 && (rows == 0 || (a && out)), "bad arguments");
+  launch_topk_values(a, (int)rows, (int)cols, k, out, static_cast<cudaStream_t>(stream));
+  LAUNCHED(c, rows ? 1 : 0);
   return 0;
 }
 
@@ -523,7 +611,7 @@ static bool use_tensor_core_path(const b200_ctx* c, const b200_moe_config& cfg, 
   // measured crossover (whole block, register kernel against tensor-core kernel): Qwen3-30B-A3B layer 12 rows per
   // expert 0.32 ms against 0.35 ms, 16 rows 0.37 against 0.34; Qwen3-235B-A22B layer 12 rows 1.01 against 1.10 ms,
   // 16 rows 1.23 against 1.08
-  return n / (max_active > 0 ? max_active : 1) >= 14;
+  return n / (max_active > 0 ? max_active : 1) >= kTensorCoreRowsPerExpert;
 }
 
 // Gate/up and down products over rows that are grouped by expert (offsets/active/n_active describe
@@ -637,7 +725,7 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   gu.n_experts = E;
   if (tc) {
     // rows gathered into expert order, converted to row-normalised fp16, in the k order the 4-bit unpack produces
-    launch_prepare_rows(x, perm, perm ? src_div : 1, n, cfg.hidden, cfg.bits == 4, xs, rs_x, st);
+    launch_prepare_rows(x, perm, nullptr, perm ? src_div : 1, n, cfg.hidden, cfg.bits == 4, xs, rs_x, st);
     c->mark(4, st);
     if (launch_grouped_qmm_tc(xs, rs_x, n, gu, 2, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, false,
                               c->err, st))

@@ -50,6 +50,7 @@ int launch_router_fused_small(const void* x, const void* w, const float* logit_b
                               uint32_t* counts, uint32_t* offsets, uint32_t* active, uint32_t* n_active,
                               unsigned int* ticket, int* err, cudaStream_t st);
 int launch_argpartition(const void* a, int rows, int cols, int kth, uint32_t* out, cudaStream_t st);
+int launch_topk_values(const void* a, int rows, int cols, int k, void* out, cudaStream_t st);
 int launch_softmax(const void* a, int rows, int cols, void* out, cudaStream_t st);
 int launch_take_along(const void* a, int rows, int cols, const uint32_t* idx, int icol, void* out, int* err,
                       cudaStream_t st);
@@ -73,8 +74,8 @@ bool prefill_shape_ok(int K, int N, int nmat);
 int launch_build_row_tiles(const uint32_t* counts, const uint32_t* offsets, int E, uint32_t* tile_expert,
                            uint32_t* tile_row0, uint32_t* tile_rows, uint32_t* n_row_tiles, int rows_per_tile,
                            cudaStream_t st);
-int launch_prepare_rows(const void* x, const uint32_t* perm, int src_div, int64_t n_rows, int K, int permute8, void* xs,
-                        float* row_scale, cudaStream_t st);
+int launch_prepare_rows(const void* x, const uint32_t* perm, const uint32_t* src_map, int src_div, int64_t n_rows, int K,
+                        int permute8, void* xs, float* row_scale, cudaStream_t st);
 int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows, const GroupedArgs& g, int nmat, int bits, const uint32_t* tile_expert,
                           const uint32_t* tile_row0, const uint32_t* tile_rows, const uint32_t* n_row_tiles, int E,
                           bool alternate, int* err, cudaStream_t st);
@@ -92,8 +93,10 @@ int launch_gather_combine(const void* y, const uint32_t* inv, const void* scores
 int launch_rms_norm(const void* x, const void* residual, const void* weight, float eps, int64_t rows, int64_t cols,
                     void* out, void* sum_out, cudaStream_t st);
 int launch_add(const void* a, const void* b, int64_t n, void* out, cudaStream_t st);
-int launch_qmm_rowmajor(const void* x, const uint32_t* wq, const void* scales, const void* biases, int64_t M, int64_t K,
-                        int64_t N, int gs, int bits, void* out, cudaStream_t st);
+// dtype: 0 float32, 1 bfloat16, 2 float16 (activations, scales, biases and result alike)
+int launch_gather_qmm_generic(const void* x, const uint32_t* wq, const void* scales, const void* biases, const uint32_t* lhs,
+                              const uint32_t* rhs, int dtype, int64_t Bx, int64_t M, int64_t K, int64_t E, int64_t N,
+                              int64_t n_idx, int transpose, int gs, int bits, void* out, int* err, cudaStream_t st);
 int launch_gather_mm(const void* a, const void* b, const uint32_t* lhs, const uint32_t* rhs, int64_t Ba, int64_t Bb,
                      int64_t M, int64_t K, int64_t N, int64_t n_idx, void* out, int* err, cudaStream_t st);
 int launch_dense_segments(uint32_t* counts, uint32_t* offsets, uint32_t* active, uint32_t* n_active, uint32_t rows,

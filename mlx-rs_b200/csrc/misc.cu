@@ -306,32 +306,100 @@ int launch_add(const void* a, const void* b, int64_t n, void* out, cudaStream_t 
   return 0;
 }
 
-// quantized_matmul with transpose = false (mlx-rs/src/ops/quantization.rs:88-122): w is
-// [K, N/epw], quantised along N; out = x . w_hat.  Not on the routed path (layers always pass
-// transpose = true); a plain one-thread-per-output kernel keeps the op surface complete.
-__global__ void qmm_rowmajor_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ wq,
-                                    const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ biases,
-                                    int64_t M, int64_t K, int64_t N, int gs, int bits, __nv_bfloat16* __restrict__ out) {
-  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= M * N) return;
-  const int64_t m = i / N, n = i % N;
+// General form of quantized_matmul / gather_qmm (mlx-rs/src/ops/quantization.rs:88-122, 160-230) on CUDA cores:
+// any activation dtype (float32, bfloat16, float16; scales, biases and the result share it), group sizes 32 / 64 /
+// 128, bits 2 / 4 / 8, both orientations of w, optional index arrays.
+//   transpose != 0: w [E, N, K*bits/32] quantised along K, out[i] = x[lhs[i]] . w_hat[rhs[i]]^T
+//   transpose == 0: w [E, K, N*bits/32] quantised along N, out[i] = x[lhs[i]] . w_hat[rhs[i]]
+// float32 arithmetic throughout (the dequantised weight is one multiply and one add, the dot product a chain of
+// fused multiply-adds in k order), so float32 callers get float32-accurate results; it is the reference
+// tests' configuration (float32 arrays, `:319-342`, `:346-423`) and the fallback for shapes the fast kernels do
+// not take.  One thread per output element.
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) gather_qmm_generic_kernel(const T* __restrict__ x, const uint32_t* __restrict__ wq,
+                                                                 const T* __restrict__ scales, const T* __restrict__ biases,
+                                                                 const uint32_t* __restrict__ lhs, const uint32_t* __restrict__ rhs,
+                                                                 int64_t Bx, int64_t M, int64_t K, int64_t E, int64_t N,
+                                                                 int64_t n_idx, int transpose, int gs, int bits,
+                                                                 T* __restrict__ out, int* __restrict__ err) {
+  const int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= n_idx * M * N) return;
+  const int64_t n = o % N, m = (o / N) % M, i = o / (N * M);
+  uint32_t bx = lhs ? lhs[i] : (uint32_t)i, e = rhs ? rhs[i] : 0u;
+  if ((int64_t)bx >= Bx || (int64_t)e >= E) {  // reported through the status word; the access is redirected, never out of bounds
+    *err = (int64_t)e >= E ? 2 : 1;
+    bx = 0;
+    e = 0;
+  }
   const int epw = 32 / bits;
   const uint32_t mask = (1u << bits) - 1u;
-  const int64_t Wp = N / epw, G = N / gs;
+  const T* xr = x + ((int64_t)bx * M + m) * K;
   float acc = 0.f;
-  for (int64_t k = 0; k < K; ++k) {
-    uint32_t q = (wq[k * Wp + n / epw] >> (bits * (n % epw))) & mask;
-    float wv = __bfloat162float(scales[k * G + n / gs]) * (float)q + __bfloat162float(biases[k * G + n / gs]);
-    acc += __bfloat162float(x[m * K + k]) * wv;
+  if (transpose) {
+    const int64_t Wp = K / epw, G = K / gs;
+    const uint32_t* wr = wq + ((int64_t)e * N + n) * Wp;
+    const T* sr = scales + ((int64_t)e * N + n) * G;
+    const T* br = biases + ((int64_t)e * N + n) * G;
+    for (int64_t g = 0; g < G; ++g) {
+      const float s = to_f32(sr[g]), b = to_f32(br[g]);
+      for (int kk = 0; kk < gs; kk += epw) {
+        const uint32_t word = wr[(g * gs + kk) / epw];
+        for (int j = 0; j < epw; ++j) {
+          const float wv = __fadd_rn(__fmul_rn(s, (float)((word >> (bits * j)) & mask)), b);
+          acc = fmaf(to_f32(xr[g * gs + kk + j]), wv, acc);
+        }
+      }
+    }
+  } else {
+    const int64_t Wp = N / epw, G = N / gs;
+    const uint32_t* we = wq + (int64_t)e * K * Wp;
+    const T* se = scales + (int64_t)e * K * G;
+    const T* be = biases + (int64_t)e * K * G;
+    for (int64_t k = 0; k < K; ++k) {
+      const uint32_t q = (we[k * Wp + n / epw] >> (bits * (n % epw))) & mask;
+      const float wv = __fadd_rn(__fmul_rn(to_f32(se[k * G + n / gs]), (float)q), to_f32(be[k * G + n / gs]));
+      acc = fmaf(to_f32(xr[k]), wv, acc);
+    }
   }
-  out[i] = __float2bfloat16_rn(acc);
+  out[o] = from_f32<T>(acc);
 }
-int launch_qmm_rowmajor(const void* x, const uint32_t* wq, const void* scales, const void* biases, int64_t M, int64_t K,
-                        int64_t N, int gs, int bits, void* out, cudaStream_t st) {
-  if (M * N == 0) return 0;
-  qmm_rowmajor_kernel<<<cdiv(M * N, 256), 256, 0, st>>>(
-      static_cast<const __nv_bfloat16*>(x), wq, static_cast<const __nv_bfloat16*>(scales),
-      static_cast<const __nv_bfloat16*>(biases), M, K, N, gs, bits, static_cast<__nv_bfloat16*>(out));
+
+int launch_gather_qmm_generic(const void* x, const uint32_t* wq, const void* scales, const void* biases, const uint32_t* lhs,
+                              const uint32_t* rhs, int dtype, int64_t Bx, int64_t M, int64_t K, int64_t E, int64_t N,
+                              int64_t n_idx, int transpose, int gs, int bits, void* out, int* err, cudaStream_t st) {
+  const int64_t total = n_idx * M * N;
+  if (total == 0) return 0;
+  const dim3 grid(cdiv(total, 256)), block(256);
+  if (dtype == 0)
+    gather_qmm_generic_kernel<float><<<grid, block, 0, st>>>(
+        static_cast<const float*>(x), wq, static_cast<const float*>(scales), static_cast<const float*>(biases), lhs, rhs, Bx, M, K,
+        E, N, n_idx, transpose, gs, bits, static_cast<float*>(out), err);
+  else if (dtype == 1)
+    gather_qmm_generic_kernel<__nv_bfloat16><<<grid, block, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(x), wq, static_cast<const __nv_bfloat16*>(scales),
+        static_cast<const __nv_bfloat16*>(biases), lhs, rhs, Bx, M, K, E, N, n_idx, transpose, gs, bits,
+        static_cast<__nv_bfloat16*>(out), err);
+  else
+    gather_qmm_generic_kernel<__half><<<grid, block, 0, st>>>(
+        static_cast<const __half*>(x), wq, static_cast<const __half*>(scales), static_cast<const __half*>(biases), lhs, rhs, Bx, M,
+        K, E, N, n_idx, transpose, gs, bits, static_cast<__half*>(out), err);
   return 0;
 }
 

@@ -645,6 +645,39 @@ __global__ void __launch_bounds__(128) argpartition_kernel(const __nv_bfloat16* 
   }
 }
 
+// topk_axis(a, k, -1) over bf16 rows (mlx-rs/src/ops/indexing/mod.rs:674-700): the k largest values of a row, written
+// in ascending order.  One warp per row, cols <= 256: k rounds of a warp-wide max over (value, inverted index) keys.
+__global__ void __launch_bounds__(128) topk_values_kernel(const __nv_bfloat16* __restrict__ a, int rows, int cols, int k,
+                                                          __nv_bfloat16* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const unsigned short* row = reinterpret_cast<const unsigned short*>(a) + (size_t)r * cols;
+  uint32_t keys[kMaxPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    const int e = lane + 32 * i;
+    keys[i] = (e < cols) ? ((order_key(row[e]) << 16) | (0xffffu - (uint32_t)e)) : 0u;
+  }
+  for (int j = 0; j < k; ++j) {
+    uint32_t best = keys[0];
+#pragma unroll
+    for (int i = 1; i < kMaxPerLane; ++i) best = max(best, keys[i]);
+    best = __reduce_max_sync(0xffffffffu, best);
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i)
+      if (keys[i] == best) keys[i] = 0u;
+    if (lane == 0) out[(size_t)r * k + (k - 1 - j)] = __ushort_as_bfloat16((unsigned short)key_to_bits(best >> 16));
+  }
+}
+
+int launch_topk_values(const void* a, int rows, int cols, int k, void* out, cudaStream_t st) {
+  if (rows == 0) return 0;
+  topk_values_kernel<<<cdiv(rows, 4), 128, 0, st>>>(static_cast<const __nv_bfloat16*>(a), rows, cols, k,
+                                                    static_cast<__nv_bfloat16*>(out));
+  return 0;
+}
+
 int launch_argpartition(const void* a, int rows, int cols, int kth, uint32_t* out, cudaStream_t st) {
   if (rows == 0) return 0;
   argpartition_kernel<<<cdiv(rows, 4), 128, 0, st>>>(static_cast<const __nv_bfloat16*>(a), rows, cols, kth, out);

@@ -16,6 +16,7 @@ from . import _lib as L
 DEFAULT_GROUP_SIZE = 64
 DEFAULT_BITS = 4
 _DT = {torch.float32: 0, torch.bfloat16: 1}
+_DT3 = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}   # activation dtypes of the matmul ops
 
 
 def _ctx(ctx):
@@ -61,15 +62,17 @@ def dequantize(w, scales, biases, group_size=DEFAULT_GROUP_SIZE, bits=DEFAULT_BI
 
 
 def quantized_matmul(x, w, scales, biases, transpose=False, group_size=DEFAULT_GROUP_SIZE, bits=DEFAULT_BITS, ctx=None):
+    """x [..., K] float32 / bfloat16 / float16; scales and biases in the same dtype -> [..., N] in that dtype."""
     _cuda(x, w, scales, biases)
-    _req(x.dtype == torch.bfloat16 and scales.dtype == torch.bfloat16, "quantized_matmul: bf16 activations and scales")
+    _req(x.dtype in _DT3 and scales.dtype == x.dtype and biases.dtype == x.dtype,
+         "quantized_matmul: float32, bfloat16 or float16 activations with scales and biases of the same dtype")
     K = x.shape[-1]
     M = x.numel() // K
     N = w.shape[0] if transpose else w.shape[1] * 32 // bits
     _req((w.shape[1] * 32 // bits == K) if transpose else (w.shape[0] == K), "quantized_matmul: shape mismatch")
     out = torch.empty(x.shape[:-1] + (N,), dtype=x.dtype, device=x.device)
     L.check(L.lib().b200_quantized_matmul(_ctx(ctx), L.ptr(x), L.ptr(w), L.ptr(scales), L.ptr(biases), int(transpose),
-                                          group_size, bits, M, K, N, L.ptr(out), L.stream_ptr()))
+                                          group_size, bits, _DT3[x.dtype], M, K, N, L.ptr(out), L.stream_ptr()))
     return out
 
 
@@ -93,21 +96,22 @@ def gather_mm(a, b, lhs_indices=None, rhs_indices=None, ctx=None):
 
 def gather_qmm(x, w, scales, biases, lhs_indices=None, rhs_indices=None, transpose=True, group_size=DEFAULT_GROUP_SIZE,
                bits=DEFAULT_BITS, sorted_indices=False, ctx=None):
-    """x [..., M, K] (batch dims flattened), w [E, N, K*bits/32] -> [*idx.shape, M, N]."""
+    """x [..., M, K] (batch dims flattened), w [E, N, K*bits/32] (transpose) or [E, K, N*bits/32] -> [*idx.shape, M, N]."""
     _cuda(x, w, scales, biases, lhs_indices, rhs_indices)
-    _req(x.dtype == torch.bfloat16 and scales.dtype == torch.bfloat16, "gather_qmm: bf16 activations and scales")
+    _req(x.dtype in _DT3 and scales.dtype == x.dtype and biases.dtype == x.dtype,
+         "gather_qmm: float32, bfloat16 or float16 activations with scales and biases of the same dtype")
     _req(rhs_indices is not None, "gather_qmm: rhs_indices is required")
     M, K = x.shape[-2], x.shape[-1]
     Bx = x.numel() // (M * K)
-    N = w.shape[-2]
-    E = w.numel() // (N * w.shape[-1])
+    N = w.shape[-2] if transpose else w.shape[-1] * 32 // bits
+    E = w.numel() // (w.shape[-2] * w.shape[-1])
     n_idx = rhs_indices.numel()
     _req(lhs_indices is None or lhs_indices.numel() == n_idx, "gather_qmm: index shapes differ")
     _req(lhs_indices is not None or Bx == n_idx, "gather_qmm: without lhs_indices x needs one batch entry per index")
     out = torch.empty(tuple(rhs_indices.shape) + (M, N), dtype=x.dtype, device=x.device)
     L.check(L.lib().b200_gather_qmm(_ctx(ctx), L.ptr(x), L.ptr(w), L.ptr(scales), L.ptr(biases), L.ptr(lhs_indices),
-                                    L.ptr(rhs_indices), int(transpose), group_size, bits, int(sorted_indices), Bx, M, K,
-                                    E, N, n_idx, L.ptr(out), L.stream_ptr()))
+                                    L.ptr(rhs_indices), int(transpose), group_size, bits, int(sorted_indices), _DT3[x.dtype],
+                                    Bx, M, K, E, N, n_idx, L.ptr(out), L.stream_ptr()))
     return out
 
 
@@ -139,6 +143,33 @@ def take_along_axis(a, indices, axis=-1, ctx=None):
     out = torch.empty(indices.shape, dtype=a.dtype, device=a.device)
     L.check(L.lib().b200_take_along_axis(_ctx(ctx), L.ptr(a), a.numel() // cols, cols, L.ptr(indices), icols,
                                          L.ptr(out), L.stream_ptr()))
+    return out
+
+
+def take_axis(x, indices, axis=0, ctx=None):
+    """take_axis(x, indices, 0) for a 2-D bf16 tensor -> [len(indices), cols]."""
+    _req(axis == 0, "take_axis: axis 0")
+    return take_rows(x, indices, 1, ctx=ctx)
+
+
+def argsort_axis(keys, axis=-1, key_bound=256, ctx=None):
+    """Stable ascending argsort along the last axis of small unsigned keys (expert indices < key_bound <= 256)."""
+    _cuda(keys)
+    _req(axis in (-1, keys.dim() - 1) and keys.dtype == torch.int32, "argsort_axis: last axis of an int32 tensor")
+    cols = keys.shape[-1]
+    out = torch.empty_like(keys)
+    L.check(L.lib().b200_argsort_axis(_ctx(ctx), L.ptr(keys), keys.numel() // max(cols, 1), cols, int(key_bound), L.ptr(out),
+                                      L.stream_ptr()))
+    return out
+
+
+def topk_axis(a, k, axis=-1, ctx=None):
+    """The k largest values along the last axis of a bf16 tensor (ascending)."""
+    _cuda(a)
+    _req(axis in (-1, a.dim() - 1) and a.dtype == torch.bfloat16, "topk_axis: last axis of a bf16 tensor")
+    cols = a.shape[-1]
+    out = torch.empty(a.shape[:-1] + (k,), dtype=a.dtype, device=a.device)
+    L.check(L.lib().b200_topk_axis(_ctx(ctx), L.ptr(a), a.numel() // cols, cols, int(k), L.ptr(out), L.stream_ptr()))
     return out
 
 

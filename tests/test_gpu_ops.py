@@ -113,8 +113,6 @@ def test_gather_qmm_switch_linear_shape(pkg, O):
     got = pkg.ops.gather_qmm(bf16_cuda(x), np_i32(wq), bf16_cuda(s), bf16_cuda(b), None, np_i32(rhs))
     pkg.default_context().check()
     assert rel_err(got.float().cpu().numpy(), ref) <= 2e-2
-    with pytest.raises(pkg.B200Error):
-        pkg.ops.gather_qmm(bf16_cuda(x), np_i32(wq), bf16_cuda(s), bf16_cuda(b), None, np_i32(rhs), transpose=False)
     bad = rhs.copy()
     bad[3] = E + 2                      # out-of-range expert: reported at the next check, nothing written for it
     pkg.ops.gather_qmm(bf16_cuda(x), np_i32(wq), bf16_cuda(s), bf16_cuda(b), None, np_i32(bad))
@@ -197,3 +195,85 @@ def test_gather_mm_reference_cases(pkg, O):
     with pytest.raises(pkg.B200Error):      # an index past the batch is reported, not read
         pkg.ops.gather_mm(bf16_cuda(a), bf16_cuda(b), None, torch.tensor([7, 0, 1, 2, 0], dtype=torch.int32).cuda())
         pkg.default_context().check()
+
+
+def f32_cuda(a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda()
+
+
+def test_reference_float32_cases(pkg, O):
+    """The reference's own op tests use float32 arrays: quantized_matmul with transpose = false equals
+    x @ dequantize(w) within 1e-3 (mlx-rs/src/ops/quantization.rs:317-342) and gather_qmm equals gather_mm on
+    the dequantised, transposed weights within 1e-4 (:344-423)."""
+    rng = np.random.default_rng(0)
+    m, n, k = 32, 128, 128
+    x = (rng.standard_normal((m, k)) / np.sqrt(k)).astype(np.float32)
+    w = (rng.standard_normal((k, n)) / np.sqrt(k)).astype(np.float32)
+    wq, s, b = pkg.ops.quantize(f32_cuda(w), 64, 4)
+    assert s.dtype == torch.float32
+    wh = pkg.ops.dequantize(wq, s, b, 64, 4).cpu().numpy()
+    got = pkg.ops.quantized_matmul(f32_cuda(x), wq, s, b, False, 64, 4).cpu().numpy()
+    assert np.abs(got - x @ wh).max() < 1e-3
+    m, n, k = 32, 64, 64
+    w3 = rng.standard_normal((3, n, k)).astype(np.float32)
+    wq, s, b = O.quantize(w3, 64, 4, bf16_params=False)
+    wh_t = np.swapaxes(O.dequantize(wq, s, b, 64, 4), -1, -2).copy()
+    rhs = np.array([2, 1], np.uint32)
+    for bx, lhs in ((1, [0, 0]), (5, [0, 2])):
+        xx = rng.standard_normal((bx, m, k)).astype(np.float32)
+        lhs = np.array(lhs, np.uint32)
+        c1 = O.gather_mm(xx, wh_t, lhs, rhs)
+        c2 = pkg.ops.gather_qmm(f32_cuda(xx), np_i32(wq), f32_cuda(s), f32_cuda(b), np_i32(lhs), np_i32(rhs), True, 64, 4)
+        pkg.default_context().check()
+        assert c2.dtype == torch.float32 and np.abs(c2.cpu().numpy() - c1).max() < 1e-4
+    # float16 activations, group 32, 8 bits, and the transpose = false form of gather_qmm (w quantised along N)
+    wk = rng.standard_normal((3, k, n)).astype(np.float32) * 0.1
+    wq, s, b = O.quantize(wk, 32, 8, bf16_params=False)
+    wh = O.dequantize(wq, s, b, 32, 8)
+    xx = (rng.standard_normal((4, 8, k)) * 0.5).astype(np.float16)
+    rhs = np.array([1, 0, 2, 2], np.uint32)
+    ref = np.einsum("bmk,bkn->bmn", xx.astype(np.float32), wh[rhs].astype(np.float16).astype(np.float32))
+    got = pkg.ops.gather_qmm(torch.from_numpy(xx).cuda(), np_i32(wq), torch.from_numpy(s.astype(np.float16)).cuda(),
+                             torch.from_numpy(b.astype(np.float16)).cuda(), None, np_i32(rhs), False, 32, 8)
+    pkg.default_context().check()
+    assert got.dtype == torch.float16 and rel_err(got.float().cpu().numpy(), ref) <= 2e-2
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_ops_reach_the_tensor_core_kernel(pkg, O, bits):
+    """quantized_matmul and gather_qmm with many rows per weight matrix (the dense quantised Linear, a SwitchLinear
+    at prefill size) run the tcgen05 kernel; same bar as the block."""
+    rng = np.random.default_rng(5 + bits)
+    M, K, N, E = 900, 512, 768, 4
+    x = O.round_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    w = O.round_bf16((rng.standard_normal((E, N, K)) * 0.05).astype(np.float32))
+    wq, s, b = O.quantize(w, 64, bits)
+    l0 = pkg.default_context().launch_count()
+    got = pkg.ops.quantized_matmul(bf16_cuda(x), np_i32(wq[0]), bf16_cuda(s[0]), bf16_cuda(b[0]), True, 64, bits)
+    assert pkg.default_context().launch_count() - l0 == 4      # segments, row tiles, row preparation, tcgen05 product
+    ref = O.quantized_matmul(x, wq[0], s[0], b[0], True, 64, bits)
+    assert close_up_to_bf16_rounding(got.float().cpu().numpy(), ref, 2e-2)
+    rhs = rng.integers(0, E, M).astype(np.uint32)
+    lhs = rng.permutation(M).astype(np.uint32)
+    ref = O.gather_qmm(x[:, None, :], wq, s, b, lhs, rhs, True, 64, bits)
+    got = pkg.ops.gather_qmm(bf16_cuda(x[:, None, :]), np_i32(wq), bf16_cuda(s), bf16_cuda(b), np_i32(lhs), np_i32(rhs),
+                             True, 64, bits)
+    pkg.default_context().check()
+    assert close_up_to_bf16_rounding(got.float().cpu().numpy(), ref, 2e-2)
+
+
+def test_argsort_take_topk_ops(pkg, O):
+    rng = np.random.default_rng(8)
+    keys = rng.integers(0, 128, (3, 5000)).astype(np.uint32)
+    got = pkg.ops.argsort_axis(np_i32(keys), -1, 128)
+    pkg.default_context().check()
+    assert np.array_equal(u32(got), O.argsort(keys))
+    x = O.round_bf16(rng.standard_normal((50, 64)).astype(np.float32))
+    idx = rng.integers(0, 50, 200).astype(np.uint32)
+    assert np.array_equal(pkg.ops.take_axis(bf16_cuda(x), np_i32(idx)).float().cpu().numpy(), x[idx])
+    a = O.round_bf16(rng.standard_normal((37, 128)).astype(np.float32))
+    a[:, 5] = a[:, 9]
+    top = pkg.ops.topk_axis(bf16_cuda(a), 8).float().cpu().numpy()
+    assert np.array_equal(top, np.sort(a, axis=-1)[:, -8:])
+    with pytest.raises(pkg.B200Error):
+        pkg.ops.topk_axis(bf16_cuda(a), 500)
