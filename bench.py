@@ -358,10 +358,11 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the step from a CUDA graph (auto: for steps of at most 1024 tokens)")
-    ap.add_argument("--ep-transport", default="peer", choices=["peer", "peer_push", "nccl"],
-                    help="N > 1: peer = dispatch kernel (peer stores) + combine kernel that reads the owners' outputs "
-                         "(peer loads); peer_push = dispatch kernel + down projection whose epilogue stores the rows back "
-                         "into the source GPU; nccl = torch.distributed all-to-all-v (the baseline they are measured against)")
+    ap.add_argument("--ep-transport", default="device", choices=["device", "peer", "peer_push", "nccl"],
+                    help="N > 1: device = the one-call block (dispatch and combine kernels over peer memory, phases ordered "
+                         "on the device, no host synchronisation); peer = the same kernels ordered by NCCL collectives with "
+                         "one host synchronisation per step; peer_push = dispatch kernel + down projection whose epilogue "
+                         "stores the rows back into the source GPU; nccl = torch.distributed all-to-all-v (the baseline)")
     ap.add_argument("--ep-chunks", type=int, default=0, choices=[0, 1, 2],
                     help="N > 1, peer transport: halves of a rank's tokens whose exchange overlaps the other half's products "
                          "(0 = default: one)")

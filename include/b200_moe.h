@@ -252,8 +252,9 @@ int b200_switch_glu_forward(b200_ctx* ctx, const b200_moe_config* cfg, const b20
 
 /* SwitchGLU over rows that are already grouped by expert: rows bf16 [n, H] with counts[e] consecutive
  * rows for expert e (device array, sum == n); out bf16 [n, H] in the same order.  The sorted-input
- * case of SwitchGlu::forward (mlx-lm/src/models/switch_layers.rs, gather_qmm with sorted_indices)
- * without the sort; used on the rows a rank receives in the expert-parallel exchange. */
+ * case of gather_qmm (mlx-rs/src/ops/quantization.rs:160-230 with sorted_indices = true; module template
+ * mlx-lm/src/models/qwen3.rs:204-255) without the sort; used on the rows a rank receives in the
+ * expert-parallel exchange. */
 int b200_switch_glu_sorted(b200_ctx* ctx, const b200_moe_config* cfg, const b200_moe_params* params, const void* rows,
                            const uint32_t* counts, int64_t n, void* out, void* stream);
 
@@ -301,6 +302,40 @@ int b200_ep_dispatch(b200_ctx* ctx, const void* x, const uint32_t* indices, cons
 int b200_ep_combine(b200_ctx* ctx, void* const* peer_y, const uint32_t* indices, const uint32_t* inv_perm,
                     const uint32_t* offsets, const uint32_t* dst_row0, const void* scores, int64_t T, int top_k,
                     int64_t hidden, int n_experts, int n_ranks, uint32_t capacity_rows, void* out, void* stream);
+
+/* ---- expert-parallel block in one call ------------------------------------------------------------
+ * b200_moe_block_forward_ep is b200_moe_block_forward for a rank of an expert-parallel group: the slot a
+ * transformer block's MLP fills (mlx-lm/src/models/qwen3.rs:310-325), with the experts sharded over the GPUs of
+ * one node.  The whole step - route, sort, exchange of the counts, dispatch, this rank's experts, combine - is
+ * enqueued on `stream` by ONE call, with no host synchronisation and no collective library: the ranks order
+ * their phases through small control blocks in each other's memory (release stores, acquire spins with a 2 s
+ * bound; expiry and buffer overflow are reported by b200_ctx_check).  Requirements: one process (or thread) per
+ * GPU, every rank makes the call for every step (a rank without tokens passes T = 0), params->router_weight is
+ * the full [E, H] router while gate/up/down hold THIS rank's experts [E / n_ranks, ...] (rank r owns the
+ * contiguous experts [r*E/n_ranks, (r+1)*E/n_ranks)).
+ *
+ * The exchange is de-duplicated: a token travels once to every rank that owns at least one of its experts (not
+ * once per assignment), the owner gathers its assignments' rows from those token rows, sums the token's expert
+ * outputs with their routing weights locally, and one partial sum per (token, rank) travels back.
+ *
+ * Set-up (collective, host side): every rank calls b200_ep_comm_create, which allocates its exchange buffers
+ * (token rows and partial sums: capacity_tokens x hidden bf16 each; bookkeeping; a control block) and returns
+ * B200_EP_COMM_HANDLES 64-byte handles; the ranks exchange the handles by any host channel and each calls
+ * b200_ep_comm_connect with all of them, rank-major ([n_ranks][B200_EP_COMM_HANDLES][64] bytes); a host barrier
+ * after connect and before destroy keeps a fast rank from touching memory that is not mapped yet / any more.
+ * capacity_rows bounds the ASSIGNMENTS (token, expert) a rank can receive in one step, capacity_tokens the token
+ * rows (at most the tokens of all ranks together); a rank that would receive more takes nothing that step (its
+ * experts' contributions are dropped, status 5). */
+#define B200_EP_COMM_HANDLES 6
+typedef struct b200_ep_comm b200_ep_comm;
+int b200_ep_comm_create(b200_ctx* ctx, int n_ranks, int rank, int n_experts, int top_k, int64_t hidden,
+                        uint32_t capacity_rows, uint32_t capacity_tokens, b200_ep_comm** out,
+                        unsigned char* handles /* [B200_EP_COMM_HANDLES][B200_EP_HANDLE_BYTES] */);
+int b200_ep_comm_connect(b200_ctx* ctx, b200_ep_comm* comm, const unsigned char* all_handles);
+int b200_ep_comm_destroy(b200_ctx* ctx, b200_ep_comm* comm);
+/* aux->out_f32 is not produced here (the returned expert outputs are bf16); the other aux fields are. */
+int b200_moe_block_forward_ep(b200_ctx* ctx, b200_ep_comm* comm, const b200_moe_config* cfg, const b200_moe_params* params,
+                              const void* x, int64_t T, void* out, const b200_moe_aux* aux, void* stream);
 
 /* MoE block forward: x bf16 [T, H] -> out bf16 [T, H]; aux may be NULL. */
 int b200_moe_block_forward(b200_ctx* ctx, const b200_moe_config* cfg, const b200_moe_params* params, const void* x,

@@ -300,7 +300,7 @@ static int run_grouped(b200_ctx* c, GroupedArgs& a, int bits, int max_active, in
     float* rs = static_cast<float*>(c->take(sizeof(float) * n));
     B200_REQUIRE(tile_expert && tile_row0 && tile_rows && n_row_tiles && xs && rs, "scratch arena too small");
     launch_build_row_tiles(counts, a.offsets, E, tile_expert, tile_row0, tile_rows, n_row_tiles, 256, st);
-    launch_prepare_rows(x, a.perm, a.src_map, 1, n, a.K, bits == 4, xs, rs, st);
+    launch_prepare_rows(x, a.perm, a.src_map, 1, n, nullptr, a.K, bits == 4, xs, rs, st);
     if (launch_grouped_qmm_tc(xs, rs, n, a, 1, bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, false, c->err, st))
       return 1;
     LAUNCHED(c, 3);
@@ -310,7 +310,7 @@ static int run_grouped(b200_ctx* c, GroupedArgs& a, int bits, int max_active, in
   void* xs = c->take(sizeof(uint16_t) * src_rows * a.K);
   float* rs = static_cast<float*>(c->take(sizeof(float) * src_rows));
   B200_REQUIRE(xs && rs, "scratch arena too small");
-  if (launch_prepare_rows_small(x, 0, src_rows, a.K, bits, xs, rs, st)) return 1;
+  if (launch_prepare_rows_small(x, 0, src_rows, nullptr, a.K, bits, xs, rs, st)) return 1;
   a.x = xs;
   a.x_rowscale = rs;
   if (launch_grouped_qmm_small(a, 1, bits, max_active, n, st)) return 1;
@@ -614,13 +614,23 @@ static bool use_tensor_core_path(const b200_ctx* c, const b200_moe_config& cfg, 
   return n / (max_active > 0 ? max_active : 1) >= kTensorCoreRowsPerExpert;
 }
 
+// Rows of an expert-parallel exchange: the sorted rows are gathered from a buffer of token rows through `map`
+// (sorted position -> token row); the numbers of sorted rows and of token rows live on the device.
+struct ExchangeRows {
+  const uint32_t* map;          // [n] sorted position -> row of x
+  int64_t src_rows_bound;       // host bound on the rows of x
+  const uint32_t* src_rows_dev; // device word: rows of x that exist
+  const uint32_t* n_dev;        // device word: sorted rows that exist
+};
+
 // Gate/up and down products over rows that are grouped by expert (offsets/active/n_active describe
 // the groups).  `perm` non-null: source row of sorted position p is perm[p] / src_div and the output
 // row is perm[p] (un-sorted on the fly); `perm` null: rows are already in expert order and stay so.
 static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_moe_params& p, const void* x,
                           const uint32_t* perm, int src_div, const uint32_t* counts, const uint32_t* offsets,
                           const uint32_t* active, const uint32_t* n_active, int64_t n, const void* scores, void* yk,
-                          cudaStream_t st, int* yk_fmt, const unsigned long long* out_row_addr = nullptr);
+                          cudaStream_t st, int* yk_fmt, const unsigned long long* out_row_addr = nullptr,
+                          const ExchangeRows* xr = nullptr);
 
 // Outputs of the token -> expert sort (scratch, or the caller's aux buffers where given).
 struct SortBufs {
@@ -663,7 +673,11 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
 static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_moe_params& p, const void* x,
                           const uint32_t* perm, int src_div, const uint32_t* counts, const uint32_t* offsets,
                           const uint32_t* active, const uint32_t* n_active, int64_t n, const void* scores, void* yk,
-                          cudaStream_t st, int* yk_fmt, const unsigned long long* out_row_addr) {
+                          cudaStream_t st, int* yk_fmt, const unsigned long long* out_row_addr, const ExchangeRows* xr) {
+  // n is the host's bound on the number of rows; with `xr` the rows that exist are counted on the device
+  // (everything below is driven by the device-side segment tables, only the row preparation needs the extra
+  // words) and are gathered from x through xr->map
+  const uint32_t* n_dev = xr ? xr->n_dev : nullptr;
   const int E = cfg.n_experts;
   void* h = c->take(sizeof(uint16_t) * n * cfg.inter);
   B200_REQUIRE(h, "scratch arena too small");
@@ -725,7 +739,7 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   gu.n_experts = E;
   if (tc) {
     // rows gathered into expert order, converted to row-normalised fp16, in the k order the 4-bit unpack produces
-    launch_prepare_rows(x, perm, nullptr, perm ? src_div : 1, n, cfg.hidden, cfg.bits == 4, xs, rs_x, st);
+    launch_prepare_rows(x, perm, xr ? xr->map : nullptr, perm ? src_div : 1, n, n_dev, cfg.hidden, cfg.bits == 4, xs, rs_x, st);
     c->mark(4, st);
     if (launch_grouped_qmm_tc(xs, rs_x, n, gu, 2, cfg.bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, false,
                               c->err, st))
@@ -734,14 +748,18 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   } else {
     // register kernel: the source rows (the tokens when rows are gathered through perm, else the n rows
     // themselves) are prepared once - fp16, row-scaled, unpack order - and every CTA copies what it needs
-    const int64_t src_rows = perm ? n / src_div : n;
+    const int64_t src_rows = xr ? xr->src_rows_bound : (perm ? n / src_div : n);
     void* xp = c->take(sizeof(uint16_t) * src_rows * cfg.hidden);
     float* rp = static_cast<float*>(c->take(sizeof(float) * src_rows));
     B200_REQUIRE(xp && rp, "scratch arena too small");
-    if (launch_prepare_rows_small(x, 0, src_rows, cfg.hidden, cfg.bits, xp, rp, st)) return 1;
+    if (launch_prepare_rows_small(x, 0, src_rows, xr ? xr->src_rows_dev : nullptr, cfg.hidden, cfg.bits, xp, rp, st)) return 1;
     c->mark(4, st);
     gu.x = xp;
     gu.x_rowscale = rp;
+    if (xr) {
+      gu.src_mode = kSrcMapDirect;
+      gu.src_map = xr->map;
+    }
     gu.out_f16 = 1;  // h in the prepared layout, ready for the down projection
     if (launch_grouped_qmm_small(gu, 2, cfg.bits, max_active, n, st)) return 1;
     LAUNCHED(c, 2);
@@ -765,7 +783,7 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   // the 2e-2 bar at T=512): float32 from the register kernel, fp16 (11 bits, half the traffic of the
   // store-bound epilogue and of the combine's reads) from the tensor-core kernel; SwitchGlu's own output is bf16
   dn.out_f32 = scores != nullptr && !tc;
-  dn.out_f16 = scores != nullptr && tc && !out_row_addr;
+  dn.out_f16 = tc && !out_row_addr && (scores != nullptr || xr != nullptr);  // exchanged rows: fp16 outputs feed the partial sums
   dn.out_row_addr = out_row_addr;   // rows go to per-row addresses (bf16): the expert-parallel return path
   if (yk_fmt) *yk_fmt = dn.out_f32 ? kOutF32 : (dn.out_f16 ? kOutF16 : kOutBf16);
   dn.K = cfg.inter;
@@ -1019,6 +1037,178 @@ int b200_ep_combine(b200_ctx* c, void* const* peer_y, const uint32_t* indices, c
                         capacity_rows, out, c->err, static_cast<cudaStream_t>(stream)))
     return 1;
   LAUNCHED(c, 1);
+  return 0;
+}
+
+// ---- one-call expert-parallel block with device-side phase ordering ------------------------------------------
+struct b200_ep_comm {
+  EpExchange x{};               // peer pointers, shape, device words
+  void* own[kEpBufs] = {};      // this rank's six peer-mapped buffers
+  bool opened[kEpBufs][kEpMaxRanks] = {};
+  void* y = nullptr;            // this rank's expert outputs by assignment row (local only)
+  uint32_t* dev = nullptr;      // backing store of the device words
+  bool connected = false;
+};
+
+int b200_ep_comm_create(b200_ctx* c, int n_ranks, int rank, int n_experts, int top_k, int64_t hidden,
+                        uint32_t capacity_rows, uint32_t capacity_tokens, b200_ep_comm** out, unsigned char* handles) {
+  CTX_ENTER(c);
+  B200_REQUIRE(out && handles, "null argument");
+  B200_REQUIRE(n_ranks >= 1 && n_ranks <= kEpMaxRanks && rank >= 0 && rank < n_ranks, "bad rank");
+  B200_REQUIRE(n_experts > 0 && n_experts <= 256 && n_experts % n_ranks == 0, "experts must divide evenly over the ranks");
+  B200_REQUIRE(top_k > 0 && top_k <= 32, "top_k must be in 1..32");
+  B200_REQUIRE(hidden > 0 && hidden % 8 == 0 && capacity_rows > 0 && capacity_tokens > 0, "bad buffer shape");
+  b200_ep_comm* e = new b200_ep_comm();
+  EpExchange& x = e->x;
+  x.G = n_ranks;
+  x.E = n_experts;
+  x.rank = rank;
+  x.k = top_k;
+  x.H = hidden;
+  x.cap_rows = capacity_rows;
+  x.cap_tok = capacity_tokens;
+  size_t bytes[kEpBufs];
+  bytes[kEpTok] = (size_t)capacity_tokens * hidden * 2;
+  bytes[kEpPart] = (size_t)capacity_tokens * hidden * 2;
+  bytes[kEpRowMap] = sizeof(uint32_t) * (size_t)capacity_rows;
+  bytes[kEpSlotRows] = sizeof(uint32_t) * (size_t)capacity_tokens * top_k;
+  bytes[kEpSlotScores] = sizeof(uint16_t) * (size_t)capacity_tokens * top_k;
+  bytes[kEpCtl] = ep_ctl_bytes(n_ranks, n_experts);
+  const int Eg = n_experts / n_ranks;
+  bool ok = true;
+  for (int i = 0; i < kEpBufs && ok; ++i) {
+    ok = cudaMalloc(&e->own[i], bytes[i]) == cudaSuccess;
+    if (ok && i == kEpCtl) ok = cudaMemset(e->own[i], 0, bytes[i]) == cudaSuccess;
+    cudaIpcMemHandle_t h;
+    if (ok) ok = cudaIpcGetMemHandle(&h, e->own[i]) == cudaSuccess;
+    if (ok) memcpy(handles + (size_t)i * B200_EP_HANDLE_BYTES, &h, sizeof(h));
+  }
+  if (ok) ok = cudaMalloc(&e->y, (size_t)capacity_rows * hidden * 2) == cudaSuccess;
+  const size_t words = (size_t)n_experts + Eg + 1 + n_ranks + 1 + n_ranks + 8;
+  if (ok) ok = cudaMalloc(reinterpret_cast<void**>(&e->dev), sizeof(uint32_t) * words) == cudaSuccess;
+  if (ok) ok = cudaMemset(e->dev, 0, sizeof(uint32_t) * words) == cudaSuccess;
+  if (ok) ok = cudaDeviceSynchronize() == cudaSuccess;
+  if (!ok) {
+    const std::string why = cudaGetErrorString(cudaGetLastError());
+    for (void* p : e->own)
+      if (p) cudaFree(p);
+    if (e->y) cudaFree(e->y);
+    if (e->dev) cudaFree(e->dev);
+    delete e;
+    B200_FAIL("cannot allocate the exchange buffers: " + why);
+  }
+  x.dst_row0 = e->dev;
+  x.local_counts = x.dst_row0 + n_experts;
+  x.n_recv = x.local_counts + Eg;
+  x.tokbase = x.n_recv + 1;
+  x.n_tok_recv = x.tokbase + n_ranks;
+  x.ntok = x.n_tok_recv + 1;
+  for (int i = 0; i < kEpBufs; ++i) x.peer[i][rank] = e->own[i];
+  *out = e;
+  return 0;
+}
+
+int b200_ep_comm_connect(b200_ctx* c, b200_ep_comm* e, const unsigned char* all_handles) {
+  CTX_ENTER(c);
+  B200_REQUIRE(e && all_handles, "null argument");
+  B200_REQUIRE(!e->connected, "already connected");
+  for (int r = 0; r < e->x.G; ++r) {
+    if (r == e->x.rank) continue;
+    for (int i = 0; i < kEpBufs; ++i) {
+      cudaIpcMemHandle_t h;
+      memcpy(&h, all_handles + ((size_t)r * kEpBufs + i) * B200_EP_HANDLE_BYTES, sizeof(h));
+      B200_CUDA(cudaIpcOpenMemHandle(&e->x.peer[i][r], h, cudaIpcMemLazyEnablePeerAccess));
+      e->opened[i][r] = true;
+    }
+  }
+  e->connected = true;
+  return 0;
+}
+
+int b200_ep_comm_destroy(b200_ctx* c, b200_ep_comm* e) {
+  if (!e) return 0;
+  CTX_ENTER(c);
+  cudaDeviceSynchronize();
+  for (int i = 0; i < kEpBufs; ++i)
+    for (int r = 0; r < e->x.G; ++r)
+      if (e->opened[i][r]) cudaIpcCloseMemHandle(e->x.peer[i][r]);
+  for (void* p : e->own)
+    if (p) cudaFree(p);
+  if (e->y) cudaFree(e->y);
+  if (e->dev) cudaFree(e->dev);
+  delete e;
+  return 0;
+}
+
+int b200_moe_block_forward_ep(b200_ctx* c, b200_ep_comm* e, const b200_moe_config* cfg, const b200_moe_params* params,
+                              const void* x, int64_t T, void* out, const b200_moe_aux* aux, void* stream) {
+  CTX_ENTER(c);
+  B200_REQUIRE(e != nullptr && (e->connected || e->x.G == 1), "the communicator is not connected");
+  if (check_cfg(cfg) || check_params(params, true)) return 1;
+  const EpExchange& ex = e->x;
+  const int G = ex.G, E = cfg->n_experts, Eg = E / G, k = cfg->top_k;
+  B200_REQUIRE(E == ex.E && cfg->hidden == ex.H && k == ex.k, "the communicator was created for another layer shape");
+  B200_REQUIRE(T >= 0 && T < (1 << 24) && T * k < (int64_t(1) << 31), "bad token count");
+  B200_REQUIRE(T == 0 || (x && out), "null tensor");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // every rank takes part in every step, also with no tokens of its own (its experts may still receive rows)
+  const int64_t n = T * k, cap = ex.cap_rows;
+  b200_moe_config local = *cfg;  // the experts this rank owns, one assignment per arriving row
+  local.n_experts = Eg;
+  local.top_k = 1;
+  const size_t route_bytes = al(sizeof(uint16_t) * T * E) + al(sizeof(double) * (size_t)E * cfg->hidden) +
+                             al(sizeof(uint32_t) * n) * 3 + al(sizeof(uint16_t) * n) + al(sizeof(uint32_t) * (E + 1)) * 3 + al(16) +
+                             al(sizeof(uint32_t) * permute_scratch_words(n, E)) + al(sizeof(uint32_t) * (size_t)G * T) +
+                             al(sizeof(uint16_t) * (size_t)ex.cap_tok * cfg->hidden) + al(sizeof(float) * ex.cap_tok) + 4096;
+  if (ctx_grow(c, route_bytes + block_scratch_bytes(local, cap))) return 1;
+  void* logits = c->take(sizeof(uint16_t) * T * E);
+  uint32_t* idx = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
+  void* scores = c->take(sizeof(uint16_t) * n);
+  double* w64 = static_cast<double*>(c->take(sizeof(double) * (size_t)E * cfg->hidden));
+  uint32_t* slot = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (size_t)G * T));
+  B200_REQUIRE(logits && idx && scores && w64 && slot, "scratch arena too small");
+  if (aux) {
+    if (aux->logits) logits = aux->logits;
+    if (aux->indices) idx = aux->indices;
+    if (aux->scores) scores = aux->scores;
+  }
+  SortBufs sb;
+  if (take_sort_bufs(c, n, E, aux, sb)) return 1;
+  // 1. route and sort this rank's tokens; which token goes to which rank
+  if (T > 0) {
+    launch_router_logits(x, params->router_weight, params->router_logit_bias, logits, (int)T, cfg->hidden, E, w64, st);
+    launch_route_topk(logits, (int)T, E, k, cfg->router_mode, cfg->norm_topk_prob, idx, scores, nullptr, st);
+    LAUNCHED(c, 2);
+  }
+  launch_permute(idx, n, E, sb.perm, sb.inv, sb.counts, sb.offsets, sb.active, sb.n_active, sb.chunk, c->err, st);
+  launch_ep_token_slots(idx, T, ex, slot, st);
+  LAUNCHED(c, permute_launches(n) + 1);
+  // 2. all-gather of the counts through the control blocks, layout of the exchange
+  launch_ep_counts_exchange(ex, sb.counts, c->err, st);
+  // 3. dispatch: every token once per destination rank, plus the owners' bookkeeping
+  launch_ep_dispatch_dedup(x, idx, sb.inv, sb.offsets, scores, slot, T, ex, c->err, st);
+  launch_ep_signal_wait(ex, 1, c->err, st);   // every rank's rows have landed
+  LAUNCHED(c, 2 + (T ? 1 : 0));
+  // 4. this rank's experts on the assignments that arrived (their number lives on the device: the launches are
+  //    sized for the buffers' capacity and follow the device-side segment tables), then the partial weighted sums
+  {
+    uint32_t* offsets = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (Eg + 1)));
+    uint32_t* active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (Eg + 1)));
+    uint32_t* n_active = static_cast<uint32_t*>(c->take(16));
+    B200_REQUIRE(offsets && active && n_active, "scratch arena too small");
+    launch_segments_from_counts(ex.local_counts, Eg, offsets, active, n_active, st);
+    LAUNCHED(c, 1);
+    ExchangeRows xr{static_cast<const uint32_t*>(e->own[kEpRowMap]), (int64_t)ex.cap_tok, ex.n_tok_recv, ex.n_recv};
+    int y_fmt = kOutBf16;
+    if (experts_sorted(c, local, *params, e->own[kEpTok], nullptr, 1, ex.local_counts, offsets, active, n_active, cap, nullptr,
+                       e->y, st, &y_fmt, nullptr, &xr))
+      return 1;
+    if (launch_ep_partial_combine(e->y, y_fmt == kOutF16, ex, c->err, st)) return 1;
+  }
+  launch_ep_signal_wait(ex, 2, c->err, st);   // every rank's partial sums are complete
+  // 5. combine: each token sums the partial sums of the ranks that own its experts
+  launch_ep_final_combine(slot, T, ex, out, st);
+  LAUNCHED(c, 2 + (T ? 1 : 0));
   return 0;
 }
 

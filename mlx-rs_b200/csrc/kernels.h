@@ -7,7 +7,7 @@
 
 namespace b200 {
 
-enum { kSrcIdent = 0, kSrcPermDiv = 1, kSrcMap = 2 };
+enum { kSrcIdent = 0, kSrcPermDiv = 1, kSrcMap = 2, kSrcMapDirect = 3 };
 enum { kOutBf16 = 0, kOutF32 = 1, kOutF16 = 2 };  // element format of a grouped product's output / of the combine's input
 
 // One grouped product over rows that are sorted by expert.
@@ -23,7 +23,8 @@ struct GroupedArgs {
   const uint32_t* n_active;   // device scalar
   const uint32_t* perm;       // sorted position -> flat assignment index (may be null for identity modes)
   const uint32_t* src_map;    // flat assignment index -> source row (kSrcMap)
-  int src_mode;               // kSrcIdent: row p; kSrcPermDiv: perm[p] / src_div; kSrcMap: src_map[perm[p]]
+  int src_mode;               // kSrcIdent: row p; kSrcPermDiv: perm[p] / src_div; kSrcMap: src_map[perm[p]];
+                              // kSrcMapDirect: src_map[p]
   int src_div;
   int dst_perm;               // 0: out row = sorted position, 1: out row = perm[p]
   const void* row_scale;      // bf16, indexed by out row; may be null
@@ -64,8 +65,8 @@ size_t permute_scratch_words(int64_t n, int E);
 // qmm_decode.cu (register kernel of the memory-bound regime)
 bool small_shape_ok(int K);
 // x [n_rows, K] bf16 (in_f16: fp16) -> prepared fp16 rows xs [n_rows, K] + row_scale [n_rows]
-int launch_prepare_rows_small(const void* x, int in_f16, int64_t n_rows, int K, int bits, void* xs, float* row_scale,
-                              cudaStream_t st);
+int launch_prepare_rows_small(const void* x, int in_f16, int64_t n_rows, const uint32_t* n_rows_dev, int K, int bits,
+                              void* xs, float* row_scale, cudaStream_t st);
 int launch_grouped_qmm_small(const GroupedArgs& a, int nmat, int bits, int max_active, int64_t rows, cudaStream_t st);
 
 // qmm_prefill.cu (tcgen05 path)
@@ -74,8 +75,9 @@ bool prefill_shape_ok(int K, int N, int nmat);
 int launch_build_row_tiles(const uint32_t* counts, const uint32_t* offsets, int E, uint32_t* tile_expert,
                            uint32_t* tile_row0, uint32_t* tile_rows, uint32_t* n_row_tiles, int rows_per_tile,
                            cudaStream_t st);
-int launch_prepare_rows(const void* x, const uint32_t* perm, const uint32_t* src_map, int src_div, int64_t n_rows, int K,
-                        int permute8, void* xs, float* row_scale, cudaStream_t st);
+// n_rows_dev (nullable): device word with the number of rows that exist (<= n_rows, the host's bound)
+int launch_prepare_rows(const void* x, const uint32_t* perm, const uint32_t* src_map, int src_div, int64_t n_rows,
+                        const uint32_t* n_rows_dev, int K, int permute8, void* xs, float* row_scale, cudaStream_t st);
 int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows, const GroupedArgs& g, int nmat, int bits, const uint32_t* tile_expert,
                           const uint32_t* tile_row0, const uint32_t* tile_rows, const uint32_t* n_row_tiles, int E,
                           bool alternate, int* err, cudaStream_t st);
@@ -122,5 +124,27 @@ int launch_ep_return_table(const uint32_t* all_counts, int G, int E, int rank, c
 int launch_ep_combine(const EpPeers& peers, const uint32_t* idx, const uint32_t* inv, const uint32_t* offsets,
                       const uint32_t* dst_row0, const void* scores, int64_t T, int k, int64_t H, int E, int G,
                       uint32_t capacity, void* out, int* err, cudaStream_t st);
+
+// One-call expert-parallel block: device-side phase ordering through control blocks mapped between the ranks, and
+// the de-duplicated exchange (one row per token and destination rank).  kEpBufs peer-mapped buffers per rank:
+enum { kEpTok = 0, kEpPart = 1, kEpRowMap = 2, kEpSlotRows = 3, kEpSlotScores = 4, kEpCtl = 5, kEpBufs = 6 };
+struct EpExchange {
+  void* peer[kEpBufs][kEpMaxRanks];  // every rank's buffers (own entry = local pointer)
+  int G, E, rank, k;
+  int64_t H;
+  uint32_t cap_rows;   // assignments a rank can receive per step
+  uint32_t cap_tok;    // token rows a rank can receive per step
+  // device words of this rank: dst_row0 [E], local_counts [E/G], n_recv, tokbase [G], n_tok_recv, ntok [G]
+  uint32_t *dst_row0, *local_counts, *n_recv, *tokbase, *n_tok_recv, *ntok;
+};
+size_t ep_ctl_bytes(int G, int E);
+// slot [G][T]: position of token t among this rank's tokens that have an expert on rank d (0xffffffff: none)
+int launch_ep_token_slots(const uint32_t* idx, int64_t T, const EpExchange& x, uint32_t* slot, cudaStream_t st);
+int launch_ep_counts_exchange(const EpExchange& x, const uint32_t* counts, int* err, cudaStream_t st);
+int launch_ep_signal_wait(const EpExchange& x, int which, int* err, cudaStream_t st);
+int launch_ep_dispatch_dedup(const void* xrows, const uint32_t* idx, const uint32_t* inv, const uint32_t* offsets,
+                             const void* scores, const uint32_t* slot, int64_t T, const EpExchange& x, int* err, cudaStream_t st);
+int launch_ep_partial_combine(const void* y, bool y_f16, const EpExchange& x, int* err, cudaStream_t st);
+int launch_ep_final_combine(const uint32_t* slot, int64_t T, const EpExchange& x, void* out, cudaStream_t st);
 
 }  // namespace b200

@@ -77,6 +77,8 @@ __global__ void __launch_bounds__(256, NT == 1 ? 2 : 1) grouped_qmm_small_kernel
         src = (int)sp;
       else if (p.src_mode == kSrcPermDiv)
         src = (int)(p.perm[sp] / (uint32_t)p.src_div);
+      else if (p.src_mode == kSrcMapDirect)
+        src = (int)p.src_map[sp];
       else
         src = (int)p.src_map[p.perm[sp]];
       s_src[tid] = src;
@@ -170,30 +172,30 @@ __global__ void __launch_bounds__(256, NT == 1 ? 2 : 1) grouped_qmm_small_kernel
 // and fp16 input unless an element is more than 2^24 below the row maximum.
 template <int BITS, bool IN_F16>
 __global__ void __launch_bounds__(256) prepare_rows_small_kernel(const uint4* __restrict__ x, int64_t n_rows,
-                                                                 int vec_per_row, uint4* __restrict__ xs,
-                                                                 float* __restrict__ row_scale) {
+                                                                 const uint32_t* __restrict__ n_rows_dev, int vec_per_row,
+                                                                 uint4* __restrict__ xs, float* __restrict__ row_scale) {
   pdl_prologue();
   const int lane = threadIdx.x & 31;
   const int64_t r = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (r >= n_rows) return;
+  if (r >= n_rows || (n_rows_dev && r >= (int64_t)*n_rows_dev)) return;
   prepare_row_warp<BITS, IN_F16>(x + (size_t)r * vec_per_row, vec_per_row, xs + (size_t)r * vec_per_row, row_scale + r, lane);
 }
 
-int launch_prepare_rows_small(const void* x, int in_f16, int64_t n_rows, int K, int bits, void* xs, float* row_scale,
-                              cudaStream_t st) {
+int launch_prepare_rows_small(const void* x, int in_f16, int64_t n_rows, const uint32_t* n_rows_dev, int K, int bits,
+                              void* xs, float* row_scale, cudaStream_t st) {
   if (n_rows == 0) return 0;
   B200_REQUIRE(K % 8 == 0, "K must be a multiple of 8");
   const dim3 grid(cdiv(n_rows, 8)), block(256);
   const uint4* xp = static_cast<const uint4*>(x);
   uint4* op = static_cast<uint4*>(xs);
   if (bits == 4 && !in_f16)
-    B200_CUDA(launch_pdl(prepare_rows_small_kernel<4, false>, grid, block, 0, st, xp, n_rows, K / 8, op, row_scale));
+    B200_CUDA(launch_pdl(prepare_rows_small_kernel<4, false>, grid, block, 0, st, xp, n_rows, n_rows_dev, K / 8, op, row_scale));
   else if (bits == 4)
-    B200_CUDA(launch_pdl(prepare_rows_small_kernel<4, true>, grid, block, 0, st, xp, n_rows, K / 8, op, row_scale));
+    B200_CUDA(launch_pdl(prepare_rows_small_kernel<4, true>, grid, block, 0, st, xp, n_rows, n_rows_dev, K / 8, op, row_scale));
   else if (!in_f16)
-    B200_CUDA(launch_pdl(prepare_rows_small_kernel<8, false>, grid, block, 0, st, xp, n_rows, K / 8, op, row_scale));
+    B200_CUDA(launch_pdl(prepare_rows_small_kernel<8, false>, grid, block, 0, st, xp, n_rows, n_rows_dev, K / 8, op, row_scale));
   else
-    B200_CUDA(launch_pdl(prepare_rows_small_kernel<8, true>, grid, block, 0, st, xp, n_rows, K / 8, op, row_scale));
+    B200_CUDA(launch_pdl(prepare_rows_small_kernel<8, true>, grid, block, 0, st, xp, n_rows, n_rows_dev, K / 8, op, row_scale));
   return 0;
 }
 

@@ -715,13 +715,15 @@ __global__ void __launch_bounds__(256) build_row_tiles_kernel(const uint32_t* __
 // than 2^28 below the row maximum.
 __global__ void __launch_bounds__(256) prepare_rows_kernel(const uint4* __restrict__ x, const uint32_t* __restrict__ perm,
                                                            const uint32_t* __restrict__ src_map, int src_div, int64_t n_rows,
-                                                           int vec_per_row, int permute8, uint4* __restrict__ xs,
+                                                           const uint32_t* __restrict__ n_rows_dev, int vec_per_row,
+                                                           int permute8, uint4* __restrict__ xs,
                                                            float* __restrict__ row_scale) {
   const int lane = threadIdx.x & 31;
   const int64_t r = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (r >= n_rows) return;
-  // source row of sorted position r: r itself, perm[r] / src_div, or src_map[perm[r]]
-  const uint32_t src = !perm ? (uint32_t)r : (src_map ? src_map[perm[r]] : perm[r] / (uint32_t)src_div);
+  // n_rows is the host's bound; the number of rows that exist may live on the device (expert-parallel exchange)
+  if (r >= n_rows || (n_rows_dev && r >= (int64_t)*n_rows_dev)) return;
+  // source row of sorted position r: r itself, src_map[r], perm[r] / src_div, or src_map[perm[r]]
+  const uint32_t src = !perm ? (src_map ? src_map[r] : (uint32_t)r) : (src_map ? src_map[perm[r]] : perm[r] / (uint32_t)src_div);
   const uint4* xr = x + (size_t)src * vec_per_row;
   uint32_t mxbits = 0;  // max over |x| as bf16 bit patterns (monotonic for non-negative floats)
   for (int c = lane; c < vec_per_row; c += 32) {
@@ -771,11 +773,11 @@ int launch_build_row_tiles(const uint32_t* counts, const uint32_t* offsets, int 
   return 0;
 }
 
-int launch_prepare_rows(const void* x, const uint32_t* perm, const uint32_t* src_map, int src_div, int64_t n_rows, int K,
-                        int permute8, void* xs, float* row_scale, cudaStream_t st) {
+int launch_prepare_rows(const void* x, const uint32_t* perm, const uint32_t* src_map, int src_div, int64_t n_rows,
+                        const uint32_t* n_rows_dev, int K, int permute8, void* xs, float* row_scale, cudaStream_t st) {
   if (n_rows == 0) return 0;
-  prepare_rows_kernel<<<cdiv(n_rows, 8), 256, 0, st>>>(static_cast<const uint4*>(x), perm, src_map, src_div, n_rows, K / 8,
-                                                       permute8, static_cast<uint4*>(xs), row_scale);
+  prepare_rows_kernel<<<cdiv(n_rows, 8), 256, 0, st>>>(static_cast<const uint4*>(x), perm, src_map, src_div, n_rows, n_rows_dev,
+                                                       K / 8, permute8, static_cast<uint4*>(xs), row_scale);
   return 0;
 }
 

@@ -316,6 +316,78 @@ class PeerExpertParallelMoe:
         return out
 
 
+class DeviceSyncExpertParallelMoe:
+    """The expert-parallel block as ONE library call per step (`b200_moe_block_forward_ep`): route, sort, exchange
+    of the counts, dispatch, this rank's experts and the combine are enqueued on the current stream with no host
+    synchronisation and no collective; the ranks order their phases through control blocks in each other's
+    memory.  Constructing and closing are collective (handles travel over torch.distributed once)."""
+
+    N_HANDLES = 6
+
+    def __init__(self, pkg, gate_weight, local_switch_mlp, n_experts, top_k, capacity_rows, capacity_tokens=None,
+                 norm_topk_prob=True, router_mode=0, router_logit_bias=None, group=None, ctx=None, keep_routing=True):
+        from . import _lib as L
+        self.pkg, self.L, self.ctx = pkg, L, (ctx or L.default_context())
+        self.group, self.G, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+        if n_experts % self.G:
+            raise ValueError("the number of experts must be divisible by the number of ranks")
+        self.gate_weight, self.mlp, self.bias = gate_weight, local_switch_mlp, router_logit_bias
+        self.E, self.k, self.hidden = n_experts, top_k, local_switch_mlp.hidden
+        self.capacity = int(capacity_rows)
+        # token rows a rank can receive: every assignment could belong to a different token
+        self.capacity_tokens = int(capacity_tokens if capacity_tokens is not None else capacity_rows)
+        self.cfg = L.MoeConfig(self.hidden, local_switch_mlp.inter, n_experts, top_k, local_switch_mlp.gate_proj.bits,
+                               local_switch_mlp.gate_proj.group_size, router_mode, int(norm_topk_prob))
+        self.params = local_switch_mlp._params(gate_weight, router_logit_bias)
+        h = C.c_void_p()
+        mine = C.create_string_buffer(self.N_HANDLES * 64)
+        L.check(L.lib().b200_ep_comm_create(self.ctx.handle, self.G, self.rank, n_experts, top_k, self.hidden, self.capacity,
+                                            self.capacity_tokens, C.byref(h), mine))
+        self._h = h
+        gathered = [None] * self.G
+        dist.all_gather_object(gathered, bytes(mine.raw), group=group)
+        L.check(L.lib().b200_ep_comm_connect(self.ctx.handle, self._h, b"".join(gathered)))
+        dist.barrier(group=group)
+        self.keep_routing, self._aux, self.last = keep_routing, None, {}
+
+    def forward(self, x, out=None):
+        L = self.L
+        T = x.shape[0]
+        if out is None:
+            out = torch.empty_like(x)
+        aux_c = None
+        if self.keep_routing:
+            if self._aux is None or self._aux["indices"].shape[0] != T:
+                dev = x.device
+                self._aux = dict(indices=torch.empty((T, self.k), dtype=torch.int32, device=dev),
+                                 scores=torch.empty((T, self.k), dtype=torch.bfloat16, device=dev),
+                                 counts=torch.empty(self.E, dtype=torch.int32, device=dev))
+            a = self._aux
+            aux_c = L.MoeAux(a["indices"].data_ptr(), a["scores"].data_ptr(), None, None, a["counts"].data_ptr(), None, None, None)
+            self.last = dict(idx=a["indices"], scores=a["scores"], counts=a["counts"])
+        L.check(L.lib().b200_moe_block_forward_ep(self.ctx.handle, self._h, C.byref(self.cfg), C.byref(self.params), L.ptr(x), T,
+                                                  L.ptr(out), C.byref(aux_c) if aux_c is not None else None, L.stream_ptr()))
+        return out
+
+    def sent_rows(self):
+        """Token rows of the last step that left this GPU: one per (token, other rank that owns one of its experts)."""
+        idx = self.last["idx"].long()
+        dest = idx // (self.E // self.G)
+        hit = torch.zeros((idx.shape[0], self.G), dtype=torch.int32, device=idx.device)
+        hit.scatter_(1, dest, 1)
+        per_rank = hit.sum(dim=0)
+        return int(per_rank.sum() - per_rank[self.rank])
+
+    def close(self):
+        """Collective: every rank stops using the buffers before any rank unmaps or frees them."""
+        if self._h:
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+            self.L.check(self.L.lib().b200_ep_comm_destroy(self.ctx.handle, self._h))
+            self._h = None
+            dist.barrier(group=self.group)
+
+
 def _device_view(address, rows, cols, device):
     """A torch bf16 [rows, cols] view of device memory the library allocated (no ownership)."""
     class _Holder:
@@ -402,7 +474,11 @@ def bench_main(args, pkg, shape, cfg, peaks, metric, unit, workload_name, clock_
            for t_ in _draw_shard(pkg, shape, args.seed, rank, Eg, dev)]
     mlp = pkg.nn.SwitchGlu(*lin)
     bufs = None
-    if args.ep_transport in ("peer", "peer_push"):
+    if args.ep_transport == "device":
+        cap = T * k * world if cfg["zipf"] else min(T * k * world, 2 * T * k + 4096)
+        ep = DeviceSyncExpertParallelMoe(pkg, wr, mlp, E, k, cap + 64, T * world, norm_topk_prob=cfg["norm_topk_prob"],
+                                         router_mode=cfg["router_mode"], router_logit_bias=bias)
+    elif args.ep_transport in ("peer", "peer_push"):
         # every rank can at worst receive every assignment of every rank; 2x the balanced load is what uniform
         # random routing needs; skewed routing (one expert per GPU owning 43 % of all rows) needs the worst case
         C_ = args.ep_chunks or 1
@@ -471,7 +547,7 @@ def bench_main(args, pkg, shape, cfg, peaks, metric, unit, workload_name, clock_
     e2e_t = torch.tensor([ev0.elapsed_time(ev1) / args.steps], device=dev)
     dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_ms = e2e_t.item()
-    sent = torch.tensor([float(ep.last["sent_rows"])], device=dev)
+    sent = torch.tensor([float(ep.sent_rows() if hasattr(ep, "sent_rows") else ep.last["sent_rows"])], device=dev)
     dist.all_reduce(sent, op=dist.ReduceOp.SUM)
     phases = None
     if bufs and len(bufs) == 1 and os.environ.get("B200_EP_PHASES"):
@@ -493,10 +569,12 @@ def bench_main(args, pkg, shape, cfg, peaks, metric, unit, workload_name, clock_
                     config=dict(workload=workload_name(T) + f" per GPU, {Eg} experts per GPU", tokens_per_gpu=T,
                                 router_mode=cfg["router_mode"], norm_topk_prob=cfg["norm_topk_prob"], zipf_skew=cfg["zipf"],
                                 l2="flushed between iterations (512 MB overwrite)",
-                                parallelism=f"ep{world} (" + (("dispatch kernel + return fused into the down projection"
-                                                               if args.ep_transport == "peer_push" else
-                                                               "dispatch/combine kernels") + " over mapped peer memory"
-                                                              if bufs else "NCCL all-to-all-v dispatch + combine") + ")",
+                                parallelism=f"ep{world} (" + (
+                                    "one library call per step: dispatch/combine kernels over mapped peer memory, phases "
+                                    "ordered on the device, no host synchronisation" if args.ep_transport == "device" else
+                                    ("dispatch kernel + return fused into the down projection" if args.ep_transport == "peer_push"
+                                     else "dispatch/combine kernels") + " over mapped peer memory, NCCL-ordered"
+                                    if bufs else "NCCL all-to-all-v dispatch + combine") + ")",
                                 ep_chunks=(len(bufs) if bufs else 1),
                                 **shape),
                     roofline=dict(bound="tensor", achieved=flops / (ms * 1e-3) / 1e12 / world, peak=peaks["tensor"],
@@ -512,6 +590,8 @@ def bench_main(args, pkg, shape, cfg, peaks, metric, unit, workload_name, clock_
     ctx.check()
     for b in bufs or []:
         b.close()
+    if hasattr(ep, "close"):
+        ep.close()
     dist.barrier()
     dist.destroy_process_group()
     if not parity["ok"]:

@@ -28,7 +28,9 @@ def _worker(rank, world, port, cfg, transport, ret):
         mlp = ep.shard_switch_mlp(pkg, full.switch_mlp, rank, world)
         T = blk["T"]
         bufs = None
-        if transport.startswith("peer"):
+        if transport == "device":
+            moe = ep.DeviceSyncExpertParallelMoe(pkg, full.gate_weight, mlp, blk["E"], blk["k"], T * blk["k"])
+        elif transport.startswith("peer"):
             bufs = [ep.PeerBuffers(pkg, blk["H"], T * blk["k"]) for _ in range(2 if transport == "peer2" else 1)]
             moe = ep.PeerExpertParallelMoe(pkg, full.gate_weight, mlp, blk["E"], blk["k"], bufs,
                                            fused_return=(transport == "peer_push"))
@@ -43,6 +45,8 @@ def _worker(rank, world, port, cfg, transport, ret):
                          counts=moe.last["counts"].cpu().numpy().view(np.uint32), lo=lo, hi=hi)
         for b in bufs or []:
             b.close()
+        if hasattr(moe, "close"):
+            moe.close()
     finally:
         dist.destroy_process_group()
 
@@ -55,7 +59,7 @@ def _free_port():
 
 @pytest.mark.parametrize("cfg", [dict(T=96, H=256, E=8, I=128, k=2, seed=3),
                                  dict(T=700, H=512, E=16, I=256, k=4, seed=5)])
-@pytest.mark.parametrize("transport", ["nccl", "peer", "peer2", "peer_push"])
+@pytest.mark.parametrize("transport", ["nccl", "peer", "peer2", "peer_push", "device"])
 def test_expert_parallel_two_gpus(O, cfg, transport):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

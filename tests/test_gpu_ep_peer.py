@@ -84,3 +84,41 @@ def test_peer_exchange_reports_overflow(pkg):
     with pytest.raises(pkg.B200Error, match="more rows"):
         pkg.default_context().check()
     pkg.default_context().check()                # the status word is cleared by the failed check
+
+
+@pytest.mark.parametrize("cfg", [dict(T=96, H=256, E=8, I=128, k=2, seed=3),          # register kernel
+                                 dict(T=2400, H=512, E=8, I=256, k=2, seed=9)])      # tensor-core regime
+def test_one_call_block_single_rank(pkg, O, cfg, tmp_path):
+    """`b200_moe_block_forward_ep` with a group of ONE rank on one GPU: the device-side phase ordering runs
+    against its own flags (a rank is its own peer), twice in a row (step counter, buffer reuse), and a step
+    whose arrivals exceed the capacity drops them and reports it.  (Two and more ranks need one GPU each:
+    tests/test_gpu_ep.py.)"""
+    import torch.distributed as dist
+    from importlib import import_module
+    ep = import_module("mlx_rs_b200.ep")
+    dist.init_process_group("gloo", init_method=f"file://{tmp_path}/rdv", rank=0, world_size=1)
+    try:
+        blk = make_block(**cfg)
+        full = to_device(pkg, blk)
+        T, E, k = blk["T"], blk["E"], blk["k"]
+        x = torch.from_numpy(blk["x"]).bfloat16().cuda()
+        ref = O.moe_block(blk["x"], blk["wr"], blk["gate"], blk["up"], blk["down"], k)
+        rms = np.sqrt((ref["out_f32"] ** 2).mean())
+        moe = ep.DeviceSyncExpertParallelMoe(pkg, full.gate_weight, full.switch_mlp, E, k, T * k)
+        for _ in range(2):
+            out = moe.forward(x)
+        pkg.default_context().check()
+        assert np.array_equal(moe.last["idx"].cpu().numpy().view(np.uint32), ref["idx"])
+        assert np.array_equal(moe.last["counts"].cpu().numpy().view(np.uint32), ref["counts"])
+        d = np.abs(out.float().cpu().numpy() - ref["out_f32"])
+        assert np.all(d <= 2e-2 * rms + 2.0 ** -7 * np.abs(ref["out_f32"]))   # expert outputs and the result are bf16
+        assert moe.sent_rows() == 0
+        moe.close()
+        small = ep.DeviceSyncExpertParallelMoe(pkg, full.gate_weight, full.switch_mlp, E, k, T * k - 1)
+        small.forward(x)
+        with pytest.raises(pkg.B200Error, match="more rows"):
+            pkg.default_context().check()
+        pkg.default_context().check()
+        small.close()
+    finally:
+        dist.destroy_process_group()
