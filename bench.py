@@ -399,6 +399,8 @@ def main():
     if world > 1:
         from importlib import import_module
         ep = import_module("mlx_rs_b200.ep")
+        if args.workload == "stack":
+            return ep.bench_stack(args, pkg, SHAPE, CFG, peaks, METRIC, UNIT, ClockSampler)
         return ep.bench_main(args, pkg, SHAPE, CFG, peaks, METRIC, UNIT, workload_name, ClockSampler, zipf_bias)
 
     if args.workload == "stack":

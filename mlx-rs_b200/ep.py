@@ -316,38 +316,63 @@ class PeerExpertParallelMoe:
         return out
 
 
-class DeviceSyncExpertParallelMoe:
-    """The expert-parallel block as ONE library call per step (`b200_moe_block_forward_ep`): route, sort, exchange
-    of the counts, dispatch, this rank's experts and the combine are enqueued on the current stream with no host
-    synchronisation and no collective; the ranks order their phases through control blocks in each other's
-    memory.  Constructing and closing are collective (handles travel over torch.distributed once)."""
-
+class EpComm:
+    """This rank's exchange buffers and control block of the one-call expert-parallel block, connected to every
+    peer's (`b200_ep_comm_create` / `_connect`).  Constructing and closing are collective: the handles travel over
+    torch.distributed once.  One communicator serves any number of layers of the same shape (their steps follow
+    one another on the stream)."""
     N_HANDLES = 6
 
-    def __init__(self, pkg, gate_weight, local_switch_mlp, n_experts, top_k, capacity_rows, capacity_tokens=None,
+    def __init__(self, n_experts, top_k, hidden, capacity_rows, capacity_tokens=None, group=None, ctx=None):
+        from . import _lib as L
+        self.L, self.ctx, self.group = L, (ctx or L.default_context()), group
+        self.G, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if n_experts % self.G:
+            raise ValueError("the number of experts must be divisible by the number of ranks")
+        self.E, self.k, self.hidden = n_experts, top_k, hidden
+        self.capacity = int(capacity_rows)
+        # token rows a rank can receive: at worst every assignment belongs to a different token
+        self.capacity_tokens = int(capacity_tokens if capacity_tokens is not None else capacity_rows)
+        h = C.c_void_p()
+        mine = C.create_string_buffer(self.N_HANDLES * 64)
+        L.check(L.lib().b200_ep_comm_create(self.ctx.handle, self.G, self.rank, n_experts, top_k, hidden, self.capacity,
+                                            self.capacity_tokens, C.byref(h), mine))
+        self.handle = h
+        gathered = [None] * self.G
+        dist.all_gather_object(gathered, bytes(mine.raw), group=group)
+        L.check(L.lib().b200_ep_comm_connect(self.ctx.handle, self.handle, b"".join(gathered)))
+        dist.barrier(group=group)
+
+    def close(self):
+        """Collective: every rank stops using the buffers before any rank unmaps or frees them."""
+        if self.handle:
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+            self.L.check(self.L.lib().b200_ep_comm_destroy(self.ctx.handle, self.handle))
+            self.handle = None
+            dist.barrier(group=self.group)
+
+
+class DeviceSyncExpertParallelMoe:
+    """The expert-parallel block as ONE library call per step (`b200_moe_block_forward_ep`): route, sort, exchange
+    of the counts, de-duplicated dispatch, this rank's experts, partial sums and the combine are enqueued on the
+    current stream with no host synchronisation and no collective; the ranks order their phases through control
+    blocks in each other's memory.  `comm` is an EpComm (shared by the layers of a stack) or the capacity in rows
+    of a communicator this object creates and owns."""
+
+    def __init__(self, pkg, gate_weight, local_switch_mlp, n_experts, top_k, comm, capacity_tokens=None,
                  norm_topk_prob=True, router_mode=0, router_logit_bias=None, group=None, ctx=None, keep_routing=True):
         from . import _lib as L
         self.pkg, self.L, self.ctx = pkg, L, (ctx or L.default_context())
-        self.group, self.G, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
-        if n_experts % self.G:
-            raise ValueError("the number of experts must be divisible by the number of ranks")
         self.gate_weight, self.mlp, self.bias = gate_weight, local_switch_mlp, router_logit_bias
         self.E, self.k, self.hidden = n_experts, top_k, local_switch_mlp.hidden
-        self.capacity = int(capacity_rows)
-        # token rows a rank can receive: every assignment could belong to a different token
-        self.capacity_tokens = int(capacity_tokens if capacity_tokens is not None else capacity_rows)
+        self._own_comm = not isinstance(comm, EpComm)
+        self.comm = comm if isinstance(comm, EpComm) else EpComm(n_experts, top_k, self.hidden, comm, capacity_tokens,
+                                                                   group=group, ctx=self.ctx)
+        self.G, self.rank = self.comm.G, self.comm.rank
         self.cfg = L.MoeConfig(self.hidden, local_switch_mlp.inter, n_experts, top_k, local_switch_mlp.gate_proj.bits,
                                local_switch_mlp.gate_proj.group_size, router_mode, int(norm_topk_prob))
         self.params = local_switch_mlp._params(gate_weight, router_logit_bias)
-        h = C.c_void_p()
-        mine = C.create_string_buffer(self.N_HANDLES * 64)
-        L.check(L.lib().b200_ep_comm_create(self.ctx.handle, self.G, self.rank, n_experts, top_k, self.hidden, self.capacity,
-                                            self.capacity_tokens, C.byref(h), mine))
-        self._h = h
-        gathered = [None] * self.G
-        dist.all_gather_object(gathered, bytes(mine.raw), group=group)
-        L.check(L.lib().b200_ep_comm_connect(self.ctx.handle, self._h, b"".join(gathered)))
-        dist.barrier(group=group)
         self.keep_routing, self._aux, self.last = keep_routing, None, {}
 
     def forward(self, x, out=None):
@@ -365,8 +390,9 @@ class DeviceSyncExpertParallelMoe:
             a = self._aux
             aux_c = L.MoeAux(a["indices"].data_ptr(), a["scores"].data_ptr(), None, None, a["counts"].data_ptr(), None, None, None)
             self.last = dict(idx=a["indices"], scores=a["scores"], counts=a["counts"])
-        L.check(L.lib().b200_moe_block_forward_ep(self.ctx.handle, self._h, C.byref(self.cfg), C.byref(self.params), L.ptr(x), T,
-                                                  L.ptr(out), C.byref(aux_c) if aux_c is not None else None, L.stream_ptr()))
+        L.check(L.lib().b200_moe_block_forward_ep(self.ctx.handle, self.comm.handle, C.byref(self.cfg), C.byref(self.params),
+                                                  L.ptr(x), T, L.ptr(out), C.byref(aux_c) if aux_c is not None else None,
+                                                  L.stream_ptr()))
         return out
 
     def sent_rows(self):
@@ -379,13 +405,8 @@ class DeviceSyncExpertParallelMoe:
         return int(per_rank.sum() - per_rank[self.rank])
 
     def close(self):
-        """Collective: every rank stops using the buffers before any rank unmaps or frees them."""
-        if self._h:
-            torch.cuda.synchronize()
-            dist.barrier(group=self.group)
-            self.L.check(self.L.lib().b200_ep_comm_destroy(self.ctx.handle, self._h))
-            self._h = None
-            dist.barrier(group=self.group)
+        if self._own_comm:
+            self.comm.close()
 
 
 def _device_view(address, rows, cols, device):
@@ -596,3 +617,95 @@ def bench_main(args, pkg, shape, cfg, peaks, metric, unit, workload_name, clock_
     dist.destroy_process_group()
     if not parity["ok"]:
         raise SystemExit("expert-parallel output differs from the single-GPU block: " + json.dumps(parity))
+
+
+def bench_stack(args, pkg, shape, cfg, peaks, metric, unit, clock_sampler):
+    """bench.py --config 2 for N > 1: the 48-layer stack of pre-RMSNorm MoE blocks with residuals, experts sharded
+    E/N per GPU, every layer the one-call expert-parallel block over one shared communicator.  The work is the
+    single-GPU run's (strong scaling): the 2048 prefill tokens are split evenly over the ranks, the 256 decode
+    steps carry ONE token, which lives on rank 0 - the other ranks take part in every step with no tokens of
+    their own (their experts still receive the token's rows).  The decode step is replayed from a CUDA graph on
+    every rank.  Timing: per-rank CUDA events, max over ranks."""
+    import json
+    import os
+    import statistics as st
+    rank, world = dist.get_rank(), dist.get_world_size()
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    H, I, E, k = shape["hidden"], shape["inter"], shape["n_experts"], shape["top_k"]
+    Eg = E // world
+    n_layers, t_prefill, n_decode = args.layers, 2048, 256
+    Tp = t_prefill // world
+    ctx = pkg.default_context()
+    comm = EpComm(E, k, H, t_prefill * k, t_prefill, ctx=ctx)
+    blocks = []
+    for l in range(n_layers):
+        g = torch.Generator(device=dev).manual_seed(args.seed + l)
+        wr = (torch.randn(E, H, generator=g, device=dev, dtype=torch.float32) * 0.02).bfloat16()
+        lin = [pkg.nn.QuantizedSwitchLinear(*t_, shape["group_size"], shape["bits"])
+               for t_ in _draw_shard(pkg, shape, args.seed + 7919 * (l + 1), rank, Eg, dev)]
+        blocks.append(DeviceSyncExpertParallelMoe(pkg, wr, pkg.nn.SwitchGlu(*lin), E, k, comm, keep_routing=False, ctx=ctx))
+    stack = pkg.nn.MoeStack(blocks, eps=1e-6)
+    gx = torch.Generator(device=dev).manual_seed(args.seed + 99 + rank)
+    xp = torch.randn(Tp, H, generator=gx, device=dev, dtype=torch.float32).bfloat16()
+    xd = torch.zeros(1 if rank == 0 else 0, H, dtype=torch.bfloat16, device=dev)
+    holder = {}
+
+    def decode_step():
+        holder["o"] = stack.forward(xd)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        decode_step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        decode_step()
+
+    def sequence():
+        out = stack.forward(xp)
+        if rank == 0:
+            xd.copy_(out[-1:])
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(n_decode):
+            graph.replay()
+            if rank == 0:
+                xd.copy_(holder["o"])
+        ev1.record()
+        return ev0, ev1
+    for _ in range(max(1, args.warmup // 3)):
+        sequence()
+    torch.cuda.synchronize()
+    dist.barrier()
+    tot, dec = [], []
+    with clock_sampler(local) as clk:
+        for _ in range(args.steps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            e0, e1 = sequence()
+            b.record()
+            torch.cuda.synchronize()
+            dist.barrier()
+            tot.append(a.elapsed_time(b))
+            dec.append(e0.elapsed_time(e1))
+    ctx.check()
+    t = torch.tensor([st.mean(tot), st.mean(dec)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, dms = t[0].item(), t[1].item()
+    if rank == 0:
+        line = dict(metric=metric, value=(t_prefill + n_decode) / (ms * 1e-3), unit=unit, n_gpus=world, steps=args.steps,
+                    warmup=args.warmup, ms_per_step=ms, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16",
+                    data="synthetic",
+                    config=dict(workload=f"configs[2]: {n_layers} x (RMSNorm eps 1e-6 + MoE block + residual), 2048-token "
+                                         f"prefill ({Tp} per GPU) then 256 single-token decode steps (the token lives on rank 0)",
+                                l2="working set 2 GB per GPU per pass, far larger than L2",
+                                parallelism=f"ep{world}, {Eg} experts per GPU, one library call per layer, phases ordered on the "
+                                            "device", cuda_graph="decode steps", **shape),
+                    prefill=dict(tokens=t_prefill, ms=ms - dms, tokens_per_s=t_prefill / ((ms - dms) * 1e-3)),
+                    decode=dict(steps=n_decode, ms_per_token=dms / n_decode, tokens_per_s=n_decode / (dms * 1e-3)),
+                    roofline=None, cpu_baseline=None, e2e=None, clocks=clk.summary())
+        print(json.dumps(line))
+    comm.close()
+    dist.barrier()
+    dist.destroy_process_group()
