@@ -87,7 +87,19 @@ typedef struct {
 const char* b200_last_error(void);
 /* Same contract as mlx_set_error_handler (mlx-rs/src/error.rs:232-251). */
 void b200_set_error_handler(void (*handler)(const char* msg, void* data), void* data, void (*dtor)(void*));
-/* Creates a context on CUDA device `device` (cudaSetDevice is called). */
+/* Creates a context on CUDA device `device` (cudaSetDevice is called).
+ *
+ * A context owns ONE scratch arena, and every call that takes a context starts handing it out from the
+ * beginning again.  Hence: one thread at a time, and one stream at a time - two calls on the same context
+ * whose kernels can overlap on the GPU (different streams without an event between them) race on the arena
+ * (tile tables, intermediate rows, the status words).  Use one context per concurrently used stream.
+ * Calls that take no scratch and may go to any stream: b200_moe_combine, b200_take_rows, b200_add,
+ * b200_rms_norm, b200_add_rms_norm, b200_softmax_axis, b200_argpartition_axis, b200_take_along_axis, b200_take_axis,
+ * b200_topk_axis, b200_quantize, b200_ep_layout, b200_ep_dispatch, b200_ep_combine, b200_ep_return_table and the b200_ep_buffer_* calls.
+ *
+ * The arena grows on demand (free + cudaMalloc after cudaDeviceSynchronize).  Growth invalidates the addresses
+ * that CUDA graphs captured earlier hold and is refused (status 1, nothing launched) while the call's stream is
+ * being captured: size the arena with b200_ctx_reserve before capturing or replaying graphs. */
 int b200_ctx_create(b200_ctx** out, int device);
 int b200_ctx_destroy(b200_ctx* ctx);
 /* Pre-sizes the scratch memory for blocks of up to `max_tokens` tokens so that later calls
@@ -278,9 +290,13 @@ int b200_ep_buffer_free(b200_ctx* ctx, void* ptr);
  * (peer_y[s], bf16 [T_s * top_k, hidden] in the source's own sorted order); b200_switch_glu_sorted_scatter
  * is b200_switch_glu_sorted whose epilogue stores each finished row to row_addr[i] (peer stores), so
  * the transfer back overlaps the products tile by tile and the source finishes with a local
- * b200_moe_combine after one barrier. */
+ * b200_moe_combine after one barrier.  n_rows = entries of row_addr (rows this rank received), capacity_rows = rows
+ * of every source's return buffer: an entry past either bound is not written (the table) or written as address 0,
+ * which the epilogue skips (the buffer), and b200_ctx_check reports it.  The grouped products likewise follow
+ * `counts` only up to `n` rows in total and report counts that promise more. */
 int b200_ep_return_table(b200_ctx* ctx, const uint32_t* all_counts, int n_ranks, int n_experts, int rank,
-                         void* const* peer_y, int64_t hidden, unsigned long long* row_addr, void* stream);
+                         void* const* peer_y, int64_t hidden, int64_t n_rows, int64_t capacity_rows,
+                         unsigned long long* row_addr, void* stream);
 int b200_switch_glu_sorted_scatter(b200_ctx* ctx, const b200_moe_config* cfg, const b200_moe_params* params,
                                    const void* rows, const uint32_t* counts, int64_t n,
                                    const unsigned long long* out_row_addr, void* stream);

@@ -69,7 +69,7 @@ EXPORTS = {
     "b200_switch_glu_sorted": (C.c_int, [C.c_void_p, C.POINTER(MoeConfig), C.POINTER(MoeParams), C.c_void_p, C.c_void_p,
                                          C.c_int64, C.c_void_p, C.c_void_p]),
     "b200_ep_return_table": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_int64,
-                                       C.c_void_p, C.c_void_p]),
+                                       C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
     "b200_switch_glu_sorted_scatter": (C.c_int, [C.c_void_p, C.POINTER(MoeConfig), C.POINTER(MoeParams), C.c_void_p,
                                                  C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "b200_ep_buffer_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),

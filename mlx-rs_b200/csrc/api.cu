@@ -62,8 +62,17 @@ struct b200_ctx {
   }
 };
 
-static int ctx_grow(b200_ctx* c, size_t bytes) {
+// Growing frees and reallocates the arena after a device-wide synchronisation.  Neither is legal while `stream` is
+// being captured into a graph (and graphs captured earlier hold addresses inside the old arena), so a capture in
+// progress makes the call fail instead: reserve the arena (b200_ctx_reserve) before capturing.
+static int ctx_grow(b200_ctx* c, size_t bytes, void* stream = nullptr) {
   if (bytes <= c->ws_bytes) return 0;
+  if (stream) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    B200_CUDA(cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &cap));
+    B200_REQUIRE(cap == cudaStreamCaptureStatusNone,
+                 "the scratch arena would have to grow during stream capture: call b200_ctx_reserve before capturing");
+  }
   B200_CUDA(cudaDeviceSynchronize());
   if (c->ws) B200_CUDA(cudaFree(c->ws));
   c->ws = nullptr;
@@ -84,7 +93,7 @@ static size_t block_scratch_bytes(const b200_moe_config& cfg, int64_t T) {
   b += al(sizeof(double) * E * cfg.hidden);          // float64 image of the router weight
   b += al(sizeof(uint32_t) * n) * 3;                 // idx, perm, inv
   b += al(sizeof(uint16_t) * n);                     // scores
-  b += al(sizeof(uint32_t) * (E + 1)) * 3 + al(16);  // counts, offsets, active, n_active
+  b += al(sizeof(uint32_t) * (E + 1)) * 4 + al(16);  // counts (twice: the caller's and the bounded copy), offsets, active, n_active
   b += al(sizeof(uint32_t) * permute_scratch_words(n, (int)E));
   b += al(sizeof(uint16_t) * n * cfg.inter);         // h (bf16, or fp16 on the tensor-core path)
   b += al(sizeof(float) * n * cfg.hidden);           // per-assignment outputs (float32, or fp16 on the tensor-core path)
@@ -197,7 +206,7 @@ int b200_ctx_check(b200_ctx* c, void* stream) {
     B200_FAIL(h == 2   ? "an expert index was out of range"
               : h == 3 ? "a kernel gave up waiting on its own pipeline (2 s limit)"
               : h == 5 ? "a rank would receive more rows than its exchange buffers hold"
-              : h == 6 ? "an expert-parallel routing table was inconsistent"
+              : h == 6 ? "per-expert counts or an expert-parallel routing table did not agree with the row count"
                        : "a gather index was out of range");
   }
   return 0;
@@ -349,7 +358,7 @@ int b200_quantized_matmul(b200_ctx* c, const void* x, const uint32_t* w, const v
     LAUNCHED(c, 1);
     return 0;
   }
-  if (ctx_grow(c, 4096 + grouped_scratch_bytes(M, M, K, 1))) return 1;
+  if (ctx_grow(c, 4096 + grouped_scratch_bytes(M, M, K, 1), stream)) return 1;
   uint32_t* seg = static_cast<uint32_t*>(c->take(64));
   launch_dense_segments(seg + 0, seg + 4, seg + 8, seg + 12, (uint32_t)M, st);
   LAUNCHED(c, 1);
@@ -395,7 +404,7 @@ int b200_gather_qmm(b200_ctx* c, const void* x, const uint32_t* w, const void* s
   }
   size_t need = al(sizeof(uint32_t) * n) * 4 + al(sizeof(uint32_t) * (E + 1)) * 3 + al(16) +
                 al(sizeof(uint32_t) * permute_scratch_words(n, (int)E)) + grouped_scratch_bytes(n, Bx * M, K, E) + 4096;
-  if (ctx_grow(c, need)) return 1;
+  if (ctx_grow(c, need, stream)) return 1;
   uint32_t* flat_e = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
   uint32_t* flat_s = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
   uint32_t* perm = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
@@ -435,8 +444,44 @@ int b200_gather_mm(b200_ctx* c, const void* a, const void* b, const uint32_t* lh
   B200_REQUIRE(rhs_indices || n_idx <= Bb, "without rhs_indices b needs one batch entry per index");
   if (n_idx == 0 || M == 0 || N == 0) return 0;
   B200_REQUIRE(a && b && out, "null tensor");
-  if (launch_gather_mm(a, b, lhs_indices, rhs_indices, Ba, Bb, M, K, N, n_idx, out, c->err, static_cast<cudaStream_t>(stream)))
-    return 1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t n = n_idx * M;
+  // enough rows to fill 128-row tiles and a shape the tensor-core kernel takes: sort the rows by matrix, gather a
+  // into that order and run the grouped tcgen05 kernel without its dequantisation stage
+  if (K % 64 == 0 && N % 8 == 0 && Bb <= 256 && n >= 512 && n < (int64_t(1) << 31) && c->qmm_path != B200_QMM_SMALL) {
+    const int E = (int)Bb;
+    const size_t tw = prefill_tile_words(n, E);
+    size_t need = al(sizeof(uint32_t) * n) * 4 + al(sizeof(uint32_t) * (E + 1)) * 3 + al(16) +
+                  al(sizeof(uint32_t) * permute_scratch_words(n, E)) + al(sizeof(uint16_t) * n * K) +
+                  (al(sizeof(uint32_t) * tw) * 3 + al(16)) + 4096;
+    if (ctx_grow(c, need, stream)) return 1;
+    uint32_t* flat_e = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
+    uint32_t* flat_s = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
+    uint32_t* perm = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
+    uint32_t* inv = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
+    uint32_t* counts = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+    uint32_t* offsets = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+    uint32_t* active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+    uint32_t* n_active = static_cast<uint32_t*>(c->take(16));
+    uint32_t* chunk = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * permute_scratch_words(n, E)));
+    void* a_sorted = c->take(sizeof(uint16_t) * n * K);
+    uint32_t* tile_expert = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
+    uint32_t* tile_row0 = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
+    uint32_t* tile_rows = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * tw));
+    uint32_t* n_row_tiles = static_cast<uint32_t*>(c->take(16));
+    B200_REQUIRE(flat_e && flat_s && perm && inv && counts && offsets && active && n_active && chunk && a_sorted && tile_expert &&
+                     tile_row0 && tile_rows && n_row_tiles,
+                 "scratch arena too small");
+    launch_expand_indices(lhs_indices, rhs_indices, n_idx, (int)M, Ba, flat_e, flat_s, c->err, st);
+    launch_permute(flat_e, n, E, perm, inv, counts, offsets, active, n_active, chunk, c->err, st);
+    launch_gather_rows(a, perm, flat_s, n, K, a_sorted, st);
+    launch_build_row_tiles(counts, offsets, E, tile_expert, tile_row0, tile_rows, n_row_tiles, 128, st);
+    if (launch_gather_mm_tc(a_sorted, n, b, E, (int)K, (int)N, perm, out, tile_expert, tile_row0, tile_rows, n_row_tiles, c->err, st))
+      return 1;
+    LAUNCHED(c, 4 + permute_launches(n));
+    return 0;
+  }
+  if (launch_gather_mm(a, b, lhs_indices, rhs_indices, Ba, Bb, M, K, N, n_idx, out, c->err, st)) return 1;
   LAUNCHED(c, 1);
   return 0;
 }
@@ -498,7 +543,7 @@ int b200_argsort_axis(b200_ctx* c, const uint32_t* keys, int64_t rows, int64_t c
   const int E = key_bound;
   size_t need = al(sizeof(uint32_t) * cols) + al(sizeof(uint32_t) * (E + 1)) * 3 + al(16) +
                 al(sizeof(uint32_t) * permute_scratch_words(cols, E)) + 4096;
-  if (ctx_grow(c, need)) return 1;
+  if (ctx_grow(c, need, stream)) return 1;
   uint32_t* inv = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * cols));
   uint32_t* counts = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
   uint32_t* offsets = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
@@ -570,7 +615,7 @@ int b200_router_topk(b200_ctx* c, const b200_moe_config* cfg, const void* x, con
   if (T == 0) return 0;
   B200_REQUIRE(x && wr && indices && scores, "null tensor");
   const size_t w64_bytes = sizeof(double) * (size_t)cfg->n_experts * cfg->hidden;
-  if (ctx_grow(c, al(sizeof(uint16_t) * T * cfg->n_experts) + al(w64_bytes) + 4096)) return 1;
+  if (ctx_grow(c, al(sizeof(uint16_t) * T * cfg->n_experts) + al(w64_bytes) + 4096, stream)) return 1;
   if (!logits) logits = c->take(sizeof(uint16_t) * T * cfg->n_experts);
   double* w64 = static_cast<double*>(c->take(w64_bytes));
   B200_REQUIRE(logits && w64, "scratch arena too small");
@@ -590,7 +635,7 @@ int b200_moe_permute(b200_ctx* c, const uint32_t* indices, int64_t n, int E, uin
   B200_REQUIRE(n == 0 || (indices && perm && inv), "null tensor");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   size_t need = al(sizeof(uint32_t) * (E + 1)) + al(16) + al(sizeof(uint32_t) * permute_scratch_words(n, E)) + 4096;
-  if (ctx_grow(c, need)) return 1;
+  if (ctx_grow(c, need, stream)) return 1;
   uint32_t* active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
   uint32_t* n_active = static_cast<uint32_t*>(c->take(16));
   uint32_t* chunk = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * permute_scratch_words(n, E)));
@@ -823,7 +868,7 @@ int b200_switch_glu_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_
   B200_REQUIRE(T >= 0 && T * cfg->top_k < (int64_t(1) << 31), "bad token count");
   if (T == 0) return 0;
   B200_REQUIRE(x && indices && out, "null tensor");
-  if (ctx_grow(c, block_scratch_bytes(*cfg, T))) return 1;
+  if (ctx_grow(c, block_scratch_bytes(*cfg, T), stream)) return 1;
   return experts_forward(c, *cfg, *params, x, indices, nullptr, T, out, nullptr, static_cast<cudaStream_t>(stream));
 }
 
@@ -835,7 +880,7 @@ int b200_moe_block_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_m
   if (T == 0) return 0;
   B200_REQUIRE(x && out, "null tensor");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (ctx_grow(c, block_scratch_bytes(*cfg, T))) return 1;
+  if (ctx_grow(c, block_scratch_bytes(*cfg, T), stream)) return 1;
   const int64_t n = T * cfg->top_k;
   void* logits = c->take(sizeof(uint16_t) * T * cfg->n_experts);
   uint32_t* idx = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
@@ -895,15 +940,16 @@ int b200_switch_glu_sorted(b200_ctx* c, const b200_moe_config* cfg, const b200_m
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   b200_moe_config one = *cfg;
   one.top_k = 1;  // n rows, one assignment each
-  if (ctx_grow(c, block_scratch_bytes(one, n))) return 1;
+  if (ctx_grow(c, block_scratch_bytes(one, n), stream)) return 1;
   const int E = cfg->n_experts;
   uint32_t* offsets = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
   uint32_t* active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
   uint32_t* n_active = static_cast<uint32_t*>(c->take(16));
-  B200_REQUIRE(offsets && active && n_active, "scratch arena too small");
-  launch_segments_from_counts(counts, E, offsets, active, n_active, st);
+  uint32_t* cnt = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  B200_REQUIRE(offsets && active && n_active && cnt, "scratch arena too small");
+  launch_segments_from_counts(counts, E, n, cnt, offsets, active, n_active, c->err, st);
   LAUNCHED(c, 1);
-  return experts_sorted(c, one, *params, rows, nullptr, 1, counts, offsets, active, n_active, n, nullptr, out, st, nullptr);
+  return experts_sorted(c, one, *params, rows, nullptr, 1, cnt, offsets, active, n_active, n, nullptr, out, st, nullptr);
 }
 
 static int fill_peers(EpPeers& pe, void* const* peers, int G);
@@ -918,20 +964,21 @@ int b200_switch_glu_sorted_scatter(b200_ctx* c, const b200_moe_config* cfg, cons
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   b200_moe_config one = *cfg;
   one.top_k = 1;
-  if (ctx_grow(c, block_scratch_bytes(one, n))) return 1;
+  if (ctx_grow(c, block_scratch_bytes(one, n), stream)) return 1;
   const int E = cfg->n_experts;
   uint32_t* offsets = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
   uint32_t* active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
   uint32_t* n_active = static_cast<uint32_t*>(c->take(16));
-  B200_REQUIRE(offsets && active && n_active, "scratch arena too small");
-  launch_segments_from_counts(counts, E, offsets, active, n_active, st);
+  uint32_t* cnt = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (E + 1)));
+  B200_REQUIRE(offsets && active && n_active && cnt, "scratch arena too small");
+  launch_segments_from_counts(counts, E, n, cnt, offsets, active, n_active, c->err, st);
   LAUNCHED(c, 1);
-  return experts_sorted(c, one, *params, rows, nullptr, 1, counts, offsets, active, n_active, n, nullptr, nullptr, st,
+  return experts_sorted(c, one, *params, rows, nullptr, 1, cnt, offsets, active, n_active, n, nullptr, nullptr, st,
                         nullptr, out_row_addr);
 }
 
 int b200_ep_return_table(b200_ctx* c, const uint32_t* all_counts, int n_ranks, int n_experts, int rank, void* const* peer_y,
-                         int64_t hidden, unsigned long long* row_addr, void* stream) {
+                         int64_t hidden, int64_t n_rows, int64_t capacity_rows, unsigned long long* row_addr, void* stream) {
   CTX_ENTER(c);
   B200_REQUIRE(all_counts && row_addr, "null tensor");
   B200_REQUIRE(n_ranks >= 1 && n_ranks <= kEpMaxRanks && rank >= 0 && rank < n_ranks, "bad rank");
@@ -939,7 +986,9 @@ int b200_ep_return_table(b200_ctx* c, const uint32_t* all_counts, int n_ranks, i
   B200_REQUIRE(hidden > 0 && hidden % 8 == 0, "hidden must be a multiple of 8");
   EpPeers pe;
   if (fill_peers(pe, peer_y, n_ranks)) return 1;
-  launch_ep_return_table(all_counts, n_ranks, n_experts, rank, pe, hidden, row_addr, static_cast<cudaStream_t>(stream));
+  B200_REQUIRE(n_rows >= 0 && capacity_rows >= 0, "bad row bounds");
+  launch_ep_return_table(all_counts, n_ranks, n_experts, rank, pe, hidden, n_rows, capacity_rows, row_addr, c->err,
+                         static_cast<cudaStream_t>(stream));
   LAUNCHED(c, 1);
   return 0;
 }
@@ -1160,7 +1209,7 @@ int b200_moe_block_forward_ep(b200_ctx* c, b200_ep_comm* e, const b200_moe_confi
                              al(sizeof(uint32_t) * n) * 3 + al(sizeof(uint16_t) * n) + al(sizeof(uint32_t) * (E + 1)) * 3 + al(16) +
                              al(sizeof(uint32_t) * permute_scratch_words(n, E)) + al(sizeof(uint32_t) * (size_t)G * T) +
                              al(sizeof(uint16_t) * (size_t)ex.cap_tok * cfg->hidden) + al(sizeof(float) * ex.cap_tok) + 4096;
-  if (ctx_grow(c, route_bytes + block_scratch_bytes(local, cap))) return 1;
+  if (ctx_grow(c, route_bytes + block_scratch_bytes(local, cap), stream)) return 1;
   void* logits = c->take(sizeof(uint16_t) * T * E);
   uint32_t* idx = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
   void* scores = c->take(sizeof(uint16_t) * n);
@@ -1195,12 +1244,13 @@ int b200_moe_block_forward_ep(b200_ctx* c, b200_ep_comm* e, const b200_moe_confi
     uint32_t* offsets = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (Eg + 1)));
     uint32_t* active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (Eg + 1)));
     uint32_t* n_active = static_cast<uint32_t*>(c->take(16));
-    B200_REQUIRE(offsets && active && n_active, "scratch arena too small");
-    launch_segments_from_counts(ex.local_counts, Eg, offsets, active, n_active, st);
+    uint32_t* cnt = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (Eg + 1)));
+    B200_REQUIRE(offsets && active && n_active && cnt, "scratch arena too small");
+    launch_segments_from_counts(ex.local_counts, Eg, cap, cnt, offsets, active, n_active, c->err, st);
     LAUNCHED(c, 1);
     ExchangeRows xr{static_cast<const uint32_t*>(e->own[kEpRowMap]), (int64_t)ex.cap_tok, ex.n_tok_recv, ex.n_recv};
     int y_fmt = kOutBf16;
-    if (experts_sorted(c, local, *params, e->own[kEpTok], nullptr, 1, ex.local_counts, offsets, active, n_active, cap, nullptr,
+    if (experts_sorted(c, local, *params, e->own[kEpTok], nullptr, 1, cnt, offsets, active, n_active, cap, nullptr,
                        e->y, st, &y_fmt, nullptr, &xr))
       return 1;
     if (launch_ep_partial_combine(e->y, y_fmt == kOutF16, ex, c->err, st)) return 1;

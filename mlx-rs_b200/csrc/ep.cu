@@ -33,13 +33,23 @@ __device__ __forceinline__ uint32_t f16x2_sat_bits(float lo, float hi) {
 }
 
 // ---- segment tables from per-expert counts ------------------------------------------------
-__global__ void segments_from_counts_kernel(const uint32_t* __restrict__ counts, int E, uint32_t* __restrict__ offsets,
-                                            uint32_t* __restrict__ active, uint32_t* __restrict__ n_active) {
+// counts_out is counts cut off where the running sum would pass n_rows (the rows the caller's buffers hold): the
+// grouped products walk counts_out / offsets, so counts that promise more rows than exist cannot make them read or
+// write past the buffers; *err = 6 reports the cut.
+__global__ void segments_from_counts_kernel(const uint32_t* __restrict__ counts, int E, int64_t n_rows,
+                                            uint32_t* __restrict__ counts_out, uint32_t* __restrict__ offsets,
+                                            uint32_t* __restrict__ active, uint32_t* __restrict__ n_active,
+                                            int* __restrict__ err) {
   if (threadIdx.x != 0) return;
   uint32_t run = 0, na = 0;
   for (int e = 0; e < E; ++e) {
     offsets[e] = run;
-    const uint32_t c = counts[e];
+    uint32_t c = counts[e];
+    if ((int64_t)run + c > n_rows) {
+      c = (uint32_t)(n_rows - run);
+      *err = 6;
+    }
+    counts_out[e] = c;
     if (c) active[na++] = e;
     run += c;
   }
@@ -47,9 +57,9 @@ __global__ void segments_from_counts_kernel(const uint32_t* __restrict__ counts,
   *n_active = na;
 }
 
-int launch_segments_from_counts(const uint32_t* counts, int E, uint32_t* offsets, uint32_t* active, uint32_t* n_active,
-                                cudaStream_t st) {
-  segments_from_counts_kernel<<<1, 32, 0, st>>>(counts, E, offsets, active, n_active);
+int launch_segments_from_counts(const uint32_t* counts, int E, int64_t n_rows, uint32_t* counts_out, uint32_t* offsets,
+                                uint32_t* active, uint32_t* n_active, int* err, cudaStream_t st) {
+  segments_from_counts_kernel<<<1, 32, 0, st>>>(counts, E, n_rows, counts_out, offsets, active, n_active, err);
   return 0;
 }
 
@@ -175,8 +185,10 @@ int launch_ep_dispatch(const void* x, const uint32_t* idx, const uint32_t* perm,
 // overlaps the products tile by tile and the source's combine reads local memory only.
 // One CTA per (local expert, source rank) segment.
 __global__ void __launch_bounds__(256) ep_return_table_kernel(const uint32_t* __restrict__ all_counts, int G, int E,
-                                                              int rank, EpPeers peers_y, int64_t row_bytes,
-                                                              unsigned long long* __restrict__ row_addr) {
+                                                              int rank, EpPeers peers_y, int64_t row_bytes, int64_t n_rows,
+                                                              int64_t capacity_rows,
+                                                              unsigned long long* __restrict__ row_addr,
+                                                              int* __restrict__ err) {
   const int Eg = E / G;
   const int el = blockIdx.x / G, s = blockIdx.x % G;
   const int e = rank * Eg + el;
@@ -194,13 +206,24 @@ __global__ void __launch_bounds__(256) ep_return_table_kernel(const uint32_t* __
   __syncthreads();
   const uint32_t len = all_counts[s * E + e];
   const unsigned long long base = reinterpret_cast<unsigned long long>(peers_y.p[s]);
-  for (uint32_t j = threadIdx.x; j < len; j += blockDim.x)
-    row_addr[s_start + j] = base + (unsigned long long)(s_src0 + j) * (unsigned long long)row_bytes;
+  for (uint32_t j = threadIdx.x; j < len; j += blockDim.x) {
+    const int64_t slot = (int64_t)s_start + j, dst = (int64_t)s_src0 + j;
+    if (slot >= n_rows) {  // the table itself ends here
+      *err = 5;
+      continue;
+    }
+    if (dst >= capacity_rows) {  // the source's return buffer ends before this row: address 0 = "drop the row"
+      *err = 5;
+      row_addr[slot] = 0ull;
+      continue;
+    }
+    row_addr[slot] = base + (unsigned long long)dst * (unsigned long long)row_bytes;
+  }
 }
 
-int launch_ep_return_table(const uint32_t* all_counts, int G, int E, int rank, const EpPeers& peers_y, int64_t H,
-                           unsigned long long* row_addr, cudaStream_t st) {
-  ep_return_table_kernel<<<(E / G) * G, 256, 0, st>>>(all_counts, G, E, rank, peers_y, H * 2, row_addr);
+int launch_ep_return_table(const uint32_t* all_counts, int G, int E, int rank, const EpPeers& peers_y, int64_t H, int64_t n_rows,
+                           int64_t capacity_rows, unsigned long long* row_addr, int* err, cudaStream_t st) {
+  ep_return_table_kernel<<<(E / G) * G, 256, 0, st>>>(all_counts, G, E, rank, peers_y, H * 2, n_rows, capacity_rows, row_addr, err);
   return 0;
 }
 

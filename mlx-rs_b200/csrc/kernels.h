@@ -101,6 +101,11 @@ int launch_gather_qmm_generic(const void* x, const uint32_t* wq, const void* sca
                               int64_t n_idx, int transpose, int gs, int bits, void* out, int* err, cudaStream_t st);
 int launch_gather_mm(const void* a, const void* b, const uint32_t* lhs, const uint32_t* rhs, int64_t Ba, int64_t Bb,
                      int64_t M, int64_t K, int64_t N, int64_t n_idx, void* out, int* err, cudaStream_t st);
+int launch_gather_rows(const void* x, const uint32_t* perm, const uint32_t* src_map, int64_t n_rows, int64_t cols, void* out,
+                       cudaStream_t st);
+int launch_gather_mm_tc(const void* a_sorted, int64_t rows, const void* b, int Bb, int K, int N, const uint32_t* perm, void* out,
+                        const uint32_t* tile_expert, const uint32_t* tile_row0, const uint32_t* tile_rows,
+                        const uint32_t* n_row_tiles, int* err, cudaStream_t st);
 int launch_dense_segments(uint32_t* counts, uint32_t* offsets, uint32_t* active, uint32_t* n_active, uint32_t rows,
                           cudaStream_t st);
 int launch_expand_indices(const uint32_t* lhs, const uint32_t* rhs, int64_t n_idx, int M, int64_t Bx, uint32_t* flat_expert,
@@ -112,15 +117,15 @@ constexpr int kEpMaxRanks = 16;
 struct EpPeers {
   void* p[kEpMaxRanks];       // the same exchange buffer on every rank, indexed by rank (own entry = local pointer)
 };
-int launch_segments_from_counts(const uint32_t* counts, int E, uint32_t* offsets, uint32_t* active, uint32_t* n_active,
-                                cudaStream_t st);
+int launch_segments_from_counts(const uint32_t* counts, int E, int64_t n_rows, uint32_t* counts_out, uint32_t* offsets,
+                                uint32_t* active, uint32_t* n_active, int* err, cudaStream_t st);
 int launch_ep_layout(const uint32_t* all_counts, int G, int E, int rank, uint32_t capacity, uint32_t* dst_row0,
                      uint32_t* local_counts, int* err, cudaStream_t st);
 int launch_ep_dispatch(const void* x, const uint32_t* idx, const uint32_t* perm, const uint32_t* offsets,
                        const uint32_t* dst_row0, int64_t n, int k, int64_t H, int E, int G, int rank, const EpPeers& peers,
                        uint32_t capacity, int* err, cudaStream_t st);
-int launch_ep_return_table(const uint32_t* all_counts, int G, int E, int rank, const EpPeers& peers_y, int64_t H,
-                           unsigned long long* row_addr, cudaStream_t st);
+int launch_ep_return_table(const uint32_t* all_counts, int G, int E, int rank, const EpPeers& peers_y, int64_t H, int64_t n_rows,
+                           int64_t capacity_rows, unsigned long long* row_addr, int* err, cudaStream_t st);
 int launch_ep_combine(const EpPeers& peers, const uint32_t* idx, const uint32_t* inv, const uint32_t* offsets,
                       const uint32_t* dst_row0, const void* scores, int64_t T, int k, int64_t H, int E, int G,
                       uint32_t capacity, void* out, int* err, cudaStream_t st);

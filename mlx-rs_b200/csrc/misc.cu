@@ -485,7 +485,7 @@ __global__ void expand_indices_kernel(const uint32_t* __restrict__ lhs, const ui
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_idx * M) return;
   int64_t b = i / M, m = i % M;
-  flat_expert[i] = rhs[b];
+  flat_expert[i] = rhs ? rhs[b] : (uint32_t)b;
   uint32_t src = lhs ? lhs[b] : (uint32_t)b;
   if ((int64_t)src >= Bx) {
     *err = 1;
@@ -493,6 +493,25 @@ __global__ void expand_indices_kernel(const uint32_t* __restrict__ lhs, const ui
   }
   flat_src[i] = src * (uint32_t)M + (uint32_t)m;
 }
+// out[p, :] = x[src_map[perm[p]], :] for rows of 2-byte elements (16-byte vectors): the rows of a gathered product
+// in the order of its sort.
+__global__ void gather_rows_kernel(const uint4* __restrict__ x, const uint32_t* __restrict__ perm,
+                                   const uint32_t* __restrict__ src_map, int64_t n_rows, int vec_per_row,
+                                   uint4* __restrict__ out) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_rows * vec_per_row) return;
+  const int64_t r = i / vec_per_row;
+  out[i] = __ldg(x + (size_t)src_map[perm[r]] * vec_per_row + (i % vec_per_row));
+}
+int launch_gather_rows(const void* x, const uint32_t* perm, const uint32_t* src_map, int64_t n_rows, int64_t cols, void* out,
+                       cudaStream_t st) {
+  if (n_rows == 0) return 0;
+  const int64_t n = n_rows * (cols / 8);
+  gather_rows_kernel<<<cdiv(n, 256), 256, 0, st>>>(static_cast<const uint4*>(x), perm, src_map, n_rows, (int)(cols / 8),
+                                                   static_cast<uint4*>(out));
+  return 0;
+}
+
 int launch_expand_indices(const uint32_t* lhs, const uint32_t* rhs, int64_t n_idx, int M, int64_t Bx, uint32_t* flat_expert,
                           uint32_t* flat_src, int* err, cudaStream_t st) {
   if (n_idx * M == 0) return 0;

@@ -154,9 +154,10 @@ __global__ void __launch_bounds__(256, NT == 1 ? 2 : 1) grouped_qmm_small_kernel
         outv = v[0];
         if (p.row_scale) outv *= bf16_bits_to_f32(reinterpret_cast<const unsigned short*>(p.row_scale)[dst]);
       }
-      if (p.out_row_addr)
-        reinterpret_cast<__nv_bfloat16*>(p.out_row_addr[sp])[n] = __float2bfloat16_rn(outv);
-      else if (p.out_f32)
+      if (p.out_row_addr) {
+        const unsigned long long da = p.out_row_addr[sp];  // 0: the table's builder found no room for this row
+        if (da) reinterpret_cast<__nv_bfloat16*>(da)[n] = __float2bfloat16_rn(outv);
+      } else if (p.out_f32)
         reinterpret_cast<float*>(p.out)[(size_t)dst * N + n] = outv;
       else
         reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)dst * N + n] = __float2bfloat16_rn(outv);

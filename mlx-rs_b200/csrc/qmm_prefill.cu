@@ -58,23 +58,34 @@ constexpr int BM = 128, BMT = 256, BK = 64, NCOL = 256;  // BMT: rows per tile =
 // packed-weight stages 3-7 % slower at every batch size; two activation + three dequantised-B stages no
 // different.  With few rows per expert a K block costs ~1.7 k cycles whatever the number of MMAs: the
 // hand-over latency between the unpack warps and the MMA issuer, not the stage count, sets that floor.)
-constexpr int A_STAGES = 3, STAGES = 2, W_STAGES = 2;
+constexpr int STAGES = 2, W_STAGES = 2;
+// BITS == 16 is the un-quantised product (gather_mm): the "packed" stage then holds a raw bf16 tile of b
+// (64 k x 256 n, 32 KB) that the unpack warps transpose into the K-major operand layout; two activation
+// stages instead of three pay for its size.
+__host__ __device__ constexpr int a_stages(int bits) { return bits == 16 ? 2 : 3; }
 constexpr int A_BYTES = BM * BK * 2;                     // 16 KB per 128-row sub-tile
 constexpr int A_STAGE_BYTES = 2 * A_BYTES;               // both sub-tiles of a K block
 constexpr int B_BYTES = NCOL * BK * 2;                   // 32 KB
-constexpr int W_BYTES = NCOL * 64;                       // 16 KB: 64 packed bytes of each of the 256 weight rows
+__host__ __device__ constexpr int w_bytes(int bits) { return bits == 16 ? NCOL * BK * 2 : NCOL * 64; }  // 16 KB: 64 packed bytes of each of the 256 weight rows
 constexpr int N_EPI = 256, N_DEQ = 256;
 constexpr int WARP_TMA_A = (N_EPI + N_DEQ) / 32, WARP_MMA = WARP_TMA_A + 1, WARP_TMA_W = WARP_TMA_A + 2;
 constexpr int N_THREADS = N_EPI + N_DEQ + 96;            // + TMA(A) warp + MMA warp + TMA(W) warp
 constexpr int CS_BUFS = 4;                // column-scale buffers (tiles in flight between dequantisation and epilogue)
-constexpr int RING_BYTES = A_STAGES * A_STAGE_BYTES + STAGES * B_BYTES + W_STAGES * W_BYTES;
+__host__ __device__ constexpr int ring_bytes(int bits) {
+  return a_stages(bits) * A_STAGE_BYTES + STAGES * B_BYTES + W_STAGES * w_bytes(bits);
+}
 constexpr int STG_LD = 20;                // floats per staged row (16 + 4): 16-byte aligned, quarter-warps hit distinct banks
-constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512 + CS_BUFS * NCOL * 4 + (N_EPI / 32) * 32 * STG_LD * 4;
+__host__ __device__ constexpr int smem_bytes(int bits) {
+  return 1024 + ring_bytes(bits) + 512 + CS_BUFS * NCOL * 4 + (N_EPI / 32) * 32 * STG_LD * 4;
+}
 
 // kind::f16, A = B = fp16, D = f32, both operands K-major, M = 128, N = 256
 constexpr uint32_t kIdesc = umma_idesc_f16(BM, NCOL);
+// the same with A = B = bf16 (format 1 in both operand fields): the un-quantised product
+constexpr uint32_t kIdescBf16 = kIdesc | (1u << 7) | (1u << 10);
+template <int BITS>
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
-  umma_f16(d_tmem, adesc, bdesc, kIdesc, accumulate);
+  umma_f16(d_tmem, adesc, bdesc, BITS == 16 ? kIdescBf16 : kIdesc, accumulate);
 }
 
 // two float32 -> packed fp16 pair (lo in the low half), round to nearest, finite overflow saturates
@@ -151,8 +162,9 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                       const __grid_constant__ CUtensorMap tmap_w1, PrefillArgs p) {
   constexpr int FEAT = (NMAT == 2) ? 128 : 256;  // output features per tile
   constexpr int WPB = BK * BITS / 32;            // packed words per row per K block (8 or 16)
-  constexpr int KPS = 16 / WPB;                  // K blocks covered by one W stage (2 or 1)
-  constexpr int CPK = WPB / 4;                   // 16-byte chunks of a row per K block (2 or 4)
+  constexpr int KPS = BITS == 16 ? 1 : 16 / WPB; // K blocks covered by one W stage (2 or 1)
+  constexpr int CPK = BITS == 16 ? 1 : WPB / 4;  // 16-byte chunks of a row per K block (2 or 4)
+  constexpr int A_STAGES = a_stages(BITS), W_BYTES = w_bytes(BITS), RING_BYTES = ring_bytes(BITS);
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* a_st = smem;
@@ -179,7 +191,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int KB = p.K / BK;
-  const int n_col_tiles = p.N / FEAT;
+  const int n_col_tiles = (p.N + FEAT - 1) / FEAT;  // the un-quantised product may end in a partial column tile
   const int G = p.K / 64;
 
   if (tid == 0) {
@@ -333,7 +345,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 x4.y *= cc.y;
                 x4.z *= cc.z;
                 x4.w *= cc.w;
-                if (d != 0xffffffffu)
+                if (d != 0xffffffffu && ct * FEAT + c + c4 < p.N)
                   *reinterpret_cast<float4*>(static_cast<float*>(p.out) + (size_t)d * p.N + ct * FEAT + c + c4) = x4;
               }
             } else {
@@ -359,7 +371,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                   o.w = bf16x2(v1.z * c1.z, v1.w * c1.w);
                 }
                 const unsigned long long da = __shfl_sync(0xffffffffu, daddr, rr);
-                if (d != 0xffffffffu) {
+                if (d != 0xffffffffu && ct * FEAT + c + cg8 < p.N && !(p.out_row_addr && da == 0ull)) {
                   __nv_bfloat16* orow = p.out_row_addr ? reinterpret_cast<__nv_bfloat16*>(da)
                                                        : static_cast<__nv_bfloat16*>(p.out) + (size_t)d * p.N;
                   *reinterpret_cast<uint4*>(orow + ct * FEAT + c + cg8) = o;
@@ -385,6 +397,44 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const int bx = col >> 7, rr = col & 127;
     const uint32_t w_row_off = (uint32_t)bx * 8192u + (uint32_t)rr * 64u;
     const uint32_t wsw = (uint32_t)((rr >> 1) & 3);
+    if constexpr (BITS == 16) {
+      // un-quantised product: this thread transposes its column of the raw [64 k][256 n] bf16 stage into the K-major
+      // operand row (natural k order, no scaling)
+      int s = 0, phase = 0, tcount = 0, ws = 0, wphase = 0;
+      bool dead = false;
+      for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x, ++tcount) {
+        colscale[(tcount % CS_BUFS) * NCOL + col] = 1.0f;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(wfull_bar(ws), wphase, abort_flag) || !mbar_wait(empty_bar(s), phase ^ 1, abort_flag)) {
+            dead = true;
+            break;
+          }
+          const unsigned short* src = reinterpret_cast<const unsigned short*>(w_st + (size_t)ws * W_BYTES) + col;
+          unsigned char* dst = b_st + (size_t)s * B_BYTES + row_off;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            uint32_t v[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t lo = src[(c * 8 + 2 * q) * NCOL], hi = src[(c * 8 + 2 * q + 1) * NCOL];
+              v[q] = lo | (hi << 16);
+            }
+            *reinterpret_cast<uint4*>(dst + (((uint32_t)c ^ sw) << 4)) = make_uint4(v[0], v[1], v[2], v[3]);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          mbar_arrive_warp(full_bar(s), lane);
+          if (++s == STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
+          mbar_arrive_warp(wempty_bar(ws), lane);
+          if (++ws == W_STAGES) {
+            ws = 0;
+            wphase ^= 1;
+          }
+        }
+      }
+    } else {
     int s = 0, phase = 0, tcount = 0, ws = 0, wphase = 0;
     constexpr float kQmax = (BITS == 4) ? 15.f : 255.f;
     RoleTimer tm((p.debug & 32) && blockIdx.x == 0 && tid == N_EPI);
@@ -533,6 +583,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     }
     tm.total(t_begin);
     tm.flush(p.err + 20 + (NMAT == 1 ? 24 : 0));
+    }
   } else if (warp == WARP_TMA_A) {
     // ------------------------------- TMA producer (A) ---------------------------------------
     if (lane == 0) {
@@ -605,8 +656,8 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {
               const uint64_t bd = umma_desc(b_addr + k * 32);
-              umma_bf16(d_addr, umma_desc(a_addr + k * 32), bd, (kb | k) ? 1u : 0u);
-              if (n_sub == 2) umma_bf16(tmem_base + NCOL, umma_desc(a_addr + A_BYTES + k * 32), bd, (kb | k) ? 1u : 0u);
+              umma_bf16<BITS>(d_addr, umma_desc(a_addr + k * 32), bd, (kb | k) ? 1u : 0u);
+              if (n_sub == 2) umma_bf16<BITS>(tmem_base + NCOL, umma_desc(a_addr + A_BYTES + k * 32), bd, (kb | k) ? 1u : 0u);
             }
           }
           umma_commit(aempty_bar(sa));  // both stages are free once these MMAs have read them
@@ -647,7 +698,9 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           tm.stop(0);
           mbar_arrive_expect_tx(wfull_bar(ws), W_BYTES);
           const uint32_t dst = smem_u32(w_st + (size_t)ws * W_BYTES);
-          if constexpr (NMAT == 2) {
+          if constexpr (BITS == 16) {  // raw bf16 tile of b[e]: 64 k rows x 256 n (columns beyond N read as zero)
+            tma_load_2d(dst, &tmap_w0, wfull_bar(ws), ct * FEAT, (int)p.tile_expert[rt] * p.K + wk * BK);
+          } else if constexpr (NMAT == 2) {
             tma_load_2d(dst, &tmap_w0, wfull_bar(ws), wk * 16, row_base);
             tma_load_2d(dst + 8192, &tmap_w1, wfull_bar(ws), wk * 16, row_base);
           } else {
@@ -848,8 +901,8 @@ int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows,
   do {                                                                                                        \
     auto kern = grouped_qmm_tc_kernel<BITSV, NMATV>;                                                          \
     static DynSmemCache attr;                                                                                 \
-    B200_CUDA(ensure_dyn_smem(kern, SMEM_BYTES, attr));                                                       \
-    kern<<<grid, N_THREADS, SMEM_BYTES, st>>>(tmap, tmap_w[0], tmap_w[1], p);                                                       \
+    B200_CUDA(ensure_dyn_smem(kern, smem_bytes(BITSV), attr));                                                \
+    kern<<<grid, N_THREADS, smem_bytes(BITSV), st>>>(tmap, tmap_w[0], tmap_w[1], p);                              \
   } while (0)
   if (bits == 4 && nmat == 2)
     B200_TC_LAUNCH(4, 2);
@@ -862,6 +915,59 @@ int launch_grouped_qmm_tc(const void* a, const float* a_row_scale, int64_t rows,
   else
     B200_FAIL("bits must be 4 or 8");
 #undef B200_TC_LAUNCH
+  return 0;
+}
+
+// Un-quantised grouped product on the same kernel (gather_mm, mlx-rs/src/ops/arithmetic.rs:1568-1632): rows of
+// a_sorted [rows, K] bf16 grouped by matrix, b [Bb, K, N] bf16 row-major, out[perm[p], :] = a_sorted[p, :] . b[matrix of p].
+// K % 64 == 0 and N % 8 == 0.
+int launch_gather_mm_tc(const void* a_sorted, int64_t rows, const void* b, int Bb, int K, int N, const uint32_t* perm, void* out,
+                        const uint32_t* tile_expert, const uint32_t* tile_row0, const uint32_t* tile_rows,
+                        const uint32_t* n_row_tiles, int* err, cudaStream_t st) {
+  if (rows == 0) return 0;
+  B200_REQUIRE(K % 64 == 0 && N % 8 == 0, "shape not supported by the tensor-core path");
+  EncodeTiledFn enc = encode_fn();
+  B200_REQUIRE(enc != nullptr, "cuTensorMapEncodeTiled is not available from the driver");
+  CUtensorMap tmap_a, tmap_b;
+  cuuint32_t estr[2] = {1, 1};
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {BK, BM};
+    CUresult cr = enc(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a_sorted), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    B200_REQUIRE(cr == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed (the activation buffer must be 16-byte aligned)");
+  }
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)Bb * K};
+    cuuint64_t strides[1] = {(cuuint64_t)N * 2};
+    cuuint32_t box[2] = {NCOL, BK};
+    CUresult cr = enc(&tmap_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(b), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    B200_REQUIRE(cr == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed for b (16-byte alignment required)");
+  }
+  PrefillArgs p{};
+  p.tile_expert = tile_expert;
+  p.tile_row0 = tile_row0;
+  p.tile_rows = tile_rows;
+  p.n_row_tiles = n_row_tiles;
+  p.perm = perm;
+  p.dst_perm = perm ? 1 : 0;
+  p.out = out;
+  p.out_fmt = kOutBf16;
+  p.K = K;
+  p.N = N;
+  p.err = err;
+  p.alt = 1;
+  const int n_sm = current_sm_count();
+  const int64_t max_tiles = (int64_t)prefill_tile_words(rows, Bb) * ((N + NCOL - 1) / NCOL);
+  const int grid = (int)(max_tiles < n_sm ? max_tiles : n_sm);
+  auto kern = grouped_qmm_tc_kernel<16, 1>;
+  static DynSmemCache attr;
+  B200_CUDA(ensure_dyn_smem(kern, smem_bytes(16), attr));
+  kern<<<grid, N_THREADS, smem_bytes(16), st>>>(tmap_a, tmap_b, tmap_b, p);
   return 0;
 }
 

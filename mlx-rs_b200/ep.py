@@ -289,7 +289,8 @@ class PeerExpertParallelMoe:
             if n_recv[c]:
                 rows_view, y_view = self._views[c]
                 if self.fused_return:
-                    addr = ops.ep_return_table(chunk_counts[c], self.rank, self.bufs[c].y_ptrs, H, n_recv[c], ctx=self.ctx)
+                    addr = ops.ep_return_table(chunk_counts[c], self.rank, self.bufs[c].y_ptrs, H, n_recv[c], self.bufs[c].capacity,
+                                               ctx=self.ctx)
                     self.mlp.forward_sorted_scatter(rows_view, tables[c][1], n_recv[c], addr)
                 else:
                     self.mlp.forward_sorted(rows_view, tables[c][1], n_recv[c], out=y_view)

@@ -247,14 +247,14 @@ def ep_layout(all_counts, rank, capacity_rows, ctx=None):
     return dst_row0, local_counts
 
 
-def ep_return_table(all_counts, rank, peer_y, hidden, n_rows, ctx=None):
+def ep_return_table(all_counts, rank, peer_y, hidden, n_rows, capacity_rows, ctx=None):
     """-> int64 [n_rows]: for every row this rank receives, the address of its output row in the source
-    rank's return buffer (peer_y: device addresses of all ranks' return buffers)."""
+    rank's return buffer (peer_y: device addresses of all ranks' return buffers, capacity_rows rows each)."""
     _cuda(all_counts)
     G, E = all_counts.shape
     addr = torch.empty(max(n_rows, 1), dtype=torch.int64, device=all_counts.device)
-    L.check(L.lib().b200_ep_return_table(_ctx(ctx), L.ptr(all_counts), G, E, rank, _ptr_array(peer_y), hidden, L.ptr(addr),
-                                         L.stream_ptr()))
+    L.check(L.lib().b200_ep_return_table(_ctx(ctx), L.ptr(all_counts), G, E, rank, _ptr_array(peer_y), hidden, n_rows,
+                                         capacity_rows, L.ptr(addr), L.stream_ptr()))
     return addr
 
 

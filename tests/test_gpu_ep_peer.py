@@ -57,7 +57,7 @@ def test_peer_exchange_emulated_ranks(pkg, O, cfg, G):
     for r in range(G):
         n_recv = int(tables[r][1].sum())
         if n_recv:
-            addr = ops.ep_return_table(all_counts, r, ret_ptrs, H, n_recv)
+            addr = ops.ep_return_table(all_counts, r, ret_ptrs, H, n_recv, cap)
             mlps[r].forward_sorted_scatter(rows_buf[r], tables[r][1], n_recv, addr)
     for r in range(G):
         idx, scores, perm, inv, counts, offsets = routed[r]
@@ -84,6 +84,35 @@ def test_peer_exchange_reports_overflow(pkg):
     with pytest.raises(pkg.B200Error, match="more rows"):
         pkg.default_context().check()
     pkg.default_context().check()                # the status word is cleared by the failed check
+
+
+def test_sorted_entry_points_keep_to_their_bounds(pkg):
+    """Counts that promise more rows than the call holds, and a return table whose buffers are too small: the
+    rows beyond the bound are neither read nor written, and the status check reports it."""
+    dev = torch.device("cuda", 0)
+    blk = make_block(T=64, H=256, E=4, I=128, k=1, seed=12)
+    mlp = to_device(pkg, blk).switch_mlp
+    ctx = pkg.default_context()
+    rows = torch.randn(40, 256, device=dev).bfloat16()
+    out = torch.full((48, 256), 7.0, dtype=torch.bfloat16, device=dev)
+    counts = torch.tensor([10, 10, 10, 30], dtype=torch.int32, device=dev)        # 60 > 40
+    mlp.forward_sorted(rows, counts, 40, out=out[:40])
+    with pytest.raises(pkg.B200Error, match="counts"):
+        ctx.check()
+    assert bool((out[40:] == 7.0).all()), "rows past the call's bound were written"
+    ok = torch.tensor([10, 10, 10, 10], dtype=torch.int32, device=dev)
+    want = mlp.forward_sorted(rows, ok, 40)
+    assert torch.equal(out[:30].view(torch.int16), want[:30].view(torch.int16))   # the first three experts are unaffected
+    # return table: one rank, its own return buffer holds 32 of the 40 rows
+    ret = torch.full((40, 256), 7.0, dtype=torch.bfloat16, device=dev)
+    all_counts = ok.reshape(1, 4)
+    addr = pkg.ops.ep_return_table(all_counts, 0, [ret.data_ptr()], 256, 40, 32)
+    with pytest.raises(pkg.B200Error, match="more rows"):
+        ctx.check()
+    assert int((addr == 0).sum()) == 8
+    mlp.forward_sorted_scatter(rows, ok, 40, addr)
+    ctx.check()
+    assert torch.equal(ret[:32].view(torch.int16), want[:32].view(torch.int16)) and bool((ret[32:] == 7.0).all())
 
 
 @pytest.mark.parametrize("cfg", [dict(T=96, H=256, E=8, I=128, k=2, seed=3),          # register kernel

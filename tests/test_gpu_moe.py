@@ -192,6 +192,36 @@ def test_bad_config_is_rejected(pkg):
                            torch.zeros((4, 128), dtype=torch.bfloat16, device="cuda"), 5)  # top_k > experts
 
 
+def test_arena_growth_is_refused_during_stream_capture(pkg):
+    """A fresh context has no scratch arena; a block forward inside a stream capture would have to allocate it
+    (cudaMalloc + device synchronisation, illegal while capturing): the call fails cleanly, the capture survives,
+    and after b200_ctx_reserve the same capture succeeds and replays the eager result."""
+    blk = make_block(T=8, H=256, E=8, I=128, k=2, seed=4)
+    ctx = pkg.Context()
+    block = to_device(pkg, blk)
+    block.ctx = block.switch_mlp.ctx = ctx
+    x = bf16_cuda(blk["x"])
+    s = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(s):
+        g.capture_begin()
+        try:
+            with pytest.raises(pkg.B200Error, match="capture"):
+                block.forward(x)
+        finally:
+            g.capture_end()
+    torch.cuda.synchronize()
+    ctx.reserve(block.config, 8)
+    want = block.forward(x)
+    g2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g2):
+        got = block.forward(x)
+    g2.replay()
+    torch.cuda.synchronize()
+    ctx.check()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
 def test_stack_of_blocks_with_norm_and_residual(pkg, O):
     # BASELINE.json configs[2] scaled down: 3 pre-RMSNorm (eps 1e-6, unit weight) MoE blocks with residuals
     T, H, E, I, k = 40, 256, 8, 128, 2

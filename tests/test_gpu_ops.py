@@ -197,6 +197,39 @@ def test_gather_mm_reference_cases(pkg, O):
         pkg.default_context().check()
 
 
+def test_gather_mm_tensor_core_branch(pkg, O):
+    """Enough rows for 128-row tiles: the product goes through the grouped tcgen05 kernel (rows sorted by matrix,
+    un-quantised bf16 operands).  4096 gathered rows over 8 matrices, ragged N (not a multiple of the 256-column tile),
+    skewed use of the matrices with one of them unused, both index arrays."""
+    rng = np.random.default_rng(77)
+    Ba, Bb, M, K, N, n_idx = 300, 8, 4, 512, 328, 1024
+    a = O.round_bf16((rng.standard_normal((Ba, M, K)) / 8).astype(np.float32))
+    b = O.round_bf16((rng.standard_normal((Bb, K, N)) / 8).astype(np.float32))
+    lhs = rng.integers(0, Ba, size=n_idx).astype(np.uint32)
+    p = np.array([0.4, 0.2, 0.0, 0.1, 0.1, 0.1, 0.05, 0.05])
+    rhs = rng.choice(Bb, size=n_idx, p=p).astype(np.uint32)
+    ref = O.gather_mm(a, b, lhs, rhs)
+    ctx = pkg.default_context()
+    before = ctx.launch_count()
+    got = pkg.ops.gather_mm(bf16_cuda(a), bf16_cuda(b), torch.from_numpy(lhs.view(np.int32)).cuda(),
+                            torch.from_numpy(rhs.view(np.int32)).cuda())
+    ctx.check()
+    assert ctx.launch_count() - before > 1, "expected the sorted tensor-core path, not the single CUDA-core launch"
+    assert tuple(got.shape) == (n_idx, M, N)
+    assert close_up_to_bf16_rounding(got.float().cpu().numpy(), ref, 1e-3)
+    # only rhs indices: entry i of a with matrix rhs[i], 4 matrices x 256 rows
+    a2 = O.round_bf16((rng.standard_normal((4, 256, 128)) / 8).astype(np.float32))
+    b2 = O.round_bf16((rng.standard_normal((4, 128, 64)) / 8).astype(np.float32))
+    got = pkg.ops.gather_mm(bf16_cuda(a2), bf16_cuda(b2), None, torch.tensor([3, 1, 0, 2], dtype=torch.int32).cuda())
+    ctx.check()
+    ref2 = np.stack([a2[i].astype(np.float64) @ b2[j].astype(np.float64) for i, j in enumerate([3, 1, 0, 2])])
+    assert close_up_to_bf16_rounding(got.float().cpu().numpy(), ref2, 1e-3)
+    with pytest.raises(pkg.B200Error):      # an index past the batch is reported on this path too
+        pkg.ops.gather_mm(bf16_cuda(a), bf16_cuda(b), torch.from_numpy(lhs.view(np.int32)).cuda(),
+                          torch.full((n_idx,), 8, dtype=torch.int32).cuda())
+        ctx.check()
+
+
 def f32_cuda(a):
     return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda()
 
