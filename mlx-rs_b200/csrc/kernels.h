@@ -36,6 +36,7 @@ struct GroupedArgs {
                               // in the A-operand layout of the same path's down projection (register kernel: prepared rows)
   int K, N;
   int n_experts;              // number of stacked weight matrices
+  int no_l2_prefetch;         // register kernel: 1 switches the whole-row L2 prefetch off (development comparisons)
 };
 
 // router.cu
