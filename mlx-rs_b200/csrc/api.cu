@@ -131,6 +131,8 @@ static int check_cfg(const b200_moe_config* cfg) {
 static inline int permute_launches(int64_t n) { return n <= 1024 ? 1 : 3; }
 // rows per expert (average over the experts that can be active) from which the tensor-core kernel is used
 constexpr int64_t kTensorCoreRowsPerExpert = 14;
+// Largest K (the block's intermediate size) whose down projection alternates its accumulators between 128-row tiles.
+constexpr int kAltDownMaxK = 1024;
 constexpr int kTicketWord = 8;  // word of the status block that the fused small-batch router uses as its ticket counter
 // Status block of a context: word 0 = device-side status, word 8 = ticket of the fused router, words 16..63 =
 // self-timing of development builds.
@@ -661,6 +663,17 @@ static bool use_tensor_core_path(const b200_ctx* c, const b200_moe_config& cfg, 
 
 // Rows of an expert-parallel exchange: the sorted rows are gathered from a buffer of token rows through `map`
 // (sorted position -> token row); the numbers of sorted rows and of token rows live on the device.
+// The block's output buffers, for batches small enough that the down projection finishes the block itself (routing
+// weights and the k-way sum in its epilogue): experts_sorted then reports *yk_fmt = kOutNone and the caller skips
+// the combine.
+struct SmallTail {
+  const uint32_t* idx;  // [T, k]
+  const uint32_t* inv;  // [T*k]
+  void* out;            // bf16 [T, H]
+  float* out_f32;       // optional
+  int64_t T;
+};
+
 struct ExchangeRows {
   const uint32_t* map;          // [n] sorted position -> row of x
   int64_t src_rows_bound;       // host bound on the rows of x
@@ -675,7 +688,7 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
                           const uint32_t* perm, int src_div, const uint32_t* counts, const uint32_t* offsets,
                           const uint32_t* active, const uint32_t* n_active, int64_t n, const void* scores, void* yk,
                           cudaStream_t st, int* yk_fmt, const unsigned long long* out_row_addr = nullptr,
-                          const ExchangeRows* xr = nullptr);
+                          const ExchangeRows* xr = nullptr, const SmallTail* tail = nullptr);
 
 // Outputs of the token -> expert sort (scratch, or the caller's aux buffers where given).
 struct SortBufs {
@@ -718,7 +731,8 @@ static int experts_forward(b200_ctx* c, const b200_moe_config& cfg, const b200_m
 static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_moe_params& p, const void* x,
                           const uint32_t* perm, int src_div, const uint32_t* counts, const uint32_t* offsets,
                           const uint32_t* active, const uint32_t* n_active, int64_t n, const void* scores, void* yk,
-                          cudaStream_t st, int* yk_fmt, const unsigned long long* out_row_addr, const ExchangeRows* xr) {
+                          cudaStream_t st, int* yk_fmt, const unsigned long long* out_row_addr, const ExchangeRows* xr,
+                          const SmallTail* tail) {
   // n is the host's bound on the number of rows; with `xr` the rows that exist are counted on the device
   // (everything below is driven by the device-side segment tables, only the row preparation needs the extra
   // words) and are gathered from x through xr->map
@@ -737,10 +751,13 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   uint32_t *tile_expert1 = nullptr, *tile_row01 = nullptr, *tile_rows1 = nullptr, *n_row_tiles1 = nullptr;
   void* xs = nullptr;
   float* rs_x = nullptr;
+  // down projection: with a short K the drain of a tile is a large share of its time and must run under the next
+  // tile's products (128-row tiles alternating between the two accumulators); with a long K it is not, and 256-row
+  // tiles whose two accumulators share every dequantised weight stage halve the dequantisation and shared-memory
+  // traffic per product
+  bool alt_down = cfg.inter <= kAltDownMaxK;
 #ifdef B200_DEV
-  static const bool alt_down = [] { const char* v = getenv("B200_TC_DEBUG"); return !(v && (atoi(v) & 64)); }();
-#else
-  constexpr bool alt_down = true;
+  if (const char* v = getenv("B200_ALT_DOWN")) alt_down = atoi(v) != 0;
 #endif
   if (tc) {
     const size_t tw = prefill_tile_words(n, E);
@@ -794,22 +811,53 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
     // register kernel: the source rows (the tokens when rows are gathered through perm, else the n rows
     // themselves) are prepared once - fp16, row-scaled, unpack order - and every CTA copies what it needs
     const int64_t src_rows = xr ? xr->src_rows_bound : (perm ? n / src_div : n);
-    void* xp = c->take(sizeof(uint16_t) * src_rows * cfg.hidden);
-    float* rp = static_cast<float*>(c->take(sizeof(float) * src_rows));
-    B200_REQUIRE(xp && rp, "scratch arena too small");
-    if (launch_prepare_rows_small(x, 0, src_rows, xr ? xr->src_rows_dev : nullptr, cfg.hidden, cfg.bits, xp, rp, st)) return 1;
-    c->mark(4, st);
-    gu.x = xp;
-    gu.x_rowscale = rp;
+    if (!xr && src_rows <= 8) {
+      // a handful of rows: every CTA prepares the rows it stages itself, which costs less than a launch
+      gu.x_bf16 = 1;
+      c->mark(4, st);
+    } else {
+      void* xp = c->take(sizeof(uint16_t) * src_rows * cfg.hidden);
+      float* rp = static_cast<float*>(c->take(sizeof(float) * src_rows));
+      B200_REQUIRE(xp && rp, "scratch arena too small");
+      if (launch_prepare_rows_small(x, 0, src_rows, xr ? xr->src_rows_dev : nullptr, cfg.hidden, cfg.bits, xp, rp, st)) return 1;
+      LAUNCHED(c, 1);
+      c->mark(4, st);
+      gu.x = xp;
+      gu.x_rowscale = rp;
+    }
     if (xr) {
       gu.src_mode = kSrcMapDirect;
       gu.src_map = xr->map;
     }
     gu.out_f16 = 1;  // h in the prepared layout, ready for the down projection
     if (launch_grouped_qmm_small(gu, 2, cfg.bits, max_active, n, st)) return 1;
-    LAUNCHED(c, 2);
+    LAUNCHED(c, 1);
   }
   c->mark(5, st);
+
+  if (!tc && tail && scores && !xr && !out_row_addr && down_combine_small_ok(tail->T, cfg.top_k, cfg.inter)) {
+    // a handful of tokens: down projection, routing weights and the k-way sum in one launch
+    DownCombineArgs dc{};
+    dc.h = h;
+    dc.idx = tail->idx;
+    dc.inv = tail->inv;
+    dc.scores = scores;
+    dc.w = p.down_proj.weight;
+    dc.scales = p.down_proj.scales;
+    dc.biases = p.down_proj.biases;
+    dc.out = tail->out;
+    dc.out_f32 = tail->out_f32;
+    dc.T = (int)tail->T;
+    dc.k = cfg.top_k;
+    dc.K = cfg.inter;
+    dc.N = cfg.hidden;
+    c->mark(6, st);
+    if (launch_down_combine_small(dc, cfg.bits, st)) return 1;
+    LAUNCHED(c, 1);
+    c->mark(7, st);
+    if (yk_fmt) *yk_fmt = kOutNone;
+    return 0;
+  }
 
   GroupedArgs dn{};
   dn.x = h;
@@ -906,8 +954,9 @@ int b200_moe_block_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_m
     LAUNCHED(c, 1);
     c->mark(1, st);
     c->mark(2, st);
+    const SmallTail tail{idx, sb.inv, out, aux ? aux->out_f32 : nullptr, T};
     if (experts_sorted(c, *cfg, *params, x, sb.perm, cfg->top_k, sb.counts, sb.offsets, sb.active, sb.n_active, n, scores,
-                       yk, st, &yk_fmt))
+                       yk, st, &yk_fmt, nullptr, nullptr, &tail))
       return 1;
   } else {
     double* w64 = static_cast<double*>(c->take(sizeof(double) * (size_t)cfg->n_experts * cfg->hidden));
@@ -921,10 +970,12 @@ int b200_moe_block_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_m
     LAUNCHED(c, 2);
     if (experts_forward(c, *cfg, *params, x, idx, scores, T, yk, aux, st, &yk_fmt)) return 1;
   }
-  if (launch_combine(yk, yk_fmt, T, cfg->top_k, cfg->hidden, out, aux ? aux->out_f32 : nullptr, st)) return 1;
+  if (yk_fmt != kOutNone) {
+    if (launch_combine(yk, yk_fmt, T, cfg->top_k, cfg->hidden, out, aux ? aux->out_f32 : nullptr, st)) return 1;
+    LAUNCHED(c, 1);
+  }
   c->mark(8, st);
   c->ev_valid = c->profiling;
-  LAUNCHED(c, 1);
   return 0;
 }
 

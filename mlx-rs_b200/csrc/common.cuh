@@ -66,6 +66,10 @@ __device__ __forceinline__ void pdl_prologue() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
+// The two halves of pdl_prologue() for kernels that fetch CONSTANT inputs (weights, which no kernel of the chain
+// writes) between them: those fetches then run while the previous kernel is still finishing.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 #ifdef B200_DEV
 bool pdl_enabled();  // development build: false when the environment variable B200_NO_PDL is set

@@ -8,7 +8,7 @@
 namespace b200 {
 
 enum { kSrcIdent = 0, kSrcPermDiv = 1, kSrcMap = 2, kSrcMapDirect = 3 };
-enum { kOutBf16 = 0, kOutF32 = 1, kOutF16 = 2 };  // element format of a grouped product's output / of the combine's input
+enum { kOutBf16 = 0, kOutF32 = 1, kOutF16 = 2, kOutNone = 3 };  // element format of a grouped product's output / of the combine's input (none: the product finished the block)
 
 // One grouped product over rows that are sorted by expert.
 struct GroupedArgs {
@@ -37,7 +37,25 @@ struct GroupedArgs {
   int K, N;
   int n_experts;              // number of stacked weight matrices
   int no_l2_prefetch;         // register kernel: 1 switches the whole-row L2 prefetch off (development comparisons)
+  int x_bf16;                 // register kernel: 1 = x holds plain bf16 rows and every CTA prepares the rows it stages
+                              // itself (a handful of rows per expert: cheaper than a preparation launch)
 };
+
+// Down projection and weighted k-way sum of a handful of tokens in one launch (register kernel family).
+struct DownCombineArgs {
+  const void* h;              // prepared fp16 rows [T*k, K] in sorted order (a gate/up epilogue with out_f16)
+  const uint32_t* idx;        // [T, k] expert of every assignment
+  const uint32_t* inv;        // [T*k] sorted position of every assignment
+  const void* scores;         // bf16 [T, k] routing weights
+  const uint32_t* w;          // packed down weights [E, N, K*bits/32]
+  const void* scales;         // bf16 [E, N, K/64]
+  const void* biases;
+  void* out;                  // bf16 [T, N]
+  float* out_f32;             // optional [T, N]: the sum before its rounding
+  int T, k, K, N;
+};
+bool down_combine_small_ok(int64_t T, int k, int K);
+int launch_down_combine_small(const DownCombineArgs& a, int bits, cudaStream_t st);
 
 // router.cu
 // w64: optional scratch of E*H doubles (the float64 image of the router weight, rewritten by the call)

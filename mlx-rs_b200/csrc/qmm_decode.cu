@@ -28,6 +28,8 @@ namespace b200 {
 
 using namespace qs;
 
+constexpr int kDownCombineMaxK = 32;  // top-k slots the fused down projection and sum keeps in shared memory
+
 template <int BITS, int NMAT, int RT, int NT>
 __global__ void __launch_bounds__(256, NT == 1 ? 2 : 1) grouped_qmm_small_kernel(GroupedArgs p) {
   constexpr int KS = 8 / (NMAT * RT);
@@ -99,10 +101,14 @@ __global__ void __launch_bounds__(256, NT == 1 ? 2 : 1) grouped_qmm_small_kernel
       else
         src = (int)p.src_map[p.perm[sp]];
       s_src[tid] = src;
-      s.rs[tid] = p.x_rowscale ? p.x_rowscale[src] : 1.0f;
+      if (!p.x_bf16) s.rs[tid] = p.x_rowscale ? p.x_rowscale[src] : 1.0f;
     }
     __syncthreads();
-    {
+    if (p.x_bf16) {  // plain bf16 rows: warp r prepares row r straight into the staged image
+      for (int r = warp; r < nrows; r += 8)
+        prepare_row_warp<BITS, false>(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.x) + (size_t)s_src[r] * K),
+                                      K / 8, reinterpret_cast<uint4*>(s.xs + (size_t)r * s.XS), s.rs + r, lane);
+    } else {
       const int nvec = K / 8;
       for (int i = tid; i < nrows * nvec; i += 256) {
         const int r = i / nvec, c = i % nvec;
@@ -183,6 +189,107 @@ __global__ void __launch_bounds__(256, NT == 1 ? 2 : 1) grouped_qmm_small_kernel
   }
 }
 
+// ---- down projection + weighted k-way sum for a handful of tokens ----------------------------------
+// out[t, n0..n0+16) = bf16( sum_j score[t, j] * (h[row(t, j), :] . W_down[e(t, j)][n, :]) ), j ascending: the down
+// projection with the routing weight (multiply before sum_axis, mlx-rs/src/ops/reduction.rs:260-275), the take with
+// the inverse order and the k-way sum in ONE launch - no per-assignment buffer, no combine kernel.  One CTA per
+// (token, 16 output features); warp j streams the 16 weight rows of the expert in slot j (then j + 8, ...) over the
+// whole K, against the token's staged row of that slot.
+template <int BITS>
+__global__ void __launch_bounds__(256, 2) down_combine_small_kernel(DownCombineArgs p) {
+  pdl_prologue();
+  extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ uint32_t s_e[kDownCombineMaxK], s_row[kDownCombineMaxK];
+  __shared__ float s_sc[kDownCombineMaxK];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gq = lane >> 2, t = lane & 3;
+  constexpr int WPT = (BITS == 4) ? 2 : 4;
+  const int K = p.K, N = p.N, k = p.k, G = K / 64;
+  const int tiles = (N + 15) / 16;
+  const int tok = blockIdx.x / tiles, n0 = (blockIdx.x % tiles) * 16;
+  const int wrow = K * BITS / 32;
+  const Staged s = staged_at(smem, K, k);
+  float* red = reinterpret_cast<float*>(smem + ((staged_bytes(K, k) + 15) & ~size_t(15)));  // [k][16]
+  if (tid < k) {
+    s_e[tid] = p.idx[(size_t)tok * k + tid];
+    s_row[tid] = p.inv[(size_t)tok * k + tid];
+    s_sc[tid] = bf16_bits_to_f32(reinterpret_cast<const unsigned short*>(p.scores)[(size_t)tok * k + tid]);
+    s.rs[tid] = 1.0f;
+  }
+  __syncthreads();
+  const unsigned short* scb = reinterpret_cast<const unsigned short*>(p.scales);
+  const unsigned short* bib = reinterpret_cast<const unsigned short*>(p.biases);
+  WeightStream<BITS> ws;
+  auto start_slot = [&](int j) {
+    const size_t e = s_e[j];
+    const size_t row_a = e * N + min(n0 + gq, N - 1), row_b = e * N + min(n0 + gq + 8, N - 1);
+    if (t < 2) {  // the rows' way from DRAM to L2 starts now, whole rows (see grouped_qmm_small_kernel)
+      l2_prefetch_bulk(p.w + (t == 0 ? row_a : row_b) * wrow, (uint32_t)wrow * 4u);
+    } else {
+      const size_t so = (t == 2 ? row_a : row_b) * G;
+      for (int o = 0; o < G * 2 + 127; o += 128) {
+        l2_prefetch_line(reinterpret_cast<const char*>(scb + so) + min(o, G * 2 - 1));
+        l2_prefetch_line(reinterpret_cast<const char*>(bib + so) + min(o, G * 2 - 1));
+      }
+    }
+    ws.start(p.w + row_a * wrow + t * WPT, p.w + row_b * wrow + t * WPT, scb + row_a * G, bib + row_a * G, scb + row_b * G,
+             bib + row_b * G, G, 0, 1);
+  };
+  if (warp < k) start_slot(warp);  // the first blocks of weights are on their way while the rows are staged
+  {
+    const int nvec = K / 8;
+    const unsigned char* hb = static_cast<const unsigned char*>(p.h);
+    for (int i = tid; i < k * nvec; i += 256) {
+      const int r = i / nvec, c = i % nvec;
+      cp_async16(s.xs + (size_t)r * s.XS + c * 16, hb + ((size_t)s_row[r] * K) * 2 + c * 16);
+    }
+    cp_async_wait_all();
+  }
+  __syncthreads();
+  stage_sums<BITS>(s, k, k, K, tid, 256);
+  __syncthreads();
+  for (int j = warp; j < k; j += 8) {
+    if (j != warp) start_slot(j);
+    float tot[1][4] = {{0.f, 0.f, 0.f, 0.f}};
+    ws.template run<1>(SingleRowFetch(s, k, j, t), tot);
+    if (t == 0) {  // column 0 of the tile is the token's row: lanes t == 0 hold weight rows gq and gq + 8
+      red[j * 16 + gq] = tot[0][0] * s_sc[j];
+      red[j * 16 + gq + 8] = tot[0][2] * s_sc[j];
+    }
+  }
+  __syncthreads();
+  if (tid < 16 && n0 + tid < N) {
+    float acc = 0.f;
+    for (int j = 0; j < k; ++j) acc += red[j * 16 + tid];
+    const size_t o = (size_t)tok * N + n0 + tid;
+    if (p.out_f32) p.out_f32[o] = acc;
+    static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(acc);
+  }
+}
+
+static size_t down_combine_smem(int K, int k) { return ((staged_bytes(K, k) + 15) & ~size_t(15)) + sizeof(float) * 16 * k; }
+
+bool down_combine_small_ok(int64_t T, int k, int K) {
+  return T >= 1 && T <= 8 && k >= 1 && k <= kDownCombineMaxK && K % 64 == 0 && down_combine_smem(K, k) <= 100 * 1024;
+}
+
+int launch_down_combine_small(const DownCombineArgs& a, int bits, cudaStream_t st) {
+  B200_REQUIRE(down_combine_small_ok(a.T, a.k, a.K), "shape not supported by the fused down projection and sum");
+  B200_REQUIRE(bits == 4 || bits == 8, "bits must be 4 or 8");
+  const size_t smem = down_combine_smem(a.K, a.k);
+  const dim3 grid((unsigned)(a.T * cdiv(a.N, 16)));
+  if (bits == 4) {
+    static DynSmemCache attr;
+    B200_CUDA(ensure_dyn_smem(down_combine_small_kernel<4>, smem, attr));
+    B200_CUDA(launch_pdl(down_combine_small_kernel<4>, grid, dim3(256), smem, st, a));
+  } else {
+    static DynSmemCache attr;
+    B200_CUDA(ensure_dyn_smem(down_combine_small_kernel<8>, smem, attr));
+    B200_CUDA(launch_pdl(down_combine_small_kernel<8>, grid, dim3(256), smem, st, a));
+  }
+  return 0;
+}
+
 // ---- activation preparation ---------------------------------------------------------------------
 // One warp per row: xs[r, :] = fp16( x[r, :] * 2^-e_r ) where 2^e_r (written to row_scale[r]) brings the
 // row's largest magnitude into [2^14, 2^15); BITS == 4: aligned groups of eight elements are stored as
@@ -252,14 +359,26 @@ static int launch_bits_nmat(const GroupedArgs& a, int max_active, int64_t rows, 
 #endif
   const bool wide = per > wide_above && staged_bytes(a.K, 32) <= 200 * 1024;
   // row tiles per CTA: the largest that still gives three CTAs per SM, among those whose K slices
-  // (8 / (NMAT * RT) of them, in blocks of four (4-bit) or two (8-bit) groups) all have work
+  // (8 / (NMAT * RT) of them, in blocks of four (4-bit) or two (8-bit) groups) all have work.  When even the
+  // smallest tiles give fewer CTAs than that, a grid between one and one and a half waves (two CTAs per SM are
+  // resident) would run a nearly empty second wave of latency-bound CTAs: the next larger tile, which fits one
+  // wave, is taken instead.
   const int gb = BITS == 4 ? 4 : 2;  // groups per block of the weight stream
   const int nblk = (a.K / 64 + gb - 1) / gb;
+  const int64_t one_wave = 2 * (int64_t)current_sm_count();
+  bool avoid_second_wave = true;
+#ifdef B200_DEV
+  if (getenv("B200_SMALL_TWO_WAVES")) avoid_second_wave = false;
+#endif
   int rt = 8 / NMAT;
   for (int cand = 8 / NMAT; cand >= 1; cand >>= 1) {
     if (8 / (NMAT * cand) > nblk) break;
+    const int64_t ctas = (int64_t)cdiv(a.N, 16 * cand) * max_active;
+    if (avoid_second_wave && cand < 8 / NMAT && ctas > one_wave && ctas < one_wave * 3 / 2 &&
+        (int64_t)cdiv(a.N, 32 * cand) * max_active >= one_wave / 2)
+      break;  // keep the previous (larger) tile
     rt = cand;
-    if ((int64_t)cdiv(a.N, 16 * cand) * max_active >= 444) break;
+    if (ctas >= one_wave * 3 / 2) break;
   }
 #define B200_DISPATCH_RT(RTV)                                                                        \
   case RTV:                                                                                          \

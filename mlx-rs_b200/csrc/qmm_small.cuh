@@ -327,6 +327,40 @@ struct StagedFetch {
   }
 };
 
+// The fetch of a warp whose tile is ONE staged row (row j of `rows` staged rows) in all eight columns: column 0 of the
+// result (lanes t == 0, elements [0] and [2]) is that row's product, the other columns repeat it.
+struct SingleRowFetch {
+  const unsigned char* xl;  // xs + j * XS + t * 32
+  const float* cj;          // the row's -C inside c4[g][pair]
+  const float* sj;          // ss + j
+  int rows, pairs;
+  const unsigned char* xb;
+  const float* cb;
+  const float* sb;
+  __device__ __forceinline__ SingleRowFetch(const Staged& s, int rows_, int j, int t)
+      : xl(s.xs + (size_t)j * s.XS + t * 32),
+        cj(reinterpret_cast<const float*>(s.c4 + (j >> 1)) + (j & 1)),
+        sj(s.ss + j),
+        rows(rows_),
+        pairs((rows_ + 1) / 2),
+        xb(nullptr),
+        cb(nullptr),
+        sb(nullptr) {}
+  __device__ __forceinline__ void block(int g0) {
+    xb = xl + g0 * 128;
+    cb = cj + (size_t)g0 * pairs * 4;
+    sb = sj + (size_t)g0 * rows;
+  }
+  __device__ __forceinline__ void operator()(int u, int, uint4& x0, uint4& x1, float4& c4, float2& s2) const {
+    const uint4* xp = reinterpret_cast<const uint4*>(xb + u * 128);
+    x0 = xp[0];
+    x1 = xp[1];
+    const float c = cb[(size_t)u * pairs * 4], sv = sb[(size_t)u * rows];
+    c4 = make_float4(c, c, c, c);
+    s2 = make_float2(sv, sv);
+  }
+};
+
 // Position of element n of a row in the prepared layout, and the factor it is stored with.
 template <int BITS>
 __device__ __forceinline__ int prepared_pos(int n) {

@@ -120,79 +120,97 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const __nv_bfloat16*
   }
 }
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------------------
-// Warp-per-expert variant for token counts that cannot fill the GPU with 64x64 tiles.
-// CTA = 8 warps = 8 experts against TT tokens whose rows are staged once in shared memory as
-// raw bf16.  A lane loads 8 consecutive weights per 128-bit load (all loads of a row are issued
-// before the first use), converts them to float64 with integer re-biasing, and accumulates one
-// float64 sum per token; a butterfly reduction over the lanes finishes each dot product.
+// Warp-per-expert variant for token counts that cannot fill the GPU with tiles.
+// CTA = 8 warps = 8 experts against kWarpTokens tokens; the token rows and the eight weight rows are
+// staged in shared memory as raw bf16 with asynchronous copies.  The weight rows are constants of the
+// chain of kernels, so their copies are issued BEFORE the programmatic-dependent-launch wait and land
+// while the previous kernel is still finishing.  The loops are deliberately not unrolled: this code
+// runs once per launch, and fully unrolled float64 arithmetic costs more in instruction fetch than it
+// saves in issue slots (measured: 23 us against 5 us for the same sums).
 // ---------------------------------------------------------------------------------------
-template <int TT>
+constexpr int kWarpTokens = 2;  // tokens per pass over the staged weight row
+constexpr int kWarpTokensMax = 8;  // most tokens a CTA stages (it then makes four passes)
+
+// copies of the CTA's eight weight rows (experts e0 .. e0+7, clamped) into ws4 [8][nvec]
+__device__ __forceinline__ void stage_router_weights(uint4* ws4, const __nv_bfloat16* __restrict__ w, int e0, int E, int H,
+                                                     int tid) {
+  const int nvec = H / 8;
+  for (int i = tid; i < 8 * nvec; i += 256) {
+    const int e = min(e0 + i / nvec, E - 1);
+    cp_async16(ws4 + i, reinterpret_cast<const uint4*>(w + (size_t)e * H) + i % nvec);
+  }
+}
+// copies of the token rows t0 .. t0+n-1 (those that exist) into xs4 [n][nvec]
+__device__ __forceinline__ void stage_router_tokens(uint4* xs4, const __nv_bfloat16* __restrict__ x, int t0, int n, int T,
+                                                    int H, int tid) {
+  const int nvec = H / 8;
+  for (int i = tid; i < n * nvec; i += 256) {
+    const int r = i / nvec;
+    if (t0 + r < T) cp_async16(xs4 + i, reinterpret_cast<const uint4*>(x + (size_t)(t0 + r) * H) + i % nvec);
+  }
+}
+// logits[t0 + j, e] for two staged tokens (j = 0, 1): exact float64 dot product of the warp's staged weight row with each
+// token row, correctly rounded to bf16 (+ the optional float32 logit bias, rounded again).
+__device__ __forceinline__ void warp_expert_logits(const uint4* xs4, const uint4* wrow, int nvec, int lane, int t0, int T,
+                                                   int e, int E, const float* __restrict__ logit_bias,
+                                                   __nv_bfloat16* __restrict__ logits) {
+  const bool two = t0 + 1 < T;
+  const uint4* xrow0 = xs4;
+  const uint4* xrow1 = xs4 + (two ? nvec : 0);
+  double a0 = 0.0, a1 = 0.0, b0 = 0.0, b1 = 0.0;
+#pragma unroll 1
+  for (int c = lane; c < nvec; c += 32) {
+    const uint4 wv = wrow[c], xv = xrow0[c], yv = xrow1[c];
+    const uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w}, xu[4] = {xv.x, xv.y, xv.z, xv.w}, yu[4] = {yv.x, yv.y, yv.z, yv.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const double wl = bf16_bits_to_f64(wu[q] & 0xffffu), wh = bf16_bits_to_f64(wu[q] >> 16);
+      a0 = fma(bf16_bits_to_f64(xu[q] & 0xffffu), wl, a0);
+      a1 = fma(bf16_bits_to_f64(xu[q] >> 16), wh, a1);
+      b0 = fma(bf16_bits_to_f64(yu[q] & 0xffffu), wl, b0);
+      b1 = fma(bf16_bits_to_f64(yu[q] >> 16), wh, b1);
+    }
+  }
+  double sum0 = a0 + a1, sum1 = b0 + b1;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, o);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, o);
+  }
+  if (e < E && lane < 2 && (lane == 0 || two)) {
+    uint32_t bits = f64_to_bf16_bits(lane == 0 ? sum0 : sum1);
+    if (logit_bias) bits = f32_to_bf16_bits(bf16_bits_to_f32(bits) + logit_bias[e]);
+    logits[(size_t)(t0 + lane) * E + e] = __ushort_as_bfloat16((unsigned short)bits);
+  }
+}
+
 __global__ void __launch_bounds__(256) router_logits_warp_kernel(const __nv_bfloat16* __restrict__ x,
                                                                  const __nv_bfloat16* __restrict__ w,
                                                                  const float* __restrict__ logit_bias,
-                                                                 __nv_bfloat16* __restrict__ logits, int T, int H, int E) {
-  extern __shared__ __align__(16) unsigned char rsm[];  // [TT][H] bf16
-  pdl_prologue();
+                                                                 __nv_bfloat16* __restrict__ logits, int T, int H, int E,
+                                                                 int tpc) {
+  extern __shared__ __align__(16) unsigned char rsm[];  // [tpc token rows][8 weight rows]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int t0 = blockIdx.y * TT;
-  const int e = blockIdx.x * 8 + warp;
-  const int nvec = H / 8;  // 128-bit vectors per row
-  // stage the token rows (zero rows past T)
-  for (int i = tid; i < TT * nvec; i += 256) {
-    int r = i / nvec, c = i % nvec;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (t0 + r < T) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + r) * H) + c);
-    reinterpret_cast<uint4*>(rsm)[i] = v;
-  }
+  const int t0 = blockIdx.y * tpc, nvec = H / 8;
+  uint4* xs4 = reinterpret_cast<uint4*>(rsm);
+  uint4* ws4 = xs4 + (size_t)tpc * nvec;
+  pdl_trigger();
+  stage_router_weights(ws4, w, blockIdx.x * 8, E, H, tid);
+  pdl_wait();
+  stage_router_tokens(xs4, x, t0, tpc, T, H, tid);
+  cp_async_wait_all();
   __syncthreads();
-  if (e >= E) return;
-  double acc[TT];
-#pragma unroll
-  for (int j = 0; j < TT; ++j) acc[j] = 0.0;
-  const uint4* wrow = reinterpret_cast<const uint4*>(w + (size_t)e * H);
-  constexpr int UN = 4;  // row vectors in flight per lane
-  for (int c0 = lane; c0 < nvec; c0 += 32 * UN) {
-    uint4 wv[UN];
-#pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      int c = c0 + 32 * u;
-      wv[u] = (c < nvec) ? __ldg(wrow + c) : make_uint4(0, 0, 0, 0);
-    }
-#pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      int c = c0 + 32 * u;
-      if (c >= nvec) break;
-      const uint32_t wu[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
-      double wd[8];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        wd[2 * q] = bf16_bits_to_f64(wu[q] & 0xffffu);
-        wd[2 * q + 1] = bf16_bits_to_f64(wu[q] >> 16);
-      }
-#pragma unroll
-      for (int j = 0; j < TT; ++j) {
-        const uint4 xv = reinterpret_cast<const uint4*>(rsm)[j * nvec + c];
-        const uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          acc[j] = fma(bf16_bits_to_f64(xu[q] & 0xffffu), wd[2 * q], acc[j]);
-          acc[j] = fma(bf16_bits_to_f64(xu[q] >> 16), wd[2 * q + 1], acc[j]);
-        }
-      }
-    }
-  }
-#pragma unroll
-  for (int j = 0; j < TT; ++j) {
-    double s = acc[j];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == 0 && t0 + j < T) {
-      uint32_t bits = f64_to_bf16_bits(s);
-      if (logit_bias) bits = f32_to_bf16_bits(bf16_bits_to_f32(bits) + logit_bias[e]);
-      logits[(size_t)(t0 + j) * E + e] = __ushort_as_bfloat16((unsigned short)bits);
-    }
-  }
+#pragma unroll 1
+  for (int j = 0; j < tpc && t0 + j < T; j += kWarpTokens)
+    warp_expert_logits(xs4 + (size_t)j * nvec, ws4 + (size_t)warp * nvec, nvec, lane, t0 + j, T, blockIdx.x * 8 + warp, E,
+                       logit_bias, logits);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -216,12 +234,6 @@ __global__ void router_weight_f64_kernel(const __nv_bfloat16* __restrict__ w, do
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) w64[i] = bf16_bits_to_f64((uint32_t)__bfloat16_as_ushort(w[i]));
 }
-
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // W64: the weight arrives as float64 (w64) and is copied, only the token rows are converted.
 template <int MT, int NE, int KC, bool W64>
@@ -388,15 +400,15 @@ static void dmma_tile_shape(int T, int E, int& mt_best, int& ne_best) {
     }
 }
 
-template <int TT>
 static int launch_router_warp(const __nv_bfloat16* xp, const __nv_bfloat16* wp, const float* logit_bias,
                               __nv_bfloat16* lp, int T, int H, int E, cudaStream_t st) {
-  size_t smem = (size_t)TT * H * 2;
-  auto kern = router_logits_warp_kernel<TT>;
+  // tokens per CTA: two (one pass) while that keeps the re-staging of the weight rows small, more beyond
+  const int tpc = T <= 32 ? 2 : (T <= 128 ? 4 : kWarpTokensMax);
+  const size_t smem = (size_t)(tpc + 8) * H * 2;
   static DynSmemCache attr;
-  B200_CUDA(ensure_dyn_smem(kern, smem, attr));
-  dim3 grid(cdiv(E, 8), cdiv(T, TT));
-  B200_CUDA(launch_pdl(kern, grid, dim3(256), smem, st, xp, wp, logit_bias, lp, T, H, E));
+  B200_CUDA(ensure_dyn_smem(router_logits_warp_kernel, smem, attr));
+  dim3 grid(cdiv(E, 8), cdiv(T, tpc));
+  B200_CUDA(launch_pdl(router_logits_warp_kernel, grid, dim3(256), smem, st, xp, wp, logit_bias, lp, T, H, E, tpc));
   return 0;
 }
 
@@ -413,7 +425,7 @@ int launch_router_logits(const void* x, const void* w, const float* logit_bias, 
 #else
   constexpr int force = 0;
 #endif
-  const bool warp_ok = (H % 8 == 0) && ((size_t)8 * H * 2 <= 200 * 1024);
+  const bool warp_ok = (H % 8 == 0) && ((size_t)(kWarpTokensMax + 8) * H * 2 <= 200 * 1024);
   const bool dmma_ok = (H % 8 == 0);
   if (dmma_ok && (force == 3 || (!force && T >= 256))) {
     int mt, ne;
@@ -437,10 +449,7 @@ int launch_router_logits(const void* x, const void* w, const float* logit_bias, 
 #undef B200_DMMA_CASE
   }
   const bool use_warp = force ? (force == 1 && warp_ok) : warp_ok;
-  if (use_warp) {
-    if (T <= 4) return launch_router_warp<1>(xp, wp, logit_bias, lp, T, H, E, st);
-    return launch_router_warp<8>(xp, wp, logit_bias, lp, T, H, E, st);
-  }
+  if (use_warp) return launch_router_warp(xp, wp, logit_bias, lp, T, H, E, st);
   if (T <= 256) {
     dim3 grid(cdiv(E, 16), cdiv(T, 8));
     router_logits_kernel<4, 2, 4><<<grid, 256, 0, st>>>(xp, wp, logit_bias, lp, T, H, E);
@@ -477,74 +486,26 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const __nv_bfloat16* __
 // job alone: a warp per token for the top-k, then the single-chunk permutation.  Nobody waits:
 // the other CTAs simply exit.  The ticket word is reset by the last CTA for the next launch.
 // ---------------------------------------------------------------------------------------
-template <int TT>
 __global__ void __launch_bounds__(256) router_fused_small_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, const float* __restrict__ logit_bias,
     __nv_bfloat16* logits, int T, int H, int E, int k, int mode, int renorm, uint32_t* idx, __nv_bfloat16* scores,
     uint32_t* __restrict__ perm, uint32_t* __restrict__ inv, uint32_t* __restrict__ counts,
     uint32_t* __restrict__ offsets, uint32_t* __restrict__ active, uint32_t* __restrict__ n_active,
     unsigned int* ticket, int* __restrict__ err) {
-  extern __shared__ __align__(16) unsigned char rsm[];  // [TT][H] bf16, later the permutation's tables
+  extern __shared__ __align__(16) unsigned char rsm[];  // token and weight rows (bf16), later the permutation's tables
   __shared__ unsigned int s_ticket;
-  pdl_prologue();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int t0 = blockIdx.y * TT;
-  const int e = blockIdx.x * 8 + warp;
-  const int nvec = H / 8;
-  for (int i = tid; i < TT * nvec; i += 256) {
-    int r = i / nvec, c = i % nvec;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (t0 + r < T) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + r) * H) + c);
-    reinterpret_cast<uint4*>(rsm)[i] = v;
-  }
-  __syncthreads();
-  if (e < E) {
-    double acc[TT];
-#pragma unroll
-    for (int j = 0; j < TT; ++j) acc[j] = 0.0;
-    const uint4* wrow = reinterpret_cast<const uint4*>(w + (size_t)e * H);
-    constexpr int UN = 4;
-    for (int c0 = lane; c0 < nvec; c0 += 32 * UN) {
-      uint4 wv[UN];
-#pragma unroll
-      for (int u = 0; u < UN; ++u) {
-        int c = c0 + 32 * u;
-        wv[u] = (c < nvec) ? __ldg(wrow + c) : make_uint4(0, 0, 0, 0);
-      }
-#pragma unroll
-      for (int u = 0; u < UN; ++u) {
-        int c = c0 + 32 * u;
-        if (c >= nvec) break;
-        const uint32_t wu[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
-        double wd[8];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          wd[2 * q] = bf16_bits_to_f64(wu[q] & 0xffffu);
-          wd[2 * q + 1] = bf16_bits_to_f64(wu[q] >> 16);
-        }
-#pragma unroll
-        for (int j = 0; j < TT; ++j) {
-          const uint4 xv = reinterpret_cast<const uint4*>(rsm)[j * nvec + c];
-          const uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            acc[j] = fma(bf16_bits_to_f64(xu[q] & 0xffffu), wd[2 * q], acc[j]);
-            acc[j] = fma(bf16_bits_to_f64(xu[q] >> 16), wd[2 * q + 1], acc[j]);
-          }
-        }
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < TT; ++j) {
-      double s = acc[j];
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      if (lane == 0 && t0 + j < T) {
-        uint32_t bits = f64_to_bf16_bits(s);
-        if (logit_bias) bits = f32_to_bf16_bits(bf16_bits_to_f32(bits) + logit_bias[e]);
-        logits[(size_t)(t0 + j) * E + e] = __ushort_as_bfloat16((unsigned short)bits);
-      }
-    }
+  const int t0 = blockIdx.y * kWarpTokens, nvec = H / 8;
+  {
+    uint4* xs4 = reinterpret_cast<uint4*>(rsm);
+    uint4* ws4 = xs4 + (size_t)kWarpTokens * nvec;
+    pdl_trigger();
+    stage_router_weights(ws4, w, blockIdx.x * 8, E, H, tid);  // constants: on their way before the wait
+    pdl_wait();
+    stage_router_tokens(xs4, x, t0, kWarpTokens, T, H, tid);
+    cp_async_wait_all();
+    __syncthreads();
+    warp_expert_logits(xs4, ws4 + (size_t)warp * nvec, nvec, lane, t0, T, blockIdx.x * 8 + warp, E, logit_bias, logits);
   }
   // publish, then take a ticket
   __threadfence();
@@ -561,24 +522,8 @@ __global__ void __launch_bounds__(256) router_fused_small_kernel(
 }
 
 bool router_fused_small_ok(int T, int H, int E, int k) {
-  return T <= 8 && (int64_t)T * k <= kChunk && H % 8 == 0 && (size_t)8 * H * 2 <= 200 * 1024 && E <= kMaxPerLane * 32;
-}
-
-template <int TT>
-static int launch_fused_small(const __nv_bfloat16* xp, const __nv_bfloat16* wp, const float* logit_bias,
-                              __nv_bfloat16* lp, int T, int H, int E, int k, int mode, int renorm, uint32_t* idx,
-                              __nv_bfloat16* scores, uint32_t* perm, uint32_t* inv, uint32_t* counts, uint32_t* offsets,
-                              uint32_t* active, uint32_t* n_active, unsigned int* ticket, int* err, cudaStream_t st) {
-  size_t smem = (size_t)TT * H * 2;
-  const size_t need = sizeof(int) * 33 * E;
-  if (smem < need) smem = need;
-  auto kern = router_fused_small_kernel<TT>;
-  static DynSmemCache attr;
-  B200_CUDA(ensure_dyn_smem(kern, smem, attr));
-  dim3 grid(cdiv(E, 8), cdiv(T, TT));
-  B200_CUDA(launch_pdl(kern, grid, dim3(256), smem, st, xp, wp, logit_bias, lp, T, H, E, k, mode, renorm, idx, scores, perm, inv,
-                       counts, offsets, active, n_active, ticket, err));
-  return 0;
+  return T <= 8 && (int64_t)T * k <= kChunk && H % 8 == 0 && (size_t)(kWarpTokens + 8) * H * 2 <= 200 * 1024 &&
+         E <= kMaxPerLane * 32;
 }
 
 int launch_router_fused_small(const void* x, const void* w, const float* logit_bias, void* logits, int T, int H, int E,
@@ -589,11 +534,15 @@ int launch_router_fused_small(const void* x, const void* w, const float* logit_b
   auto wp = static_cast<const __nv_bfloat16*>(w);
   auto lp = static_cast<__nv_bfloat16*>(logits);
   auto sp = static_cast<__nv_bfloat16*>(scores);
-  if (T <= 4)
-    return launch_fused_small<1>(xp, wp, logit_bias, lp, T, H, E, k, mode, renorm, idx, sp, perm, inv, counts, offsets,
-                                 active, n_active, ticket, err, st);
-  return launch_fused_small<8>(xp, wp, logit_bias, lp, T, H, E, k, mode, renorm, idx, sp, perm, inv, counts, offsets,
-                               active, n_active, ticket, err, st);
+  size_t smem = (size_t)(kWarpTokens + 8) * H * 2;
+  const size_t need = sizeof(int) * 33 * E;
+  if (smem < need) smem = need;
+  static DynSmemCache attr;
+  B200_CUDA(ensure_dyn_smem(router_fused_small_kernel, smem, attr));
+  dim3 grid(cdiv(E, 8), cdiv(T, kWarpTokens));
+  B200_CUDA(launch_pdl(router_fused_small_kernel, grid, dim3(256), smem, st, xp, wp, logit_bias, lp, T, H, E, k, mode, renorm, idx,
+                       sp, perm, inv, counts, offsets, active, n_active, ticket, err));
+  return 0;
 }
 
 int launch_route_topk(const void* logits, int T, int E, int k, int mode, int renorm, uint32_t* idx, void* scores,

@@ -44,6 +44,15 @@ def test_tiny_exhaustive(pkg, O, T, E, k):
     check_block(pkg, O, make_block(T, 128, E, 64, k, seed=T * 10 + E + k))
 
 
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("T,k", [(1, 8), (5, 3), (8, 12)])
+def test_handful_of_tokens_fused_tail(pkg, O, bits, T, k):
+    """At most eight tokens: the gate/up CTAs prepare their own activation rows and the down projection finishes
+    the block (routing weights and k-way sum in its epilogue).  K = 320 leaves a ragged last block of groups in
+    both bit widths; k = 12 makes warps take a second expert slot."""
+    check_block(pkg, O, make_block(T, 320, 16, 192, k, bits=bits, seed=T * 7 + k + bits))
+
+
 @pytest.fixture(scope="module")
 def config0():
     """BASELINE.json configs[0]: hidden 2048, 128 experts, top-8 renormalised, inter 768, 4-bit, 64 tokens."""
