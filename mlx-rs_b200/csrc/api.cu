@@ -131,8 +131,6 @@ static int check_cfg(const b200_moe_config* cfg) {
 static inline int permute_launches(int64_t n) { return n <= 1024 ? 1 : 3; }
 // rows per expert (average over the experts that can be active) from which the tensor-core kernel is used
 constexpr int64_t kTensorCoreRowsPerExpert = 14;
-// Largest K (the block's intermediate size) whose down projection alternates its accumulators between 128-row tiles.
-constexpr int kAltDownMaxK = 1024;
 constexpr int kTicketWord = 8;  // word of the status block that the fused small-batch router uses as its ticket counter
 // Status block of a context: word 0 = device-side status, word 8 = ticket of the fused router, words 16..63 =
 // self-timing of development builds.
@@ -311,7 +309,8 @@ static int run_grouped(b200_ctx* c, GroupedArgs& a, int bits, int max_active, in
     float* rs = static_cast<float*>(c->take(sizeof(float) * n));
     B200_REQUIRE(tile_expert && tile_row0 && tile_rows && n_row_tiles && xs && rs, "scratch arena too small");
     launch_build_row_tiles(counts, a.offsets, E, tile_expert, tile_row0, tile_rows, n_row_tiles, 256, st);
-    launch_prepare_rows(x, a.perm, a.src_map, 1, n, nullptr, a.K, bits == 4, xs, rs, st);
+    // rows that exist = offsets[E]: assignments with an out-of-range matrix index were left out of the sort
+    launch_prepare_rows(x, a.perm, a.src_map, 1, n, a.offsets + E, a.K, bits == 4, xs, rs, st);
     if (launch_grouped_qmm_tc(xs, rs, n, a, 1, bits, tile_expert, tile_row0, tile_rows, n_row_tiles, E, false, c->err, st))
       return 1;
     LAUNCHED(c, 3);
@@ -476,8 +475,8 @@ int b200_gather_mm(b200_ctx* c, const void* a, const void* b, const uint32_t* lh
                  "scratch arena too small");
     launch_expand_indices(lhs_indices, rhs_indices, n_idx, (int)M, Ba, flat_e, flat_s, c->err, st);
     launch_permute(flat_e, n, E, perm, inv, counts, offsets, active, n_active, chunk, c->err, st);
-    launch_gather_rows(a, perm, flat_s, n, K, a_sorted, st);
-    launch_build_row_tiles(counts, offsets, E, tile_expert, tile_row0, tile_rows, n_row_tiles, 128, st);
+    launch_gather_rows(a, perm, flat_s, n, offsets + E, K, a_sorted, st);
+    launch_build_row_tiles(counts, offsets, E, tile_expert, tile_row0, tile_rows, n_row_tiles, 256, st);
     if (launch_gather_mm_tc(a_sorted, n, b, E, (int)K, (int)N, perm, out, tile_expert, tile_row0, tile_rows, n_row_tiles, c->err, st))
       return 1;
     LAUNCHED(c, 4 + permute_launches(n));
@@ -736,7 +735,7 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   // n is the host's bound on the number of rows; with `xr` the rows that exist are counted on the device
   // (everything below is driven by the device-side segment tables, only the row preparation needs the extra
   // words) and are gathered from x through xr->map
-  const uint32_t* n_dev = xr ? xr->n_dev : nullptr;
+  const uint32_t* n_dev = xr ? xr->n_dev : offsets + cfg.n_experts;  // (sorted rows that exist: offsets[E])
   const int E = cfg.n_experts;
   void* h = c->take(sizeof(uint16_t) * n * cfg.inter);
   B200_REQUIRE(h, "scratch arena too small");
@@ -751,11 +750,11 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   uint32_t *tile_expert1 = nullptr, *tile_row01 = nullptr, *tile_rows1 = nullptr, *n_row_tiles1 = nullptr;
   void* xs = nullptr;
   float* rs_x = nullptr;
-  // down projection: with a short K the drain of a tile is a large share of its time and must run under the next
-  // tile's products (128-row tiles alternating between the two accumulators); with a long K it is not, and 256-row
-  // tiles whose two accumulators share every dequantised weight stage halve the dequantisation and shared-memory
-  // traffic per product
-  bool alt_down = cfg.inter <= kAltDownMaxK;
+  // down projection: 256-row tiles whose two accumulators share every dequantised weight stage, like gate/up.
+  // (128-row tiles alternating between the accumulators, so that one tile's drain runs under the next tile's
+  // products, measured slower at every K once the outputs became fp16: 1.132 against 1.111 ms per step at K = 768,
+  // 3.86 against 3.58 ms at K = 1536, 14.6 against 12.5 ms at K = 14336.)
+  bool alt_down = false;
 #ifdef B200_DEV
   if (const char* v = getenv("B200_ALT_DOWN")) alt_down = atoi(v) != 0;
 #endif
@@ -964,11 +963,26 @@ int b200_moe_block_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_m
     launch_router_logits(x, params->router_weight, params->router_logit_bias, logits, (int)T, cfg->hidden, cfg->n_experts,
                          w64, st);
     c->mark(1, st);
-    launch_route_topk(logits, (int)T, cfg->n_experts, cfg->top_k, cfg->router_mode, cfg->norm_topk_prob, idx, scores,
-                      nullptr, st);
-    c->mark(2, st);
-    LAUNCHED(c, 2);
-    if (experts_forward(c, *cfg, *params, x, idx, scores, T, yk, aux, st, &yk_fmt)) return 1;
+    if (route_topk_sort_ok((int)T, cfg->n_experts, cfg->top_k)) {
+      // up to 1024 assignments: the routing kernel's last CTA also sorts them (stage 2 reads as zero)
+      SortBufs sb;
+      if (take_sort_bufs(c, n, cfg->n_experts, aux, sb)) return 1;
+      if (launch_route_topk_sort(logits, (int)T, cfg->n_experts, cfg->top_k, cfg->router_mode, cfg->norm_topk_prob, idx, scores,
+                                 sb.perm, sb.inv, sb.counts, sb.offsets, sb.active, sb.n_active,
+                                 reinterpret_cast<unsigned int*>(c->err + kTicketWord), c->err, st))
+        return 1;
+      c->mark(2, st);
+      LAUNCHED(c, 2);
+      if (experts_sorted(c, *cfg, *params, x, sb.perm, cfg->top_k, sb.counts, sb.offsets, sb.active, sb.n_active, n, scores,
+                         yk, st, &yk_fmt))
+        return 1;
+    } else {
+      launch_route_topk(logits, (int)T, cfg->n_experts, cfg->top_k, cfg->router_mode, cfg->norm_topk_prob, idx, scores,
+                        nullptr, st);
+      c->mark(2, st);
+      LAUNCHED(c, 2);
+      if (experts_forward(c, *cfg, *params, x, idx, scores, T, yk, aux, st, &yk_fmt)) return 1;
+    }
   }
   if (yk_fmt != kOutNone) {
     if (launch_combine(yk, yk_fmt, T, cfg->top_k, cfg->hidden, out, aux ? aux->out_f32 : nullptr, st)) return 1;

@@ -36,7 +36,6 @@ struct GroupedArgs {
                               // in the A-operand layout of the same path's down projection (register kernel: prepared rows)
   int K, N;
   int n_experts;              // number of stacked weight matrices
-  int no_l2_prefetch;         // register kernel: 1 switches the whole-row L2 prefetch off (development comparisons)
   int x_bf16;                 // register kernel: 1 = x holds plain bf16 rows and every CTA prepares the rows it stages
                               // itself (a handful of rows per expert: cheaper than a preparation launch)
 };
@@ -69,6 +68,11 @@ int launch_router_fused_small(const void* x, const void* w, const float* logit_b
                               int k, int mode, int renorm, uint32_t* idx, void* scores, uint32_t* perm, uint32_t* inv,
                               uint32_t* counts, uint32_t* offsets, uint32_t* active, uint32_t* n_active,
                               unsigned int* ticket, int* err, cudaStream_t st);
+// top-k + token -> expert sort in one launch (T*k <= 1024); `ticket` is a zero-initialised device word
+bool route_topk_sort_ok(int T, int E, int k);
+int launch_route_topk_sort(const void* logits, int T, int E, int k, int mode, int renorm, uint32_t* idx, void* scores,
+                           uint32_t* perm, uint32_t* inv, uint32_t* counts, uint32_t* offsets, uint32_t* active,
+                           uint32_t* n_active, unsigned int* ticket, int* err, cudaStream_t st);
 int launch_argpartition(const void* a, int rows, int cols, int kth, uint32_t* out, cudaStream_t st);
 int launch_topk_values(const void* a, int rows, int cols, int k, void* out, cudaStream_t st);
 int launch_softmax(const void* a, int rows, int cols, void* out, cudaStream_t st);
@@ -120,8 +124,8 @@ int launch_gather_qmm_generic(const void* x, const uint32_t* wq, const void* sca
                               int64_t n_idx, int transpose, int gs, int bits, void* out, int* err, cudaStream_t st);
 int launch_gather_mm(const void* a, const void* b, const uint32_t* lhs, const uint32_t* rhs, int64_t Ba, int64_t Bb,
                      int64_t M, int64_t K, int64_t N, int64_t n_idx, void* out, int* err, cudaStream_t st);
-int launch_gather_rows(const void* x, const uint32_t* perm, const uint32_t* src_map, int64_t n_rows, int64_t cols, void* out,
-                       cudaStream_t st);
+int launch_gather_rows(const void* x, const uint32_t* perm, const uint32_t* src_map, int64_t n_rows, const uint32_t* n_valid,
+                       int64_t cols, void* out, cudaStream_t st);
 int launch_gather_mm_tc(const void* a_sorted, int64_t rows, const void* b, int Bb, int K, int N, const uint32_t* perm, void* out,
                         const uint32_t* tile_expert, const uint32_t* tile_row0, const uint32_t* tile_rows,
                         const uint32_t* n_row_tiles, int* err, cudaStream_t st);

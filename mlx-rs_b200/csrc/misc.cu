@@ -494,20 +494,24 @@ __global__ void expand_indices_kernel(const uint32_t* __restrict__ lhs, const ui
   flat_src[i] = src * (uint32_t)M + (uint32_t)m;
 }
 // out[p, :] = x[src_map[perm[p]], :] for rows of 2-byte elements (16-byte vectors): the rows of a gathered product
-// in the order of its sort.
+// in the order of its sort.  Only the first *n_valid sorted positions exist (assignments whose matrix index was out
+// of range are left out of the sort and perm holds nothing for the tail).
 __global__ void gather_rows_kernel(const uint4* __restrict__ x, const uint32_t* __restrict__ perm,
-                                   const uint32_t* __restrict__ src_map, int64_t n_rows, int vec_per_row,
-                                   uint4* __restrict__ out) {
+                                   const uint32_t* __restrict__ src_map, int64_t n_rows,
+                                   const uint32_t* __restrict__ n_valid, int vec_per_row, uint4* __restrict__ out) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_rows * vec_per_row) return;
   const int64_t r = i / vec_per_row;
-  out[i] = __ldg(x + (size_t)src_map[perm[r]] * vec_per_row + (i % vec_per_row));
+  if (r >= (int64_t)*n_valid) return;
+  const uint32_t a = perm[r];
+  if ((int64_t)a >= n_rows) return;
+  out[i] = __ldg(x + (size_t)src_map[a] * vec_per_row + (i % vec_per_row));
 }
-int launch_gather_rows(const void* x, const uint32_t* perm, const uint32_t* src_map, int64_t n_rows, int64_t cols, void* out,
-                       cudaStream_t st) {
+int launch_gather_rows(const void* x, const uint32_t* perm, const uint32_t* src_map, int64_t n_rows, const uint32_t* n_valid,
+                       int64_t cols, void* out, cudaStream_t st) {
   if (n_rows == 0) return 0;
   const int64_t n = n_rows * (cols / 8);
-  gather_rows_kernel<<<cdiv(n, 256), 256, 0, st>>>(static_cast<const uint4*>(x), perm, src_map, n_rows, (int)(cols / 8),
+  gather_rows_kernel<<<cdiv(n, 256), 256, 0, st>>>(static_cast<const uint4*>(x), perm, src_map, n_rows, n_valid, (int)(cols / 8),
                                                    static_cast<uint4*>(out));
   return 0;
 }

@@ -36,7 +36,7 @@ __device__ __forceinline__ void permute_small_block(const uint32_t* idx, int n, 
   for (int q = 0; q < R; ++q) {
     const int i = q * NT + threadIdx.x;
     valid[q] = i < n;
-    e[q] = valid[q] ? idx[i] : 0u;
+    e[q] = valid[q] ? __ldcg(idx + i) : 0u;  // possibly written by other CTAs of the same launch: read at L2
     if (valid[q] && e[q] >= (uint32_t)E) {
       *err = 2;
       valid[q] = false;

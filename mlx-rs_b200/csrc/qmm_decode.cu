@@ -66,23 +66,6 @@ __global__ void __launch_bounds__(256, NT == 1 ? 2 : 1) grouped_qmm_small_kernel
   const __half* x16 = static_cast<const __half*>(p.x);
 
   const size_t soff_a = row_a * G, soff_b = row_b * G;
-  // The CTA's weight rows start their way from DRAM to L2 now, all of them: the register stream below holds only two
-  // blocks per lane in flight (64 KB per SM), too little to cover DRAM latency at full bandwidth; with the rows already
-  // on their way its loads find them in L2.  Lanes t = 0 / 1 ask for the packed rows a / b, t = 2 / 3 for their scales
-  // and biases.
-  if (ks == 0 && !p.no_l2_prefetch) {
-    if (t < 2) {
-      l2_prefetch_bulk(p.w[mt] + (t == 0 ? row_a : row_b) * wrow, (uint32_t)wrow * 4u);
-    } else {
-      const size_t so = (t == 2 ? soff_a : soff_b);
-      const char* ps = reinterpret_cast<const char*>(sc_base + so);
-      const char* pb = reinterpret_cast<const char*>(bi_base + so);
-      for (int o = 0; o < G * 2 + 127; o += 128) {
-        l2_prefetch_line(ps + min(o, G * 2 - 1));
-        l2_prefetch_line(pb + min(o, G * 2 - 1));
-      }
-    }
-  }
   for (int p0 = 0; p0 < m; p0 += ROWS) {
     const int nrows = min(ROWS, m - p0);
     // the first block of weights is on its way while the activation rows are staged
@@ -223,15 +206,6 @@ __global__ void __launch_bounds__(256, 2) down_combine_small_kernel(DownCombineA
   auto start_slot = [&](int j) {
     const size_t e = s_e[j];
     const size_t row_a = e * N + min(n0 + gq, N - 1), row_b = e * N + min(n0 + gq + 8, N - 1);
-    if (t < 2) {  // the rows' way from DRAM to L2 starts now, whole rows (see grouped_qmm_small_kernel)
-      l2_prefetch_bulk(p.w + (t == 0 ? row_a : row_b) * wrow, (uint32_t)wrow * 4u);
-    } else {
-      const size_t so = (t == 2 ? row_a : row_b) * G;
-      for (int o = 0; o < G * 2 + 127; o += 128) {
-        l2_prefetch_line(reinterpret_cast<const char*>(scb + so) + min(o, G * 2 - 1));
-        l2_prefetch_line(reinterpret_cast<const char*>(bib + so) + min(o, G * 2 - 1));
-      }
-    }
     ws.start(p.w + row_a * wrow + t * WPT, p.w + row_b * wrow + t * WPT, scb + row_a * G, bib + row_a * G, scb + row_b * G,
              bib + row_b * G, G, 0, 1);
   };
@@ -334,12 +308,6 @@ static int launch_cfg(const GroupedArgs& a, int max_active, cudaStream_t st) {
   static DynSmemCache attr;
   B200_CUDA(ensure_dyn_smem(kern, smem, attr));
   dim3 grid(cdiv(a.N, 16 * RT), max_active);
-#ifdef B200_DEV
-  GroupedArgs dev_args = a;
-  if (getenv("B200_SMALL_NO_PREFETCH")) dev_args.no_l2_prefetch = 1;
-  B200_CUDA(launch_pdl(kern, grid, dim3(256), smem, st, dev_args));
-  return 0;
-#endif
   B200_CUDA(launch_pdl(kern, grid, dim3(256), smem, st, a));
   return 0;
 }

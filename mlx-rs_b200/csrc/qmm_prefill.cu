@@ -776,7 +776,12 @@ __global__ void __launch_bounds__(256) prepare_rows_kernel(const uint4* __restri
   // n_rows is the host's bound; the number of rows that exist may live on the device (expert-parallel exchange)
   if (r >= n_rows || (n_rows_dev && r >= (int64_t)*n_rows_dev)) return;
   // source row of sorted position r: r itself, src_map[r], perm[r] / src_div, or src_map[perm[r]]
-  const uint32_t src = !perm ? (src_map ? src_map[r] : (uint32_t)r) : (src_map ? src_map[perm[r]] : perm[r] / (uint32_t)src_div);
+  uint32_t a = (uint32_t)r;
+  if (perm) {
+    a = perm[r];
+    if ((int64_t)a >= n_rows) return;  // not an assignment of this call (never written by the sort): no row to read
+  }
+  const uint32_t src = !perm ? (src_map ? src_map[r] : (uint32_t)r) : (src_map ? src_map[a] : a / (uint32_t)src_div);
   const uint4* xr = x + (size_t)src * vec_per_row;
   uint32_t mxbits = 0;  // max over |x| as bf16 bit patterns (monotonic for non-negative floats)
   for (int c = lane; c < vec_per_row; c += 32) {
@@ -960,7 +965,7 @@ int launch_gather_mm_tc(const void* a_sorted, int64_t rows, const void* b, int B
   p.K = K;
   p.N = N;
   p.err = err;
-  p.alt = 1;
+  p.alt = 0;  // 256-row tiles: both accumulators share every transposed stage of b
   const int n_sm = current_sm_count();
   const int64_t max_tiles = (int64_t)prefill_tile_words(rows, Bb) * ((N + NCOL - 1) / NCOL);
   const int grid = (int)(max_tiles < n_sm ? max_tiles : n_sm);

@@ -122,11 +122,6 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src)
                : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-// Asks for `bytes` (a multiple of 16, from a 16-byte aligned address) to be brought from DRAM into L2; returns at once.
-__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void l2_prefetch_line(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
 // After the copies have landed (cp_async_wait_all + barrier by the caller): per (row, group) the sums S and -C of
 // the first n_valid of the `rows` staged rows (the others are never read back: an MMA column only depends on its

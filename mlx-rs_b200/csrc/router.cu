@@ -480,6 +480,49 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const __nv_bfloat16* __
 }
 
 // ---------------------------------------------------------------------------------------
+// Routing and the token -> expert sort in one launch, for T*k <= 1024 assignments: a warp per token
+// for the top-k, then every CTA publishes its indices (fence) and takes a ticket; the CTA that draws
+// the last one runs the single-chunk permutation.  Nobody waits; the ticket word is reset by the
+// last CTA for the next launch.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) route_topk_sort_kernel(const __nv_bfloat16* __restrict__ logits, int T, int E, int k,
+                                                              int mode, int renorm, uint32_t* idx, __nv_bfloat16* scores,
+                                                              uint32_t* __restrict__ perm, uint32_t* __restrict__ inv,
+                                                              uint32_t* __restrict__ counts, uint32_t* __restrict__ offsets,
+                                                              uint32_t* __restrict__ active, uint32_t* __restrict__ n_active,
+                                                              unsigned int* ticket, int* __restrict__ err) {
+  extern __shared__ int topk_sort_sh[];  // the permutation's tables
+  __shared__ unsigned int s_ticket;
+  pdl_prologue();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int t = blockIdx.x * 8 + warp;
+  if (t < T) route_topk_token<false>(logits, t, lane, E, k, mode, renorm, idx, scores, nullptr);
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_ticket = atomicAdd(ticket, 1u);
+  __syncthreads();
+  if (s_ticket != gridDim.x - 1) return;
+  __threadfence();
+  if (tid == 0) *ticket = 0u;
+  permute_small_block<256>(idx, T * k, E, perm, inv, counts, offsets, active, n_active, err, topk_sort_sh);
+}
+
+bool route_topk_sort_ok(int T, int E, int k) { return (int64_t)T * k <= kChunk && E <= kMaxPerLane * 32; }
+
+int launch_route_topk_sort(const void* logits, int T, int E, int k, int mode, int renorm, uint32_t* idx, void* scores,
+                           uint32_t* perm, uint32_t* inv, uint32_t* counts, uint32_t* offsets, uint32_t* active,
+                           uint32_t* n_active, unsigned int* ticket, int* err, cudaStream_t st) {
+  if (T == 0) return 0;
+  const size_t smem = sizeof(int) * 33 * E;
+  static DynSmemCache attr;
+  B200_CUDA(ensure_dyn_smem(route_topk_sort_kernel, smem, attr));
+  B200_CUDA(launch_pdl(route_topk_sort_kernel, dim3(cdiv(T, 8)), dim3(256), smem, st, static_cast<const __nv_bfloat16*>(logits), T,
+                       E, k, mode, renorm, idx, static_cast<__nv_bfloat16*>(scores), perm, inv, counts, offsets, active, n_active,
+                       ticket, err));
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
 // Small batches (T*k <= 1024): logits, routing and the token -> expert sort in ONE launch.
 // Every CTA computes its logits like router_logits_warp_kernel, publishes them (fence) and takes a
 // ticket; the CTA that draws the last ticket knows that all logits are in memory and finishes the
