@@ -338,6 +338,42 @@ def run_stack(args, pkg, torch, dev, peaks):
     print(json.dumps(line))
 
 
+def run_gather_mm(args, pkg, torch, dev, peaks):
+    """ops.gather_mm (mlx-rs/src/ops/arithmetic.rs:1568-1632) on un-quantised bf16 experts of the config's gate shape:
+    a [T*k, 1, H], b [E, H, I], uniformly random rhs indices -> [T*k, 1, I].  Side measurement (row f1 of the
+    scope table), not the headline metric: one JSON line with the whole-call time (index expansion, sort, row
+    gather, grouped tcgen05 product) against the measured dense bf16 peak."""
+    H, I, E, k = (SHAPE[n] for n in ("hidden", "inter", "n_experts", "top_k"))
+    rows = args.tokens * k
+    g = torch.Generator(device=dev).manual_seed(args.seed)
+    a = (torch.randn(rows, 1, H, generator=g, device=dev) / 8).bfloat16()
+    b = (torch.randn(E, H, I, generator=g, device=dev) / 8).bfloat16()
+    rhs = torch.randint(0, E, (rows,), generator=g, device=dev, dtype=torch.int32)
+    flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    ctx = pkg.default_context()
+    l0 = ctx.launch_count()
+    with ClockSampler(dev.index or 0) as clk:
+        times = time_steps(torch, lambda: pkg.ops.gather_mm(a, b, None, rhs), args.steps, args.warmup,
+                           lambda: flush_buf.fill_(1))
+    ctx.check()
+    out = pkg.ops.gather_mm(a, b, None, rhs)
+    idx = torch.randint(0, rows, (256,), generator=g, device=dev)
+    ref = torch.einsum("rk,rkn->rn", a[idx, 0].float(), b[rhs[idx].long()].float())
+    err = float((out[idx, 0].float() - ref).abs().max() / ref.abs().max())
+    ms = statistics.mean(times)
+    flops = 2.0 * rows * H * I
+    print(json.dumps(dict(metric="gather_mm_tflops", value=flops / (ms * 1e-3) / 1e12, unit="TFLOP/s", n_gpus=1, steps=args.steps,
+                          warmup=args.warmup, ms_per_step=ms, higher_is_better=True, dtype="bf16", data="synthetic",
+                          config=dict(workload=f"gather_mm a[{rows},1,{H}] x b[{E},{H},{I}], random rhs indices",
+                                      l2="flushed between iterations (512 MB overwrite)"),
+                          roofline=dict(bound="tensor", achieved=flops / (ms * 1e-3) / 1e12, peak=peaks["tensor"], unit="TFLOP/s",
+                                        frac=flops / (ms * 1e-3) / 1e12 / peaks["tensor"], traffic=None,
+                                        peak_source=peaks["source"], kernel="whole gather_mm call"),
+                          check=dict(rows_sampled=256, max_rel_err_vs_float32=err),
+                          gpu_launches=(ctx.launch_count() - l0) // (args.steps + args.warmup + 1) * args.steps,
+                          clocks=clk.summary())))
+
+
 def main():
     global SHAPE, CFG
     ap = argparse.ArgumentParser()
@@ -345,8 +381,9 @@ def main():
                     help="BASELINE.json configs index: 1 = Qwen3-30B-A3B layer (default, the metric's configuration), "
                          "2 = its 48-layer stack, 3 = Qwen3-235B-A22B layer, 4 = Mixtral layer with skewed routing")
     ap.add_argument("--bits", type=int, default=None, choices=[4, 8], help="weight bits (configs[4] asks for both)")
-    ap.add_argument("--workload", default=None, choices=["layer", "stack"],
-                    help="layer: one MoE layer; stack: configs[2] (implied by --config 2)")
+    ap.add_argument("--workload", default=None, choices=["layer", "stack", "gather_mm"],
+                    help="layer: one MoE layer; stack: configs[2] (implied by --config 2); gather_mm: the un-quantised "
+                         "gathered product (the op behind a bf16 SwitchLinear) at the config's gate shape, tokens x top_k rows")
     ap.add_argument("--layers", type=int, default=48)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -405,6 +442,8 @@ def main():
 
     if args.workload == "stack":
         return run_stack(args, pkg, torch, dev, peaks)
+    if args.workload == "gather_mm":
+        return run_gather_mm(args, pkg, torch, dev, peaks)
     ctx = pkg.default_context()
     ctx.set_qmm_path(dict(auto=ctx.QMM_AUTO, small=ctx.QMM_SMALL, tensor_core=ctx.QMM_TENSOR_CORE)[args.qmm_path])
     block = build_block(pkg, torch, args.seed, SHAPE, dev)

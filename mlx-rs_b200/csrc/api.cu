@@ -750,11 +750,13 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   uint32_t *tile_expert1 = nullptr, *tile_row01 = nullptr, *tile_rows1 = nullptr, *n_row_tiles1 = nullptr;
   void* xs = nullptr;
   float* rs_x = nullptr;
-  // down projection: 256-row tiles whose two accumulators share every dequantised weight stage, like gate/up.
-  // (128-row tiles alternating between the accumulators, so that one tile's drain runs under the next tile's
-  // products, measured slower at every K once the outputs became fp16: 1.132 against 1.111 ms per step at K = 768,
-  // 3.86 against 3.58 ms at K = 1536, 14.6 against 12.5 ms at K = 14336.)
-  bool alt_down = false;
+  // down projection: 256-row tiles whose two accumulators share every dequantised weight stage, like gate/up, once
+  // experts hold enough rows to use both accumulators.  (128-row tiles alternating between the accumulators, so that
+  // one tile's drain runs under the next tile's products, measured slower at every K once the outputs became fp16:
+  // 1.132 against 1.111 ms per step at K = 768, 3.86 against 3.58 ms at K = 1536, 14.6 against 12.5 ms at K = 14336.)
+  // With fewer than 128 rows per expert a tile never reaches its second accumulator, and alternating is what hides
+  // the drain: 88 against 116 us at 32 rows per expert.
+  bool alt_down = n / (max_active > 0 ? max_active : 1) < 128;
 #ifdef B200_DEV
   if (const char* v = getenv("B200_ALT_DOWN")) alt_down = atoi(v) != 0;
 #endif
