@@ -401,7 +401,7 @@ def main():
                          "one host synchronisation per step; peer_push = dispatch kernel + down projection whose epilogue "
                          "stores the rows back into the source GPU; nccl = torch.distributed all-to-all-v (the baseline)")
     ap.add_argument("--ep-chunks", type=int, default=0, choices=[0, 1, 2],
-                    help="N > 1, peer transport: halves of a rank's tokens whose exchange overlaps the other half's products "
+                    help="N > 1: halves of a rank's tokens whose exchange overlaps the other half's products "
                          "(0 = default: one)")
     ap.add_argument("--qmm-path", default="auto", choices=["auto", "small", "tensor_core"],
                     help="pin the grouped-product kernel (default: the library chooses)")

@@ -349,6 +349,15 @@ int b200_ep_comm_create(b200_ctx* ctx, int n_ranks, int rank, int n_experts, int
                         unsigned char* handles /* [B200_EP_COMM_HANDLES][B200_EP_HANDLE_BYTES] */);
 int b200_ep_comm_connect(b200_ctx* ctx, b200_ep_comm* comm, const unsigned char* all_handles);
 int b200_ep_comm_destroy(b200_ctx* ctx, b200_ep_comm* comm);
+/* Half-steps per step, 1 (default) or 2; EVERY rank of the group must set the same value before the next step.
+ * With 2 a step runs as two complete exchanges over consecutive halves of each rank's tokens, on separate buffers and
+ * control words (a communicator always holds both sets): the exchange kernels go to a stream the communicator owns
+ * and are joined back into the caller's stream before the call's work ends there, so that the dispatch of the second
+ * half and the return of the first run under the other half's expert products.  Measured at 8192 tokens per rank on 2
+ * and 4 GPUs it is slower than one step (the second set of small launches costs more than the overlap returns), so
+ * it is left to the caller; aux->perm / inv_perm / offsets (which describe one sort of the whole step) cannot be
+ * asked for then. */
+int b200_ep_comm_set_chunks(b200_ctx* ctx, b200_ep_comm* comm, int chunks);
 /* aux->out_f32 is not produced here (the returned expert outputs are bf16); the other aux fields are. */
 int b200_moe_block_forward_ep(b200_ctx* ctx, b200_ep_comm* comm, const b200_moe_config* cfg, const b200_moe_params* params,
                               const void* x, int64_t T, void* out, const b200_moe_aux* aux, void* stream);

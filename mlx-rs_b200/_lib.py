@@ -101,6 +101,7 @@ EXPORTS = {
                                       C.POINTER(C.c_void_p), C.c_char_p]),
     "b200_ep_comm_connect": (C.c_int, [C.c_void_p, C.c_void_p, C.c_char_p]),
     "b200_ep_comm_destroy": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b200_ep_comm_set_chunks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int]),
     "b200_moe_block_forward_ep": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(MoeConfig), C.POINTER(MoeParams), C.c_void_p,
                                             C.c_int64, C.c_void_p, C.POINTER(MoeAux), C.c_void_p]),
     "b200_moe_block_forward": (C.c_int, [C.c_void_p, C.POINTER(MoeConfig), C.POINTER(MoeParams), C.c_void_p, C.c_int64,

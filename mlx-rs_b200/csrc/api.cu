@@ -1157,14 +1157,37 @@ int b200_ep_combine(b200_ctx* c, void* const* peer_y, const uint32_t* indices, c
 }
 
 // ---- one-call expert-parallel block with device-side phase ordering ------------------------------------------
+constexpr int kEpChunks = 2;  // exchange sets per communicator: a step may run as two half-steps that overlap
 struct b200_ep_comm {
-  EpExchange x{};               // peer pointers, shape, device words
+  EpExchange x{};               // shape; peer pointers and device words of exchange set 0
+  EpExchange xc[kEpChunks];     // the exchange sets: every peer-mapped buffer holds kEpChunks equal parts
+  size_t part_bytes[kEpBufs] = {};
   void* own[kEpBufs] = {};      // this rank's six peer-mapped buffers
+  void* peer_base[kEpBufs][kEpMaxRanks] = {};
   bool opened[kEpBufs][kEpMaxRanks] = {};
-  void* y = nullptr;            // this rank's expert outputs by assignment row (local only)
+  void* y = nullptr;            // this rank's expert outputs by assignment row (local only; the half-steps use it in turn)
   uint32_t* dev = nullptr;      // backing store of the device words
   bool connected = false;
+  int chunks = 1;               // half-steps per step (b200_ep_comm_set_chunks)
+  cudaStream_t side = nullptr;  // exchange kernels of one half-step run here under the other half-step's products
+  cudaEvent_t ev_fork = nullptr, ev_a[kEpChunks] = {}, ev_b[kEpChunks] = {}, ev_join = nullptr;
 };
+static void ep_comm_views(b200_ep_comm* e) {
+  for (int ch = 0; ch < kEpChunks; ++ch) {
+    EpExchange& v = e->xc[ch];
+    const EpExchange keep = v;
+    v = e->x;
+    v.dst_row0 = keep.dst_row0;
+    v.local_counts = keep.local_counts;
+    v.n_recv = keep.n_recv;
+    v.tokbase = keep.tokbase;
+    v.n_tok_recv = keep.n_tok_recv;
+    v.ntok = keep.ntok;
+    for (int i = 0; i < kEpBufs; ++i)
+      for (int r = 0; r < e->x.G; ++r)
+        v.peer[i][r] = e->peer_base[i][r] ? static_cast<unsigned char*>(e->peer_base[i][r]) + (size_t)ch * e->part_bytes[i] : nullptr;
+  }
+}
 
 int b200_ep_comm_create(b200_ctx* c, int n_ranks, int rank, int n_experts, int top_k, int64_t hidden,
                         uint32_t capacity_rows, uint32_t capacity_tokens, b200_ep_comm** out, unsigned char* handles) {
@@ -1193,16 +1216,24 @@ int b200_ep_comm_create(b200_ctx* c, int n_ranks, int rank, int n_experts, int t
   const int Eg = n_experts / n_ranks;
   bool ok = true;
   for (int i = 0; i < kEpBufs && ok; ++i) {
-    ok = cudaMalloc(&e->own[i], bytes[i]) == cudaSuccess;
-    if (ok && i == kEpCtl) ok = cudaMemset(e->own[i], 0, bytes[i]) == cudaSuccess;
+    bytes[i] = al(bytes[i]);
+    e->part_bytes[i] = bytes[i];
+    ok = cudaMalloc(&e->own[i], kEpChunks * bytes[i]) == cudaSuccess;
+    if (ok && i == kEpCtl) ok = cudaMemset(e->own[i], 0, kEpChunks * bytes[i]) == cudaSuccess;
     cudaIpcMemHandle_t h;
     if (ok) ok = cudaIpcGetMemHandle(&h, e->own[i]) == cudaSuccess;
     if (ok) memcpy(handles + (size_t)i * B200_EP_HANDLE_BYTES, &h, sizeof(h));
   }
   if (ok) ok = cudaMalloc(&e->y, (size_t)capacity_rows * hidden * 2) == cudaSuccess;
   const size_t words = (size_t)n_experts + Eg + 1 + n_ranks + 1 + n_ranks + 8;
-  if (ok) ok = cudaMalloc(reinterpret_cast<void**>(&e->dev), sizeof(uint32_t) * words) == cudaSuccess;
-  if (ok) ok = cudaMemset(e->dev, 0, sizeof(uint32_t) * words) == cudaSuccess;
+  if (ok) ok = cudaMalloc(reinterpret_cast<void**>(&e->dev), sizeof(uint32_t) * words * kEpChunks) == cudaSuccess;
+  if (ok) ok = cudaMemset(e->dev, 0, sizeof(uint32_t) * words * kEpChunks) == cudaSuccess;
+  int prio_lo = 0, prio_hi = 0;
+  if (ok) ok = cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi) == cudaSuccess;
+  if (ok) ok = cudaStreamCreateWithPriority(&e->side, cudaStreamNonBlocking, prio_hi) == cudaSuccess;
+  cudaEvent_t* evs[] = {&e->ev_fork, &e->ev_a[0], &e->ev_a[1], &e->ev_b[0], &e->ev_b[1], &e->ev_join};
+  for (cudaEvent_t* ev : evs)
+    if (ok) ok = cudaEventCreateWithFlags(ev, cudaEventDisableTiming) == cudaSuccess;
   if (ok) ok = cudaDeviceSynchronize() == cudaSuccess;
   if (!ok) {
     const std::string why = cudaGetErrorString(cudaGetLastError());
@@ -1210,17 +1241,32 @@ int b200_ep_comm_create(b200_ctx* c, int n_ranks, int rank, int n_experts, int t
       if (p) cudaFree(p);
     if (e->y) cudaFree(e->y);
     if (e->dev) cudaFree(e->dev);
+    if (e->side) cudaStreamDestroy(e->side);
+    for (cudaEvent_t* ev : evs)
+      if (*ev) cudaEventDestroy(*ev);
     delete e;
     B200_FAIL("cannot allocate the exchange buffers: " + why);
   }
-  x.dst_row0 = e->dev;
-  x.local_counts = x.dst_row0 + n_experts;
-  x.n_recv = x.local_counts + Eg;
-  x.tokbase = x.n_recv + 1;
-  x.n_tok_recv = x.tokbase + n_ranks;
-  x.ntok = x.n_tok_recv + 1;
-  for (int i = 0; i < kEpBufs; ++i) x.peer[i][rank] = e->own[i];
+  for (int ch = 0; ch < kEpChunks; ++ch) {
+    EpExchange& v = e->xc[ch];
+    v.dst_row0 = e->dev + (size_t)ch * words;
+    v.local_counts = v.dst_row0 + n_experts;
+    v.n_recv = v.local_counts + Eg;
+    v.tokbase = v.n_recv + 1;
+    v.n_tok_recv = v.tokbase + n_ranks;
+    v.ntok = v.n_tok_recv + 1;
+  }
+  for (int i = 0; i < kEpBufs; ++i) e->peer_base[i][rank] = e->own[i];
+  ep_comm_views(e);
   *out = e;
+  return 0;
+}
+
+int b200_ep_comm_set_chunks(b200_ctx* c, b200_ep_comm* e, int chunks) {
+  CTX_ENTER(c);
+  B200_REQUIRE(e != nullptr, "null communicator");
+  B200_REQUIRE(chunks >= 1 && chunks <= kEpChunks, "chunks must be 1 or 2");
+  e->chunks = chunks;
   return 0;
 }
 
@@ -1233,10 +1279,11 @@ int b200_ep_comm_connect(b200_ctx* c, b200_ep_comm* e, const unsigned char* all_
     for (int i = 0; i < kEpBufs; ++i) {
       cudaIpcMemHandle_t h;
       memcpy(&h, all_handles + ((size_t)r * kEpBufs + i) * B200_EP_HANDLE_BYTES, sizeof(h));
-      B200_CUDA(cudaIpcOpenMemHandle(&e->x.peer[i][r], h, cudaIpcMemLazyEnablePeerAccess));
+      B200_CUDA(cudaIpcOpenMemHandle(&e->peer_base[i][r], h, cudaIpcMemLazyEnablePeerAccess));
       e->opened[i][r] = true;
     }
   }
+  ep_comm_views(e);
   e->connected = true;
   return 0;
 }
@@ -1247,11 +1294,14 @@ int b200_ep_comm_destroy(b200_ctx* c, b200_ep_comm* e) {
   cudaDeviceSynchronize();
   for (int i = 0; i < kEpBufs; ++i)
     for (int r = 0; r < e->x.G; ++r)
-      if (e->opened[i][r]) cudaIpcCloseMemHandle(e->x.peer[i][r]);
+      if (e->opened[i][r]) cudaIpcCloseMemHandle(e->peer_base[i][r]);
   for (void* p : e->own)
     if (p) cudaFree(p);
   if (e->y) cudaFree(e->y);
   if (e->dev) cudaFree(e->dev);
+  if (e->side) cudaStreamDestroy(e->side);
+  for (cudaEvent_t ev : {e->ev_fork, e->ev_a[0], e->ev_a[1], e->ev_b[0], e->ev_b[1], e->ev_join})
+    if (ev) cudaEventDestroy(ev);
   delete e;
   return 0;
 }
@@ -1261,71 +1311,136 @@ int b200_moe_block_forward_ep(b200_ctx* c, b200_ep_comm* e, const b200_moe_confi
   CTX_ENTER(c);
   B200_REQUIRE(e != nullptr && (e->connected || e->x.G == 1), "the communicator is not connected");
   if (check_cfg(cfg) || check_params(params, true)) return 1;
-  const EpExchange& ex = e->x;
-  const int G = ex.G, E = cfg->n_experts, Eg = E / G, k = cfg->top_k;
-  B200_REQUIRE(E == ex.E && cfg->hidden == ex.H && k == ex.k, "the communicator was created for another layer shape");
+  const int G = e->x.G, E = cfg->n_experts, Eg = E / G, k = cfg->top_k;
+  B200_REQUIRE(E == e->x.E && cfg->hidden == e->x.H && k == e->x.k, "the communicator was created for another layer shape");
   B200_REQUIRE(T >= 0 && T < (1 << 24) && T * k < (int64_t(1) << 31), "bad token count");
   B200_REQUIRE(T == 0 || (x && out), "null tensor");
+  const int nch = e->chunks;
+  B200_REQUIRE(nch == 1 || !aux || (!aux->perm && !aux->inv_perm && !aux->offsets),
+               "perm, inv_perm and offsets of the whole step do not exist when the step runs as two half-steps");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // every rank takes part in every step, also with no tokens of its own (its experts may still receive rows)
-  const int64_t n = T * k, cap = ex.cap_rows;
+  const int64_t n = T * k, cap = e->x.cap_rows;
   b200_moe_config local = *cfg;  // the experts this rank owns, one assignment per arriving row
   local.n_experts = Eg;
   local.top_k = 1;
   const size_t route_bytes = al(sizeof(uint16_t) * T * E) + al(sizeof(double) * (size_t)E * cfg->hidden) +
-                             al(sizeof(uint32_t) * n) * 3 + al(sizeof(uint16_t) * n) + al(sizeof(uint32_t) * (E + 1)) * 3 + al(16) +
-                             al(sizeof(uint32_t) * permute_scratch_words(n, E)) + al(sizeof(uint32_t) * (size_t)G * T) +
-                             al(sizeof(uint16_t) * (size_t)ex.cap_tok * cfg->hidden) + al(sizeof(float) * ex.cap_tok) + 4096;
+                             al(sizeof(uint32_t) * n) * 3 + al(sizeof(uint16_t) * n) +
+                             (al(sizeof(uint32_t) * (E + 1)) * 4 + al(16)) * (kEpChunks + 1) +
+                             al(sizeof(uint32_t) * permute_scratch_words(n, E)) * kEpChunks + al(sizeof(uint32_t) * (size_t)G * T) * 2 +
+                             al(sizeof(uint16_t) * (size_t)e->x.cap_tok * cfg->hidden) + al(sizeof(float) * e->x.cap_tok) + 8192;
   if (ctx_grow(c, route_bytes + block_scratch_bytes(local, cap), stream)) return 1;
   void* logits = c->take(sizeof(uint16_t) * T * E);
   uint32_t* idx = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * n));
   void* scores = c->take(sizeof(uint16_t) * n);
   double* w64 = static_cast<double*>(c->take(sizeof(double) * (size_t)E * cfg->hidden));
-  uint32_t* slot = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (size_t)G * T));
-  B200_REQUIRE(logits && idx && scores && w64 && slot, "scratch arena too small");
+  B200_REQUIRE(logits && idx && scores && w64, "scratch arena too small");
   if (aux) {
     if (aux->logits) logits = aux->logits;
     if (aux->indices) idx = aux->indices;
     if (aux->scores) scores = aux->scores;
   }
-  SortBufs sb;
-  if (take_sort_bufs(c, n, E, aux, sb)) return 1;
-  // 1. route and sort this rank's tokens; which token goes to which rank
+  // 1. route this rank's tokens
   if (T > 0) {
     launch_router_logits(x, params->router_weight, params->router_logit_bias, logits, (int)T, cfg->hidden, E, w64, st);
     launch_route_topk(logits, (int)T, E, k, cfg->router_mode, cfg->norm_topk_prob, idx, scores, nullptr, st);
     LAUNCHED(c, 2);
   }
-  launch_permute(idx, n, E, sb.perm, sb.inv, sb.counts, sb.offsets, sb.active, sb.n_active, sb.chunk, c->err, st);
-  launch_ep_token_slots(idx, T, ex, slot, st);
-  LAUNCHED(c, permute_launches(n) + 1);
-  // 2. all-gather of the counts through the control blocks, layout of the exchange
-  launch_ep_counts_exchange(ex, sb.counts, c->err, st);
-  // 3. dispatch: every token once per destination rank, plus the owners' bookkeeping
-  launch_ep_dispatch_dedup(x, idx, sb.inv, sb.offsets, scores, slot, T, ex, c->err, st);
-  launch_ep_signal_wait(ex, 1, c->err, st);   // every rank's rows have landed
-  LAUNCHED(c, 2 + (T ? 1 : 0));
-  // 4. this rank's experts on the assignments that arrived (their number lives on the device: the launches are
-  //    sized for the buffers' capacity and follow the device-side segment tables), then the partial weighted sums
-  {
+  // The step runs as nch half-steps over consecutive halves of the tokens, each a complete exchange on its own set of
+  // buffers and control words.  With two, the exchange kernels (small enough to share an SM with the persistent
+  // tensor-core CTAs) go to the communicator's side stream: the dispatch of the second half and the return of the
+  // first run under the other half's expert products.
+  struct Half {
+    int64_t t0, Tc;
+    SortBufs sb;
+    uint32_t* slot;
+  } half[kEpChunks];
+  for (int ch = 0; ch < nch; ++ch) {
+    Half& h = half[ch];
+    h.t0 = ch == 0 ? 0 : half[0].Tc;
+    h.Tc = nch == 1 ? T : (ch == 0 ? (T + 1) / 2 : T - (T + 1) / 2);
+    const int64_t nc = h.Tc * k;
+    if (take_sort_bufs(c, nc, E, nch == 1 ? aux : nullptr, h.sb)) return 1;
+    h.slot = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (size_t)G * (h.Tc > 0 ? h.Tc : 1)));
+    B200_REQUIRE(h.slot, "scratch arena too small");
+    // sort of the half's assignments; which of its tokens goes to which rank
+    launch_permute(idx + h.t0 * k, nc, E, h.sb.perm, h.sb.inv, h.sb.counts, h.sb.offsets, h.sb.active, h.sb.n_active, h.sb.chunk,
+                   c->err, st);
+    launch_ep_token_slots(idx + h.t0 * k, h.Tc, e->xc[ch], h.slot, st);
+    LAUNCHED(c, permute_launches(nc) + 1);
+  }
+  if (nch == 2 && aux && aux->counts) {
+    launch_add_u32(half[0].sb.counts, half[1].sb.counts, E, aux->counts, st);
+    LAUNCHED(c, 1);
+  }
+  const unsigned char* xb = static_cast<const unsigned char*>(x);
+  unsigned char* ob = static_cast<unsigned char*>(out);
+  const size_t row_bytes = (size_t)cfg->hidden * 2;
+  // 2.-3. all-gather of the counts through the control blocks, layout of the exchange; dispatch: every token once per
+  //       destination rank, plus the owners' bookkeeping; "my rows have landed" to every peer, wait for all peers
+  auto exchange_out = [&](int ch, cudaStream_t s_) {
+    const Half& h = half[ch];
+    launch_ep_counts_exchange(e->xc[ch], h.sb.counts, c->err, s_);
+    launch_ep_dispatch_dedup(xb + h.t0 * row_bytes, idx + h.t0 * k, h.sb.inv, h.sb.offsets,
+                             static_cast<const unsigned char*>(scores) + h.t0 * k * 2, h.slot, h.Tc, e->xc[ch], c->err, s_);
+    launch_ep_signal_wait(e->xc[ch], 1, c->err, s_);
+    LAUNCHED(c, 2 + (h.Tc ? 1 : 0));
+  };
+  // 4. this rank's experts on the assignments that arrived (their number lives on the device: the launches are sized
+  //    for the buffers' capacity and follow the device-side segment tables), then the partial weighted sums
+  const size_t scratch_mark = c->ws_used;
+  auto experts = [&](int ch, cudaStream_t s_) -> int {
+    c->ws_used = scratch_mark;  // the half-steps' products run one after the other on the same stream: same scratch
+    const EpExchange& ex = e->xc[ch];
     uint32_t* offsets = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (Eg + 1)));
     uint32_t* active = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (Eg + 1)));
     uint32_t* n_active = static_cast<uint32_t*>(c->take(16));
     uint32_t* cnt = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * (Eg + 1)));
     B200_REQUIRE(offsets && active && n_active && cnt, "scratch arena too small");
-    launch_segments_from_counts(ex.local_counts, Eg, cap, cnt, offsets, active, n_active, c->err, st);
+    launch_segments_from_counts(ex.local_counts, Eg, cap, cnt, offsets, active, n_active, c->err, s_);
     LAUNCHED(c, 1);
-    ExchangeRows xr{static_cast<const uint32_t*>(e->own[kEpRowMap]), (int64_t)ex.cap_tok, ex.n_tok_recv, ex.n_recv};
+    ExchangeRows xr{static_cast<const uint32_t*>(ex.peer[kEpRowMap][ex.rank]), (int64_t)ex.cap_tok, ex.n_tok_recv, ex.n_recv};
     int y_fmt = kOutBf16;
-    if (experts_sorted(c, local, *params, e->own[kEpTok], nullptr, 1, cnt, offsets, active, n_active, cap, nullptr,
-                       e->y, st, &y_fmt, nullptr, &xr))
+    if (experts_sorted(c, local, *params, ex.peer[kEpTok][ex.rank], nullptr, 1, cnt, offsets, active, n_active, cap, nullptr, e->y,
+                       s_, &y_fmt, nullptr, &xr))
       return 1;
-    if (launch_ep_partial_combine(e->y, y_fmt == kOutF16, ex, c->err, st)) return 1;
+    if (launch_ep_partial_combine(e->y, y_fmt == kOutF16, ex, c->err, s_)) return 1;
+    LAUNCHED(c, 1);
+    return 0;
+  };
+  // 5. "my partial sums are complete" to every peer, wait for all peers; combine: each token sums the partial sums of
+  //    the ranks that own its experts
+  auto exchange_back = [&](int ch, cudaStream_t s_) {
+    const Half& h = half[ch];
+    launch_ep_signal_wait(e->xc[ch], 2, c->err, s_);
+    launch_ep_final_combine(h.slot, h.Tc, e->xc[ch], ob + h.t0 * row_bytes, s_);
+    LAUNCHED(c, 1 + (h.Tc ? 1 : 0));
+  };
+  if (nch == 1) {
+    exchange_out(0, st);
+    if (experts(0, st)) return 1;
+    exchange_back(0, st);
+    return 0;
   }
-  launch_ep_signal_wait(ex, 2, c->err, st);   // every rank's partial sums are complete
-  // 5. combine: each token sums the partial sums of the ranks that own its experts
-  launch_ep_final_combine(slot, T, ex, out, st);
-  LAUNCHED(c, 2 + (T ? 1 : 0));
+  cudaStream_t side = e->side;
+  B200_CUDA(cudaEventRecord(e->ev_fork, st));
+  B200_CUDA(cudaStreamWaitEvent(side, e->ev_fork, 0));
+  exchange_out(0, side);
+  B200_CUDA(cudaEventRecord(e->ev_a[0], side));
+  exchange_out(1, side);  // under the first half's products
+  B200_CUDA(cudaEventRecord(e->ev_a[1], side));
+  B200_CUDA(cudaStreamWaitEvent(st, e->ev_a[0], 0));
+  if (experts(0, st)) return 1;
+  B200_CUDA(cudaEventRecord(e->ev_b[0], st));
+  B200_CUDA(cudaStreamWaitEvent(side, e->ev_b[0], 0));
+  exchange_back(0, side);  // under the second half's products
+  B200_CUDA(cudaStreamWaitEvent(st, e->ev_a[1], 0));
+  if (experts(1, st)) return 1;
+  B200_CUDA(cudaEventRecord(e->ev_b[1], st));
+  B200_CUDA(cudaStreamWaitEvent(side, e->ev_b[1], 0));
+  exchange_back(1, side);
+  B200_CUDA(cudaEventRecord(e->ev_join, side));
+  B200_CUDA(cudaStreamWaitEvent(st, e->ev_join, 0));
   return 0;
 }
 

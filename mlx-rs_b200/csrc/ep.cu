@@ -484,6 +484,15 @@ __global__ void __launch_bounds__(32) ep_signal_wait_kernel(EpExchange x, int wh
   }
 }
 
+__global__ void add_u32_kernel(const uint32_t* __restrict__ a, const uint32_t* __restrict__ b, int n, uint32_t* __restrict__ out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = a[i] + b[i];
+}
+int launch_add_u32(const uint32_t* a, const uint32_t* b, int n, uint32_t* out, cudaStream_t st) {
+  if (n > 0) add_u32_kernel<<<cdiv(n, 256), 256, 0, st>>>(a, b, n, out);
+  return 0;
+}
+
 int launch_ep_counts_exchange(const EpExchange& x, const uint32_t* counts, int* err, cudaStream_t st) {
   ep_counts_exchange_kernel<<<1, 256, 0, st>>>(x, counts, err);
   return 0;

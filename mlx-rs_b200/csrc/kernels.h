@@ -174,5 +174,6 @@ int launch_ep_dispatch_dedup(const void* xrows, const uint32_t* idx, const uint3
                              const void* scores, const uint32_t* slot, int64_t T, const EpExchange& x, int* err, cudaStream_t st);
 int launch_ep_partial_combine(const void* y, bool y_f16, const EpExchange& x, int* err, cudaStream_t st);
 int launch_ep_final_combine(const uint32_t* slot, int64_t T, const EpExchange& x, void* out, cudaStream_t st);
+int launch_add_u32(const uint32_t* a, const uint32_t* b, int n, uint32_t* out, cudaStream_t st);
 
 }  // namespace b200

@@ -339,10 +339,17 @@ class EpComm:
         L.check(L.lib().b200_ep_comm_create(self.ctx.handle, self.G, self.rank, n_experts, top_k, hidden, self.capacity,
                                             self.capacity_tokens, C.byref(h), mine))
         self.handle = h
+        self.chunks = 1
         gathered = [None] * self.G
         dist.all_gather_object(gathered, bytes(mine.raw), group=group)
         L.check(L.lib().b200_ep_comm_connect(self.ctx.handle, self.handle, b"".join(gathered)))
         dist.barrier(group=group)
+
+    def set_chunks(self, chunks):
+        """Half-steps per step (1 or 2); every rank must set the same value.  Two: the exchange of one half of the
+        tokens runs under the expert products of the other half."""
+        self.L.check(self.L.lib().b200_ep_comm_set_chunks(self.ctx.handle, self.handle, int(chunks)))
+        self.chunks = int(chunks)
 
     def close(self):
         """Collective: every rank stops using the buffers before any rank unmaps or frees them."""
@@ -500,6 +507,10 @@ def bench_main(args, pkg, shape, cfg, peaks, metric, unit, workload_name, clock_
         cap = T * k * world if cfg["zipf"] else min(T * k * world, 2 * T * k + 4096)
         ep = DeviceSyncExpertParallelMoe(pkg, wr, mlp, E, k, cap + 64, T * world, norm_topk_prob=cfg["norm_topk_prob"],
                                          router_mode=cfg["router_mode"], router_logit_bias=bias)
+        # two half-steps (the exchange of one half under the products of the other) only on request: measured slower
+        # than one at 2 and 4 GPUs (1.43 against 1.29 ms and 1.53 against 1.46 ms per step at 8192 tokens per GPU) -
+        # the second set of small launches costs more than the overlap returns
+        ep.comm.set_chunks(args.ep_chunks or 1)
     elif args.ep_transport in ("peer", "peer_push"):
         # every rank can at worst receive every assignment of every rank; 2x the balanced load is what uniform
         # random routing needs; skewed routing (one expert per GPU owning 43 % of all rows) needs the worst case
@@ -597,7 +608,7 @@ def bench_main(args, pkg, shape, cfg, peaks, metric, unit, workload_name, clock_
                                     ("dispatch kernel + return fused into the down projection" if args.ep_transport == "peer_push"
                                      else "dispatch/combine kernels") + " over mapped peer memory, NCCL-ordered"
                                     if bufs else "NCCL all-to-all-v dispatch + combine") + ")",
-                                ep_chunks=(len(bufs) if bufs else 1),
+                                ep_chunks=(len(bufs) if bufs else getattr(getattr(ep, "comm", None), "chunks", 1)),
                                 **shape),
                     roofline=dict(bound="tensor", achieved=flops / (ms * 1e-3) / 1e12 / world, peak=peaks["tensor"],
                                   unit="TFLOP/s", frac=flops / (ms * 1e-3) / 1e12 / world / peaks["tensor"],

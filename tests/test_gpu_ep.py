@@ -28,8 +28,10 @@ def _worker(rank, world, port, cfg, transport, ret):
         mlp = ep.shard_switch_mlp(pkg, full.switch_mlp, rank, world)
         T = blk["T"]
         bufs = None
-        if transport == "device":
+        if transport.startswith("device"):
             moe = ep.DeviceSyncExpertParallelMoe(pkg, full.gate_weight, mlp, blk["E"], blk["k"], T * blk["k"])
+            if transport == "device2":          # two half-steps: exchanges on the side stream under the other half's products
+                moe.comm.set_chunks(2)
         elif transport.startswith("peer"):
             bufs = [ep.PeerBuffers(pkg, blk["H"], T * blk["k"]) for _ in range(2 if transport == "peer2" else 1)]
             moe = ep.PeerExpertParallelMoe(pkg, full.gate_weight, mlp, blk["E"], blk["k"], bufs,
@@ -58,8 +60,9 @@ def _free_port():
 
 
 @pytest.mark.parametrize("cfg", [dict(T=96, H=256, E=8, I=128, k=2, seed=3),
-                                 dict(T=700, H=512, E=16, I=256, k=4, seed=5)])
-@pytest.mark.parametrize("transport", ["nccl", "peer", "peer2", "peer_push", "device"])
+                                 dict(T=700, H=512, E=16, I=256, k=4, seed=5),
+                                 dict(T=4801, H=512, E=8, I=256, k=2, seed=9)])     # tensor-core regime, odd halves
+@pytest.mark.parametrize("transport", ["nccl", "peer", "peer2", "peer_push", "device", "device2"])
 def test_expert_parallel_two_gpus(O, cfg, transport):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

@@ -115,9 +115,10 @@ def test_sorted_entry_points_keep_to_their_bounds(pkg):
     assert torch.equal(ret[:32].view(torch.int16), want[:32].view(torch.int16)) and bool((ret[32:] == 7.0).all())
 
 
+@pytest.mark.parametrize("chunks", [1, 2])
 @pytest.mark.parametrize("cfg", [dict(T=96, H=256, E=8, I=128, k=2, seed=3),          # register kernel
-                                 dict(T=2400, H=512, E=8, I=256, k=2, seed=9)])      # tensor-core regime
-def test_one_call_block_single_rank(pkg, O, cfg, tmp_path):
+                                 dict(T=2401, H=512, E=8, I=256, k=2, seed=9)])      # tensor-core regime
+def test_one_call_block_single_rank(pkg, O, cfg, chunks, tmp_path):
     """`b200_moe_block_forward_ep` with a group of ONE rank on one GPU: the device-side phase ordering runs
     against its own flags (a rank is its own peer), twice in a row (step counter, buffer reuse), and a step
     whose arrivals exceed the capacity drops them and reports it.  (Two and more ranks need one GPU each:
@@ -134,6 +135,7 @@ def test_one_call_block_single_rank(pkg, O, cfg, tmp_path):
         ref = O.moe_block(blk["x"], blk["wr"], blk["gate"], blk["up"], blk["down"], k)
         rms = np.sqrt((ref["out_f32"] ** 2).mean())
         moe = ep.DeviceSyncExpertParallelMoe(pkg, full.gate_weight, full.switch_mlp, E, k, T * k)
+        moe.comm.set_chunks(chunks)      # two: the step as two half-steps, exchanges on the communicator's side stream
         for _ in range(2):
             out = moe.forward(x)
         pkg.default_context().check()
