@@ -100,6 +100,7 @@ static size_t block_scratch_bytes(const b200_moe_config& cfg, int64_t T) {
   b += al(sizeof(uint16_t) * n * cfg.hidden);        // rows gathered into expert order, fp16 (tensor-core path)
   b += al(sizeof(float) * n);                        // their row scales
   b += (al(sizeof(uint32_t) * prefill_tile_words(n, (int)E)) * 3 + al(16)) * 2;
+  b += al(sizeof(uint32_t) * kExpertDescWords * (size_t)(E < n ? E : n));  // per-expert records of the register kernels
   return b + 4096;
 }
 
@@ -780,6 +781,7 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
   }
   c->mark(3, st);
 
+  uint32_t* expert_desc = nullptr;
   GroupedArgs gu{};
   gu.x = x;
   gu.w[0] = p.gate_proj.weight;
@@ -831,6 +833,18 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
       gu.src_map = xr->map;
     }
     gu.out_f16 = 1;  // h in the prepared layout, ready for the down projection
+    if (!gu.x_bf16) {
+      // one record per active expert: the products' CTAs then start with one load instead of four dependent ones
+      expert_desc = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * kExpertDescWords * (size_t)max_active));
+      B200_REQUIRE(expert_desc, "scratch arena too small");
+      if (launch_expert_descs(active, n_active, offsets, gu.perm, gu.src_map, gu.src_mode, gu.src_div, max_active, expert_desc, st))
+        return 1;
+      LAUNCHED(c, 1);
+      gu.desc = expert_desc;
+#ifdef B200_DEV
+      if (getenv("B200_SMALL_NO_DESC")) gu.desc = expert_desc = nullptr;
+#endif
+    }
     if (launch_grouped_qmm_small(gu, 2, cfg.bits, max_active, n, st)) return 1;
     LAUNCHED(c, 1);
   }
@@ -894,6 +908,7 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
     LAUNCHED(c, 1);
   } else {
     c->mark(6, st);
+    dn.desc = expert_desc;  // (its source rows are the sorted positions themselves)
     if (launch_grouped_qmm_small(dn, 1, cfg.bits, max_active, n, st)) return 1;
     LAUNCHED(c, 1);
   }

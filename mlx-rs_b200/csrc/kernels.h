@@ -36,6 +36,8 @@ struct GroupedArgs {
                               // in the A-operand layout of the same path's down projection (register kernel: prepared rows)
   int K, N;
   int n_experts;              // number of stacked weight matrices
+  const uint32_t* desc;       // register kernel, optional: per active expert one 64-byte record (launch_expert_descs) that
+                              // replaces the look-ups of n_active, active, offsets and the first eight source rows
   int x_bf16;                 // register kernel: 1 = x holds plain bf16 rows and every CTA prepares the rows it stages
                               // itself (a handful of rows per expert: cheaper than a preparation launch)
 };
@@ -53,6 +55,11 @@ struct DownCombineArgs {
   float* out_f32;             // optional [T, N]: the sum before its rounding
   int T, k, K, N;
 };
+// desc [max_active][16] uint32: {expert, first sorted position, rows, 0, source row of the first eight sorted
+// positions (by the given gather mode), 0...}; entries past the number of active experts have rows = 0.
+constexpr int kExpertDescWords = 16;
+int launch_expert_descs(const uint32_t* active, const uint32_t* n_active, const uint32_t* offsets, const uint32_t* perm,
+                        const uint32_t* src_map, int src_mode, int src_div, int max_active, uint32_t* desc, cudaStream_t st);
 bool down_combine_small_ok(int64_t T, int k, int K);
 int launch_down_combine_small(const DownCombineArgs& a, int bits, cudaStream_t st);
 

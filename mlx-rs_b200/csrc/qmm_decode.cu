@@ -172,6 +172,46 @@ __global__ void __launch_bounds__(256, NT == 1 ? 2 : 1) grouped_qmm_small_kernel
   }
 }
 
+// ---- per-expert records --------------------------------------------------------------------------------------
+// What a CTA of the grouped product needs to know about its expert, gathered into one 64-byte record so that the
+// CTA's prologue is one load instead of a chain of four dependent ones (n_active -> active -> offsets -> perm).
+__global__ void __launch_bounds__(256) expert_desc_kernel(const uint32_t* __restrict__ active, const uint32_t* __restrict__ n_active,
+                                                          const uint32_t* __restrict__ offsets, const uint32_t* __restrict__ perm,
+                                                          const uint32_t* __restrict__ src_map, int src_mode, int src_div,
+                                                          int max_active, uint32_t* __restrict__ desc) {
+  pdl_prologue();
+  const int lane = threadIdx.x & 31;
+  const int ea = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (ea >= max_active) return;
+  uint32_t v = 0;
+  if (ea < (int)*n_active) {
+    const uint32_t e = active[ea], seg0 = offsets[e], m = offsets[e + 1] - seg0;
+    if (lane == 0) v = e;
+    if (lane == 1) v = seg0;
+    if (lane == 2) v = m;
+    if (lane >= 4 && lane < 12 && (uint32_t)(lane - 4) < m) {
+      const uint32_t sp = seg0 + (uint32_t)(lane - 4);
+      if (src_mode == kSrcIdent)
+        v = sp;
+      else if (src_mode == kSrcPermDiv)
+        v = perm[sp] / (uint32_t)src_div;
+      else if (src_mode == kSrcMapDirect)
+        v = src_map[sp];
+      else
+        v = src_map[perm[sp]];
+    }
+  }
+  if (lane < kExpertDescWords) desc[(size_t)ea * kExpertDescWords + lane] = v;
+}
+
+int launch_expert_descs(const uint32_t* active, const uint32_t* n_active, const uint32_t* offsets, const uint32_t* perm,
+                        const uint32_t* src_map, int src_mode, int src_div, int max_active, uint32_t* desc, cudaStream_t st) {
+  if (max_active == 0) return 0;
+  B200_CUDA(launch_pdl(expert_desc_kernel, dim3(cdiv(max_active, 8)), dim3(256), 0, st, active, n_active, offsets, perm, src_map,
+                       src_mode, src_div, max_active, desc));
+  return 0;
+}
+
 // ---- the same product with the CTA's whole weight slice requested up front --------------------------------------
 // The register stream above keeps two blocks per lane in flight, and a CTA's prologue (segment look-up, row
 // staging, sums: 4-5 us measured) runs with only those two on their way, so the memory system idles for a third of
@@ -217,8 +257,20 @@ __global__ void __launch_bounds__(256, 2) grouped_qmm_staged_kernel(GroupedArgs 
 
   pdl_prologue();
   const int ea = blockIdx.y;
-  if (ea >= (int)*p.n_active) return;
-  const int e = p.active[ea];
+  int e, m;
+  uint32_t seg0;
+  if (p.desc) {  // one load instead of the chain n_active -> active -> offsets
+    const uint4 d = __ldg(reinterpret_cast<const uint4*>(p.desc + (size_t)ea * kExpertDescWords));
+    e = (int)d.x;
+    seg0 = d.y;
+    m = (int)d.z;
+    if (m == 0) return;
+  } else {
+    if (ea >= (int)*p.n_active) return;
+    e = p.active[ea];
+    seg0 = 0;
+    m = -1;  // looked up below, after the weight copies are on their way
+  }
   const int K = p.K, N = p.N, G = K / 64;
   const int bpw = (G / GB) / KS;  // blocks per warp (the launcher guarantees the divisions are exact, bpw <= 8)
   extern __shared__ __align__(16) unsigned char smem[];
@@ -256,8 +308,10 @@ __global__ void __launch_bounds__(256, 2) grouped_qmm_staged_kernel(GroupedArgs 
     }
   }
 
-  const uint32_t seg0 = p.offsets[e];
-  const int m = (int)(p.offsets[e + 1] - seg0);
+  if (m < 0) {
+    seg0 = p.offsets[e];
+    m = (int)(p.offsets[e + 1] - seg0);
+  }
   const int swa = (gq * SW) & 7;  // rows gq and gq + 8 share the swizzle
   // passes of eight rows; after the first one the weights are resident in shared memory
   for (int p0 = 0; p0 < m; p0 += ROWS) {
@@ -268,6 +322,8 @@ __global__ void __launch_bounds__(256, 2) grouped_qmm_staged_kernel(GroupedArgs 
     int src;
     if (p.src_mode == kSrcIdent)
       src = (int)sp;
+    else if (p.desc && p0 == 0)
+      src = (int)__ldg(p.desc + (size_t)ea * kExpertDescWords + 4 + tid);
     else if (p.src_mode == kSrcPermDiv)
       src = (int)(p.perm[sp] / (uint32_t)p.src_div);
     else if (p.src_mode == kSrcMapDirect)
