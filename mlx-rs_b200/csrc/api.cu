@@ -837,7 +837,8 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
       // one record per active expert: the products' CTAs then start with one load instead of four dependent ones
       expert_desc = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * kExpertDescWords * (size_t)max_active));
       B200_REQUIRE(expert_desc, "scratch arena too small");
-      if (launch_expert_descs(active, n_active, offsets, gu.perm, gu.src_map, gu.src_mode, gu.src_div, max_active, expert_desc, st))
+      if (launch_expert_descs(active, n_active, offsets, gu.perm, gu.src_map, gu.src_mode, gu.src_div, gu.x_rowscale, max_active,
+                              expert_desc, st))
         return 1;
       LAUNCHED(c, 1);
       gu.desc = expert_desc;

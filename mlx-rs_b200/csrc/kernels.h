@@ -55,11 +55,13 @@ struct DownCombineArgs {
   float* out_f32;             // optional [T, N]: the sum before its rounding
   int T, k, K, N;
 };
-// desc [max_active][16] uint32: {expert, first sorted position, rows, 0, source row of the first eight sorted
-// positions (by the given gather mode), 0...}; entries past the number of active experts have rows = 0.
-constexpr int kExpertDescWords = 16;
+// desc [max_active][32] uint32: {expert, first sorted position, rows, 0, source row of the first eight sorted
+// positions (by the given gather mode), the row scale of those eight source rows (float bits; 1.0 without
+// row_scale), 0...}; entries past the number of active experts have rows = 0.
+constexpr int kExpertDescWords = 32;
 int launch_expert_descs(const uint32_t* active, const uint32_t* n_active, const uint32_t* offsets, const uint32_t* perm,
-                        const uint32_t* src_map, int src_mode, int src_div, int max_active, uint32_t* desc, cudaStream_t st);
+                        const uint32_t* src_map, int src_mode, int src_div, const float* row_scale, int max_active,
+                        uint32_t* desc, cudaStream_t st);
 bool down_combine_small_ok(int64_t T, int k, int K);
 int launch_down_combine_small(const DownCombineArgs& a, int bits, cudaStream_t st);
 

@@ -178,7 +178,8 @@ __global__ void __launch_bounds__(256, NT == 1 ? 2 : 1) grouped_qmm_small_kernel
 __global__ void __launch_bounds__(256) expert_desc_kernel(const uint32_t* __restrict__ active, const uint32_t* __restrict__ n_active,
                                                           const uint32_t* __restrict__ offsets, const uint32_t* __restrict__ perm,
                                                           const uint32_t* __restrict__ src_map, int src_mode, int src_div,
-                                                          int max_active, uint32_t* __restrict__ desc) {
+                                                          const float* __restrict__ row_scale, int max_active,
+                                                          uint32_t* __restrict__ desc) {
   pdl_prologue();
   const int lane = threadIdx.x & 31;
   const int ea = blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -189,8 +190,8 @@ __global__ void __launch_bounds__(256) expert_desc_kernel(const uint32_t* __rest
     if (lane == 0) v = e;
     if (lane == 1) v = seg0;
     if (lane == 2) v = m;
-    if (lane >= 4 && lane < 12 && (uint32_t)(lane - 4) < m) {
-      const uint32_t sp = seg0 + (uint32_t)(lane - 4);
+    if (lane >= 4 && lane < 20 && (uint32_t)((lane - 4) & 7) < m) {
+      const uint32_t sp = seg0 + (uint32_t)((lane - 4) & 7);
       if (src_mode == kSrcIdent)
         v = sp;
       else if (src_mode == kSrcPermDiv)
@@ -199,16 +200,18 @@ __global__ void __launch_bounds__(256) expert_desc_kernel(const uint32_t* __rest
         v = src_map[sp];
       else
         v = src_map[perm[sp]];
+      if (lane >= 12) v = __float_as_uint(row_scale ? row_scale[v] : 1.0f);
     }
   }
-  if (lane < kExpertDescWords) desc[(size_t)ea * kExpertDescWords + lane] = v;
+  desc[(size_t)ea * kExpertDescWords + lane] = v;
 }
 
 int launch_expert_descs(const uint32_t* active, const uint32_t* n_active, const uint32_t* offsets, const uint32_t* perm,
-                        const uint32_t* src_map, int src_mode, int src_div, int max_active, uint32_t* desc, cudaStream_t st) {
+                        const uint32_t* src_map, int src_mode, int src_div, const float* row_scale, int max_active,
+                        uint32_t* desc, cudaStream_t st) {
   if (max_active == 0) return 0;
   B200_CUDA(launch_pdl(expert_desc_kernel, dim3(cdiv(max_active, 8)), dim3(256), 0, st, active, n_active, offsets, perm, src_map,
-                       src_mode, src_div, max_active, desc));
+                       src_mode, src_div, row_scale, max_active, desc));
   return 0;
 }
 
@@ -288,22 +291,25 @@ __global__ void __launch_bounds__(256, 2) grouped_qmm_staged_kernel(GroupedArgs 
   // ---- all weight blocks of this warp, on their way before anything else ------------------------
   {
     const unsigned char* wb = reinterpret_cast<const unsigned char*>(p.w[mt]);
-    const unsigned char* scb = reinterpret_cast<const unsigned char*>(p.scales[mt]);
-    const unsigned char* bib = reinterpret_cast<const unsigned char*>(p.biases[mt]);
     const int c = lane & 7;
+    const unsigned char* rowp[4];  // the four rows this lane copies chunk c of
+    uint32_t dsto[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int r = (lane >> 3) + 4 * q;
+      rowp[q] = wb + ((size_t)e * N + min(n0 + r, N - 1)) * wrow_bytes + c * 16;
+      dsto[q] = (uint32_t)(r * 128 + ((c ^ ((r * SW) & 7)) << 4));
+    }
     const int sb_row = lane & 15;
-    const size_t sb_src_row = ((size_t)e * N + min(n0 + sb_row, N - 1)) * G * 2;
-    const unsigned char* sb_src = ((lane >> 4) ? bib : scb) + sb_src_row;
+    const unsigned char* sb_src = reinterpret_cast<const unsigned char*>((lane >> 4) ? p.biases[mt] : p.scales[mt]) +
+                                  ((size_t)e * N + min(n0 + sb_row, N - 1)) * G * 2;
+    const uint32_t sb_dst = 2048 + (lane >> 4) * 128 + sb_row * 8;
     for (int j = 0; j < bpw; ++j) {
       const int bk = ks + j * KS;
       unsigned char* blk = wsm + (size_t)j * kStagedBlockBytes;
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int r = (lane >> 3) + 4 * q;
-        const size_t row = (size_t)e * N + min(n0 + r, N - 1);
-        cp_async16(blk + r * 128 + ((c ^ ((r * SW) & 7)) << 4), wb + row * wrow_bytes + (size_t)bk * 128 + c * 16);
-      }
-      cp_async_small(blk + 2048 + (lane >> 4) * 128 + sb_row * 8, sb_src + (size_t)bk * GB * 2, GB * 2);
+      for (int q = 0; q < 4; ++q) cp_async16(blk + dsto[q], rowp[q] + (size_t)bk * 128);
+      cp_async_small(blk + sb_dst, sb_src + (size_t)bk * GB * 2, GB * 2);
       cp_async_commit();
     }
   }
@@ -316,22 +322,28 @@ __global__ void __launch_bounds__(256, 2) grouped_qmm_staged_kernel(GroupedArgs 
   // passes of eight rows; after the first one the weights are resident in shared memory
   for (int p0 = 0; p0 < m; p0 += ROWS) {
   const int nrows = min(ROWS, m - p0);
-  // ---- stage the prepared rows: plain loads, so that the weight copies' groups stay the only pending ones ----
+  // ---- stage the prepared rows: asynchronous copies in a group BEHIND the weights' (groups complete in order, so
+  //      the wait below also covers the weights - which have had the whole prologue to arrive) ----
   if (tid < nrows) {
     const uint32_t sp = seg0 + p0 + tid;
     int src;
-    if (p.src_mode == kSrcIdent)
-      src = (int)sp;
-    else if (p.desc && p0 == 0)
+    float rsv = 1.0f;
+    if (p.src_mode != kSrcIdent && p.desc && p0 == 0) {  // (a record's source rows are those of the gathering product)
       src = (int)__ldg(p.desc + (size_t)ea * kExpertDescWords + 4 + tid);
-    else if (p.src_mode == kSrcPermDiv)
-      src = (int)(p.perm[sp] / (uint32_t)p.src_div);
-    else if (p.src_mode == kSrcMapDirect)
-      src = (int)p.src_map[sp];
-    else
-      src = (int)p.src_map[p.perm[sp]];
+      rsv = __uint_as_float(__ldg(p.desc + (size_t)ea * kExpertDescWords + 12 + tid));
+    } else {
+      if (p.src_mode == kSrcIdent)
+        src = (int)sp;
+      else if (p.src_mode == kSrcPermDiv)
+        src = (int)(p.perm[sp] / (uint32_t)p.src_div);
+      else if (p.src_mode == kSrcMapDirect)
+        src = (int)p.src_map[sp];
+      else
+        src = (int)p.src_map[p.perm[sp]];
+      if (!p.x_bf16 && p.x_rowscale) rsv = p.x_rowscale[src];
+    }
     s_src[tid] = src;
-    if (!p.x_bf16) s.rs[tid] = p.x_rowscale ? p.x_rowscale[src] : 1.0f;
+    if (!p.x_bf16) s.rs[tid] = rsv;
   }
   __syncthreads();
   if (p.x_bf16) {
@@ -340,20 +352,14 @@ __global__ void __launch_bounds__(256, 2) grouped_qmm_staged_kernel(GroupedArgs 
                                     K / 8, reinterpret_cast<uint4*>(s.xs + (size_t)r * s.XS), s.rs + r, lane);
   } else {
     const int nvec = K / 8;
-    const uint4* x16 = static_cast<const uint4*>(p.x);
-    for (int i0 = tid; i0 < nrows * nvec; i0 += 256 * 4) {
-      uint4 v[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i = i0 + u * 256;
-        if (i < nrows * nvec) v[u] = __ldg(x16 + (size_t)s_src[i / nvec] * nvec + i % nvec);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i = i0 + u * 256;
-        if (i < nrows * nvec) *reinterpret_cast<uint4*>(s.xs + (size_t)(i / nvec) * s.XS + (i % nvec) * 16) = v[u];
-      }
+    const unsigned char* x16 = static_cast<const unsigned char*>(p.x);
+    for (int r = warp; r < nrows; r += 8) {  // warp r copies row r
+      const unsigned char* srow = x16 + (size_t)s_src[r] * K * 2;
+      unsigned char* drow = s.xs + (size_t)r * s.XS;
+      for (int cc = lane; cc < nvec; cc += 32) cp_async16(drow + cc * 16, srow + cc * 16);
     }
+    cp_async_commit();
+    cp_async_wait_pending(0);
   }
   __syncthreads();
   stage_sums<BITS>(s, ROWS, nrows, K, tid, 256);
@@ -363,8 +369,10 @@ __global__ void __launch_bounds__(256, 2) grouped_qmm_staged_kernel(GroupedArgs 
   float tot[1][4] = {{0.f, 0.f, 0.f, 0.f}};
   StagedFetch<ROWS> fetch(s, gq, t);
   for (int j = 0; j < bpw; ++j) {
-    cp_async_wait_pending(bpw - 1 - j);  // (nothing is pending any more in a second pass)
-    __syncwarp();  // every lane's copies of block j have landed
+    if (p.x_bf16) {  // (otherwise the wait for the rows has covered the weights)
+      cp_async_wait_pending(bpw - 1 - j);
+      __syncwarp();  // every lane's copies of block j have landed
+    }
     const int bk = ks + j * KS;
     const unsigned char* blk = wsm + (size_t)j * kStagedBlockBytes;
     fetch.block(bk * GB);
