@@ -191,26 +191,69 @@ __device__ __forceinline__ void warp_expert_logits(const uint4* xs4, const uint4
   }
 }
 
+// The stand-alone kernel (9 to 255 tokens) converts its TPC token rows to float64 ONCE per CTA, into shared memory
+// (chunk q of the 8-element vector c of token j at ((j * 4 + q) * nvec + c) * 16 bytes, so that the lanes of a warp
+// read consecutive 16-byte chunks), instead of once per expert warp: with the conversions of the token side gone
+// from the inner loop, an iteration is 8 weight conversions, 4 * TPC shared loads and 8 * TPC float64 FMAs.
+template <int TPC>
 __global__ void __launch_bounds__(256) router_logits_warp_kernel(const __nv_bfloat16* __restrict__ x,
                                                                  const __nv_bfloat16* __restrict__ w,
                                                                  const float* __restrict__ logit_bias,
-                                                                 __nv_bfloat16* __restrict__ logits, int T, int H, int E,
-                                                                 int tpc) {
-  extern __shared__ __align__(16) unsigned char rsm[];  // [tpc token rows][8 weight rows]
+                                                                 __nv_bfloat16* __restrict__ logits, int T, int H, int E) {
+  extern __shared__ __align__(16) unsigned char rsm[];  // [8 weight rows, raw bf16][TPC token rows, float64]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int t0 = blockIdx.y * tpc, nvec = H / 8;
-  uint4* xs4 = reinterpret_cast<uint4*>(rsm);
-  uint4* ws4 = xs4 + (size_t)tpc * nvec;
+  const int t0 = blockIdx.y * TPC, nvec = H / 8;
+  uint4* ws4 = reinterpret_cast<uint4*>(rsm);
+  double2* xd = reinterpret_cast<double2*>(ws4 + (size_t)8 * nvec);
   pdl_trigger();
-  stage_router_weights(ws4, w, blockIdx.x * 8, E, H, tid);
+  stage_router_weights(ws4, w, blockIdx.x * 8, E, H, tid);  // constants: on their way before the wait
   pdl_wait();
-  stage_router_tokens(xs4, x, t0, tpc, T, H, tid);
+  for (int i = tid; i < TPC * nvec; i += 256) {
+    const int j = i / nvec, c = i % nvec;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t0 + j < T) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + j) * H) + c);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      xd[(size_t)(j * 4 + q) * nvec + c] = make_double2(bf16_bits_to_f64(u[q] & 0xffffu), bf16_bits_to_f64(u[q] >> 16));
+  }
   cp_async_wait_all();
   __syncthreads();
+  const int e = blockIdx.x * 8 + warp;
+  const uint4* wrow = ws4 + (size_t)warp * nvec;
+  double acc[TPC][2];
+#pragma unroll
+  for (int j = 0; j < TPC; ++j) acc[j][0] = acc[j][1] = 0.0;
 #pragma unroll 1
-  for (int j = 0; j < tpc && t0 + j < T; j += kWarpTokens)
-    warp_expert_logits(xs4 + (size_t)j * nvec, ws4 + (size_t)warp * nvec, nvec, lane, t0 + j, T, blockIdx.x * 8 + warp, E,
-                       logit_bias, logits);
+  for (int c = lane; c < nvec; c += 32) {
+    const uint4 wv = wrow[c];
+    const uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
+    double wl[4], wh[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      wl[q] = bf16_bits_to_f64(wu[q] & 0xffffu);
+      wh[q] = bf16_bits_to_f64(wu[q] >> 16);
+    }
+#pragma unroll
+    for (int j = 0; j < TPC; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const double2 xv = xd[(size_t)(j * 4 + q) * nvec + c];
+        acc[j][0] = fma(xv.x, wl[q], acc[j][0]);
+        acc[j][1] = fma(xv.y, wh[q], acc[j][1]);
+      }
+  }
+#pragma unroll
+  for (int j = 0; j < TPC; ++j) {
+    double sum = acc[j][0] + acc[j][1];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0 && e < E && t0 + j < T) {
+      uint32_t bits = f64_to_bf16_bits(sum);
+      if (logit_bias) bits = f32_to_bf16_bits(bf16_bits_to_f32(bits) + logit_bias[e]);
+      logits[(size_t)(t0 + j) * E + e] = __ushort_as_bfloat16((unsigned short)bits);
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -400,16 +443,30 @@ static void dmma_tile_shape(int T, int E, int& mt_best, int& ne_best) {
     }
 }
 
+template <int TPC>
+static int launch_router_warp_tpc(const __nv_bfloat16* xp, const __nv_bfloat16* wp, const float* logit_bias,
+                                  __nv_bfloat16* lp, int T, int H, int E, cudaStream_t st) {
+  const size_t smem = (size_t)8 * H * 2 + (size_t)TPC * H * 8;
+  static DynSmemCache attr;
+  B200_CUDA(ensure_dyn_smem(router_logits_warp_kernel<TPC>, smem, attr));
+  dim3 grid(cdiv(E, 8), cdiv(T, TPC));
+  B200_CUDA(launch_pdl(router_logits_warp_kernel<TPC>, grid, dim3(256), smem, st, xp, wp, logit_bias, lp, T, H, E));
+  return 0;
+}
+// tokens per CTA: two while that keeps the re-staging of the weight rows small, more beyond (as far as the float64
+// rows fit in shared memory)
+static int router_warp_tpc(int T, int H) {
+  int tpc = T <= 32 ? 2 : (T <= 128 ? 4 : kWarpTokensMax);
+  while (tpc > 2 && (size_t)8 * H * 2 + (size_t)tpc * H * 8 > 200 * 1024) tpc >>= 1;
+  return tpc;
+}
 static int launch_router_warp(const __nv_bfloat16* xp, const __nv_bfloat16* wp, const float* logit_bias,
                               __nv_bfloat16* lp, int T, int H, int E, cudaStream_t st) {
-  // tokens per CTA: two (one pass) while that keeps the re-staging of the weight rows small, more beyond
-  const int tpc = T <= 32 ? 2 : (T <= 128 ? 4 : kWarpTokensMax);
-  const size_t smem = (size_t)(tpc + 8) * H * 2;
-  static DynSmemCache attr;
-  B200_CUDA(ensure_dyn_smem(router_logits_warp_kernel, smem, attr));
-  dim3 grid(cdiv(E, 8), cdiv(T, tpc));
-  B200_CUDA(launch_pdl(router_logits_warp_kernel, grid, dim3(256), smem, st, xp, wp, logit_bias, lp, T, H, E, tpc));
-  return 0;
+  switch (router_warp_tpc(T, H)) {
+    case 2: return launch_router_warp_tpc<2>(xp, wp, logit_bias, lp, T, H, E, st);
+    case 4: return launch_router_warp_tpc<4>(xp, wp, logit_bias, lp, T, H, E, st);
+    default: return launch_router_warp_tpc<8>(xp, wp, logit_bias, lp, T, H, E, st);
+  }
 }
 
 int launch_router_logits(const void* x, const void* w, const float* logit_bias, void* logits, int T, int H, int E,
@@ -425,7 +482,7 @@ int launch_router_logits(const void* x, const void* w, const float* logit_bias, 
 #else
   constexpr int force = 0;
 #endif
-  const bool warp_ok = (H % 8 == 0) && ((size_t)(kWarpTokensMax + 8) * H * 2 <= 200 * 1024);
+  const bool warp_ok = (H % 8 == 0) && ((size_t)8 * H * 2 + (size_t)2 * H * 8 <= 200 * 1024);
   const bool dmma_ok = (H % 8 == 0);
   if (dmma_ok && (force == 3 || (!force && T >= 256))) {
     int mt, ne;

@@ -44,20 +44,26 @@ __device__ __forceinline__ void route_topk_token(const __nv_bfloat16* logits, in
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     double ex[kMaxPerLane];
     double s = 0.0;
+    const int nper = (E + 31) >> 5;  // experts per lane that exist (warp-uniform bound of the loops below)
 #pragma unroll
     for (int i = 0; i < kMaxPerLane; ++i) {
-      int e = lane + 32 * i;
-      ex[i] = (e < E) ? exp((double)lf[i] - (double)m) : 0.0;
-      s += ex[i];
+      ex[i] = 0.0;
+      if (i < nper) {
+        const int e = lane + 32 * i;
+        if (e < E) ex[i] = exp((double)lf[i] - (double)m);
+        s += ex[i];
+      }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
 #pragma unroll
     for (int i = 0; i < kMaxPerLane; ++i) {
-      int e = lane + 32 * i;
-      bits[i] = f64_to_bf16_bits(ex[i] / s);
-      if (probs && e < E) probs[(size_t)t * E + e] = __ushort_as_bfloat16((unsigned short)bits[i]);
-      if (e >= E) bits[i] = 0xff80u;
+      const int e = lane + 32 * i;
+      bits[i] = 0xff80u;
+      if (i < nper && e < E) {
+        bits[i] = f64_to_bf16_bits(ex[i] / s);
+        if (probs) probs[(size_t)t * E + e] = __ushort_as_bfloat16((unsigned short)bits[i]);
+      }
     }
   }
 
