@@ -672,6 +672,7 @@ struct SmallTail {
   void* out;            // bf16 [T, H]
   float* out_f32;       // optional
   int64_t T;
+  const uint32_t* desc; // per-expert records written by the routing kernel (tokens as source rows, no row scales)
 };
 
 struct ExchangeRows {
@@ -817,6 +818,7 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
     if (!xr && src_rows <= 8) {
       // a handful of rows: every CTA prepares the rows it stages itself, which costs less than a launch
       gu.x_bf16 = 1;
+      if (tail && tail->desc && perm && src_div == cfg.top_k) gu.desc = tail->desc;
       c->mark(4, st);
     } else {
       void* xp = c->take(sizeof(uint16_t) * src_rows * cfg.hidden);
@@ -963,15 +965,18 @@ int b200_moe_block_forward(b200_ctx* c, const b200_moe_config* cfg, const b200_m
     // small batch: logits, routing and the sort in one launch (stages 1 and 2 read as zero)
     SortBufs sb;
     if (take_sort_bufs(c, n, cfg->n_experts, aux, sb)) return 1;
+    const int desc_entries = (int)(cfg->n_experts < n ? cfg->n_experts : n);
+    uint32_t* desc = static_cast<uint32_t*>(c->take(sizeof(uint32_t) * kExpertDescWords * (size_t)desc_entries));
+    B200_REQUIRE(desc, "scratch arena too small");
     if (launch_router_fused_small(x, params->router_weight, params->router_logit_bias, logits, (int)T, cfg->hidden,
                                   cfg->n_experts, cfg->top_k, cfg->router_mode, cfg->norm_topk_prob, idx, scores, sb.perm,
                                   sb.inv, sb.counts, sb.offsets, sb.active, sb.n_active,
-                                  reinterpret_cast<unsigned int*>(c->err + kTicketWord), c->err, st))
+                                  reinterpret_cast<unsigned int*>(c->err + kTicketWord), c->err, desc, desc_entries, st))
       return 1;
     LAUNCHED(c, 1);
     c->mark(1, st);
     c->mark(2, st);
-    const SmallTail tail{idx, sb.inv, out, aux ? aux->out_f32 : nullptr, T};
+    const SmallTail tail{idx, sb.inv, out, aux ? aux->out_f32 : nullptr, T, desc};
     if (experts_sorted(c, *cfg, *params, x, sb.perm, cfg->top_k, sb.counts, sb.offsets, sb.active, sb.n_active, n, scores,
                        yk, st, &yk_fmt, nullptr, nullptr, &tail))
       return 1;

@@ -11,6 +11,8 @@ enum { kSrcIdent = 0, kSrcPermDiv = 1, kSrcMap = 2, kSrcMapDirect = 3 };
 enum { kOutBf16 = 0, kOutF32 = 1, kOutF16 = 2, kOutNone = 3 };  // element format of a grouped product's output / of the combine's input (none: the product finished the block)
 
 // One grouped product over rows that are sorted by expert.
+constexpr int kExpertDescWords = 32;  // uint32 words of a per-expert record (launch_expert_descs)
+
 struct GroupedArgs {
   const void* x;              // source rows [*, K]: bf16 for the tensor-core path's own preparation; PREPARED fp16 rows
                               // (launch_prepare_rows_small, or an out_f16 gate/up epilogue) for the register kernel
@@ -58,7 +60,6 @@ struct DownCombineArgs {
 // desc [max_active][32] uint32: {expert, first sorted position, rows, 0, source row of the first eight sorted
 // positions (by the given gather mode), the row scale of those eight source rows (float bits; 1.0 without
 // row_scale), 0...}; entries past the number of active experts have rows = 0.
-constexpr int kExpertDescWords = 32;
 int launch_expert_descs(const uint32_t* active, const uint32_t* n_active, const uint32_t* offsets, const uint32_t* perm,
                         const uint32_t* src_map, int src_mode, int src_div, const float* row_scale, int max_active,
                         uint32_t* desc, cudaStream_t st);
@@ -76,7 +77,7 @@ bool router_fused_small_ok(int T, int H, int E, int k);
 int launch_router_fused_small(const void* x, const void* w, const float* logit_bias, void* logits, int T, int H, int E,
                               int k, int mode, int renorm, uint32_t* idx, void* scores, uint32_t* perm, uint32_t* inv,
                               uint32_t* counts, uint32_t* offsets, uint32_t* active, uint32_t* n_active,
-                              unsigned int* ticket, int* err, cudaStream_t st);
+                              unsigned int* ticket, int* err, uint32_t* desc, int desc_entries, cudaStream_t st);
 // top-k + token -> expert sort in one launch (T*k <= 1024); `ticket` is a zero-initialised device word
 bool route_topk_sort_ok(int T, int E, int k);
 int launch_route_topk_sort(const void* logits, int T, int E, int k, int mode, int renorm, uint32_t* idx, void* scores,

@@ -38,10 +38,19 @@ __global__ void __launch_bounds__(256, NT == 1 ? 2 : 1) grouped_qmm_small_kernel
 
   pdl_prologue();
   const int ea = blockIdx.y;
-  if (ea >= (int)*p.n_active) return;
-  const int e = p.active[ea];
-  const uint32_t seg0 = p.offsets[e];
-  const int m = (int)(p.offsets[e + 1] - seg0);
+  int e, m;
+  uint32_t seg0;
+  if (p.desc) {  // one load instead of the chain n_active -> active -> offsets
+    const uint4 d = __ldg(reinterpret_cast<const uint4*>(p.desc + (size_t)ea * kExpertDescWords));
+    e = (int)d.x;
+    seg0 = d.y;
+    m = (int)d.z;
+  } else {
+    if (ea >= (int)*p.n_active) return;
+    e = p.active[ea];
+    seg0 = p.offsets[e];
+    m = (int)(p.offsets[e + 1] - seg0);
+  }
   if (m <= 0) return;
 
   const int K = p.K, N = p.N, G = K / 64;
@@ -77,6 +86,8 @@ __global__ void __launch_bounds__(256, NT == 1 ? 2 : 1) grouped_qmm_small_kernel
       int src;
       if (p.src_mode == kSrcIdent)
         src = (int)sp;
+      else if (p.desc && p0 == 0 && tid < 8)  // (a record holds the first eight source rows)
+        src = (int)__ldg(p.desc + (size_t)ea * kExpertDescWords + 4 + tid);
       else if (p.src_mode == kSrcPermDiv)
         src = (int)(p.perm[sp] / (uint32_t)p.src_div);
       else if (p.src_mode == kSrcMapDirect)

@@ -591,7 +591,7 @@ __global__ void __launch_bounds__(256) router_fused_small_kernel(
     __nv_bfloat16* logits, int T, int H, int E, int k, int mode, int renorm, uint32_t* idx, __nv_bfloat16* scores,
     uint32_t* __restrict__ perm, uint32_t* __restrict__ inv, uint32_t* __restrict__ counts,
     uint32_t* __restrict__ offsets, uint32_t* __restrict__ active, uint32_t* __restrict__ n_active,
-    unsigned int* ticket, int* __restrict__ err) {
+    unsigned int* ticket, int* __restrict__ err, uint32_t* __restrict__ desc, int desc_entries) {
   extern __shared__ __align__(16) unsigned char rsm[];  // token and weight rows (bf16), later the permutation's tables
   __shared__ unsigned int s_ticket;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -619,6 +619,25 @@ __global__ void __launch_bounds__(256) router_fused_small_kernel(
   __syncthreads();  // idx written by this block is read back below
   permute_small_block<256>(idx, T * k, E, perm, inv, counts, offsets, active, n_active, err,
                            reinterpret_cast<int*>(rsm));
+  if (desc) {
+    // per active expert one record {expert, first sorted position, rows, 0, token of the first eight rows, ...}: the
+    // grouped products' CTAs then start with one load instead of the chain n_active -> active -> offsets -> perm
+    __syncthreads();  // perm, offsets and active of this block are in memory
+    const int na = (int)*n_active;
+    for (int i = tid; i < desc_entries * kExpertDescWords; i += 256) {
+      const int ea = i / kExpertDescWords, wd = i % kExpertDescWords;
+      uint32_t v = 0;
+      if (ea < na) {
+        const uint32_t e = active[ea], seg0 = offsets[e], m = offsets[e + 1] - seg0;
+        if (wd == 0) v = e;
+        if (wd == 1) v = seg0;
+        if (wd == 2) v = m;
+        if (wd >= 4 && wd < 12 && (uint32_t)(wd - 4) < m) v = perm[seg0 + (uint32_t)(wd - 4)] / (uint32_t)k;
+        if (wd >= 12 && wd < 20) v = 0x3f800000u;  // (row scales are computed by the CTAs that prepare the rows)
+      }
+      desc[i] = v;
+    }
+  }
 }
 
 bool router_fused_small_ok(int T, int H, int E, int k) {
@@ -629,7 +648,7 @@ bool router_fused_small_ok(int T, int H, int E, int k) {
 int launch_router_fused_small(const void* x, const void* w, const float* logit_bias, void* logits, int T, int H, int E,
                               int k, int mode, int renorm, uint32_t* idx, void* scores, uint32_t* perm, uint32_t* inv,
                               uint32_t* counts, uint32_t* offsets, uint32_t* active, uint32_t* n_active,
-                              unsigned int* ticket, int* err, cudaStream_t st) {
+                              unsigned int* ticket, int* err, uint32_t* desc, int desc_entries, cudaStream_t st) {
   auto xp = static_cast<const __nv_bfloat16*>(x);
   auto wp = static_cast<const __nv_bfloat16*>(w);
   auto lp = static_cast<__nv_bfloat16*>(logits);
@@ -641,7 +660,7 @@ int launch_router_fused_small(const void* x, const void* w, const float* logit_b
   B200_CUDA(ensure_dyn_smem(router_fused_small_kernel, smem, attr));
   dim3 grid(cdiv(E, 8), cdiv(T, kWarpTokens));
   B200_CUDA(launch_pdl(router_fused_small_kernel, grid, dim3(256), smem, st, xp, wp, logit_bias, lp, T, H, E, k, mode, renorm, idx,
-                       sp, perm, inv, counts, offsets, active, n_active, ticket, err));
+                       sp, perm, inv, counts, offsets, active, n_active, ticket, err, desc, desc_entries));
   return 0;
 }
 
