@@ -299,7 +299,30 @@ __global__ void __launch_bounds__(256, 2) grouped_qmm_staged_kernel(GroupedArgs 
   const int n0 = blockIdx.x * (16 * RT) + rt * 16;
   const int wrow_bytes = K * BITS / 8;
 
-  // ---- all weight blocks of this warp, on their way before anything else ------------------------
+  // With a record, the first pass's rows are known at once: warp r asks for row r FIRST (commit group 0), then come
+  // the weights, so that the rows can be waited for alone and the K loop waits block by block.  Without a record the
+  // rows follow the weights and one wait covers everything.
+  const bool rows_first = p.desc && p.src_mode != kSrcIdent ? true : (p.src_mode == kSrcIdent && m >= 0);
+  const int nvec = K / 8;
+  if (rows_first && !p.x_bf16) {
+    const int nrows0 = min(ROWS, m);
+    if (warp < nrows0) {
+      const int src = p.src_mode == kSrcIdent ? (int)(seg0 + warp) : (int)__ldg(p.desc + (size_t)ea * kExpertDescWords + 4 + warp);
+      const unsigned char* srow = static_cast<const unsigned char*>(p.x) + (size_t)src * K * 2;
+      unsigned char* drow = s.xs + (size_t)warp * s.XS;
+      for (int cc = lane; cc < nvec; cc += 32) cp_async16(drow + cc * 16, srow + cc * 16);
+    }
+    if (tid < nrows0) {
+      float rsv = 1.0f;
+      if (p.src_mode != kSrcIdent)
+        rsv = __uint_as_float(__ldg(p.desc + (size_t)ea * kExpertDescWords + 12 + tid));
+      else if (p.x_rowscale)
+        rsv = p.x_rowscale[seg0 + tid];
+      s.rs[tid] = rsv;
+    }
+    cp_async_commit();
+  }
+  // ---- all weight blocks of this warp, on their way ---------------------------------------------
   {
     const unsigned char* wb = reinterpret_cast<const unsigned char*>(p.w[mt]);
     const int c = lane & 7;
@@ -333,16 +356,16 @@ __global__ void __launch_bounds__(256, 2) grouped_qmm_staged_kernel(GroupedArgs 
   // passes of eight rows; after the first one the weights are resident in shared memory
   for (int p0 = 0; p0 < m; p0 += ROWS) {
   const int nrows = min(ROWS, m - p0);
-  // ---- stage the prepared rows: asynchronous copies in a group BEHIND the weights' (groups complete in order, so
-  //      the wait below also covers the weights - which have had the whole prologue to arrive) ----
-  if (tid < nrows) {
-    const uint32_t sp = seg0 + p0 + tid;
-    int src;
-    float rsv = 1.0f;
-    if (p.src_mode != kSrcIdent && p.desc && p0 == 0) {  // (a record's source rows are those of the gathering product)
-      src = (int)__ldg(p.desc + (size_t)ea * kExpertDescWords + 4 + tid);
-      rsv = __uint_as_float(__ldg(p.desc + (size_t)ea * kExpertDescWords + 12 + tid));
-    } else {
+  bool block_waits = p.x_bf16 != 0;  // the K loop waits for its blocks one by one
+  if (rows_first && !p.x_bf16 && p0 == 0) {
+    cp_async_wait_pending(bpw);  // the rows (group 0); the weights' groups may still be on their way
+    block_waits = true;
+  } else {
+    // ---- stage the prepared rows: asynchronous copies in a group BEHIND the weights' (groups complete in order, so
+    //      the wait below also covers the weights - which have had the whole prologue to arrive) ----
+    if (tid < nrows) {
+      const uint32_t sp = seg0 + p0 + tid;
+      int src;
       if (p.src_mode == kSrcIdent)
         src = (int)sp;
       else if (p.src_mode == kSrcPermDiv)
@@ -351,26 +374,24 @@ __global__ void __launch_bounds__(256, 2) grouped_qmm_staged_kernel(GroupedArgs 
         src = (int)p.src_map[sp];
       else
         src = (int)p.src_map[p.perm[sp]];
-      if (!p.x_bf16 && p.x_rowscale) rsv = p.x_rowscale[src];
+      s_src[tid] = src;
+      if (!p.x_bf16) s.rs[tid] = p.x_rowscale ? p.x_rowscale[src] : 1.0f;
     }
-    s_src[tid] = src;
-    if (!p.x_bf16) s.rs[tid] = rsv;
-  }
-  __syncthreads();
-  if (p.x_bf16) {
-    for (int r = warp; r < nrows; r += 8)
-      prepare_row_warp<BITS, false>(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.x) + (size_t)s_src[r] * K),
-                                    K / 8, reinterpret_cast<uint4*>(s.xs + (size_t)r * s.XS), s.rs + r, lane);
-  } else {
-    const int nvec = K / 8;
-    const unsigned char* x16 = static_cast<const unsigned char*>(p.x);
-    for (int r = warp; r < nrows; r += 8) {  // warp r copies row r
-      const unsigned char* srow = x16 + (size_t)s_src[r] * K * 2;
-      unsigned char* drow = s.xs + (size_t)r * s.XS;
-      for (int cc = lane; cc < nvec; cc += 32) cp_async16(drow + cc * 16, srow + cc * 16);
+    __syncthreads();
+    if (p.x_bf16) {
+      for (int r = warp; r < nrows; r += 8)
+        prepare_row_warp<BITS, false>(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.x) + (size_t)s_src[r] * K),
+                                      K / 8, reinterpret_cast<uint4*>(s.xs + (size_t)r * s.XS), s.rs + r, lane);
+    } else {
+      const unsigned char* x16 = static_cast<const unsigned char*>(p.x);
+      for (int r = warp; r < nrows; r += 8) {  // warp r copies row r
+        const unsigned char* srow = x16 + (size_t)s_src[r] * K * 2;
+        unsigned char* drow = s.xs + (size_t)r * s.XS;
+        for (int cc = lane; cc < nvec; cc += 32) cp_async16(drow + cc * 16, srow + cc * 16);
+      }
+      cp_async_commit();
+      cp_async_wait_pending(0);
     }
-    cp_async_commit();
-    cp_async_wait_pending(0);
   }
   __syncthreads();
   stage_sums<BITS>(s, ROWS, nrows, K, tid, 256);
@@ -380,7 +401,7 @@ __global__ void __launch_bounds__(256, 2) grouped_qmm_staged_kernel(GroupedArgs 
   float tot[1][4] = {{0.f, 0.f, 0.f, 0.f}};
   StagedFetch<ROWS> fetch(s, gq, t);
   for (int j = 0; j < bpw; ++j) {
-    if (p.x_bf16) {  // (otherwise the wait for the rows has covered the weights)
+    if (block_waits) {  // (otherwise the wait for the rows has covered the weights)
       cp_async_wait_pending(bpw - 1 - j);
       __syncwarp();  // every lane's copies of block j have landed
     }
