@@ -132,6 +132,9 @@ static int check_cfg(const b200_moe_config* cfg) {
 static inline int permute_launches(int64_t n) { return n <= 1024 ? 1 : 3; }
 // rows per expert (average over the experts that can be active) from which the tensor-core kernel is used
 constexpr int64_t kTensorCoreRowsPerExpert = 14;
+// the same when both products of the block can use the register kernel's shared-memory-resident variant, whose
+// further passes over an expert's rows cost no weight traffic
+constexpr int64_t kTensorCoreRowsPerExpertStaged = 19;
 constexpr int kTicketWord = 8;  // word of the status block that the fused small-batch router uses as its ticket counter
 // Status block of a context: word 0 = device-side status, word 8 = ticket of the fused router, words 16..63 =
 // self-timing of development builds.
@@ -655,10 +658,12 @@ static bool use_tensor_core_path(const b200_ctx* c, const b200_moe_config& cfg, 
   if (!small_shape_ok(cfg.hidden) || !small_shape_ok(cfg.inter)) return true;
   if (c->qmm_path == B200_QMM_SMALL) return false;
   if (c->qmm_path == B200_QMM_TENSOR_CORE) return true;
-  // measured crossover (whole block, register kernel against tensor-core kernel): Qwen3-30B-A3B layer 12 rows per
-  // expert 0.32 ms against 0.35 ms, 16 rows 0.37 against 0.34; Qwen3-235B-A22B layer 12 rows 1.01 against 1.10 ms,
-  // 16 rows 1.23 against 1.08
-  return n / (max_active > 0 ? max_active : 1) >= kTensorCoreRowsPerExpert;
+  // measured crossover (whole block, register kernel against tensor-core kernel).  Qwen3-235B-A22B layer (gate/up
+  // too wide for the shared-memory-resident variant): 12 rows per expert 1.01 against 1.10 ms, 16 rows 1.14 against
+  // 1.05.  Qwen3-30B-A3B layer (resident variant for both products): 16 rows 0.292 against 0.332 ms, 18 rows 0.316
+  // against 0.333, 20 rows 0.344 against 0.333
+  const bool resident = small_staged_ok(cfg.hidden, cfg.bits, 2) && small_staged_ok(cfg.inter, cfg.bits, 1);
+  return n / (max_active > 0 ? max_active : 1) >= (resident ? kTensorCoreRowsPerExpertStaged : kTensorCoreRowsPerExpert);
 }
 
 // Rows of an expert-parallel exchange: the sorted rows are gathered from a buffer of token rows through `map`

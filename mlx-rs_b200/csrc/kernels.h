@@ -63,6 +63,8 @@ struct DownCombineArgs {
 int launch_expert_descs(const uint32_t* active, const uint32_t* n_active, const uint32_t* offsets, const uint32_t* perm,
                         const uint32_t* src_map, int src_mode, int src_div, const float* row_scale, int max_active,
                         uint32_t* desc, cudaStream_t st);
+// whether the register kernel's variant that keeps a CTA's weight slice in shared memory applies to a product over K
+bool small_staged_ok(int K, int bits, int nmat);
 bool down_combine_small_ok(int64_t T, int k, int K);
 int launch_down_combine_small(const DownCombineArgs& a, int bits, cudaStream_t st);
 
