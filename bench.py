@@ -188,7 +188,7 @@ def cpu_block_inputs(T_sample, shape, cfg, seed):
 
 def cpu_sample_tokens(T, shape):
     """Tokens of the bounded CPU sample: about 4e10 flop per forward (a fraction of a second to a few
-    seconds on the host cores), at most 512 tokens (a T = 512 slice for the large points)."""
+    seconds on the host cores), at most 512 tokens."""
     per_token = shape["top_k"] * 3 * 2 * shape["hidden"] * shape["inter"]
     return int(max(8, min(T, 512, 4e10 // per_token)))
 
