@@ -53,6 +53,22 @@ def test_handful_of_tokens_fused_tail(pkg, O, bits, T, k):
     check_block(pkg, O, make_block(T, 320, 16, 192, k, bits=bits, seed=T * 7 + k + bits))
 
 
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("T,H,E,I,k", [(40, 256, 8, 128, 2),      # 10 rows per expert: two 8-row passes
+                                       (100, 512, 8, 320, 2),     # 25 rows per expert; I = 320 leaves a ragged group
+                                       (64, 1024, 16, 256, 4)])   # K slices over several blocks
+def test_resident_slice_variant(pkg, O, bits, T, H, E, I, k):
+    """Register regime beyond a handful of tokens: the variant of the grouped product that copies a CTA's whole
+    weight slice into shared memory (both bit widths, several passes per expert, per-expert records), next to
+    shapes where only one of the two products can use it."""
+    ctx = pkg.default_context()
+    ctx.set_qmm_path(ctx.QMM_SMALL)
+    try:
+        check_block(pkg, O, make_block(T, H, E, I, k, bits=bits, seed=T + H + bits))
+    finally:
+        ctx.set_qmm_path(ctx.QMM_AUTO)
+
+
 @pytest.fixture(scope="module")
 def config0():
     """BASELINE.json configs[0]: hidden 2048, 128 experts, top-8 renormalised, inter 768, 4-bit, 64 tokens."""
