@@ -408,6 +408,9 @@ __global__ void __launch_bounds__(256, 2) grouped_qmm_staged_kernel(GroupedArgs 
     const int bk = ks + j * KS;
     const unsigned char* blk = wsm + (size_t)j * kStagedBlockBytes;
     fetch.block(bk * GB);
+    // the block's scales and biases of rows gq and gq + 8: one 8-byte load each (GB bf16 numbers per row)
+    const uint2 sc_a = *reinterpret_cast<const uint2*>(blk + 2048 + gq * 8), sc_b = *reinterpret_cast<const uint2*>(blk + 2048 + (gq + 8) * 8);
+    const uint2 bi_a = *reinterpret_cast<const uint2*>(blk + 2176 + gq * 8), bi_b = *reinterpret_cast<const uint2*>(blk + 2176 + (gq + 8) * 8);
 #pragma unroll
     for (int u = 0; u < GB; ++u) {
       typename WVec<BITS>::T wa, wb;
@@ -420,9 +423,7 @@ __global__ void __launch_bounds__(256, 2) grouped_qmm_staged_kernel(GroupedArgs 
         wa = *reinterpret_cast<const uint4*>(blk + gq * 128 + off);
         wb = *reinterpret_cast<const uint4*>(blk + (gq + 8) * 128 + off);
       }
-      const unsigned short* sbp = reinterpret_cast<const unsigned short*>(blk + 2048);
-      const float fsa = bf16_bits_to_f32(sbp[gq * 4 + u]), fba = bf16_bits_to_f32(sbp[64 + gq * 4 + u]);
-      const float fsb = bf16_bits_to_f32(sbp[(gq + 8) * 4 + u]), fbb = bf16_bits_to_f32(sbp[64 + (gq + 8) * 4 + u]);
+      const float fsa = bf16_of(sc_a, u), fba = bf16_of(bi_a, u), fsb = bf16_of(sc_b, u), fbb = bf16_of(bi_b, u);
       uint4 x0, x1;
       float4 c4;
       float2 s2;
