@@ -824,6 +824,7 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
       // a handful of rows: every CTA prepares the rows it stages itself, which costs less than a launch
       gu.x_bf16 = 1;
       if (tail && tail->desc && perm && src_div == cfg.top_k) gu.desc = tail->desc;
+      gu.late_trigger = 1;  // lets the fused down projection fetch routing outputs and weights before its wait
       c->mark(4, st);
     } else {
       void* xp = c->take(sizeof(uint16_t) * src_rows * cfg.hidden);
@@ -874,6 +875,7 @@ static int experts_sorted(b200_ctx* c, const b200_moe_config& cfg, const b200_mo
     dc.k = cfg.top_k;
     dc.K = cfg.inter;
     dc.N = cfg.hidden;
+    dc.early_routing = gu.late_trigger;
     c->mark(6, st);
     if (launch_down_combine_small(dc, cfg.bits, st)) return 1;
     LAUNCHED(c, 1);

@@ -40,6 +40,8 @@ struct GroupedArgs {
   int n_experts;              // number of stacked weight matrices
   const uint32_t* desc;       // register kernel, optional: per active expert one 64-byte record (launch_expert_descs) that
                               // replaces the look-ups of n_active, active, offsets and the first eight source rows
+  int late_trigger;           // register kernel: 1 = let the next kernel launch only after this one's own dependency wait,
+                              // so that the next kernel may read the outputs of this one's predecessors before ITS wait
   int x_bf16;                 // register kernel: 1 = x holds plain bf16 rows and every CTA prepares the rows it stages
                               // itself (a handful of rows per expert: cheaper than a preparation launch)
 };
@@ -56,6 +58,8 @@ struct DownCombineArgs {
   void* out;                  // bf16 [T, N]
   float* out_f32;             // optional [T, N]: the sum before its rounding
   int T, k, K, N;
+  int early_routing;          // 1: idx, inv and scores are complete when this kernel's CTAs start (its predecessor was
+                              // launched with late_trigger), so they and the first weight blocks are fetched before the wait
 };
 // desc [max_active][32] uint32: {expert, first sorted position, rows, 0, source row of the first eight sorted
 // positions (by the given gather mode), the row scale of those eight source rows (float bits; 1.0 without

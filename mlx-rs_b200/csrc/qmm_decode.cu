@@ -36,7 +36,12 @@ __global__ void __launch_bounds__(256, NT == 1 ? 2 : 1) grouped_qmm_small_kernel
   constexpr int ROWS = 8 * NT;  // activation rows per pass
   static_assert(NMAT * RT * KS == 8, "eight warps");
 
-  pdl_prologue();
+  if (p.late_trigger) {  // the next kernel starts once this one's predecessors are complete, not before
+    pdl_wait();
+    pdl_trigger();
+  } else {
+    pdl_prologue();
+  }
   const int ea = blockIdx.y;
   int e, m;
   uint32_t seg0;
@@ -522,7 +527,11 @@ static int launch_staged(const GroupedArgs& a, int max_active, cudaStream_t st) 
 // whole K, against the token's staged row of that slot.
 template <int BITS>
 __global__ void __launch_bounds__(256, 2) down_combine_small_kernel(DownCombineArgs p) {
-  pdl_prologue();
+  // With early_routing the routing outputs (written two kernels back) are complete when this CTA starts: they and the
+  // first weight blocks - constants - are fetched BEFORE the dependency wait, under the gate/up kernel's tail; only
+  // h, which that kernel writes, waits.
+  pdl_trigger();
+  if (!p.early_routing) pdl_wait();
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ uint32_t s_e[kDownCombineMaxK], s_row[kDownCombineMaxK];
   __shared__ float s_sc[kDownCombineMaxK];
@@ -552,6 +561,7 @@ __global__ void __launch_bounds__(256, 2) down_combine_small_kernel(DownCombineA
              bib + row_b * G, G, 0, 1);
   };
   if (warp < k) start_slot(warp);  // the first blocks of weights are on their way while the rows are staged
+  if (p.early_routing) pdl_wait();
   {
     const int nvec = K / 8;
     const unsigned char* hb = static_cast<const unsigned char*>(p.h);
