@@ -365,6 +365,13 @@ int b200_moe_block_forward_ep(b200_ctx* ctx, b200_ep_comm* comm, const b200_moe_
 /* MoE block forward: x bf16 [T, H] -> out bf16 [T, H]; aux may be NULL. */
 int b200_moe_block_forward(b200_ctx* ctx, const b200_moe_config* cfg, const b200_moe_params* params, const void* x,
                            int64_t T, void* out, const b200_moe_aux* aux, void* stream);
+/* The block with the pre-norm of a transformer layer's MLP half in front of it (mlx-lm/src/models/qwen3.rs:310-325,
+ * fast::rms_norm mlx-rs/src/fast.rs:178-205):  s = bf16(x + residual)  (residual NULL: s = x),
+ * out = block(rms_norm(s, norm_weight, eps)).  sum_out (optional, only with a residual) receives s, the new residual
+ * stream.  Same results, bit for bit, as b200_add_rms_norm followed by b200_moe_block_forward, in one call. */
+int b200_moe_block_forward_prenorm(b200_ctx* ctx, const b200_moe_config* cfg, const b200_moe_params* params, const void* x,
+                                   const void* residual, const void* norm_weight, float eps, int64_t T, void* sum_out,
+                                   void* out, const b200_moe_aux* aux, void* stream);
 
 #ifdef __cplusplus
 }

@@ -106,6 +106,9 @@ EXPORTS = {
                                             C.c_int64, C.c_void_p, C.POINTER(MoeAux), C.c_void_p]),
     "b200_moe_block_forward": (C.c_int, [C.c_void_p, C.POINTER(MoeConfig), C.POINTER(MoeParams), C.c_void_p, C.c_int64,
                                          C.c_void_p, C.POINTER(MoeAux), C.c_void_p]),
+    "b200_moe_block_forward_prenorm": (C.c_int, [C.c_void_p, C.POINTER(MoeConfig), C.POINTER(MoeParams), C.c_void_p,
+                                                 C.c_void_p, C.c_void_p, C.c_float, C.c_int64, C.c_void_p, C.c_void_p,
+                                                 C.POINTER(MoeAux), C.c_void_p]),
 }
 
 

@@ -92,6 +92,39 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
+// One row of residual add + RMSNorm by a block of 256 threads (all of them call it): s = bf16(x + residual) where a
+// residual is given (written to sum_out when asked for), out = bf16(w * s * rsqrt(mean(s^2) + eps)).  `part` is
+// shared scratch of 8 floats.  The reduction order is fixed, so every caller gets the same bits.
+__device__ __forceinline__ void block_rms_norm_row(const __nv_bfloat16* __restrict__ xr, const __nv_bfloat16* __restrict__ res,
+                                                   const __nv_bfloat16* __restrict__ weight, float eps, int64_t cols,
+                                                   __nv_bfloat16* out, __nv_bfloat16* sum_out, float* part) {
+  float ss = 0.f;
+  for (int64_t c = threadIdx.x; c < cols; c += 256) {
+    float v = __bfloat162float(xr[c]);
+    if (res) {
+      __nv_bfloat16 s = __float2bfloat16_rn(v + __bfloat162float(res[c]));
+      if (sum_out) sum_out[c] = s;
+      v = __bfloat162float(s);
+    }
+    ss += v * v;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  __syncthreads();  // (part may still be read by a previous call)
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += part[i];
+  const float inv = rsqrtf(tot / (float)cols + eps);
+  for (int64_t c = threadIdx.x; c < cols; c += 256) {
+    float v = __bfloat162float(xr[c]);
+    if (res) v = __bfloat162float(__float2bfloat16_rn(v + __bfloat162float(res[c])));
+    const float wv = weight ? __bfloat162float(weight[c]) : 1.0f;
+    out[c] = __float2bfloat16_rn(wv * (v * inv));
+  }
+}
+
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the CURRENT device only, and one process
 // may hold contexts on several devices: remember, per kernel instantiation and device, the largest size
 // that has been set.  One cache object per kernel (a function-local static at the launch site).

@@ -257,32 +257,9 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const __nv_bfloat16* __re
                                                        __nv_bfloat16* __restrict__ out, __nv_bfloat16* __restrict__ sum_out) {
   pdl_prologue();
   const int64_t r = blockIdx.x;
-  const __nv_bfloat16* xr = x + r * cols;
   __shared__ float part[8];
-  float ss = 0.f;
-  for (int64_t c = threadIdx.x; c < cols; c += 256) {
-    float v = __bfloat162float(xr[c]);
-    if (residual) {
-      __nv_bfloat16 s = __float2bfloat16_rn(v + __bfloat162float(residual[r * cols + c]));
-      if (sum_out) sum_out[r * cols + c] = s;
-      v = __bfloat162float(s);
-    }
-    ss += v * v;
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
-  __syncthreads();
-  float tot = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) tot += part[i];
-  const float inv = rsqrtf(tot / (float)cols + eps);
-  for (int64_t c = threadIdx.x; c < cols; c += 256) {
-    float v = __bfloat162float(xr[c]);
-    if (residual) v = __bfloat162float(__float2bfloat16_rn(v + __bfloat162float(residual[r * cols + c])));
-    float wv = weight ? __bfloat162float(weight[c]) : 1.0f;
-    out[r * cols + c] = __float2bfloat16_rn(wv * (v * inv));
-  }
+  block_rms_norm_row(x + r * cols, residual ? residual + r * cols : nullptr, weight, eps, cols, out + r * cols,
+                     (residual && sum_out) ? sum_out + r * cols : nullptr, part);
 }
 
 int launch_rms_norm(const void* x, const void* residual, const void* weight, float eps, int64_t rows, int64_t cols,

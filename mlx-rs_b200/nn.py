@@ -139,6 +139,25 @@ class MoeBlock:
         return (out, aux) if return_aux else out
 
 
+def _forward_prenorm(self, x, residual=None, weight=None, eps=1e-5, out=None):
+    """out = block(rms_norm(x + residual, weight, eps)) in one library call -> (x + residual or x itself, out):
+    the pre-norm MLP half of a transformer layer (mlx-lm/src/models/qwen3.rs:310-325)."""
+    ops._cuda(x, residual, weight, out)
+    ops._req(x.dtype == torch.bfloat16 and x.shape[-1] == self.switch_mlp.hidden, "MoeBlock: bf16 x [.., hidden]")
+    ops._req(residual is None or (residual.shape == x.shape and residual.dtype == x.dtype), "residual must match x")
+    T = x.numel() // x.shape[-1]
+    if out is None:
+        out = torch.empty_like(x)
+    s = torch.empty_like(x) if residual is not None else None
+    L.check(L.lib().b200_moe_block_forward_prenorm(ops._ctx(self.ctx), C.byref(self._cfg), C.byref(self._params), L.ptr(x),
+                                                   L.ptr(residual), L.ptr(weight), float(eps), T, L.ptr(s), L.ptr(out), None,
+                                                   L.stream_ptr()))
+    return (s if s is not None else x), out
+
+
+MoeBlock.forward_prenorm = _forward_prenorm
+
+
 def router_topk(x, gate_weight, top_k, router_mode=ROUTER_SOFTMAX_TOPK, norm_topk_prob=True, logit_bias=None,
                 return_logits=False, ctx=None):
     """Router alone -> (indices [T,k] int32, scores [T,k] bf16[, logits [T,E] bf16])."""
@@ -214,7 +233,8 @@ class MoeStack:
     """A stack of pre-norm MoE blocks with residual connections and no attention (BASELINE.json
     configs[2]): per layer  h <- h + block(rms_norm(h, weight, eps)), the wiring of a transformer
     block's MLP half (mlx-lm/src/models/qwen3.rs:310-325) with the MLP replaced by the routed block.
-    The residual add of layer l is fused with the norm of layer l+1 (one kernel)."""
+    The residual add of layer l is fused with the norm of layer l+1 and handed to the block's entry point
+    (`b200_moe_block_forward_prenorm`)."""
 
     def __init__(self, blocks, norm_weights=None, eps=1e-6, ctx=None):
         self.blocks, self.eps, self.ctx = list(blocks), eps, ctx
@@ -224,11 +244,8 @@ class MoeStack:
         h = x
         y = None
         for blk, w in zip(self.blocks, self.norm_weights):
-            if y is None:
-                normed = ops.rms_norm(h, w, self.eps, ctx=self.ctx)
-            else:
-                h, normed = ops.add_rms_norm(h, y, w, self.eps, ctx=self.ctx)
-            y = blk.forward(normed)
+            # residual add of the previous layer, this layer's norm and the block: one library call
+            h, y = blk.forward_prenorm(h, y, w, self.eps)
         out = torch.empty_like(h)
         L.check(L.lib().b200_add(ops._ctx(self.ctx), L.ptr(h), L.ptr(y), h.numel(), L.ptr(out), L.stream_ptr()))
         return out

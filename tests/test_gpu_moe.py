@@ -266,6 +266,28 @@ def test_stack_of_blocks_with_norm_and_residual(pkg, O):
     assert ok.mean() >= 0.9, f"only {ok.mean():.2f} of the tokens agree"
 
 
+@pytest.mark.parametrize("T", [1, 5, 8, 40])
+def test_prenorm_entry_point_equals_norm_then_block(pkg, T):
+    """b200_moe_block_forward_prenorm against b200_add_rms_norm + b200_moe_block_forward, bit for bit, in the
+    handful-of-tokens path and beyond it; with and without a residual and a norm weight."""
+    blk = make_block(T, 256, 8, 128, 2, seed=300 + T)
+    block = to_device(pkg, blk)
+    g = torch.Generator().manual_seed(T)
+    h = bf16_cuda(blk["x"])
+    res = (torch.randn(T, 256, generator=g) * 0.5).bfloat16().cuda()
+    w = (1.0 + 0.1 * torch.randn(256, generator=g)).bfloat16().cuda()
+    for residual, weight in ((None, None), (res, None), (res, w)):
+        if residual is None:
+            s_want, normed = h, pkg.ops.rms_norm(h, weight, 1e-6)
+        else:
+            s_want, normed = pkg.ops.add_rms_norm(h, residual, weight, 1e-6)
+        want = block.forward(normed)
+        s_got, got = block.forward_prenorm(h, residual, weight, 1e-6)
+        pkg.default_context().check()
+        assert torch.equal(s_got.view(torch.int16), s_want.view(torch.int16))
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
 def test_host_pipeline_matches_direct_calls(pkg):
     """Five pipelined submits from pinned host buffers (depth 2: slots are reused) return exactly what
     block.forward returns for the same rows."""
