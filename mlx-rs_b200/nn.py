@@ -244,8 +244,16 @@ class MoeStack:
         h = x
         y = None
         for blk, w in zip(self.blocks, self.norm_weights):
-            # residual add of the previous layer, this layer's norm and the block: one library call
-            h, y = blk.forward_prenorm(h, y, w, self.eps)
+            if hasattr(blk, "forward_prenorm"):
+                # residual add of the previous layer, this layer's norm and the block: one library call
+                h, y = blk.forward_prenorm(h, y, w, self.eps)
+                continue
+            # any other block with a forward(x) (the expert-parallel block): norm kernel, then the block
+            if y is None:
+                normed = ops.rms_norm(h, w, self.eps, ctx=self.ctx)
+            else:
+                h, normed = ops.add_rms_norm(h, y, w, self.eps, ctx=self.ctx)
+            y = blk.forward(normed)
         out = torch.empty_like(h)
         L.check(L.lib().b200_add(ops._ctx(self.ctx), L.ptr(h), L.ptr(y), h.numel(), L.ptr(out), L.stream_ptr()))
         return out

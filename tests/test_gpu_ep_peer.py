@@ -153,3 +153,30 @@ def test_one_call_block_single_rank(pkg, O, cfg, chunks, tmp_path):
         small.close()
     finally:
         dist.destroy_process_group()
+
+
+def test_stack_of_expert_parallel_blocks_single_rank(pkg, tmp_path):
+    """MoeStack over blocks that only have forward(x) (the one-call expert-parallel block, here a group of one rank)
+    against the same stack over plain blocks: bit for bit, since a rank that is its own peer computes the same
+    sums in the same order except for the fp16 partial sums of the exchange."""
+    import torch.distributed as dist
+    from importlib import import_module
+    ep = import_module("mlx_rs_b200.ep")
+    dist.init_process_group("gloo", init_method=f"file://{tmp_path}/rdv", rank=0, world_size=1)
+    try:
+        T, H, E, I, k = 24, 256, 8, 128, 2
+        blks = [make_block(T, H, E, I, k, seed=500 + l) for l in range(3)]
+        plain = [to_device(pkg, b) for b in blks]
+        comm = ep.EpComm(E, k, H, T * k, T)
+        eps_ = [ep.DeviceSyncExpertParallelMoe(pkg, p.gate_weight, p.switch_mlp, E, k, comm, keep_routing=False) for p in plain]
+        x = torch.from_numpy(blks[0]["x"]).bfloat16().cuda()
+        want = pkg.nn.MoeStack(plain, eps=1e-6).forward(x)
+        got = pkg.nn.MoeStack(eps_, eps=1e-6).forward(x)
+        pkg.default_context().check()
+        d = (got.float() - want.float()).abs()
+        rms = float(want.float().pow(2).mean().sqrt())
+        ok = (d <= 2e-2 * rms + 2.0 ** -7 * want.float().abs()).all(dim=1)
+        assert float(ok.float().mean()) >= 0.9      # (a last-bit difference can flip a near-tie in a later layer's routing)
+        comm.close()
+    finally:
+        dist.destroy_process_group()
