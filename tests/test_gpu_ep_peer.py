@@ -157,8 +157,7 @@ def test_one_call_block_single_rank(pkg, O, cfg, chunks, tmp_path):
 
 def test_stack_of_expert_parallel_blocks_single_rank(pkg, tmp_path):
     """MoeStack over blocks that only have forward(x) (the one-call expert-parallel block, here a group of one rank)
-    against the same stack over plain blocks: bit for bit, since a rank that is its own peer computes the same
-    sums in the same order except for the fp16 partial sums of the exchange."""
+    against the same stack over plain blocks, within the output tolerance (the exchange keeps fp16 partial sums)."""
     import torch.distributed as dist
     from importlib import import_module
     ep = import_module("mlx_rs_b200.ep")
