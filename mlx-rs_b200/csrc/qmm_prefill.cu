@@ -122,6 +122,13 @@ struct PrefillArgs {
 // dequantise 8 codes of one 4-bit word -> 16 bytes of fp16 (k order [0,4,1,5,2,6,3,7]).
 // OR-ing a nibble into the mantissa of 1024.0 gives 1024+q (low nibbles) or 1024+16q (nibbles
 // taken in place at bits 4..7); both are brought back to q exactly before the affine step.
+// (mask and magic number are register operands of ONE lop3; written as C the AND and the OR become two
+// instructions with an immediate each)
+__device__ __forceinline__ uint32_t and_or_b32(uint32_t a, uint32_t mask, uint32_t magic) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(magic));
+  return d;
+}
 __device__ __forceinline__ uint4 deq_word4(uint32_t w, __half2 s2, __half2 b2) {
   const __half2 k1024 = __floats2half2_rn(1024.f, 1024.f);
   const __half2 k16th = __floats2half2_rn(0.0625f, 0.0625f), km64 = __floats2half2_rn(-64.f, -64.f);
@@ -130,8 +137,8 @@ __device__ __forceinline__ uint4 deq_word4(uint32_t w, __half2 s2, __half2 b2) {
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const uint32_t v = w >> (8 * h);
-    uint32_t lo = (v & 0x000f000fu) | 0x64006400u;  // (1024 + q_j,     1024 + q_{j+4}),     j = 2h
-    uint32_t hi = (v & 0x00f000f0u) | 0x64006400u;  // (1024 + 16 q_j', 1024 + 16 q_{j'+4}), j' = 2h+1
+    uint32_t lo = and_or_b32(v, 0x000f000fu, 0x64006400u);  // (1024 + q_j,     1024 + q_{j+4}),     j = 2h
+    uint32_t hi = and_or_b32(v, 0x00f000f0u, 0x64006400u);  // (1024 + 16 q_j', 1024 + 16 q_{j'+4}), j' = 2h+1
     __half2 q0 = __hsub2(*reinterpret_cast<__half2*>(&lo), k1024);
     __half2 q1 = __hfma2(*reinterpret_cast<__half2*>(&hi), k16th, km64);
     __half2 v0 = __hfma2(q0, s2, b2), v1 = __hfma2(q1, s2, b2);
