@@ -240,6 +240,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const int sub = warp >> 2, q4 = warp & 3;
     int tphase = 0, tcount = 0;
     RoleTimer tm((p.debug & 32) && blockIdx.x == 0 && tid == 0);
+    RoleTimer tm2((p.debug & 32) && blockIdx.x == 0 && tid == 0 && NMAT == 1);
     float* stg = stage_buf + warp * (32 * STG_LD);
     const int tb = alt ? sub : 0;  // which accumulator barrier pair this warp uses
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
@@ -328,18 +329,18 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                                      : 1.0f);
           uint32_t v[16];
           tmem_ld16(lane_addr, v);
+          if (p.out_fmt == kOutF32) {
 #pragma unroll 1
-          for (int c = 0; c < 256; c += 16) {
-            tmem_ld_wait();
-            __syncwarp();
+            for (int c = 0; c < 256; c += 16) {
+              tmem_ld_wait();
+              __syncwarp();
 #pragma unroll
-            for (int i = 0; i < 16; i += 4)
-              *reinterpret_cast<float4*>(stg + lane * STG_LD + i) =
-                  make_float4(__uint_as_float(v[i]) * sc, __uint_as_float(v[i + 1]) * sc, __uint_as_float(v[i + 2]) * sc,
-                              __uint_as_float(v[i + 3]) * sc);
-            if (c + 16 < 256) tmem_ld16(lane_addr + c + 16, v);
-            __syncwarp();
-            if (p.out_fmt == kOutF32) {
+              for (int i = 0; i < 16; i += 4)
+                *reinterpret_cast<float4*>(stg + lane * STG_LD + i) =
+                    make_float4(__uint_as_float(v[i]) * sc, __uint_as_float(v[i + 1]) * sc, __uint_as_float(v[i + 2]) * sc,
+                                __uint_as_float(v[i + 3]) * sc);
+              if (c + 16 < 256) tmem_ld16(lane_addr + c + 16, v);
+              __syncwarp();
               // 4 lanes per row (4 columns = 16 bytes each): 64 bytes per row, 8 rows per instruction
               const int c4 = (lane & 3) * 4;
               const float4 cc = *reinterpret_cast<const float4*>(cs + c + c4);
@@ -355,35 +356,58 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 if (d != 0xffffffffu && ct * FEAT + c + c4 < p.N)
                   *reinterpret_cast<float4*>(static_cast<float*>(p.out) + (size_t)d * p.N + ct * FEAT + c + c4) = x4;
               }
-            } else {
-              const int cg8 = (lane & 1) * 8;
-              const float4 c0 = *reinterpret_cast<const float4*>(cs + c + cg8);
-              const float4 c1 = *reinterpret_cast<const float4*>(cs + c + cg8 + 4);
+            }
+          } else {
+            // 2-byte outputs: a pass covers 32 columns.  The thread scales and converts its row's values and
+            // stages them as 64 bytes (16-byte chunks XOR-swizzled by (row / 2) % 4: the row-wise writes and the
+            // reads below, 4 lanes per row, both touch every bank once); a store instruction then covers 8 rows x
+            // 64 contiguous bytes, half as many separate segments per byte as a 16-column pass would give.
+            unsigned char* stg8 = reinterpret_cast<unsigned char*>(stg);
+            const uint32_t my_row = (uint32_t)lane * 64u, my_sw = (uint32_t)(lane >> 1) & 3u;
+#pragma unroll 1
+            for (int c = 0; c < 256; c += 32) {
+              tm2.start();
+              __syncwarp();  // the previous pass's readers are done with the staging buffer
 #pragma unroll
-              for (int it = 0; it < 2; ++it) {
-                const int rr = it * 16 + (lane >> 1);
-                const uint32_t d = __shfl_sync(0xffffffffu, dst, rr);
-                const float4 v0 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8);
-                const float4 v1 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8 + 4);
-                uint4 o;
-                if (p.out_fmt == kOutF16) {
-                  o.x = f16x2_sat(v0.x * c0.x, v0.y * c0.y);
-                  o.y = f16x2_sat(v0.z * c0.z, v0.w * c0.w);
-                  o.z = f16x2_sat(v1.x * c1.x, v1.y * c1.y);
-                  o.w = f16x2_sat(v1.z * c1.z, v1.w * c1.w);
-                } else {
-                  o.x = bf16x2(v0.x * c0.x, v0.y * c0.y);
-                  o.y = bf16x2(v0.z * c0.z, v0.w * c0.w);
-                  o.z = bf16x2(v1.x * c1.x, v1.y * c1.y);
-                  o.w = bf16x2(v1.z * c1.z, v1.w * c1.w);
+              for (int half = 0; half < 2; ++half) {
+                tmem_ld_wait();
+                uint32_t o[8];
+#pragma unroll
+                for (int i = 0; i < 16; i += 4) {
+                  const float4 cc = *reinterpret_cast<const float4*>(cs + c + half * 16 + i);
+                  const float x0 = (__uint_as_float(v[i]) * sc) * cc.x, x1 = (__uint_as_float(v[i + 1]) * sc) * cc.y;
+                  const float x2 = (__uint_as_float(v[i + 2]) * sc) * cc.z, x3 = (__uint_as_float(v[i + 3]) * sc) * cc.w;
+                  if (p.out_fmt == kOutF16) {
+                    o[i / 2] = f16x2_sat(x0, x1);
+                    o[i / 2 + 1] = f16x2_sat(x2, x3);
+                  } else {
+                    o[i / 2] = bf16x2(x0, x1);
+                    o[i / 2 + 1] = bf16x2(x2, x3);
+                  }
                 }
-                const unsigned long long da = __shfl_sync(0xffffffffu, daddr, rr);
-                if (d != 0xffffffffu && ct * FEAT + c + cg8 < p.N && !(p.out_row_addr && da == 0ull)) {
+                if (c + half * 16 + 16 < 256) tmem_ld16(lane_addr + c + half * 16 + 16, v);
+                *reinterpret_cast<uint4*>(stg8 + my_row + ((((uint32_t)half * 2u) ^ my_sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                *reinterpret_cast<uint4*>(stg8 + my_row + ((((uint32_t)half * 2u + 1u) ^ my_sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+              }
+              __syncwarp();
+              tm2.stop(1);
+              tm2.start();
+              const uint32_t ch = (uint32_t)lane & 3u;
+              const int col = ct * FEAT + c + (int)ch * 8;
+#pragma unroll
+              for (int it = 0; it < 4; ++it) {
+                const int rr = it * 8 + (lane >> 2);
+                const uint32_t d = __shfl_sync(0xffffffffu, dst, rr);
+                unsigned long long da = 0ull;
+                if (p.out_row_addr) da = __shfl_sync(0xffffffffu, daddr, rr);
+                const uint4 o4 = *reinterpret_cast<const uint4*>(stg8 + rr * 64 + ((ch ^ ((uint32_t)(rr >> 1) & 3u)) << 4));
+                if (d != 0xffffffffu && col < p.N && !(p.out_row_addr && da == 0ull)) {
                   __nv_bfloat16* orow = p.out_row_addr ? reinterpret_cast<__nv_bfloat16*>(da)
                                                        : static_cast<__nv_bfloat16*>(p.out) + (size_t)d * p.N;
-                  *reinterpret_cast<uint4*>(orow + ct * FEAT + c + cg8) = o;
+                  *reinterpret_cast<uint4*>(orow + col) = o4;
                 }
               }
+              tm2.stop(2);
             }
           }
         }
@@ -393,6 +417,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       tm.stop(1);
     }
     tm.flush(p.err + 16 + (NMAT == 1 ? 24 : 0));
+    tm2.flush(p.err + 60);
   } else if (warp < (N_EPI + N_DEQ) / 32) {
     // ------------------------------- B dequantisation --------------------------------------
     const int col = tid - N_EPI;  // accumulator column = B tile row, 0..255
