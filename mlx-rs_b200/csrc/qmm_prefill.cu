@@ -266,61 +266,63 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(sub * NCOL);
       if (alt || sub * 128 < rows) {  // (warp-uniform) this accumulator holds rows of the tile
         if constexpr (NMAT == 2) {
+          // A pass covers 32 h columns: the thread computes its row's values from two 16-column loads of each
+          // matrix, converts them and stages 64 bytes (chunks XOR-swizzled as in the down projection's epilogue
+          // below); a store instruction covers 8 rows x 64 contiguous bytes.
           uint32_t g[16], u[16];
           tmem_ld16(lane_addr, g);
           tmem_ld16(lane_addr + 128, u);
+          unsigned char* stg8 = reinterpret_cast<unsigned char*>(stg);
+          const uint32_t my_row = (uint32_t)lane * 64u, my_sw = (uint32_t)(lane >> 1) & 3u;
 #pragma unroll 1
-          for (int c = 0; c < 128; c += 16) {
-            tmem_ld_wait();
-            __syncwarp();  // the previous chunk's readers are done with the staging buffer
+          for (int c = 0; c < 128; c += 32) {
+            __syncwarp();  // the previous pass's readers are done with the staging buffer
 #pragma unroll
-            for (int i = 0; i < 16; i += 4) {
-              const float4 cg = *reinterpret_cast<const float4*>(cs + c + i);
-              const float4 cu = *reinterpret_cast<const float4*>(cs + 128 + c + i);
-              const float cgs[4] = {cg.x, cg.y, cg.z, cg.w}, cus[4] = {cu.x, cu.y, cu.z, cu.w};
-              float h[4];
+            for (int half = 0; half < 2; ++half) {
+              const int cc0 = c + half * 16;
+              tmem_ld_wait();
+              float h[16];
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const float gv = __uint_as_float(g[i + q]) * (cgs[q] * ar), uv = __uint_as_float(u[i + q]) * (cus[q] * ar);
-                h[q] = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
+              for (int i = 0; i < 16; i += 4) {
+                const float4 cg = *reinterpret_cast<const float4*>(cs + cc0 + i);
+                const float4 cu = *reinterpret_cast<const float4*>(cs + 128 + cc0 + i);
+                const float cgs[4] = {cg.x, cg.y, cg.z, cg.w}, cus[4] = {cu.x, cu.y, cu.z, cu.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const float gv = __uint_as_float(g[i + q]) * (cgs[q] * ar), uv = __uint_as_float(u[i + q]) * (cus[q] * ar);
+                  h[i + q] = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
+                }
               }
-              *reinterpret_cast<float4*>(stg + lane * STG_LD + i) = make_float4(h[0], h[1], h[2], h[3]);
-            }
-            if (c + 16 < 128) {  // next chunk's accumulators travel while this one is stored
-              tmem_ld16(lane_addr + c + 16, g);
-              tmem_ld16(lane_addr + 128 + c + 16, u);
-            }
-            __syncwarp();
-            // 2 lanes per row (8 columns = 16 bytes of bf16 each), 16 rows per store instruction
-#pragma unroll
-            for (int it = 0; it < 2; ++it) {
-              const int rr = it * 16 + (lane >> 1), cg8 = (lane & 1) * 8;
-              const uint32_t d = __shfl_sync(0xffffffffu, dst, rr);
-              const float4 v0 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8);
-              const float4 v1 = *reinterpret_cast<const float4*>(stg + rr * STG_LD + cg8 + 4);
+              if (cc0 + 16 < 128) {  // the next accumulator columns travel while these are converted and stored
+                tmem_ld16(lane_addr + cc0 + 16, g);
+                tmem_ld16(lane_addr + 128 + cc0 + 16, u);
+              }
               // h = bf16(silu(g) * u) is the value the down projection consumes; kOutF16 stores that same
               // value as fp16 (exact for 2^-14 <= |h| <= 65504, saturating beyond), the A-operand format of
               // the tensor-core down projection, so no conversion pass is needed between the two products
-              float e0, e1, e2, e3, e4, e5, e6, e7;
-              if constexpr (BITS == 4) {  // the consumer (down projection) reads k in [0,4,1,5,2,6,3,7] order
-                e0 = v0.x, e1 = v1.x, e2 = v0.y, e3 = v1.y, e4 = v0.z, e5 = v1.z, e6 = v0.w, e7 = v1.w;
-              } else {
-                e0 = v0.x, e1 = v0.y, e2 = v0.z, e3 = v0.w, e4 = v1.x, e5 = v1.y, e6 = v1.z, e7 = v1.w;
+              uint32_t o[8];
+#pragma unroll
+              for (int g8 = 0; g8 < 2; ++g8) {
+                const float* e = h + g8 * 8;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  // 4-bit consumer (down projection) reads k in [0,4,1,5,2,6,3,7] order within a group of eight
+                  const float lo = (BITS == 4) ? e[q] : e[2 * q], hi = (BITS == 4) ? e[q + 4] : e[2 * q + 1];
+                  o[g8 * 4 + q] = (p.out_fmt == kOutF16) ? f16x2_sat(round_to_bf16(lo), round_to_bf16(hi)) : bf16x2(lo, hi);
+                }
               }
-              uint4 o;
-              if (p.out_fmt == kOutF16) {
-                o.x = f16x2_sat(round_to_bf16(e0), round_to_bf16(e1));
-                o.y = f16x2_sat(round_to_bf16(e2), round_to_bf16(e3));
-                o.z = f16x2_sat(round_to_bf16(e4), round_to_bf16(e5));
-                o.w = f16x2_sat(round_to_bf16(e6), round_to_bf16(e7));
-              } else {
-                o.x = bf16x2(e0, e1);
-                o.y = bf16x2(e2, e3);
-                o.z = bf16x2(e4, e5);
-                o.w = bf16x2(e6, e7);
-              }
+              *reinterpret_cast<uint4*>(stg8 + my_row + ((((uint32_t)half * 2u) ^ my_sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+              *reinterpret_cast<uint4*>(stg8 + my_row + ((((uint32_t)half * 2u + 1u) ^ my_sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+            }
+            __syncwarp();
+            const uint32_t ch = (uint32_t)lane & 3u;
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+              const int rr = it * 8 + (lane >> 2);
+              const uint32_t d = __shfl_sync(0xffffffffu, dst, rr);
+              const uint4 o4 = *reinterpret_cast<const uint4*>(stg8 + rr * 64 + ((ch ^ ((uint32_t)(rr >> 1) & 3u)) << 4));
               if (d != 0xffffffffu)
-                *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)d * p.N + ct * FEAT + c + cg8) = o;
+                *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)d * p.N + ct * FEAT + c + (int)ch * 8) = o4;
             }
           }
         } else {
