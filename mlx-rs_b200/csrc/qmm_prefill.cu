@@ -264,6 +264,7 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       tm.start();
       tc_fence_after();
       const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(sub * NCOL);
+      bool released = false;  // (warp-uniform) the accumulator has been handed back before the last stores
       if (alt || sub * 128 < rows) {  // (warp-uniform) this accumulator holds rows of the tile
         if constexpr (NMAT == 2) {
           // A pass covers 32 h columns: the thread computes its row's values from two 16-column loads of each
@@ -281,6 +282,11 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             for (int half = 0; half < 2; ++half) {
               const int cc0 = c + half * 16;
               tmem_ld_wait();
+              if (cc0 + 16 >= 128) {  // the last columns are in registers: the accumulator can be refilled from here on
+                tc_fence_before();
+                mbar_arrive_warp(tempty_bar(tb), lane);
+                released = true;
+              }
               float h[16];
 #pragma unroll
               for (int i = 0; i < 16; i += 4) {
@@ -373,6 +379,11 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 #pragma unroll
               for (int half = 0; half < 2; ++half) {
                 tmem_ld_wait();
+                if (c + half * 16 + 16 >= 256) {  // last columns in registers: release the accumulator now
+                  tc_fence_before();
+                  mbar_arrive_warp(tempty_bar(tb), lane);
+                  released = true;
+                }
                 uint32_t o[8];
 #pragma unroll
                 for (int i = 0; i < 16; i += 4) {
@@ -414,8 +425,10 @@ grouped_qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
         }
       }
-      tc_fence_before();
-      mbar_arrive_warp(tempty_bar(tb), lane);
+      if (!released) {
+        tc_fence_before();
+        mbar_arrive_warp(tempty_bar(tb), lane);
+      }
       tm.stop(1);
     }
     tm.flush(p.err + 16 + (NMAT == 1 ? 24 : 0));
